@@ -1,0 +1,259 @@
+/* pelica_moe.h - C ABI of the B200 (sm_100a) mixture-of-experts FFN path.
+ *
+ * This is the boundary a Pelica engine binds instead of its own expert code.
+ * Pelica (Rust + WGSL) has no FFI for this path; the functions below replace
+ * its four in-process seams, cited per entry point as "replaces: file:line"
+ * (paths inside the Pelica source tree).
+ *
+ * Conventions
+ *  - Every function returns int32_t: 0 = PM_OK, negative = PM_ERR_*. Nothing
+ *    throws or aborts across the boundary. pm_last_error() gives a
+ *    thread-local, human-readable string for the last failure.
+ *  - Host pointers belong to the caller and are only read/written during the
+ *    call. Weight bytes are copied (and re-laid out) at upload, so the caller
+ *    may free or unmap them afterwards, as Pelica drops its `Pin` after upload
+ *    (src/ds4.rs:1749).
+ *  - `x`, `y`, ids, weights ... may be host or device pointers; the library
+ *    asks the CUDA runtime which. Host buffers are staged through the
+ *    context's pinned staging area.
+ *  - One pm_ctx per GPU, used by one host thread at a time. All work is
+ *    ordered on the context's stream; calls that return results into host
+ *    memory synchronise, calls on device pointers do not (use pm_sync).
+ *  - There is no CPU fallback: without a CUDA device pm_ctx_create fails.
+ */
+#ifndef PELICA_MOE_H
+#define PELICA_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PM_API __attribute__((visibility("default")))
+
+/* ---- error codes ------------------------------------------------------ */
+enum {
+  PM_OK = 0,
+  PM_ERR_INVALID = -1,     /* bad argument / shape the path does not take   */
+  PM_ERR_UNSUPPORTED = -2, /* a type or mode that is not built              */
+  PM_ERR_CUDA = -3,        /* a CUDA runtime call failed (see last error)   */
+  PM_ERR_OOM = -4,         /* device or pinned allocation failed            */
+  PM_ERR_STATE = -5,       /* weights missing, layer not finalised ...      */
+  PM_ERR_TIMEOUT = -6,     /* a bounded device-side wait gave up            */
+  PM_ERR_LIMIT = -7        /* a size beyond a documented fixed maximum      */
+};
+
+/* ---- ggml tensor type ids (src/gguf.rs:85-121) ------------------------- */
+enum {
+  PM_TYPE_F32 = 0,
+  PM_TYPE_F16 = 1,
+  PM_TYPE_Q8_0 = 8,   /* 32 values / 34 B  */
+  PM_TYPE_Q4_K = 12,  /* 256 values / 144 B */
+  PM_TYPE_Q6_K = 14,  /* 256 values / 210 B */
+  PM_TYPE_BF16 = 30,
+  PM_TYPE_MXFP4 = 39  /* 32 values / 17 B  */
+};
+
+/* ---- router gating (src/moe_kernels.rs:1019-1081, src/oss_kernels.rs:15-35,
+ *      src/ds4.rs:1371-1426, src/q4x.rs:2213-2231, src/forward.rs:488-504) - */
+enum {
+  PM_GATE_SOFTMAX_ALL = 0,      /* softmax over all experts, select on p(+bias) */
+  PM_GATE_SIGMOID = 1,          /* sigmoid scores, select on s(+bias)           */
+  PM_GATE_SQRT_SOFTPLUS = 2,    /* sqrt(softplus(v)), select on s(+bias)        */
+  PM_GATE_SOFTMAX_SELECTED = 3  /* top-k by logit, softmax over the selected    */
+};
+
+/* ---- expert activation (src/moe_kernels.rs:1183, src/ds4_cpu.rs:311,
+ *      src/oss_batch.rs:785) ----------------------------------------------- */
+enum {
+  PM_ACT_SILU = 0,       /* h = g/(1+exp(-g)) * u                                  */
+  PM_ACT_SILU_CLAMP = 1, /* g=min(g,lim); u=clamp(u,-lim,lim) first (lim>0)        */
+  PM_ACT_OSS_GLU = 2     /* x=min(g+bg,lim); y=clamp(u+bu,-lim,lim);
+                            h = x/(1+exp(-alpha*x))*(y+1)                           */
+};
+
+/* ---- activation arithmetic ------------------------------------------------ */
+enum {
+  PM_AQ_F32 = 0,      /* f32 activations x dequantised weights (src/oss_batch.rs:767-877) */
+  PM_AQ_Q8X_256 = 1   /* int8 per 256 values, f32 scale, 8 partial sums
+                         (`Q8x`, src/ds4_cpu.rs:7-36); the hidden vector is
+                         re-quantised before down (src/ds4_cpu.rs:306-317)        */
+};
+
+/* ---- where the routing weight is applied ------------------------------- */
+enum {
+  PM_FOLD_BEFORE_DOWN = 0, /* h *= w_t before down (src/ds4_cpu.rs:312)             */
+  PM_FOLD_IN_COMBINE = 1   /* y += w * down(h) (src/moe_kernels.rs:1798-1802);
+                              with expert biases: w*(down+bias) (src/oss_batch.rs:89) */
+};
+
+enum { PM_SHARED_NONE = 0, PM_SHARED_PLAIN = 1, PM_SHARED_SIGMOID_GATED = 2 };
+
+/* fixed maxima of the path (the reference: NEMAX 512, KMAX 8,
+ * src/moe_kernels.rs:16-20; q4x routes up to 16) */
+#define PM_MAX_EXPERTS 512
+#define PM_MAX_TOPK 16
+#define PM_MAX_TOKENS 16384
+
+/* One MoE FFN layer. Plain data; copy freely. */
+typedef struct pm_layer_desc {
+  int32_t d;            /* hidden size                                      */
+  int32_t ff;           /* expert intermediate size                         */
+  int32_t n_exp;        /* routed experts in the model                      */
+  int32_t top_k;
+  int32_t gating;       /* PM_GATE_*                                        */
+  int32_t norm_w;       /* 1: w /= max(sum_k w, 2^-14) (src/moe_kernels.rs:1073) */
+  float w_scale;        /* 0 = none; else w *= w_scale                      */
+  int32_t n_group;      /* 0 = off; group-limited selection                 */
+  int32_t topk_group;
+  int32_t act;          /* PM_ACT_*                                         */
+  float act_limit;      /* lim (0 = no clamp)                               */
+  float act_alpha;      /* OSS_GLU alpha (1.702)                            */
+  int32_t type_gate, type_up, type_down; /* PM_TYPE_*                       */
+  int32_t act_quant;    /* PM_AQ_*                                          */
+  int32_t weight_fold;  /* PM_FOLD_*                                        */
+  int32_t has_expert_bias; /* f32 bias per gate/up/down row (gpt-oss)       */
+  int32_t shared;       /* PM_SHARED_*                                      */
+  int32_t shared_ff;    /* intermediate size of the shared expert           */
+  int32_t first_local_expert; /* expert parallelism: this context holds     */
+  int32_t n_exp_local;        /* experts [first, first+n_local); 0 = all    */
+} pm_layer_desc;
+
+/* Dispatch plan of one call (src/moe_kernels.rs:24-34,1086-1129 layout;
+ * token lists in ascending token order as src/ds4.rs:1461-1472).
+ * All arrays are caller-allocated (host or device):
+ *   active[n_exp], offset[n_exp], count[n_exp], pair_token[T*k], pair_pos[T*k] */
+typedef struct pm_plan_out {
+  int32_t *n_active;     /* [1]  experts with >= 1 pair                     */
+  uint32_t *active;      /* expert ids, ascending                           */
+  uint32_t *offset;      /* exclusive prefix sum of count                   */
+  uint32_t *count;
+  uint32_t *pair_token;  /* token of pair p; per expert ascending token     */
+  uint32_t *pair_pos;    /* pair of (t,k) = pair_pos[t*k_top + k]           */
+} pm_plan_out;
+
+typedef struct pm_ctx pm_ctx;
+typedef struct pm_layer pm_layer;
+typedef struct pm_stack pm_stack;
+
+/* ---- library ----------------------------------------------------------- */
+PM_API const char *pm_last_error(void);
+PM_API const char *pm_version(void);
+/* bytes per block / values per block of a ggml type (src/gguf.rs:85-121);
+ * returns 0 for a type this path does not decode */
+PM_API size_t pm_type_block_bytes(int32_t ggml_type);
+PM_API size_t pm_type_block_values(int32_t ggml_type);
+
+/* ---- context ----------------------------------------------------------- */
+/* replaces: wgpu device + queue per engine (src/moe.rs:786, src/ds4_gpu.rs:568) */
+PM_API int32_t pm_ctx_create(int32_t device, pm_ctx **out);
+PM_API int32_t pm_ctx_destroy(pm_ctx *ctx);
+/* replaces: Pending::wait (src/ds4_gpu.rs:733) */
+PM_API int32_t pm_sync(pm_ctx *ctx);
+/* the CUDA stream all work of this context is ordered on (cudaStream_t) */
+PM_API void *pm_ctx_stream(pm_ctx *ctx);
+/* kernels launched by this context since creation (bench bookkeeping) */
+PM_API int64_t pm_ctx_launch_count(pm_ctx *ctx);
+/* device-timed interval on the context's stream, in milliseconds */
+PM_API int32_t pm_timer_start(pm_ctx *ctx);
+PM_API int32_t pm_timer_stop(pm_ctx *ctx, float *ms);
+/* writes a buffer larger than L2 (evicts cached weights between timed runs) */
+PM_API int32_t pm_flush_l2(pm_ctx *ctx);
+/* device memory helpers for callers that keep activations resident */
+PM_API int32_t pm_dev_alloc(pm_ctx *ctx, size_t bytes, void **out);
+PM_API int32_t pm_dev_free(pm_ctx *ctx, void *p);
+PM_API int32_t pm_copy(pm_ctx *ctx, void *dst, const void *src, size_t bytes);
+
+/* ---- layer ------------------------------------------------------------- */
+/* replaces: the per-layer FFN block of the recorded op list (src/moe.rs:1377-1437)
+ * and the layer tensors of src/ds4.rs / src/oss.rs:521-527 */
+PM_API int32_t pm_layer_create(pm_ctx *ctx, const pm_layer_desc *desc, pm_layer **out);
+PM_API int32_t pm_layer_destroy(pm_layer *layer);
+/* router weight [n_exp][d] (f32, or bf16 when dtype == PM_TYPE_BF16);
+ * logit_bias [n_exp] is added before top-k (gpt-oss, src/oss_batch.rs:478);
+ * select_bias [n_exp] only ranks (exp_probs_b, src/moe_kernels.rs:1047);
+ * either may be NULL */
+PM_API int32_t pm_layer_set_router(pm_layer *layer, const void *w, int32_t dtype,
+                                   const float *logit_bias, const float *select_bias);
+/* raw GGUF block bytes, row-major: gate/up [ff][d], down [d][ff]
+ * (`Pin::piece(0..2)`, src/ds4_io.rs:220-234); biases f32 or NULL.
+ * `e` is the global expert id; must be local to this context. */
+PM_API int32_t pm_layer_set_expert(pm_layer *layer, int32_t e, const uint8_t *gate,
+                                   const uint8_t *up, const uint8_t *down, const float *bias_gate,
+                                   const float *bias_up, const float *bias_down);
+/* shared expert (src/moe.rs:1422-1434): same types as the routed experts;
+ * gate_inp [d] f32 is the scalar sigmoid gate (src/moe_kernels.rs:1805) or NULL */
+PM_API int32_t pm_layer_set_shared(pm_layer *layer, const uint8_t *gate, const uint8_t *up,
+                                   const uint8_t *down, const float *gate_inp);
+/* usage[e] += pairs routed to e on every forward (src/moe_kernels.rs:1114);
+ * out[n_exp] host */
+PM_API int32_t pm_layer_read_usage(pm_layer *layer, uint32_t *out);
+
+/* ---- the operator ------------------------------------------------------ */
+/* y[T][d] = sum_k w[t,k] * expert_{id[t,k]}(x[t]) (+ shared(x[t])).
+ * x is the normed activation the engines hand to their FFN (src/moe.rs:1367).
+ * flags: PM_FWD_ACCUMULATE adds into y (the residual, src/moe_kernels.rs:1808).
+ * replaces: src/moe.rs:1377-1437, ds4 `ffn` src/ds4.rs:1428-1763,
+ *           `Model::moe` src/forward.rs:481-753 */
+#define PM_FWD_ACCUMULATE 1u
+PM_API int32_t pm_moe_forward(pm_layer *layer, const float *x, int32_t T, float *y,
+                              uint32_t flags);
+
+/* split entry points (parity tests; callers that own part of the pipeline) */
+/* logits[T][n_exp] = W_r x (+ logit bias); replaces `matvec` src/moe_kernels.rs:140,
+ * `cpu::dot` loop src/ds4.rs:1376-1383 */
+PM_API int32_t pm_router_logits(pm_layer *layer, const float *x, int32_t T, float *logits);
+/* ids[T][k] (descending score), w[T][k]; replaces `plan` head
+ * src/moe_kernels.rs:1019-1081, `TOPK` src/oss_kernels.rs:15-35 */
+PM_API int32_t pm_route(pm_layer *layer, const float *x, int32_t T, uint32_t *ids, float *w);
+PM_API int32_t pm_route_logits(pm_layer *layer, const float *logits, int32_t T, uint32_t *ids,
+                               float *w);
+/* replaces: `plan` tail src/moe_kernels.rs:1083-1129, rows[e] src/ds4.rs:1461-1472 */
+PM_API int32_t pm_plan(pm_layer *layer, const uint32_t *ids, int32_t T, pm_plan_out *out);
+/* pair_out[P][d]: expert outputs per pair in plan order (weights folded when
+ * the layer says BEFORE_DOWN); replaces `ds4_cpu::expert` src/ds4_cpu.rs:297-328,
+ * `expert`/`expert_dec` src/moe_kernels.rs:1170,1423 */
+PM_API int32_t pm_experts(pm_layer *layer, const float *x, int32_t T, const uint32_t *ids,
+                          const float *w, float *pair_out);
+/* y from pair outputs; replaces `combine` src/moe_kernels.rs:1787-1813 */
+PM_API int32_t pm_combine(pm_layer *layer, const float *pair_out, const uint32_t *ids,
+                          const float *w, const float *shared_out, int32_t T, float *y,
+                          uint32_t flags);
+
+/* ---- format checks (bit-exact against the reference arithmetic) -------- */
+/* replaces: `deq4` src/moe_kernels.rs:63-84, `deq_row` src/q4x_cpu.rs:443-496 */
+PM_API int32_t pm_dequant(pm_ctx *ctx, int32_t ggml_type, const uint8_t *blocks,
+                          size_t n_values, float *out);
+/* replaces: `Q8x::new` src/ds4_cpu.rs:13-35 ; n % 256 == 0;
+ * q[n], scale[n/256], bsum[n/32] */
+PM_API int32_t pm_quant_act(pm_ctx *ctx, int32_t mode, const float *x, size_t n, int8_t *q,
+                            float *scale, int32_t *bsum);
+
+/* ---- layer stacks (the benchmark's unit: x <- x + moe(rmsnorm(x)) per layer) */
+/* the engines' layer loop around the FFN (src/moe.rs:1279-1440 `after` ops:
+ * rmsnorm, FFN, residual add) reduced to its MoE part */
+PM_API int32_t pm_stack_create(pm_ctx *ctx, pm_layer **layers, int32_t n_layers, float eps,
+                               pm_stack **out);
+PM_API int32_t pm_stack_destroy(pm_stack *stack);
+/* x[T][d] in, x_out[T][d] out (may alias); every layer: xn = x/rms(x) (unit
+ * norm weight), x += moe(xn) */
+PM_API int32_t pm_stack_forward(pm_stack *stack, const float *x, int32_t T, float *x_out);
+
+/* ---- synthetic weights generated on the device (benchmark set-up) ------ */
+/* fills every expert (and the router, biases, shared expert) of `layer` with
+ * N(0, sigma) weights quantised to the layer's types by on-device encoders;
+ * deterministic in (seed, expert, tensor, element) */
+PM_API int32_t pm_layer_fill_synthetic(pm_layer *layer, uint64_t seed, float sigma);
+/* raw GGUF-format bytes of one expert tensor as stored by the library,
+ * converted back from its device layout (which = 0 gate, 1 up, 2 down);
+ * `out` host, sized rows*cols/block_values*block_bytes */
+PM_API int32_t pm_layer_get_expert(pm_layer *layer, int32_t e, int32_t which, uint8_t *out);
+PM_API int32_t pm_layer_get_router(pm_layer *layer, float *w, float *logit_bias,
+                                   float *select_bias);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PELICA_MOE_H */

@@ -1,0 +1,281 @@
+"""Synthetic MoE layers: the named config shapes, seeded weights and the GGUF
+block encoders (Q4_K, Q6_K, MXFP4, Q8_0) that quantise them.
+
+Pelica has no quantiser for these formats (it only reads them from GGUF files,
+src/gguf.rs:85-121), so the encoders here are this repository's own. Any valid
+encoder serves: the CUDA path and its checker consume the same bytes. The block
+layouts follow the decoders they must round-trip through
+(src/ds4_cpu.rs:45-83, src/moe_kernels.rs:73,75,80).
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import numpy as np
+
+# ggml type ids (src/gguf.rs:85-121)
+F32, F16, Q8_0, Q4_K, Q6_K, BF16, MXFP4 = 0, 1, 8, 12, 14, 30, 39
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), MXFP4: (32, 17)}
+
+GATE_SOFTMAX_ALL, GATE_SIGMOID, GATE_SQRT_SOFTPLUS, GATE_SOFTMAX_SELECTED = 0, 1, 2, 3
+ACT_SILU, ACT_SILU_CLAMP, ACT_OSS_GLU = 0, 1, 2
+AQ_F32, AQ_Q8X_256 = 0, 1
+FOLD_BEFORE_DOWN, FOLD_IN_COMBINE = 0, 1
+SHARED_NONE, SHARED_PLAIN, SHARED_SIGMOID_GATED = 0, 1, 2
+
+
+def row_bytes(ggml_type: int, ncols: int) -> int:
+    v, b = BLOCK[ggml_type]
+    assert ncols % v == 0
+    return ncols // v * b
+
+
+# --------------------------------------------------------------------------
+# encoders
+# --------------------------------------------------------------------------
+
+def _round_half_away(x):
+    return np.sign(x) * np.floor(np.abs(x) + 0.5)
+
+
+def encode_q4_k(x: np.ndarray) -> np.ndarray:
+    """f32 [..., n] (n % 256 == 0) -> uint8 [..., n/256*144]."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 8, 32)
+    nb = xb.shape[0]
+    mn = np.minimum(xb.min(-1), 0.0)
+    mx = xb.max(-1)
+    scale = np.maximum(mx - mn, 0.0) / 15.0
+    mins = -mn
+    d = (scale.max(-1) / 63.0).astype(np.float16)
+    dmin = (mins.max(-1) / 63.0).astype(np.float16)
+    df, dmf = d.astype(np.float32), dmin.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(df[:, None] > 0, _round_half_away(scale / df[:, None]), 0.0)
+        m = np.where(dmf[:, None] > 0, _round_half_away(mins / dmf[:, None]), 0.0)
+        sc = np.clip(sc, 0, 63)
+        m = np.clip(m, 0, 63)
+        step = df[:, None] * sc
+        q = np.where(step[..., None] > 0,
+                     _round_half_away((xb + (dmf[:, None] * m)[..., None]) / step[..., None]), 0.0)
+    q = np.clip(q, 0, 15).astype(np.uint8)
+    sc = sc.astype(np.uint8)
+    m = m.astype(np.uint8)
+    out = np.zeros((nb, 144), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(nb, 2)
+    s = out[:, 4:16]
+    s[:, 0:4] = sc[:, 0:4] | ((sc[:, 4:8] >> 4) << 6)
+    s[:, 4:8] = m[:, 0:4] | ((m[:, 4:8] >> 4) << 6)
+    s[:, 8:12] = (sc[:, 4:8] & 15) | ((m[:, 4:8] & 15) << 4)
+    qq = q.reshape(nb, 4, 2, 32)
+    out[:, 16:144] = (qq[:, :, 0, :] | (qq[:, :, 1, :] << 4)).reshape(nb, 128)
+    return out.reshape(*lead, -1)
+
+
+def encode_q6_k(x: np.ndarray) -> np.ndarray:
+    """f32 [..., n] (n % 256 == 0) -> uint8 [..., n/256*210]."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 16, 16)
+    nb = xb.shape[0]
+    gs = np.abs(xb).max(-1) / 31.0
+    d = (gs.max(-1) / 127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(df[:, None] > 0, _round_half_away(gs / df[:, None]), 0.0)
+        sc = np.clip(sc, 0, 127)
+        step = df[:, None] * sc
+        q = np.where(step[..., None] > 0, _round_half_away(xb / step[..., None]), 0.0)
+    q = (np.clip(q, -32, 31) + 32).astype(np.uint8).reshape(nb, 256)
+    out = np.zeros((nb, 210), np.uint8)
+    # value v = 128 n + 32 qt + l  (src/moe_kernels.rs:75)
+    qv = q.reshape(nb, 2, 4, 32)  # [n][qt][l]
+    lo = qv & 15
+    hi = qv >> 4
+    ql = out[:, 0:128].reshape(nb, 2, 2, 32)  # byte 64n + 32*(qt&1) + l
+    ql[:, :, 0, :] = lo[:, :, 0, :] | (lo[:, :, 2, :] << 4)
+    ql[:, :, 1, :] = lo[:, :, 1, :] | (lo[:, :, 3, :] << 4)
+    qh = out[:, 128:192].reshape(nb, 2, 32)
+    qh[:] = hi[:, :, 0, :] | (hi[:, :, 1, :] << 2) | (hi[:, :, 2, :] << 4) | (hi[:, :, 3, :] << 6)
+    out[:, 192:208] = sc.astype(np.int8).view(np.uint8)
+    out[:, 208:210] = d.view(np.uint8).reshape(nb, 2)
+    return out.reshape(*lead, -1)
+
+
+_MX_TABLE = np.array([0, 1, 2, 3, 4, 6, 8, 12], np.float32)  # doubled E2M1 (src/moe_kernels.rs:109)
+
+
+def encode_mxfp4(x: np.ndarray) -> np.ndarray:
+    """f32 [..., n] (n % 32 == 0) -> uint8 [..., n/32*17]."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 32)
+    nb = xb.shape[0]
+    amax = np.abs(xb).max(-1)
+    with np.errstate(divide="ignore"):
+        ex = np.where(amax > 0, np.floor(np.log2(np.maximum(amax, 1e-38))) - 3, -126.0)
+    e = np.clip(ex + 128, 2, 254).astype(np.int32)  # scale = 2^(e-128) (src/oss_kernels.rs:42-45)
+    s = np.exp2((e - 128).astype(np.float32))
+    mag = np.abs(xb) / s[:, None]
+    code = np.abs(mag[..., None] - _MX_TABLE).argmin(-1).astype(np.uint8)
+    code |= ((xb < 0) & (code > 0)).astype(np.uint8) << 3
+    out = np.zeros((nb, 17), np.uint8)
+    out[:, 0] = e.astype(np.uint8)
+    out[:, 1:17] = code[:, 0:16] | (code[:, 16:32] << 4)
+    return out.reshape(*lead, -1)
+
+
+def encode_q8_0(x: np.ndarray) -> np.ndarray:
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 32)
+    nb = xb.shape[0]
+    d = (np.abs(xb).max(-1) / 127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(df[:, None] > 0, _round_half_away(xb / df[:, None]), 0.0)
+    q = np.clip(q, -127, 127).astype(np.int8)
+    out = np.zeros((nb, 34), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:34] = q.view(np.uint8)
+    return out.reshape(*lead, -1)
+
+
+ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0}
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """f32 -> nearest-even bf16 -> f32 (the reference loads bf16 biases as f32, src/oss.rs:255-260)."""
+    b = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    b = (b + 0x7FFF + ((b >> 16) & 1)) & 0xFFFF0000
+    return b.astype(np.uint32).view(np.float32)
+
+
+# --------------------------------------------------------------------------
+# configs
+# --------------------------------------------------------------------------
+
+@dataclasses.dataclass
+class Config:
+    """A layer shape; field names follow pm_layer_desc."""
+
+    name: str
+    d: int
+    ff: int
+    n_exp: int
+    top_k: int
+    gating: int = GATE_SOFTMAX_ALL
+    norm_w: int = 0
+    w_scale: float = 0.0
+    n_group: int = 0
+    topk_group: int = 0
+    act: int = ACT_SILU
+    act_limit: float = 0.0
+    act_alpha: float = 0.0
+    type_gate: int = Q4_K
+    type_up: int = Q4_K
+    type_down: int = Q4_K
+    act_quant: int = AQ_Q8X_256
+    weight_fold: int = FOLD_BEFORE_DOWN
+    has_expert_bias: int = 0
+    shared: int = SHARED_NONE
+    shared_ff: int = 0
+    first_local_expert: int = 0
+    n_exp_local: int = 0
+    n_layers: int = 1
+    logit_bias: bool = False
+    select_bias_sigma: float = 0.0
+    sigma: float = 0.02
+
+    def desc_fields(self) -> dict:
+        names = ["d", "ff", "n_exp", "top_k", "gating", "norm_w", "w_scale", "n_group", "topk_group", "act",
+                 "act_limit", "act_alpha", "type_gate", "type_up", "type_down", "act_quant", "weight_fold",
+                 "has_expert_bias", "shared", "shared_ff", "first_local_expert", "n_exp_local"]
+        return {n: getattr(self, n) for n in names}
+
+    def expert_bytes(self) -> int:
+        b = row_bytes(self.type_gate, self.d) * self.ff + row_bytes(self.type_up, self.d) * self.ff
+        b += row_bytes(self.type_down, self.ff) * self.d
+        if self.has_expert_bias:
+            b += 4 * (2 * self.ff + self.d)
+        return b
+
+    def scaled(self, **kw) -> "Config":
+        return dataclasses.replace(self, **kw)
+
+
+# the five benchmark shapes
+C1_OLMOE = Config("olmoe-1b-7b", d=2048, ff=1024, n_exp=64, top_k=8, gating=GATE_SOFTMAX_ALL, norm_w=0)
+C2_QWEN3 = Config("qwen3-30b-a3b", d=2048, ff=768, n_exp=128, top_k=8, gating=GATE_SOFTMAX_ALL, norm_w=1,
+                  type_down=Q6_K, n_layers=48)
+C3_GPTOSS = Config("gpt-oss-20b", d=2880, ff=2880, n_exp=32, top_k=4, gating=GATE_SOFTMAX_SELECTED,
+                   act=ACT_OSS_GLU, act_limit=7.0, act_alpha=1.702, type_gate=MXFP4, type_up=MXFP4,
+                   type_down=MXFP4, act_quant=AQ_F32, weight_fold=FOLD_IN_COMBINE, has_expert_bias=1,
+                   n_layers=24, logit_bias=True)
+C4_DSV3 = Config("deepseek-v3-shaped", d=7168, ff=2048, n_exp=256, top_k=8, gating=GATE_SIGMOID, norm_w=1,
+                 w_scale=2.5, n_group=8, topk_group=4, shared=SHARED_PLAIN, shared_ff=2048, n_layers=58,
+                 select_bias_sigma=0.01)
+C5_ZIPF = Config("qwen3-zipf", d=2048, ff=768, n_exp=128, top_k=8, gating=GATE_SOFTMAX_ALL, norm_w=1)
+CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF}
+
+
+def make_weights(cfg: Config, seed: int, experts=None) -> dict:
+    """Seeded N(0, sigma) weights quantised to cfg's types (numpy; test sizes).
+
+    Returns the dict oracle.Layer and pelica_b200.MoeLayer.load take.
+    """
+    rng = np.random.default_rng(seed)
+    E, d, ff = cfg.n_exp, cfg.d, cfg.ff
+    w = {"router": rng.normal(0, cfg.sigma, (E, d)).astype(np.float32)}
+    if cfg.logit_bias:
+        w["logit_bias"] = bf16_round(rng.normal(0, cfg.sigma, E).astype(np.float32))
+    if cfg.select_bias_sigma > 0:
+        w["select_bias"] = rng.normal(0, cfg.select_bias_sigma, E).astype(np.float32)
+    gate = np.zeros((E, row_bytes(cfg.type_gate, d) * ff), np.uint8)
+    up = np.zeros((E, row_bytes(cfg.type_up, d) * ff), np.uint8)
+    down = np.zeros((E, row_bytes(cfg.type_down, ff) * d), np.uint8)
+    for e in range(E):
+        g = rng.normal(0, cfg.sigma, (ff, d)).astype(np.float32)
+        u = rng.normal(0, cfg.sigma, (ff, d)).astype(np.float32)
+        dn = rng.normal(0, cfg.sigma, (d, ff)).astype(np.float32)
+        if experts is not None and e not in experts:
+            continue
+        gate[e] = ENCODERS[cfg.type_gate](g).ravel()
+        up[e] = ENCODERS[cfg.type_up](u).ravel()
+        down[e] = ENCODERS[cfg.type_down](dn).ravel()
+    w.update(gate=gate, up=up, down=down)
+    if cfg.has_expert_bias:
+        w["bias_gate"] = bf16_round(rng.normal(0, cfg.sigma, (E, ff)).astype(np.float32))
+        w["bias_up"] = bf16_round(rng.normal(0, cfg.sigma, (E, ff)).astype(np.float32))
+        w["bias_down"] = bf16_round(rng.normal(0, cfg.sigma, (E, d)).astype(np.float32))
+    if cfg.shared:
+        sf = cfg.shared_ff
+        w["shared_gate"] = ENCODERS[cfg.type_gate](rng.normal(0, cfg.sigma, (sf, d)).astype(np.float32)).ravel()
+        w["shared_up"] = ENCODERS[cfg.type_up](rng.normal(0, cfg.sigma, (sf, d)).astype(np.float32)).ravel()
+        w["shared_down"] = ENCODERS[cfg.type_down](rng.normal(0, cfg.sigma, (d, sf)).astype(np.float32)).ravel()
+        if cfg.shared == SHARED_SIGMOID_GATED:
+            w["shared_gate_inp"] = rng.normal(0, cfg.sigma, d).astype(np.float32)
+    return w
+
+
+def make_activations(T: int, d: int, seed: int, eps: float = 1e-6) -> np.ndarray:
+    """f32 N(0,1) [T,d], RMS-normalised with unit weight (src/moe.rs:758 eps)."""
+    rng = np.random.default_rng(seed)
+    x = rng.normal(0, 1, (T, d)).astype(np.float32)
+    ms = (x.astype(np.float64) ** 2).mean(-1, keepdims=True)
+    return (x / np.sqrt(ms + eps)).astype(np.float32)
+
+
+def zipf_router_bias(n_exp: int, seed: int, s: float = 1.2, dead: int = 8, strength: float = 1.0) -> np.ndarray:
+    """Logit offsets that make expert popularity follow rank^-s over a seeded
+    permutation, with the `dead` least popular experts pushed to never win."""
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(n_exp)
+    rank = np.empty(n_exp, np.int64)
+    rank[perm] = np.arange(1, n_exp + 1)
+    bias = (-s * np.log(rank.astype(np.float64)) * strength).astype(np.float32)
+    if dead:
+        bias[perm[-dead:]] = -1.0e4
+    return bias
