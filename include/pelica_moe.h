@@ -161,6 +161,16 @@ PM_API int32_t pm_timer_start(pm_ctx *ctx);
 PM_API int32_t pm_timer_stop(pm_ctx *ctx, float *ms);
 /* writes a buffer larger than L2 (evicts cached weights between timed runs) */
 PM_API int32_t pm_flush_l2(pm_ctx *ctx);
+/* per-phase device timing (CUDA events around each phase of the operator):
+ * enable, run, then read milliseconds and span counts per phase; phase names
+ * by index below pm_profile_phases(). Costs two event records per phase. */
+PM_API int32_t pm_profile_enable(pm_ctx *ctx, int32_t on);
+PM_API int32_t pm_profile_phases(void);
+PM_API const char *pm_profile_phase_name(int32_t i);
+PM_API int32_t pm_profile_read(pm_ctx *ctx, float *ms, int64_t *spans);
+/* pinned host memory for activations that cross the bus every call */
+PM_API int32_t pm_host_alloc(pm_ctx *ctx, size_t bytes, void **out);
+PM_API int32_t pm_host_free(pm_ctx *ctx, void *p);
 /* device memory helpers for callers that keep activations resident */
 PM_API int32_t pm_dev_alloc(pm_ctx *ctx, size_t bytes, void **out);
 PM_API int32_t pm_dev_free(pm_ctx *ctx, void *p);
@@ -244,14 +254,19 @@ PM_API int32_t pm_stack_forward(pm_stack *stack, const float *x, int32_t T, floa
 /* ---- synthetic weights generated on the device (benchmark set-up) ------ */
 /* fills every expert (and the router, biases, shared expert) of `layer` with
  * N(0, sigma) weights quantised to the layer's types by on-device encoders;
- * deterministic in (seed, expert, tensor, element) */
-PM_API int32_t pm_layer_fill_synthetic(pm_layer *layer, uint64_t seed, float sigma);
+ * deterministic in (seed, expert, tensor, element). A router logit bias /
+ * selection bias is generated when its sigma is > 0. */
+PM_API int32_t pm_layer_fill_synthetic(pm_layer *layer, uint64_t seed, float sigma,
+                                       float logit_bias_sigma, float select_bias_sigma);
 /* raw GGUF-format bytes of one expert tensor as stored by the library,
  * converted back from its device layout (which = 0 gate, 1 up, 2 down);
  * `out` host, sized rows*cols/block_values*block_bytes */
 PM_API int32_t pm_layer_get_expert(pm_layer *layer, int32_t e, int32_t which, uint8_t *out);
 PM_API int32_t pm_layer_get_router(pm_layer *layer, float *w, float *logit_bias,
                                    float *select_bias);
+/* f32 biases of expert e (NULL entries are skipped); layers with has_expert_bias */
+PM_API int32_t pm_layer_get_expert_bias(pm_layer *layer, int32_t e, float *bias_gate,
+                                        float *bias_up, float *bias_down);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,1157 @@
+// api.cu - the C ABI (include/pelica_moe.h): contexts, layers, the operator
+// and its split entry points, layer stacks, synthetic fill.
+//
+// Host orchestration only; every computation is a kernel of this library.
+// There is no CPU fallback: without a CUDA device pm_ctx_create fails.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "moe_internal.cuh"
+
+void launch_synth_blocks(const Launch &L, int type, uint8_t *raw, size_t nb, uint64_t seed,
+                         float sigma);
+void launch_synth_f32(const Launch &L, float *out, size_t n, uint64_t seed, float sigma,
+                      int bf16_round);
+
+// ---------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+static int32_t fail(int32_t code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CU(call)                                                                       \
+  do {                                                                                 \
+    cudaError_t e_ = (call);                                                           \
+    if (e_ != cudaSuccess)                                                             \
+      return fail(e_ == cudaErrorMemoryAllocation ? PM_ERR_OOM : PM_ERR_CUDA,          \
+                  "%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+  } while (0)
+#define TRY(call)            \
+  do {                       \
+    int32_t r_ = (call);     \
+    if (r_ != PM_OK) return r_; \
+  } while (0)
+
+extern "C" const char *pm_last_error(void) { return g_err; }
+extern "C" const char *pm_version(void) { return "pelica-moe-b200 0.1 (sm_100a)"; }
+
+extern "C" size_t pm_type_block_bytes(int32_t t) {
+  switch (t) {
+    case PM_TYPE_Q8_0: return 34;
+    case PM_TYPE_Q4_K: return 144;
+    case PM_TYPE_Q6_K: return 210;
+    case PM_TYPE_MXFP4: return 17;
+  }
+  return 0;
+}
+extern "C" size_t pm_type_block_values(int32_t t) {
+  switch (t) {
+    case PM_TYPE_Q8_0:
+    case PM_TYPE_MXFP4: return 32;
+    case PM_TYPE_Q4_K:
+    case PM_TYPE_Q6_K: return 256;
+  }
+  return 0;
+}
+static size_t raw_bytes(int type, size_t rows, size_t cols) {
+  return rows * (cols / pm_type_block_values(type)) * pm_type_block_bytes(type);
+}
+
+// ---------------------------------------------------------------------------
+// context
+// ---------------------------------------------------------------------------
+struct pm_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int64_t launches = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // workspace: one region, carved per call
+  uint8_t *ws = nullptr;
+  size_t ws_cap = 0, ws_off = 0;
+  // staging for weight uploads
+  uint8_t *stage = nullptr;
+  size_t stage_cap = 0;
+  void *flush = nullptr;
+  size_t flush_bytes = 0;
+  // optional per-phase timing (CUDA events on the stream)
+  bool prof_on = false;
+  std::vector<cudaEvent_t> prof_ev;
+  size_t prof_used = 0;
+  std::vector<int> prof_phase;  // phase of event pair i
+  Launch launch() { return Launch{stream, &launches}; }
+};
+
+enum { PH_ROUTER = 0, PH_ROUTE, PH_PLAN, PH_QUANT_X, PH_GATEUP, PH_QUANT_H, PH_DOWN, PH_SHARED,
+       PH_COMBINE, PH_NORM, PH_FUSED, PH_N };
+static const char *PH_NAMES[PH_N] = {"router", "route", "plan", "quant_x", "gateup", "quant_h",
+                                     "down", "shared", "combine", "rmsnorm", "fused"};
+
+struct ProfSpan {
+  pm_ctx *c;
+  bool on;
+  ProfSpan(pm_ctx *ctx, int phase) : c(ctx), on(ctx->prof_on) {
+    if (!on) return;
+    if (c->prof_used + 2 > c->prof_ev.size()) {
+      for (int i = 0; i < 64; i++) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) { on = false; return; }
+        c->prof_ev.push_back(e);
+      }
+    }
+    c->prof_phase.push_back(phase);
+    cudaEventRecord(c->prof_ev[c->prof_used], c->stream);
+  }
+  ~ProfSpan() {
+    if (!on) return;
+    cudaEventRecord(c->prof_ev[c->prof_used + 1], c->stream);
+    c->prof_used += 2;
+  }
+};
+#define PROF(c, ph) ProfSpan prof_span_##ph(c, ph)
+
+static bool is_device_ptr(const void *p) {
+  if (!p) return false;
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+static int32_t ws_reserve(pm_ctx *c, size_t bytes) {
+  c->ws_off = 0;
+  if (bytes <= c->ws_cap) return PM_OK;
+  CU(cudaStreamSynchronize(c->stream));
+  if (c->ws) CU(cudaFree(c->ws));
+  c->ws = nullptr;
+  c->ws_cap = 0;
+  size_t cap = bytes + bytes / 8 + (1 << 20);
+  CU(cudaMalloc(&c->ws, cap));
+  c->ws_cap = cap;
+  return PM_OK;
+}
+template <typename T>
+static T *ws_take(pm_ctx *c, size_t n) {
+  size_t off = (c->ws_off + 255) & ~(size_t)255;
+  c->ws_off = off + n * sizeof(T);
+  return (T *)(c->ws + off);
+}
+static size_t al(size_t b) { return (b + 255) & ~(size_t)255; }
+
+static int32_t stage_reserve(pm_ctx *c, size_t bytes) {
+  if (bytes <= c->stage_cap) return PM_OK;
+  CU(cudaStreamSynchronize(c->stream));
+  if (c->stage) CU(cudaFree(c->stage));
+  c->stage = nullptr;
+  c->stage_cap = 0;
+  CU(cudaMalloc(&c->stage, bytes));
+  c->stage_cap = bytes;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_ctx_create(int32_t device, pm_ctx **out) {
+  if (!out) return fail(PM_ERR_INVALID, "pm_ctx_create: out is null");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(PM_ERR_CUDA, "pm_ctx_create: no CUDA device (%s); this library has no CPU path",
+                cudaGetErrorString(e));
+  if (device < 0 || device >= n) return fail(PM_ERR_INVALID, "pm_ctx_create: device %d of %d", device, n);
+  CU(cudaSetDevice(device));
+  pm_ctx *c = new (std::nothrow) pm_ctx();
+  if (!c) return fail(PM_ERR_OOM, "pm_ctx_create: host allocation");
+  c->device = device;
+  CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  CU(cudaEventCreate(&c->ev0));
+  CU(cudaEventCreate(&c->ev1));
+  *out = c;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_ctx_destroy(pm_ctx *c) {
+  if (!c) return PM_OK;
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  if (c->ws) cudaFree(c->ws);
+  if (c->stage) cudaFree(c->stage);
+  if (c->flush) cudaFree(c->flush);
+  for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
+  cudaEventDestroy(c->ev0);
+  cudaEventDestroy(c->ev1);
+  cudaStreamDestroy(c->stream);
+  delete c;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_sync(pm_ctx *c) {
+  if (!c) return fail(PM_ERR_INVALID, "pm_sync: null context");
+  CU(cudaStreamSynchronize(c->stream));
+  CU(cudaGetLastError());
+  return PM_OK;
+}
+extern "C" void *pm_ctx_stream(pm_ctx *c) { return c ? (void *)c->stream : nullptr; }
+extern "C" int64_t pm_ctx_launch_count(pm_ctx *c) { return c ? c->launches : 0; }
+
+extern "C" int32_t pm_timer_start(pm_ctx *c) {
+  CU(cudaEventRecord(c->ev0, c->stream));
+  return PM_OK;
+}
+extern "C" int32_t pm_timer_stop(pm_ctx *c, float *ms) {
+  CU(cudaEventRecord(c->ev1, c->stream));
+  CU(cudaEventSynchronize(c->ev1));
+  CU(cudaEventElapsedTime(ms, c->ev0, c->ev1));
+  return PM_OK;
+}
+extern "C" int32_t pm_flush_l2(pm_ctx *c) {
+  const size_t bytes = (size_t)256 << 20;  // 2x the 126 MB L2
+  if (!c->flush) {
+    CU(cudaMalloc(&c->flush, bytes));
+    c->flush_bytes = bytes;
+  }
+  CU(cudaMemsetAsync(c->flush, 0x5a, c->flush_bytes, c->stream));
+  return PM_OK;
+}
+extern "C" int32_t pm_profile_enable(pm_ctx *c, int32_t on) {
+  if (!c) return fail(PM_ERR_INVALID, "pm_profile_enable: null context");
+  CU(cudaStreamSynchronize(c->stream));
+  c->prof_on = on != 0;
+  c->prof_used = 0;
+  c->prof_phase.clear();
+  return PM_OK;
+}
+extern "C" int32_t pm_profile_phases(void) { return PH_N; }
+extern "C" const char *pm_profile_phase_name(int32_t i) {
+  return (i >= 0 && i < PH_N) ? PH_NAMES[i] : "";
+}
+extern "C" int32_t pm_profile_read(pm_ctx *c, float *ms, int64_t *spans) {
+  if (!c || !ms || !spans) return fail(PM_ERR_INVALID, "pm_profile_read: null argument");
+  CU(cudaStreamSynchronize(c->stream));
+  for (int i = 0; i < PH_N; i++) { ms[i] = 0.0f; spans[i] = 0; }
+  for (size_t i = 0; i < c->prof_phase.size(); i++) {
+    float t = 0.0f;
+    CU(cudaEventElapsedTime(&t, c->prof_ev[2 * i], c->prof_ev[2 * i + 1]));
+    ms[c->prof_phase[i]] += t;
+    spans[c->prof_phase[i]]++;
+  }
+  c->prof_used = 0;
+  c->prof_phase.clear();
+  return PM_OK;
+}
+extern "C" int32_t pm_host_alloc(pm_ctx *c, size_t bytes, void **out) {
+  if (!c || !out) return fail(PM_ERR_INVALID, "pm_host_alloc: null argument");
+  CU(cudaSetDevice(c->device));
+  CU(cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault));
+  return PM_OK;
+}
+extern "C" int32_t pm_host_free(pm_ctx *c, void *p) {
+  CU(cudaFreeHost(p));
+  return PM_OK;
+}
+extern "C" int32_t pm_dev_alloc(pm_ctx *c, size_t bytes, void **out) {
+  CU(cudaSetDevice(c->device));
+  CU(cudaMalloc(out, bytes ? bytes : 1));
+  return PM_OK;
+}
+extern "C" int32_t pm_dev_free(pm_ctx *c, void *p) {
+  CU(cudaStreamSynchronize(c->stream));
+  CU(cudaFree(p));
+  return PM_OK;
+}
+extern "C" int32_t pm_copy(pm_ctx *c, void *dst, const void *src, size_t bytes) {
+  CU(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, c->stream));
+  if (!is_device_ptr(dst) || !is_device_ptr(src)) CU(cudaStreamSynchronize(c->stream));
+  return PM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// layer
+// ---------------------------------------------------------------------------
+struct pm_layer {
+  pm_ctx *ctx = nullptr;
+  LayerDev dev{};
+  std::vector<void *> owned;
+  std::vector<uint8_t> expert_set;
+  bool router_set = false, shared_set = false;
+  float *router_w = nullptr, *logit_bias = nullptr, *select_bias = nullptr;
+  float *bias_gate = nullptr, *bias_up = nullptr, *bias_down = nullptr, *gate_inp = nullptr;
+};
+
+static bool type_ok(int t) {
+  return t == PM_TYPE_Q4_K || t == PM_TYPE_Q6_K || t == PM_TYPE_MXFP4 || t == PM_TYPE_Q8_0;
+}
+
+static int32_t wmat_alloc(pm_layer *ly, WMat &W, int type, int n_exp, int rows, int cols) {
+  W.type = type;
+  W.rows = rows;
+  W.cols = cols;
+  for (int p = 0; p < 4; p++) {
+    W.plane[p] = nullptr;
+    W.stride[p] = wmat_plane_bytes(type, rows, cols, p);
+    if (W.stride[p]) {
+      // 256 spare bytes: vector loads of a partial last chunk never leave the allocation
+      CU(cudaMalloc(&W.plane[p], W.stride[p] * (size_t)n_exp + 256));
+      ly->owned.push_back(W.plane[p]);
+    }
+  }
+  return PM_OK;
+}
+
+static int32_t validate_desc(const pm_layer_desc *D) {
+  if (D->d < 32 || D->ff < 32 || D->d % 32 || D->ff % 32)
+    return fail(PM_ERR_INVALID, "d and ff must be multiples of 32 (d=%d ff=%d)", D->d, D->ff);
+  if (D->n_exp < 1 || D->n_exp > PM_MAX_EXPERTS)
+    return fail(PM_ERR_LIMIT, "n_exp %d outside 1..%d", D->n_exp, PM_MAX_EXPERTS);
+  if (D->top_k < 1 || D->top_k > PM_MAX_TOPK || D->top_k > D->n_exp)
+    return fail(PM_ERR_LIMIT, "top_k %d outside 1..%d", D->top_k, PM_MAX_TOPK);
+  if (D->gating < 0 || D->gating > PM_GATE_SOFTMAX_SELECTED)
+    return fail(PM_ERR_INVALID, "gating %d", D->gating);
+  if (D->n_group > 0) {
+    if (D->n_exp % D->n_group || D->topk_group < 1 || D->topk_group > D->n_group ||
+        D->n_exp / D->n_group < 2 || D->topk_group * (D->n_exp / D->n_group) < D->top_k ||
+        D->n_group > PM_MAX_EXPERTS / 2)
+      return fail(PM_ERR_INVALID, "group-limited selection: n_group=%d topk_group=%d n_exp=%d",
+                  D->n_group, D->topk_group, D->n_exp);
+  }
+  if (D->act < 0 || D->act > PM_ACT_OSS_GLU) return fail(PM_ERR_INVALID, "act %d", D->act);
+  if (!type_ok(D->type_gate) || !type_ok(D->type_up) || !type_ok(D->type_down))
+    return fail(PM_ERR_UNSUPPORTED, "expert tensor types %d/%d/%d", D->type_gate, D->type_up,
+                D->type_down);
+  if (D->act_quant == PM_AQ_Q8X_256) {
+    if (D->d % 256 || D->ff % 256)
+      return fail(PM_ERR_INVALID, "Q8x activations need d and ff multiples of 256 (src/ds4_cpu.rs:15)");
+    const int ts[3] = {D->type_gate, D->type_up, D->type_down};
+    for (int t : ts)
+      if (t != PM_TYPE_Q4_K && t != PM_TYPE_Q6_K)
+        return fail(PM_ERR_UNSUPPORTED, "Q8x activations pair with Q4_K / Q6_K weights only");
+    if (D->shared && D->shared_ff % 256) return fail(PM_ERR_INVALID, "shared_ff %% 256");
+  } else if (D->act_quant != PM_AQ_F32) {
+    return fail(PM_ERR_UNSUPPORTED, "act_quant %d", D->act_quant);
+  }
+  const int ts[3] = {D->type_gate, D->type_up, D->type_down};
+  const int cs[3] = {D->d, D->d, D->ff};
+  for (int i = 0; i < 3; i++)
+    if (cs[i] % (int)pm_type_block_values(ts[i]))
+      return fail(PM_ERR_INVALID, "row length %d is not whole blocks of type %d", cs[i], ts[i]);
+  if (D->weight_fold != PM_FOLD_BEFORE_DOWN && D->weight_fold != PM_FOLD_IN_COMBINE)
+    return fail(PM_ERR_INVALID, "weight_fold %d", D->weight_fold);
+  if (D->shared < 0 || D->shared > PM_SHARED_SIGMOID_GATED) return fail(PM_ERR_INVALID, "shared");
+  if (D->shared && (D->shared_ff < 32 || D->shared_ff % 32))
+    return fail(PM_ERR_INVALID, "shared_ff %d", D->shared_ff);
+  if (D->n_exp_local < 0 || D->first_local_expert < 0 ||
+      D->first_local_expert + D->n_exp_local > D->n_exp)
+    return fail(PM_ERR_INVALID, "local expert range");
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_destroy(pm_layer *ly) {
+  if (!ly) return PM_OK;
+  cudaSetDevice(ly->ctx->device);
+  cudaStreamSynchronize(ly->ctx->stream);
+  for (void *p : ly->owned) cudaFree(p);
+  delete ly;
+  return PM_OK;
+}
+
+template <typename T>
+static int32_t dev_new(pm_layer *ly, T **out, size_t n, bool zero) {
+  CU(cudaMalloc(out, (n ? n : 1) * sizeof(T)));
+  ly->owned.push_back(*out);
+  if (zero) CU(cudaMemsetAsync(*out, 0, (n ? n : 1) * sizeof(T), ly->ctx->stream));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_create(pm_ctx *ctx, const pm_layer_desc *desc, pm_layer **out) {
+  if (!ctx || !desc || !out) return fail(PM_ERR_INVALID, "pm_layer_create: null argument");
+  TRY(validate_desc(desc));
+  CU(cudaSetDevice(ctx->device));
+  pm_layer *ly = new (std::nothrow) pm_layer();
+  if (!ly) return fail(PM_ERR_OOM, "host allocation");
+  ly->ctx = ctx;
+  LayerDev &dv = ly->dev;
+  dv.desc = *desc;
+  dv.n_local = desc->n_exp_local > 0 ? desc->n_exp_local : desc->n_exp;
+  dv.first_local = desc->n_exp_local > 0 ? desc->first_local_expert : 0;
+  ly->expert_set.assign((size_t)dv.n_local, 0);
+  int32_t rc = PM_OK;
+  auto chk = [&](int32_t r) { if (rc == PM_OK) rc = r; };
+  const int E = desc->n_exp, d = desc->d, ff = desc->ff, nl = dv.n_local;
+  chk(dev_new(ly, &ly->router_w, (size_t)E * d, true));
+  chk(dev_new(ly, &dv.usage, (size_t)E, true));
+  if (rc == PM_OK) chk(wmat_alloc(ly, dv.gate, desc->type_gate, nl, ff, d));
+  if (rc == PM_OK) chk(wmat_alloc(ly, dv.up, desc->type_up, nl, ff, d));
+  if (rc == PM_OK) chk(wmat_alloc(ly, dv.down, desc->type_down, nl, d, ff));
+  if (rc == PM_OK && desc->has_expert_bias) {
+    chk(dev_new(ly, &ly->bias_gate, (size_t)nl * ff, true));
+    chk(dev_new(ly, &ly->bias_up, (size_t)nl * ff, true));
+    chk(dev_new(ly, &ly->bias_down, (size_t)nl * d, true));
+  }
+  if (rc == PM_OK && desc->shared) {
+    chk(wmat_alloc(ly, dv.sgate, desc->type_gate, 1, desc->shared_ff, d));
+    chk(wmat_alloc(ly, dv.sup, desc->type_up, 1, desc->shared_ff, d));
+    chk(wmat_alloc(ly, dv.sdown, desc->type_down, 1, d, desc->shared_ff));
+  }
+  if (rc != PM_OK) {
+    pm_layer_destroy(ly);
+    return rc;
+  }
+  dv.router = ly->router_w;
+  dv.bias_gate = ly->bias_gate;
+  dv.bias_up = ly->bias_up;
+  dv.bias_down = ly->bias_down;
+  *out = ly;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_set_router(pm_layer *ly, const void *w, int32_t dtype,
+                                       const float *logit_bias, const float *select_bias) {
+  if (!ly || !w) return fail(PM_ERR_INVALID, "pm_layer_set_router: null argument");
+  pm_ctx *c = ly->ctx;
+  CU(cudaSetDevice(c->device));
+  const pm_layer_desc &D = ly->dev.desc;
+  size_t n = (size_t)D.n_exp * D.d;
+  if (dtype == PM_TYPE_F32) {
+    CU(cudaMemcpyAsync(ly->router_w, w, n * 4, cudaMemcpyDefault, c->stream));
+  } else if (dtype == PM_TYPE_BF16) {
+    // bf16 -> f32 is exact (src/quant.rs:282: dot_bf16 == dot_f32 bit for bit)
+    if (is_device_ptr(w)) return fail(PM_ERR_UNSUPPORTED, "bf16 router must be a host pointer");
+    std::vector<uint32_t> tmp(n);
+    const uint16_t *s = (const uint16_t *)w;
+    for (size_t i = 0; i < n; i++) tmp[i] = (uint32_t)s[i] << 16;
+    CU(cudaMemcpyAsync(ly->router_w, tmp.data(), n * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+  } else {
+    return fail(PM_ERR_UNSUPPORTED, "router dtype %d (f32 or bf16)", dtype);
+  }
+  if (logit_bias) {
+    if (!ly->logit_bias) TRY(dev_new(ly, &ly->logit_bias, (size_t)D.n_exp, false));
+    CU(cudaMemcpyAsync(ly->logit_bias, logit_bias, (size_t)D.n_exp * 4, cudaMemcpyDefault, c->stream));
+    ly->dev.logit_bias = ly->logit_bias;
+  }
+  if (select_bias) {
+    if (!ly->select_bias) TRY(dev_new(ly, &ly->select_bias, (size_t)D.n_exp, false));
+    CU(cudaMemcpyAsync(ly->select_bias, select_bias, (size_t)D.n_exp * 4, cudaMemcpyDefault, c->stream));
+    ly->dev.select_bias = ly->select_bias;
+  }
+  CU(cudaStreamSynchronize(c->stream));
+  ly->router_set = true;
+  return PM_OK;
+}
+
+// raw GGUF bytes (host or device) -> planes of expert slot `el`
+static int32_t upload_mat(pm_layer *ly, WMat &W, int el, const uint8_t *raw) {
+  pm_ctx *c = ly->ctx;
+  size_t bytes = raw_bytes(W.type, (size_t)W.rows, (size_t)W.cols);
+  size_t nb = (size_t)W.rows * (W.cols / pm_type_block_values(W.type));
+  const uint8_t *src = raw;
+  if (!is_device_ptr(raw)) {
+    TRY(stage_reserve(c, bytes));
+    CU(cudaMemcpyAsync(c->stage, raw, bytes, cudaMemcpyHostToDevice, c->stream));
+    src = c->stage;
+  }
+  uint8_t *p[4];
+  for (int i = 0; i < 4; i++) p[i] = W.plane[i] ? W.plane[i] + (size_t)el * W.stride[i] : nullptr;
+  launch_repack(c->launch(), W.type, src, nb, p[0], p[1], p[2], p[3]);
+  CU(cudaGetLastError());
+  CU(cudaStreamSynchronize(c->stream));  // the staging buffer is reused by the next upload
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_set_expert(pm_layer *ly, int32_t e, const uint8_t *gate,
+                                       const uint8_t *up, const uint8_t *down,
+                                       const float *bias_gate, const float *bias_up,
+                                       const float *bias_down) {
+  if (!ly || !gate || !up || !down) return fail(PM_ERR_INVALID, "pm_layer_set_expert: null argument");
+  LayerDev &dv = ly->dev;
+  int el = e - dv.first_local;
+  if (el < 0 || el >= dv.n_local)
+    return fail(PM_ERR_INVALID, "expert %d is not local to this context [%d, %d)", e, dv.first_local,
+                dv.first_local + dv.n_local);
+  CU(cudaSetDevice(ly->ctx->device));
+  TRY(upload_mat(ly, dv.gate, el, gate));
+  TRY(upload_mat(ly, dv.up, el, up));
+  TRY(upload_mat(ly, dv.down, el, down));
+  if (dv.desc.has_expert_bias) {
+    if (!bias_gate || !bias_up || !bias_down)
+      return fail(PM_ERR_INVALID, "layer has expert biases; all three are required");
+    cudaStream_t s = ly->ctx->stream;
+    int ff = dv.desc.ff, d = dv.desc.d;
+    CU(cudaMemcpyAsync(ly->bias_gate + (size_t)el * ff, bias_gate, (size_t)ff * 4, cudaMemcpyDefault, s));
+    CU(cudaMemcpyAsync(ly->bias_up + (size_t)el * ff, bias_up, (size_t)ff * 4, cudaMemcpyDefault, s));
+    CU(cudaMemcpyAsync(ly->bias_down + (size_t)el * d, bias_down, (size_t)d * 4, cudaMemcpyDefault, s));
+    CU(cudaStreamSynchronize(s));
+  }
+  ly->expert_set[(size_t)el] = 1;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_set_shared(pm_layer *ly, const uint8_t *gate, const uint8_t *up,
+                                       const uint8_t *down, const float *gate_inp) {
+  if (!ly || !gate || !up || !down) return fail(PM_ERR_INVALID, "pm_layer_set_shared: null argument");
+  LayerDev &dv = ly->dev;
+  if (!dv.desc.shared) return fail(PM_ERR_STATE, "layer was created without a shared expert");
+  CU(cudaSetDevice(ly->ctx->device));
+  TRY(upload_mat(ly, dv.sgate, 0, gate));
+  TRY(upload_mat(ly, dv.sup, 0, up));
+  TRY(upload_mat(ly, dv.sdown, 0, down));
+  if (dv.desc.shared == PM_SHARED_SIGMOID_GATED) {
+    if (!gate_inp) return fail(PM_ERR_INVALID, "sigmoid-gated shared expert needs gate_inp");
+    if (!ly->gate_inp) TRY(dev_new(ly, &ly->gate_inp, (size_t)dv.desc.d, false));
+    CU(cudaMemcpyAsync(ly->gate_inp, gate_inp, (size_t)dv.desc.d * 4, cudaMemcpyDefault, ly->ctx->stream));
+    CU(cudaStreamSynchronize(ly->ctx->stream));
+    dv.shared_gate_inp = ly->gate_inp;
+  }
+  ly->shared_set = true;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_read_usage(pm_layer *ly, uint32_t *out) {
+  if (!ly || !out) return fail(PM_ERR_INVALID, "pm_layer_read_usage: null argument");
+  CU(cudaMemcpyAsync(out, ly->dev.usage, (size_t)ly->dev.desc.n_exp * 4, cudaMemcpyDeviceToHost,
+                     ly->ctx->stream));
+  CU(cudaStreamSynchronize(ly->ctx->stream));
+  return PM_OK;
+}
+
+static int32_t layer_ready(const pm_layer *ly, bool need_experts) {
+  if (!ly) return fail(PM_ERR_INVALID, "null layer");
+  if (!ly->router_set) return fail(PM_ERR_STATE, "router weights not set");
+  if (need_experts) {
+    for (size_t i = 0; i < ly->expert_set.size(); i++)
+      if (!ly->expert_set[i])
+        return fail(PM_ERR_STATE, "expert %d has no weights", (int)i + ly->dev.first_local);
+    if (ly->dev.desc.shared && !ly->shared_set) return fail(PM_ERR_STATE, "shared expert not set");
+  }
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_get_expert(pm_layer *ly, int32_t e, int32_t which, uint8_t *out) {
+  if (!ly || !out || which < 0 || which > 2) return fail(PM_ERR_INVALID, "pm_layer_get_expert");
+  LayerDev &dv = ly->dev;
+  pm_ctx *c = ly->ctx;
+  bool shared = e < 0;
+  int el = shared ? 0 : e - dv.first_local;
+  if (!shared && (el < 0 || el >= dv.n_local)) return fail(PM_ERR_INVALID, "expert %d not local", e);
+  if (shared && !dv.desc.shared) return fail(PM_ERR_STATE, "no shared expert");
+  WMat &W = shared ? (which == 0 ? dv.sgate : which == 1 ? dv.sup : dv.sdown)
+                   : (which == 0 ? dv.gate : which == 1 ? dv.up : dv.down);
+  size_t bytes = raw_bytes(W.type, (size_t)W.rows, (size_t)W.cols);
+  size_t nb = (size_t)W.rows * (W.cols / pm_type_block_values(W.type));
+  CU(cudaSetDevice(c->device));
+  TRY(stage_reserve(c, bytes));
+  const uint8_t *p[4];
+  for (int i = 0; i < 4; i++) p[i] = W.plane[i] ? W.plane[i] + (size_t)el * W.stride[i] : nullptr;
+  launch_unpack(c->launch(), W.type, c->stage, nb, p[0], p[1], p[2], p[3]);
+  CU(cudaGetLastError());
+  CU(cudaMemcpyAsync(out, c->stage, bytes, cudaMemcpyDeviceToHost, c->stream));
+  CU(cudaStreamSynchronize(c->stream));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_get_router(pm_layer *ly, float *w, float *logit_bias,
+                                       float *select_bias) {
+  if (!ly) return fail(PM_ERR_INVALID, "pm_layer_get_router");
+  const pm_layer_desc &D = ly->dev.desc;
+  cudaStream_t s = ly->ctx->stream;
+  if (w) CU(cudaMemcpyAsync(w, ly->router_w, (size_t)D.n_exp * D.d * 4, cudaMemcpyDeviceToHost, s));
+  if (logit_bias && ly->logit_bias)
+    CU(cudaMemcpyAsync(logit_bias, ly->logit_bias, (size_t)D.n_exp * 4, cudaMemcpyDeviceToHost, s));
+  if (select_bias && ly->select_bias)
+    CU(cudaMemcpyAsync(select_bias, ly->select_bias, (size_t)D.n_exp * 4, cudaMemcpyDeviceToHost, s));
+  CU(cudaStreamSynchronize(s));
+  return PM_OK;
+}
+
+// synthetic weights, generated and quantised on the device
+static int32_t synth_mat(pm_layer *ly, WMat &W, int n_exp, uint64_t seed, float sigma) {
+  pm_ctx *c = ly->ctx;
+  size_t per = raw_bytes(W.type, (size_t)W.rows, (size_t)W.cols);
+  size_t nb_per = (size_t)W.rows * (W.cols / pm_type_block_values(W.type));
+  if (W.type == PM_TYPE_Q8_0) return fail(PM_ERR_UNSUPPORTED, "synthetic Q8_0");
+  // groups of experts so the raw staging stays below ~1 GB
+  int group = (int)((((size_t)1 << 30) / per) ? (((size_t)1 << 30) / per) : 1);
+  if (group > n_exp) group = n_exp;
+  TRY(stage_reserve(c, per * (size_t)group));
+  for (int e0 = 0; e0 < n_exp; e0 += group) {
+    int n = n_exp - e0 < group ? n_exp - e0 : group;
+    launch_synth_blocks(c->launch(), W.type, c->stage, nb_per * n,
+                        seed + 0x1000193ull * (uint64_t)e0, sigma);
+    uint8_t *p[4];
+    for (int i = 0; i < 4; i++) p[i] = W.plane[i] ? W.plane[i] + (size_t)e0 * W.stride[i] : nullptr;
+    launch_repack(c->launch(), W.type, c->stage, nb_per * n, p[0], p[1], p[2], p[3]);
+    CU(cudaGetLastError());
+  }
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_get_expert_bias(pm_layer *ly, int32_t e, float *bg, float *bu,
+                                            float *bd) {
+  if (!ly) return fail(PM_ERR_INVALID, "pm_layer_get_expert_bias");
+  const LayerDev &dv = ly->dev;
+  int el = e - dv.first_local;
+  if (!dv.desc.has_expert_bias) return fail(PM_ERR_STATE, "layer has no expert biases");
+  if (el < 0 || el >= dv.n_local) return fail(PM_ERR_INVALID, "expert %d not local", e);
+  cudaStream_t s = ly->ctx->stream;
+  int ff = dv.desc.ff, d = dv.desc.d;
+  if (bg) CU(cudaMemcpyAsync(bg, ly->bias_gate + (size_t)el * ff, (size_t)ff * 4, cudaMemcpyDeviceToHost, s));
+  if (bu) CU(cudaMemcpyAsync(bu, ly->bias_up + (size_t)el * ff, (size_t)ff * 4, cudaMemcpyDeviceToHost, s));
+  if (bd) CU(cudaMemcpyAsync(bd, ly->bias_down + (size_t)el * d, (size_t)d * 4, cudaMemcpyDeviceToHost, s));
+  CU(cudaStreamSynchronize(s));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_layer_fill_synthetic(pm_layer *ly, uint64_t seed, float sigma,
+                                           float logit_bias_sigma, float select_bias_sigma) {
+  if (!ly) return fail(PM_ERR_INVALID, "pm_layer_fill_synthetic: null layer");
+  pm_ctx *c = ly->ctx;
+  LayerDev &dv = ly->dev;
+  const pm_layer_desc &D = dv.desc;
+  CU(cudaSetDevice(c->device));
+  Launch L = c->launch();
+  launch_synth_f32(L, ly->router_w, (size_t)D.n_exp * D.d, seed ^ 0x11, sigma, 0);
+  if (logit_bias_sigma > 0.0f) {
+    if (!ly->logit_bias) TRY(dev_new(ly, &ly->logit_bias, (size_t)D.n_exp, false));
+    launch_synth_f32(L, ly->logit_bias, (size_t)D.n_exp, seed ^ 0xcc, logit_bias_sigma, 1);
+    dv.logit_bias = ly->logit_bias;
+  }
+  if (select_bias_sigma > 0.0f) {
+    if (!ly->select_bias) TRY(dev_new(ly, &ly->select_bias, (size_t)D.n_exp, false));
+    launch_synth_f32(L, ly->select_bias, (size_t)D.n_exp, seed ^ 0xdd, select_bias_sigma, 0);
+    dv.select_bias = ly->select_bias;
+  }
+  TRY(synth_mat(ly, dv.gate, dv.n_local, seed ^ 0x22 ^ ((uint64_t)dv.first_local << 32), sigma));
+  TRY(synth_mat(ly, dv.up, dv.n_local, seed ^ 0x33 ^ ((uint64_t)dv.first_local << 32), sigma));
+  TRY(synth_mat(ly, dv.down, dv.n_local, seed ^ 0x44 ^ ((uint64_t)dv.first_local << 32), sigma));
+  if (D.has_expert_bias) {
+    launch_synth_f32(L, ly->bias_gate, (size_t)dv.n_local * D.ff, seed ^ 0x55, sigma, 1);
+    launch_synth_f32(L, ly->bias_up, (size_t)dv.n_local * D.ff, seed ^ 0x66, sigma, 1);
+    launch_synth_f32(L, ly->bias_down, (size_t)dv.n_local * D.d, seed ^ 0x77, sigma, 1);
+  }
+  if (D.shared) {
+    TRY(synth_mat(ly, dv.sgate, 1, seed ^ 0x88, sigma));
+    TRY(synth_mat(ly, dv.sup, 1, seed ^ 0x99, sigma));
+    TRY(synth_mat(ly, dv.sdown, 1, seed ^ 0xaa, sigma));
+    if (D.shared == PM_SHARED_SIGMOID_GATED) {
+      if (!ly->gate_inp) TRY(dev_new(ly, &ly->gate_inp, (size_t)D.d, false));
+      launch_synth_f32(L, ly->gate_inp, (size_t)D.d, seed ^ 0xbb, sigma, 0);
+      dv.shared_gate_inp = ly->gate_inp;
+    }
+    ly->shared_set = true;
+  }
+  CU(cudaGetLastError());
+  CU(cudaStreamSynchronize(c->stream));
+  ly->router_set = true;
+  std::fill(ly->expert_set.begin(), ly->expert_set.end(), 1);
+  return PM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// the pipeline on device pointers
+// ---------------------------------------------------------------------------
+struct Scratch {
+  float *logits;
+  uint32_t *ids;
+  float *w;
+  PlanDev plan;
+  int8_t *xq; float *xd; int32_t *xbsum;
+  float *h; int8_t *hq; float *hd; int32_t *hbsum;
+  float *eo;
+  // shared expert
+  int *one; uint32_t *zero_u, *tcount, *iota;
+  float *sh; int8_t *shq; float *shd; int32_t *shbsum;
+  float *shared_out, *shared_logit;
+};
+
+static size_t scratch_bytes(const pm_layer_desc &D, int T) {
+  size_t P = (size_t)T * D.top_k, E = (size_t)D.n_exp, d = (size_t)D.d, ff = (size_t)D.ff;
+  size_t b = 0;
+  b += al(T * E * 4) + al(P * 4) * 2;                  // logits, ids, w
+  b += al(4) + al(E * 4) * 5 + al(P * 4) * 3;          // plan
+  b += al(T * d) + al(T * (d / 256 + 1) * 4) + al(T * (d / 32) * 4);
+  b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 256 + 1) * 4) + al(P * (ff / 32) * 4);
+  b += al(P * d * 4);
+  if (D.shared) {
+    size_t sf = (size_t)D.shared_ff;
+    b += al(4) + al(4) * 2 + al((size_t)T * 4);
+    b += al(T * sf * 4) + al(T * sf) + al(T * (sf / 256 + 1) * 4) + al(T * (sf / 32) * 4);
+    b += al(T * d * 4) + al((size_t)T * 4);
+  }
+  return b + 4096;
+}
+
+static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) {
+  size_t P = (size_t)T * D.top_k, E = (size_t)D.n_exp, d = (size_t)D.d, ff = (size_t)D.ff;
+  S.logits = ws_take<float>(c, T * E);
+  S.ids = ws_take<uint32_t>(c, P);
+  S.w = ws_take<float>(c, P);
+  S.plan.n_active = ws_take<int>(c, 1);
+  S.plan.active = ws_take<uint32_t>(c, E);
+  S.plan.offset = ws_take<uint32_t>(c, E);
+  S.plan.count = ws_take<uint32_t>(c, E);
+  S.plan.base = ws_take<uint32_t>(c, E);
+  S.plan.cnt = ws_take<uint32_t>(c, E);
+  S.plan.pair_token = ws_take<uint32_t>(c, P);
+  S.plan.pair_pos = ws_take<uint32_t>(c, P);
+  S.plan.pair_src = ws_take<uint32_t>(c, P);
+  S.xq = ws_take<int8_t>(c, T * d);
+  S.xd = ws_take<float>(c, T * (d / 256 + 1));
+  S.xbsum = ws_take<int32_t>(c, T * (d / 32));
+  S.h = ws_take<float>(c, P * ff);
+  S.hq = ws_take<int8_t>(c, P * ff);
+  S.hd = ws_take<float>(c, P * (ff / 256 + 1));
+  S.hbsum = ws_take<int32_t>(c, P * (ff / 32));
+  S.eo = ws_take<float>(c, P * d);
+  if (D.shared) {
+    size_t sf = (size_t)D.shared_ff;
+    S.one = ws_take<int>(c, 1);
+    S.zero_u = ws_take<uint32_t>(c, 1);
+    S.tcount = ws_take<uint32_t>(c, 1);
+    S.iota = ws_take<uint32_t>(c, (size_t)T);
+    S.sh = ws_take<float>(c, T * sf);
+    S.shq = ws_take<int8_t>(c, T * sf);
+    S.shd = ws_take<float>(c, T * (sf / 256 + 1));
+    S.shbsum = ws_take<int32_t>(c, T * (sf / 32));
+    S.shared_out = ws_take<float>(c, T * d);
+    S.shared_logit = ws_take<float>(c, (size_t)T);
+  } else {
+    S.shared_out = nullptr;
+    S.shared_logit = nullptr;
+  }
+}
+
+static Groups plan_groups(const PlanDev &pl, int E) {
+  Groups g;
+  g.n_groups = pl.n_active;
+  g.expert = pl.active;
+  g.offset = pl.offset;
+  g.count = pl.count;
+  g.pair_token = pl.pair_token;
+  g.pair_src = pl.pair_src;
+  g.max_groups = E;
+  return g;
+}
+
+// routed experts: x (and its Q8x form) -> eo[P][d]
+static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, const float *w) {
+  pm_ctx *c = ly->ctx;
+  const LayerDev &dv = ly->dev;
+  const pm_layer_desc &D = dv.desc;
+  Launch L = c->launch();
+  int P = T * D.top_k;
+  Groups g = plan_groups(S.plan, D.n_exp);
+  bool q8 = D.act_quant == PM_AQ_Q8X_256;
+  if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum); }
+  { PROF(c, PH_GATEUP); launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h); }
+  if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum); }
+  { PROF(c, PH_DOWN); launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo); }
+  CU(cudaGetLastError());
+  return PM_OK;
+}
+
+// shared expert over every token -> S.shared_out (and the gate logit)
+static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
+  pm_ctx *c = ly->ctx;
+  const LayerDev &dv = ly->dev;
+  const pm_layer_desc &D = dv.desc;
+  if (!D.shared) return PM_OK;
+  PROF(c, PH_SHARED);
+  Launch L = c->launch();
+  const int one = 1;
+  const uint32_t zero = 0, tc = (uint32_t)T;
+  CU(cudaMemcpyAsync(S.one, &one, 4, cudaMemcpyHostToDevice, c->stream));
+  CU(cudaMemcpyAsync(S.zero_u, &zero, 4, cudaMemcpyHostToDevice, c->stream));
+  CU(cudaMemcpyAsync(S.tcount, &tc, 4, cudaMemcpyHostToDevice, c->stream));
+  launch_iota(L, S.iota, (uint32_t)T);
+  Groups g;
+  g.n_groups = S.one;
+  g.expert = S.zero_u;
+  g.offset = S.zero_u;
+  g.count = S.tcount;
+  g.pair_token = S.iota;
+  g.pair_src = nullptr;
+  g.max_groups = 1;
+  bool q8 = D.act_quant == PM_AQ_Q8X_256;
+  // (S.xq holds the tokens' Q8x form already when the routed experts ran first)
+  if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum);
+  launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
+  if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum);
+  launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
+  if (D.shared == PM_SHARED_SIGMOID_GATED) launch_shared_gate_logit(L, dv, x, T, S.shared_logit);
+  else S.shared_logit = nullptr;
+  CU(cudaGetLastError());
+  return PM_OK;
+}
+
+// the whole layer on device pointers (workspace already reserved and carved)
+static int32_t dev_forward(pm_layer *ly, const float *x, int T, float *y, bool accumulate,
+                           Scratch &S) {
+  pm_ctx *c = ly->ctx;
+  const LayerDev &dv = ly->dev;
+  Launch L = c->launch();
+  { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
+  { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
+  { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan); }
+  TRY(dev_experts(ly, x, T, S, S.w));
+  TRY(dev_shared(ly, x, T, S));
+  {
+    PROF(c, PH_COMBINE);
+    launch_combine(L, dv, S.eo, S.plan.pair_pos, S.w, S.shared_out, S.shared_logit, T, y, accumulate);
+  }
+  CU(cudaGetLastError());
+  return PM_OK;
+}
+
+static int32_t check_T(int32_t T) {
+  if (T < 0 || T > PM_MAX_TOKENS) return fail(PM_ERR_LIMIT, "T=%d outside 0..%d", T, PM_MAX_TOKENS);
+  return PM_OK;
+}
+
+// host-or-device input -> device pointer (staged in the workspace when host)
+template <typename T>
+static int32_t in_dev(pm_ctx *c, const T *p, size_t n, const T **out) {
+  if (is_device_ptr(p)) {
+    *out = p;
+    return PM_OK;
+  }
+  T *t = ws_take<T>(c, n);
+  CU(cudaMemcpyAsync(t, p, n * sizeof(T), cudaMemcpyHostToDevice, c->stream));
+  *out = t;
+  return PM_OK;
+}
+struct OutBuf {
+  void *host = nullptr;
+  void *dev = nullptr;
+  size_t bytes = 0;
+};
+template <typename T>
+static T *out_dev(pm_ctx *c, T *p, size_t n, OutBuf &ob) {
+  if (is_device_ptr(p)) return p;
+  T *t = ws_take<T>(c, n);
+  ob.host = p;
+  ob.dev = t;
+  ob.bytes = n * sizeof(T);
+  return t;
+}
+static int32_t out_flush(pm_ctx *c, OutBuf *obs, int n) {
+  bool any = false;
+  for (int i = 0; i < n; i++)
+    if (obs[i].host && obs[i].bytes) {
+      CU(cudaMemcpyAsync(obs[i].host, obs[i].dev, obs[i].bytes, cudaMemcpyDeviceToHost, c->stream));
+      any = true;
+    }
+  if (any) CU(cudaStreamSynchronize(c->stream));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_moe_forward(pm_layer *ly, const float *x, int32_t T, float *y,
+                                  uint32_t flags) {
+  TRY(layer_ready(ly, true));
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  if (!x || !y) return fail(PM_ERR_INVALID, "pm_moe_forward: null x or y");
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * D.d;
+  TRY(ws_reserve(c, scratch_bytes(D, T) + 2 * al(n * 4)));
+  const float *xd;
+  TRY(in_dev(c, x, n, &xd));
+  OutBuf ob;
+  float *yd = out_dev(c, y, n, ob);
+  bool acc = flags & PM_FWD_ACCUMULATE;
+  if (acc && ob.host) CU(cudaMemcpyAsync(yd, y, n * 4, cudaMemcpyHostToDevice, c->stream));
+  Scratch S;
+  scratch_carve(c, D, T, S);
+  TRY(dev_forward(ly, xd, T, yd, acc, S));
+  return out_flush(c, &ob, 1);
+}
+
+extern "C" int32_t pm_router_logits(pm_layer *ly, const float *x, int32_t T, float *logits) {
+  TRY(layer_ready(ly, false));
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * D.d, nl = (size_t)T * D.n_exp;
+  TRY(ws_reserve(c, al(n * 4) + al(nl * 4) + 4096));
+  const float *xd;
+  TRY(in_dev(c, x, n, &xd));
+  OutBuf ob;
+  float *ld = out_dev(c, logits, nl, ob);
+  launch_router(c->launch(), ly->dev, xd, T, ld);
+  CU(cudaGetLastError());
+  return out_flush(c, &ob, 1);
+}
+
+extern "C" int32_t pm_route_logits(pm_layer *ly, const float *logits, int32_t T, uint32_t *ids,
+                                   float *w) {
+  TRY(layer_ready(ly, false));
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t nl = (size_t)T * D.n_exp, P = (size_t)T * D.top_k;
+  TRY(ws_reserve(c, al(nl * 4) + 2 * al(P * 4) + 4096));
+  const float *ld;
+  TRY(in_dev(c, logits, nl, &ld));
+  OutBuf ob[2];
+  uint32_t *idd = out_dev(c, ids, P, ob[0]);
+  float *wd = out_dev(c, w, P, ob[1]);
+  launch_route(c->launch(), ly->dev, ld, T, idd, wd);
+  CU(cudaGetLastError());
+  return out_flush(c, ob, 2);
+}
+
+extern "C" int32_t pm_route(pm_layer *ly, const float *x, int32_t T, uint32_t *ids, float *w) {
+  TRY(layer_ready(ly, false));
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * D.d, nl = (size_t)T * D.n_exp, P = (size_t)T * D.top_k;
+  TRY(ws_reserve(c, al(n * 4) + al(nl * 4) + 2 * al(P * 4) + 4096));
+  const float *xd;
+  TRY(in_dev(c, x, n, &xd));
+  float *ld = ws_take<float>(c, nl);
+  OutBuf ob[2];
+  uint32_t *idd = out_dev(c, ids, P, ob[0]);
+  float *wd = out_dev(c, w, P, ob[1]);
+  launch_router(c->launch(), ly->dev, xd, T, ld);
+  launch_route(c->launch(), ly->dev, ld, T, idd, wd);
+  CU(cudaGetLastError());
+  return out_flush(c, ob, 2);
+}
+
+static void plan_carve(pm_ctx *c, int E, size_t P, PlanDev &pl) {
+  pl.n_active = ws_take<int>(c, 1);
+  pl.active = ws_take<uint32_t>(c, (size_t)E);
+  pl.offset = ws_take<uint32_t>(c, (size_t)E);
+  pl.count = ws_take<uint32_t>(c, (size_t)E);
+  pl.base = ws_take<uint32_t>(c, (size_t)E);
+  pl.cnt = ws_take<uint32_t>(c, (size_t)E);
+  pl.pair_token = ws_take<uint32_t>(c, P);
+  pl.pair_pos = ws_take<uint32_t>(c, P);
+  pl.pair_src = ws_take<uint32_t>(c, P);
+}
+
+static int32_t check_ids_host(const pm_layer_desc &D, const uint32_t *ids, size_t P) {
+  for (size_t i = 0; i < P; i++)
+    if (ids[i] >= (uint32_t)D.n_exp)
+      return fail(PM_ERR_INVALID, "expert id %u at %zu is outside 0..%d", ids[i], i, D.n_exp - 1);
+  return PM_OK;
+}
+
+extern "C" int32_t pm_plan(pm_layer *ly, const uint32_t *ids, int32_t T, pm_plan_out *out) {
+  if (!ly || !out) return fail(PM_ERR_INVALID, "pm_plan: null argument");
+  TRY(check_T(T));
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t P = (size_t)T * D.top_k, E = (size_t)D.n_exp;
+  if (P && !is_device_ptr(ids)) TRY(check_ids_host(D, ids, P));
+  TRY(ws_reserve(c, al(P * 4) * 4 + al(E * 4) * 5 + 8192));
+  const uint32_t *idd = nullptr;
+  if (P) TRY(in_dev(c, ids, P, &idd));
+  PlanDev pl;
+  plan_carve(c, D.n_exp, P, pl);
+  // the plan of a split call does not count towards usage[]
+  LayerDev tmp = ly->dev;
+  tmp.usage = nullptr;
+  launch_plan(c->launch(), tmp, idd, T, pl);
+  CU(cudaGetLastError());
+  cudaStream_t s = c->stream;
+  CU(cudaMemcpyAsync(out->n_active, pl.n_active, 4, cudaMemcpyDefault, s));
+  CU(cudaMemcpyAsync(out->active, pl.active, E * 4, cudaMemcpyDefault, s));
+  CU(cudaMemcpyAsync(out->offset, pl.offset, E * 4, cudaMemcpyDefault, s));
+  CU(cudaMemcpyAsync(out->count, pl.count, E * 4, cudaMemcpyDefault, s));
+  if (P) {
+    CU(cudaMemcpyAsync(out->pair_token, pl.pair_token, P * 4, cudaMemcpyDefault, s));
+    CU(cudaMemcpyAsync(out->pair_pos, pl.pair_pos, P * 4, cudaMemcpyDefault, s));
+  }
+  CU(cudaStreamSynchronize(s));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_experts(pm_layer *ly, const float *x, int32_t T, const uint32_t *ids,
+                              const float *w, float *pair_out) {
+  TRY(layer_ready(ly, true));
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  if (!x || !ids || !w || !pair_out) return fail(PM_ERR_INVALID, "pm_experts: null argument");
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * D.d, P = (size_t)T * D.top_k;
+  if (!is_device_ptr(ids)) TRY(check_ids_host(D, ids, P));
+  TRY(ws_reserve(c, scratch_bytes(D, T) + al(n * 4) + 2 * al(P * 4) + al(P * D.d * 4)));
+  const float *xd, *wd;
+  const uint32_t *idd;
+  TRY(in_dev(c, x, n, &xd));
+  TRY(in_dev(c, ids, P, &idd));
+  TRY(in_dev(c, w, P, &wd));
+  Scratch S;
+  scratch_carve(c, D, T, S);
+  LayerDev tmp = ly->dev;
+  tmp.usage = nullptr;
+  launch_plan(c->launch(), tmp, idd, T, S.plan);
+  TRY(dev_experts(ly, xd, T, S, wd));
+  CU(cudaMemcpyAsync(pair_out, S.eo, P * D.d * 4, cudaMemcpyDefault, c->stream));
+  CU(cudaStreamSynchronize(c->stream));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_combine(pm_layer *ly, const float *pair_out, const uint32_t *ids,
+                              const float *w, const float *shared_out, int32_t T, float *y,
+                              uint32_t flags) {
+  if (!ly) return fail(PM_ERR_INVALID, "pm_combine: null layer");
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  if (!pair_out || !ids || !w || !y) return fail(PM_ERR_INVALID, "pm_combine: null argument");
+  pm_ctx *c = ly->ctx;
+  const pm_layer_desc &D = ly->dev.desc;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * D.d, P = (size_t)T * D.top_k, E = (size_t)D.n_exp;
+  if (!is_device_ptr(ids)) TRY(check_ids_host(D, ids, P));
+  TRY(ws_reserve(c, al(P * D.d * 4) + al(P * 4) * 5 + al(E * 4) * 5 + 3 * al(n * 4) + 8192));
+  const float *pod, *wd, *sod = nullptr;
+  const uint32_t *idd;
+  TRY(in_dev(c, pair_out, P * D.d, &pod));
+  TRY(in_dev(c, ids, P, &idd));
+  TRY(in_dev(c, w, P, &wd));
+  if (shared_out) TRY(in_dev(c, shared_out, n, &sod));
+  OutBuf ob;
+  float *yd = out_dev(c, y, n, ob);
+  bool acc = flags & PM_FWD_ACCUMULATE;
+  if (acc && ob.host) CU(cudaMemcpyAsync(yd, y, n * 4, cudaMemcpyHostToDevice, c->stream));
+  PlanDev pl;
+  plan_carve(c, D.n_exp, P, pl);
+  LayerDev tmp = ly->dev;
+  tmp.usage = nullptr;
+  launch_plan(c->launch(), tmp, idd, T, pl);
+  launch_combine(c->launch(), ly->dev, pod, pl.pair_pos, wd, sod, nullptr, T, yd, acc);
+  CU(cudaGetLastError());
+  return out_flush(c, &ob, 1);
+}
+
+// ---------------------------------------------------------------------------
+// format checks
+// ---------------------------------------------------------------------------
+extern "C" int32_t pm_dequant(pm_ctx *c, int32_t type, const uint8_t *blocks, size_t n_values,
+                              float *out) {
+  if (!c || !blocks || !out) return fail(PM_ERR_INVALID, "pm_dequant: null argument");
+  if (!type_ok(type)) return fail(PM_ERR_UNSUPPORTED, "pm_dequant: type %d", type);
+  size_t bv = pm_type_block_values(type), bb = pm_type_block_bytes(type);
+  if (n_values % bv) return fail(PM_ERR_INVALID, "pm_dequant: %zu values is not whole blocks", n_values);
+  if (n_values == 0) return PM_OK;
+  CU(cudaSetDevice(c->device));
+  size_t nb = n_values / bv, rawb = nb * bb;
+  size_t pb[4];
+  for (int p = 0; p < 4; p++) pb[p] = wmat_plane_bytes(type, 1, (int)bv, p) * nb;
+  TRY(ws_reserve(c, al(rawb) + al(pb[0]) + al(pb[1]) + al(pb[2]) + al(pb[3]) + al(n_values * 4) + 4096));
+  const uint8_t *rd;
+  TRY(in_dev(c, blocks, rawb, &rd));
+  uint8_t *p[4];
+  for (int i = 0; i < 4; i++) p[i] = pb[i] ? ws_take<uint8_t>(c, pb[i]) : nullptr;
+  OutBuf ob;
+  float *od = out_dev(c, out, n_values, ob);
+  launch_repack(c->launch(), type, rd, nb, p[0], p[1], p[2], p[3]);
+  launch_dequant(c->launch(), type, n_values, p[0], p[1], p[2], p[3], od);
+  CU(cudaGetLastError());
+  return out_flush(c, &ob, 1);
+}
+
+extern "C" int32_t pm_quant_act(pm_ctx *c, int32_t mode, const float *x, size_t n, int8_t *q,
+                                float *scale, int32_t *bsum) {
+  if (!c || !x || !q || !scale || !bsum) return fail(PM_ERR_INVALID, "pm_quant_act: null argument");
+  if (mode != PM_AQ_Q8X_256) return fail(PM_ERR_UNSUPPORTED, "pm_quant_act: mode %d", mode);
+  if (n % 256) return fail(PM_ERR_INVALID, "pm_quant_act: n %% 256 != 0 (src/ds4_cpu.rs:15)");
+  if (n == 0) return PM_OK;
+  CU(cudaSetDevice(c->device));
+  TRY(ws_reserve(c, al(n * 4) + al(n) + al(n / 256 * 4) + al(n / 32 * 4) + 4096));
+  const float *xd;
+  TRY(in_dev(c, x, n, &xd));
+  OutBuf ob[3];
+  int8_t *qd = out_dev(c, q, n, ob[0]);
+  float *sd = out_dev(c, scale, n / 256, ob[1]);
+  int32_t *bd = out_dev(c, bsum, n / 32, ob[2]);
+  launch_quant_q8x(c->launch(), xd, 1, (int)n, qd, sd, bd);
+  CU(cudaGetLastError());
+  return out_flush(c, ob, 3);
+}
+
+// ---------------------------------------------------------------------------
+// layer stacks
+// ---------------------------------------------------------------------------
+struct pm_stack {
+  pm_ctx *ctx = nullptr;
+  std::vector<pm_layer *> layers;
+  float eps = 1e-6f;
+};
+
+extern "C" int32_t pm_stack_create(pm_ctx *ctx, pm_layer **layers, int32_t n, float eps,
+                                   pm_stack **out) {
+  if (!ctx || !layers || n < 1 || !out) return fail(PM_ERR_INVALID, "pm_stack_create");
+  for (int i = 0; i < n; i++) {
+    if (!layers[i] || layers[i]->ctx != ctx) return fail(PM_ERR_INVALID, "layer %d: wrong context", i);
+    if (layers[i]->dev.desc.d != layers[0]->dev.desc.d)
+      return fail(PM_ERR_INVALID, "layer %d: hidden size differs", i);
+  }
+  pm_stack *s = new (std::nothrow) pm_stack();
+  if (!s) return fail(PM_ERR_OOM, "host allocation");
+  s->ctx = ctx;
+  s->layers.assign(layers, layers + n);
+  s->eps = eps;
+  *out = s;
+  return PM_OK;
+}
+extern "C" int32_t pm_stack_destroy(pm_stack *s) {
+  delete s;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_stack_forward(pm_stack *s, const float *x, int32_t T, float *x_out) {
+  if (!s || !x || !x_out) return fail(PM_ERR_INVALID, "pm_stack_forward: null argument");
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  pm_ctx *c = s->ctx;
+  CU(cudaSetDevice(c->device));
+  for (pm_layer *ly : s->layers) TRY(layer_ready(ly, true));
+  const int d = s->layers[0]->dev.desc.d;
+  size_t n = (size_t)T * d;
+  size_t need = 0;
+  for (pm_layer *ly : s->layers) {
+    size_t b = scratch_bytes(ly->dev.desc, T);
+    if (b > need) need = b;
+  }
+  TRY(ws_reserve(c, need + 3 * al(n * 4)));
+  // residual stream: in place in x_out when it is a device pointer
+  float *xc = is_device_ptr(x_out) ? x_out : ws_take<float>(c, n);
+  float *xn = ws_take<float>(c, n);
+  if (xc != x) CU(cudaMemcpyAsync(xc, x, n * 4, cudaMemcpyDefault, c->stream));
+  size_t mark = c->ws_off;
+  for (pm_layer *ly : s->layers) {
+    c->ws_off = mark;
+    Scratch S;
+    scratch_carve(c, ly->dev.desc, T, S);
+    { PROF(c, PH_NORM); launch_rmsnorm(c->launch(), xc, T, d, s->eps, xn); }
+    TRY(dev_forward(ly, xn, T, xc, true, S));
+  }
+  if (xc != x_out) {
+    CU(cudaMemcpyAsync(x_out, xc, n * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+  }
+  return PM_OK;
+}

@@ -1,0 +1,832 @@
+// kernels_basic.cu - the general (any token count) kernels of the MoE path:
+// block-format re-layout and decode, activation quantiser, router, top-k,
+// dispatch plan, grouped gate/up + activation, grouped down, combine.
+//
+// Integer work (block decode, quantised dots, routing, plan) is bit-exact
+// against the reference CPU code; float tails follow `row_scalar`'s order
+// (src/ds4_cpu.rs:59-83). Citations are paths inside the Pelica source tree.
+#include "moe_internal.cuh"
+
+#define KLAUNCH(L, kern, grid, block, smem, ...)            \
+  do {                                                      \
+    kern<<<grid, block, smem, (L).stream>>>(__VA_ARGS__);   \
+    if ((L).count) ++*(L).count;                            \
+  } while (0)
+
+// ===========================================================================
+// block formats: GGUF bytes <-> device planes
+// ===========================================================================
+
+__global__ void k_repack_q6k(const uint8_t *__restrict__ raw, size_t nb, uint8_t *ql, uint8_t *qh,
+                             uint8_t *sc, uint8_t *d) {
+  // one thread per 2 bytes of a 210-byte block: 105 threads per block
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t b = i / 105;
+  int j = (int)(i % 105) * 2;
+  if (b >= nb) return;
+  uint16_t v = *(const uint16_t *)(raw + b * 210 + j);
+  uint8_t *dst;
+  if (j < 128) dst = ql + b * 128 + j;
+  else if (j < 192) dst = qh + b * 64 + (j - 128);
+  else if (j < 208) dst = sc + b * 16 + (j - 192);
+  else dst = d + b * 2;
+  *(uint16_t *)dst = v;
+}
+__global__ void k_unpack_q6k(uint8_t *raw, size_t nb, const uint8_t *ql, const uint8_t *qh,
+                             const uint8_t *sc, const uint8_t *d) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t b = i / 105;
+  int j = (int)(i % 105) * 2;
+  if (b >= nb) return;
+  const uint8_t *src;
+  if (j < 128) src = ql + b * 128 + j;
+  else if (j < 192) src = qh + b * 64 + (j - 128);
+  else if (j < 208) src = sc + b * 16 + (j - 192);
+  else src = d + b * 2;
+  *(uint16_t *)(raw + b * 210 + j) = *(const uint16_t *)src;
+}
+// byte-granular split: `head` bytes to plane h, the rest to plane r (or swapped)
+__global__ void k_repack_split(const uint8_t *__restrict__ raw, size_t nb, int bb, int head,
+                               uint8_t *ph, uint8_t *pr, int back) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t b = i / bb;
+  int j = (int)(i % bb);
+  if (b >= nb) return;
+  uint8_t *rawm = const_cast<uint8_t *>(raw);
+  uint8_t *p = j < head ? ph + b * head + j : pr + b * (bb - head) + (j - head);
+  if (back) rawm[b * bb + j] = *p;
+  else *p = raw[b * bb + j];
+}
+
+void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t nb, uint8_t *p0,
+                   uint8_t *p1, uint8_t *p2, uint8_t *p3) {
+  if (nb == 0) return;
+  switch (type) {
+    case PM_TYPE_Q4_K:
+      cudaMemcpyAsync(p0, raw, nb * 144, cudaMemcpyDeviceToDevice, L.stream);
+      break;
+    case PM_TYPE_Q6_K: {
+      size_t n = nb * 105;
+      KLAUNCH(L, k_repack_q6k, (unsigned)((n + 255) / 256), 256, 0, raw, nb, p0, p1, p2, p3);
+      break;
+    }
+    case PM_TYPE_MXFP4: {  // scale byte first in the raw block, nibbles after
+      size_t n = nb * 17;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 17, 1, p1, p0, 0);
+      break;
+    }
+    case PM_TYPE_Q8_0: {
+      size_t n = nb * 34;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 34, 2, p1, p0, 0);
+      break;
+    }
+  }
+}
+void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uint8_t *p0,
+                   const uint8_t *p1, const uint8_t *p2, const uint8_t *p3) {
+  if (nb == 0) return;
+  switch (type) {
+    case PM_TYPE_Q4_K:
+      cudaMemcpyAsync(raw, p0, nb * 144, cudaMemcpyDeviceToDevice, L.stream);
+      break;
+    case PM_TYPE_Q6_K: {
+      size_t n = nb * 105;
+      KLAUNCH(L, k_unpack_q6k, (unsigned)((n + 255) / 256), 256, 0, raw, nb, p0, p1, p2, p3);
+      break;
+    }
+    case PM_TYPE_MXFP4: {
+      size_t n = nb * 17;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 17, 1,
+              const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
+      break;
+    }
+    case PM_TYPE_Q8_0: {
+      size_t n = nb * 34;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 34, 2,
+              const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
+      break;
+    }
+  }
+}
+
+// value v of block b, from the device planes (`deq4`, src/moe_kernels.rs:63-84)
+template <int TYPE>
+__device__ __forceinline__ float deq_value(const uint8_t *p0, const uint8_t *p1, const uint8_t *p2,
+                                           const uint8_t *p3, size_t b, int v) {
+  if (TYPE == PM_TYPE_Q4_K) {  // (d*sc)*q - dmin*m (src/moe_kernels.rs:73)
+    const uint8_t *blk = p0 + b * 144;
+    const uint32_t *hw = (const uint32_t *)blk;
+    uint32_t h0 = hw[0];
+    int sc, m;
+    pm_q4k_scmin(hw[1], hw[2], hw[3], v / 32, sc, m);
+    int c = v / 64, i = v % 32;
+    uint8_t byte = blk[16 + 32 * c + i];
+    int q = (v % 64) >= 32 ? (byte >> 4) : (byte & 15);
+    float d = pm_f16(h0), dmin = pm_f16(h0 >> 16);
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
+  } else if (TYPE == PM_TYPE_Q6_K) {  // (d*sc)*(q-32) (src/moe_kernels.rs:75)
+    int n = v / 128, r = v % 128, qt = r / 32, l = r % 32;
+    uint8_t qlb = p0[b * 128 + 64 * n + l + 32 * (qt & 1)];
+    int lo = qt >= 2 ? (qlb >> 4) : (qlb & 15);
+    int hb = (p1[b * 64 + 32 * n + l] >> (2 * qt)) & 3;
+    int k = 8 * n + l / 16 + 2 * qt;
+    float sc = (float)(int8_t)p2[b * 16 + k];
+    float d = pm_f16(*(const uint16_t *)(p3 + b * 2));
+    return __fmul_rn(__fmul_rn(d, sc), __fsub_rn((float)(lo | (hb << 4)), 32.0f));
+  } else if (TYPE == PM_TYPE_MXFP4) {  // e8(e)*KV_MX[q] (src/moe_kernels.rs:80)
+    uint8_t byte = p0[b * 16 + (v & 15)];
+    uint32_t c = v >= 16 ? (byte >> 4) : (byte & 15);
+    return __fmul_rn(pm_e8(p1[b]), pm_e2m1(c));
+  } else {  // Q8_0: d*q (src/moe_kernels.rs:68)
+    float d = pm_f16(*(const uint16_t *)(p1 + b * 2));
+    return __fmul_rn(d, (float)(int8_t)p0[b * 32 + v]);
+  }
+}
+
+template <int TYPE, int BV>
+__global__ void k_dequant(size_t n, const uint8_t *p0, const uint8_t *p1, const uint8_t *p2,
+                          const uint8_t *p3, float *out) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[i] = deq_value<TYPE>(p0, p1, p2, p3, i / BV, (int)(i % BV));
+}
+
+void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, const uint8_t *p1,
+                    const uint8_t *p2, const uint8_t *p3, float *out) {
+  if (n == 0) return;
+  unsigned g = (unsigned)((n + 255) / 256);
+  switch (type) {
+    case PM_TYPE_Q4_K: KLAUNCH(L, (k_dequant<PM_TYPE_Q4_K, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_Q6_K: KLAUNCH(L, (k_dequant<PM_TYPE_Q6_K, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_MXFP4: KLAUNCH(L, (k_dequant<PM_TYPE_MXFP4, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_Q8_0: KLAUNCH(L, (k_dequant<PM_TYPE_Q8_0, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+  }
+}
+
+// ===========================================================================
+// activation quantiser: `Q8x::new` (src/ds4_cpu.rs:13-35)
+// ===========================================================================
+// one 256-thread CTA per 256-value block; warp w owns bsum[w]
+__global__ void __launch_bounds__(256) k_quant_q8x(const float *__restrict__ x, size_t n_blocks,
+                                                  int8_t *q, float *d, int32_t *bsum) {
+  __shared__ float wmax[8];
+  size_t b = blockIdx.x;
+  if (b >= n_blocks) return;
+  int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float v = x[b * 256 + tid];
+  float a = pm_warp_max(fabsf(v));
+  if (lane == 0) wmax[warp] = a;
+  __syncthreads();
+  float amax = wmax[0];
+#pragma unroll
+  for (int i = 1; i < 8; i++) amax = fmaxf(amax, wmax[i]);
+  int r = 0;
+  if (amax != 0.0f) {
+    float id = __fdiv_rn(127.0f, amax);
+    float f = roundf(__fmul_rn(v, id));  // half away from zero, as f32::round
+    f = fminf(fmaxf(f, -127.0f), 127.0f);
+    r = (int)f;
+  }
+  q[b * 256 + tid] = (int8_t)r;
+  int s = pm_warp_sum_i32(r);
+  if (lane == 0) bsum[b * 8 + warp] = s;
+  if (tid == 0) d[b] = amax != 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+}
+
+void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d,
+                      int32_t *bsum) {
+  size_t nb = rows * (size_t)(n / 256);
+  if (nb == 0) return;
+  KLAUNCH(L, k_quant_q8x, (unsigned)nb, 256, 0, x, nb, q, d, bsum);
+}
+
+// ===========================================================================
+// router logits: `dot_f32` order (src/quant.rs:215-236; src/ds4.rs:1376-1383)
+// ===========================================================================
+// CTA = 8 warps; blockIdx.y = token, each warp one expert; x[t] staged in
+// shared memory. lane L runs the fma chain over columns L, L+32, ...
+__global__ void __launch_bounds__(256) k_router(const float *__restrict__ wr,
+                                                const float *__restrict__ bias,
+                                                const float *__restrict__ x, int E, int d,
+                                                float *logits) {
+  extern __shared__ float xs[];
+  int t = blockIdx.y;
+  for (int i = threadIdx.x; i < d; i += 256) xs[i] = x[(size_t)t * d + i];
+  __syncthreads();
+  int lane = threadIdx.x & 31;
+  int e = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (e >= E) return;
+  const float *w = wr + (size_t)e * d;
+  float acc = 0.0f;
+  for (int c = lane; c < d; c += 32) acc = __fmaf_rn(w[c], xs[c], acc);
+  float s = pm_warp_sum_dot(acc);
+  if (lane == 0) {
+    if (bias) s = __fadd_rn(s, bias[e]);
+    logits[(size_t)t * E + e] = s;
+  }
+}
+
+void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits) {
+  if (T == 0) return;
+  int E = ly.desc.n_exp, d = ly.desc.d;
+  dim3 grid((E + 7) / 8, T);
+  KLAUNCH(L, k_router, grid, 256, (size_t)d * 4, ly.router, ly.logit_bias, x, E, d, logits);
+}
+
+__global__ void __launch_bounds__(256) k_gate_logit(const float *__restrict__ wv,
+                                                    const float *__restrict__ x, int T, int d,
+                                                    float *out) {
+  int lane = threadIdx.x & 31;
+  int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  float acc = 0.0f;
+  for (int c = lane; c < d; c += 32) acc = __fmaf_rn(wv[c], x[(size_t)t * d + c], acc);
+  float s = pm_warp_sum_dot(acc);
+  if (lane == 0) out[t] = s;
+}
+void launch_shared_gate_logit(const Launch &L, const LayerDev &ly, const float *x, int T,
+                              float *out) {
+  if (T == 0) return;
+  KLAUNCH(L, k_gate_logit, (T + 7) / 8, 256, 0, ly.shared_gate_inp, x, T, ly.desc.d, out);
+}
+
+// ===========================================================================
+// top-k and weights (src/moe_kernels.rs:1019-1081, src/oss_kernels.rs:15-35,
+// src/ds4.rs:1371-1426, src/q4x.rs:2213-2231)
+// ===========================================================================
+#define NPER (PM_MAX_EXPERTS / 32)
+
+// one warp per token; lane L holds experts L, L+32, ...
+__global__ void __launch_bounds__(128) k_route(pm_layer_desc D, const float *__restrict__ logits,
+                                               const float *__restrict__ sel_bias, int T,
+                                               uint32_t *ids, float *wout) {
+  __shared__ float sm_sv[4][PM_MAX_EXPERTS];
+  __shared__ float sm_gs[4][PM_MAX_EXPERTS / 2];
+  __shared__ unsigned char sm_keep[4][PM_MAX_EXPERTS / 2];
+  int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+  int t = blockIdx.x * 4 + wi;
+  if (t >= T) return;
+  const int E = D.n_exp, K = D.top_k;
+  const float *lg = logits + (size_t)t * E;
+  float pr[NPER], sv[NPER];
+  float mx = PM_NEG;
+#pragma unroll
+  for (int i = 0; i < NPER; i++) {
+    int e = lane + 32 * i;
+    float v = e < E ? lg[e] : PM_NEG;
+    pr[i] = v;
+    mx = fmaxf(mx, v);
+  }
+  if (D.gating == PM_GATE_SOFTMAX_ALL) {
+    mx = pm_warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPER; i++) {
+      int e = lane + 32 * i;
+      if (e < E) {
+        pr[i] = pm_exp(__fsub_rn(pr[i], mx));
+        sum = __fadd_rn(sum, pr[i]);
+      }
+    }
+    sum = pm_warp_sum_16_1(sum);
+#pragma unroll
+    for (int i = 0; i < NPER; i++) pr[i] = __fdiv_rn(pr[i], sum);
+  } else if (D.gating == PM_GATE_SIGMOID) {
+#pragma unroll
+    for (int i = 0; i < NPER; i++)
+      if (lane + 32 * i < E) pr[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, pm_exp(-pr[i])));
+  } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {
+#pragma unroll
+    for (int i = 0; i < NPER; i++)
+      if (lane + 32 * i < E) {
+        float v = pr[i];
+        float sp = v > 20.0f ? v : pm_log1p(pm_exp(v));
+        pr[i] = __fsqrt_rn(sp);
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < NPER; i++) {
+    int e = lane + 32 * i;
+    sv[i] = e < E ? (sel_bias ? __fadd_rn(pr[i], sel_bias[e]) : pr[i]) : PM_NEG;
+  }
+  // group-limited selection (this repository's definition: group score = sum of
+  // the group's two largest biased scores; best topk_group groups stay, ties ->
+  // lower group index)
+  if (D.n_group > 0) {
+    float *ssv = sm_sv[wi];
+    float *gsc = sm_gs[wi];
+    unsigned char *keep = sm_keep[wi];
+#pragma unroll
+    for (int i = 0; i < NPER; i++)
+      if (lane + 32 * i < E) ssv[lane + 32 * i] = sv[i];
+    __syncwarp();
+    const int G = D.n_group, gs = E / G;
+    for (int g = lane; g < G; g += 32) {  // lane g scores groups g, g+32, ...
+      int i1 = 0;
+      float v1 = ssv[g * gs];
+      for (int i = 1; i < gs; i++)
+        if (ssv[g * gs + i] > v1) { v1 = ssv[g * gs + i]; i1 = i; }
+      float v2 = PM_NEG;
+      for (int i = 0; i < gs; i++)
+        if (i != i1 && ssv[g * gs + i] > v2) v2 = ssv[g * gs + i];
+      gsc[g] = __fadd_rn(v1, v2);
+      keep[g] = 0;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      for (int r = 0; r < D.topk_group; r++) {
+        int bg = -1;
+        float bv = 0.0f;
+        for (int g = 0; g < G; g++) {
+          if (keep[g]) continue;
+          float v = gsc[g];
+          if (bg < 0 || v > bv) { bv = v; bg = g; }
+        }
+        keep[bg] = 1;
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < NPER; i++) {
+      int e = lane + 32 * i;
+      if (e < E && !keep[e / gs]) sv[i] = PM_NEG;
+    }
+  }
+  // K rounds of (max, lowest index)
+  float tw[PM_MAX_TOPK];
+  uint32_t te[PM_MAX_TOPK];
+  float wsum = 0.0f;
+#pragma unroll 1
+  for (int k = 0; k < K; k++) {
+    float bv = PM_NEG;
+    uint32_t bi = 0xffffffffu;
+#pragma unroll
+    for (int i = 0; i < NPER; i++) {
+      int e = lane + 32 * i;
+      if (e < E && (bi == 0xffffffffu || sv[i] > bv)) { bv = sv[i]; bi = (uint32_t)e; }
+    }
+    float m = pm_warp_max(bi == 0xffffffffu ? PM_NEG : bv);
+    uint32_t e = pm_warp_min_u32((bi != 0xffffffffu && bv == m) ? bi : 0xffffffffu);
+    float mine = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPER; i++)
+      if ((uint32_t)(lane + 32 * i) == e) { mine = pr[i]; sv[i] = PM_NEG; }
+    // only the owning lane has a non-zero `mine`; a shuffle fetches it exactly
+    float w = __shfl_sync(PM_FULL, mine, e & 31);
+    te[k] = e;
+    tw[k] = w;
+    wsum = __fadd_rn(wsum, w);
+  }
+  if (lane == 0) {
+    if (D.gating == PM_GATE_SOFTMAX_SELECTED) {  // src/oss_kernels.rs:31-32
+      float ev[PM_MAX_TOPK];
+      float sum = 0.0f;
+      for (int k = 0; k < K; k++) {
+        ev[k] = pm_exp(__fsub_rn(tw[k], tw[0]));
+        sum = __fadd_rn(sum, ev[k]);
+      }
+      for (int k = 0; k < K; k++) {
+        float x = __fdiv_rn(ev[k], sum);
+        if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
+        tw[k] = x;
+      }
+    } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {  // src/ds4.rs:1416-1424
+      for (int k = 0; k < K; k++) {
+        float x = __fdiv_rn(tw[k], wsum);
+        if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
+        tw[k] = x;
+      }
+    } else {  // src/moe_kernels.rs:1072-1074
+      for (int k = 0; k < K; k++) {
+        float x = tw[k];
+        if (D.norm_w) x = __fdiv_rn(x, fmaxf(wsum, 6.103515625e-5f));
+        if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
+        tw[k] = x;
+      }
+    }
+    for (int k = 0; k < K; k++) {
+      ids[(size_t)t * K + k] = te[k];
+      wout[(size_t)t * K + k] = tw[k];
+    }
+  }
+}
+
+void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int T, uint32_t *ids,
+                  float *w) {
+  if (T == 0) return;
+  KLAUNCH(L, k_route, (T + 3) / 4, 128, 0, ly.desc, logits, ly.select_bias, T, ids, w);
+}
+
+// ===========================================================================
+// dispatch plan (src/moe_kernels.rs:1083-1129 layout; ascending (token, k)
+// within an expert as src/ds4.rs:1461-1472)
+// ===========================================================================
+__global__ void k_plan_zero(uint32_t *cnt, int E) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < E) cnt[i] = 0;
+}
+__global__ void k_plan_count(const uint32_t *__restrict__ ids, int P, uint32_t *cnt) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < P) atomicAdd(&cnt[ids[i]], 1u);
+}
+// single CTA of 512 threads: exclusive scans over the experts
+__global__ void __launch_bounds__(512) k_plan_scan(PlanDev pl, int E, uint32_t *usage) {
+  __shared__ uint32_t s_c[PM_MAX_EXPERTS], s_a[PM_MAX_EXPERTS];
+  int e = threadIdx.x;
+  uint32_t c = e < E ? pl.cnt[e] : 0;
+  s_c[e] = c;
+  s_a[e] = c > 0;
+  __syncthreads();
+  // Hillis-Steele inclusive scans (512 wide)
+  for (int off = 1; off < PM_MAX_EXPERTS; off <<= 1) {
+    uint32_t vc = e >= off ? s_c[e - off] : 0, va = e >= off ? s_a[e - off] : 0;
+    __syncthreads();
+    s_c[e] += vc;
+    s_a[e] += va;
+    __syncthreads();
+  }
+  uint32_t o = s_c[e] - c, na = s_a[e] - (c > 0);
+  if (e < E) {
+    pl.base[e] = o;
+    if (c > 0) {
+      pl.active[na] = (uint32_t)e;
+      pl.offset[na] = o;
+      pl.count[na] = c;
+      if (usage) usage[e] += c;
+    }
+  }
+  __syncthreads();
+  uint32_t total_a = s_a[PM_MAX_EXPERTS - 1];
+  if (e < E && (uint32_t)e >= total_a) {
+    pl.active[e] = 0;
+    pl.offset[e] = 0;
+    pl.count[e] = 0;
+  }
+  if (e == 0) *pl.n_active = (int)total_a;
+}
+// one CTA per expert walks all pairs in order: stable placement
+__global__ void __launch_bounds__(256) k_plan_place(const uint32_t *__restrict__ ids, int P, int K,
+                                                    PlanDev pl) {
+  __shared__ uint32_t wsum[8];
+  uint32_t e = blockIdx.x;
+  uint32_t total = pl.cnt[e];
+  if (total == 0) return;
+  uint32_t base = pl.base[e];
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t run = 0;
+  for (int i0 = 0; i0 < P && run < total; i0 += 256) {
+    int i = i0 + threadIdx.x;
+    bool hit = i < P && ids[i] == e;
+    uint32_t bal = __ballot_sync(PM_FULL, hit);
+    if (lane == 0) wsum[warp] = __popc(bal);
+    __syncthreads();
+    uint32_t before = 0, all = 0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      uint32_t v = wsum[w];
+      if (w < warp) before += v;
+      all += v;
+    }
+    if (hit) {
+      uint32_t p = base + run + before + __popc(bal & ((1u << lane) - 1));
+      pl.pair_pos[i] = p;
+      pl.pair_token[p] = (uint32_t)(i / K);
+      pl.pair_src[p] = (uint32_t)i;
+    }
+    run += all;
+    __syncthreads();
+  }
+}
+
+void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev pl) {
+  int E = ly.desc.n_exp, K = ly.desc.top_k, P = T * K;
+  KLAUNCH(L, k_plan_zero, (E + 255) / 256, 256, 0, pl.cnt, E);
+  if (P > 0) KLAUNCH(L, k_plan_count, (P + 255) / 256, 256, 0, ids, P, pl.cnt);
+  KLAUNCH(L, k_plan_scan, 1, 512, 0, pl, E, ly.usage);
+  if (P > 0) KLAUNCH(L, k_plan_place, E, 256, 0, ids, P, K, pl);
+}
+
+__global__ void k_iota(uint32_t *p, uint32_t n) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = i;
+}
+void launch_iota(const Launch &L, uint32_t *p, uint32_t n) {
+  if (n) KLAUNCH(L, k_iota, (n + 255) / 256, 256, 0, p, n);
+}
+
+// ===========================================================================
+// rows
+// ===========================================================================
+
+// Q4_K row . Q8x activations, one warp; every lane returns the row's sum.
+// Integer sums per block as `row_scalar` (src/ds4_cpu.rs:59-83), the float
+// term of block b = x.d[b]*(d*isum - dmin*msum), added in block order.
+__device__ __forceinline__ float row_q4k_q8x(const uint8_t *__restrict__ rowp, int nb,
+                                             const int8_t *__restrict__ xq,
+                                             const float *__restrict__ xd,
+                                             const int32_t *__restrict__ xbsum, int lane) {
+  float total = 0.0f;
+  const int nchunks = nb * 4;  // 32-byte chunks of quants: block b = ci/4, c = ci%4
+  for (int c0 = 0; c0 < nchunks; c0 += 32) {
+    int ci = c0 + lane;
+    bool valid = ci < nchunks;
+    int b = ci >> 2, c = ci & 3;
+    int pi = 0, pm = 0;
+    float dd = 0.0f, dmin = 0.0f;
+    if (valid) {
+      const uint8_t *blk = rowp + (size_t)b * 144;
+      uint4 hdr = __ldg((const uint4 *)blk);
+      const uint4 *qp = (const uint4 *)(blk + 16 + 32 * c);
+      uint4 q0 = __ldg(qp), q1 = __ldg(qp + 1);
+      const int4 *xp = (const int4 *)(xq + (size_t)b * 256 + 64 * c);
+      int4 xl0 = xp[0], xl1 = xp[1], xh0 = xp[2], xh1 = xp[3];
+      int lo = 0, hi = 0;
+      const uint32_t M = 0x0f0f0f0fu;
+      lo = __dp4a((int)(q0.x & M), xl0.x, lo); hi = __dp4a((int)((q0.x >> 4) & M), xh0.x, hi);
+      lo = __dp4a((int)(q0.y & M), xl0.y, lo); hi = __dp4a((int)((q0.y >> 4) & M), xh0.y, hi);
+      lo = __dp4a((int)(q0.z & M), xl0.z, lo); hi = __dp4a((int)((q0.z >> 4) & M), xh0.z, hi);
+      lo = __dp4a((int)(q0.w & M), xl0.w, lo); hi = __dp4a((int)((q0.w >> 4) & M), xh0.w, hi);
+      lo = __dp4a((int)(q1.x & M), xl1.x, lo); hi = __dp4a((int)((q1.x >> 4) & M), xh1.x, hi);
+      lo = __dp4a((int)(q1.y & M), xl1.y, lo); hi = __dp4a((int)((q1.y >> 4) & M), xh1.y, hi);
+      lo = __dp4a((int)(q1.z & M), xl1.z, lo); hi = __dp4a((int)((q1.z >> 4) & M), xh1.z, hi);
+      lo = __dp4a((int)(q1.w & M), xl1.w, lo); hi = __dp4a((int)((q1.w >> 4) & M), xh1.w, hi);
+      int sc0, m0, sc1, m1;
+      pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c, sc0, m0);
+      pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c + 1, sc1, m1);
+      pi = sc0 * lo + sc1 * hi;
+      pm = m0 * xbsum[b * 8 + 2 * c] + m1 * xbsum[b * 8 + 2 * c + 1];
+      dd = pm_f16(hdr.x);
+      dmin = pm_f16(hdr.x >> 16);
+    }
+    pi += __shfl_xor_sync(PM_FULL, pi, 1);
+    pm += __shfl_xor_sync(PM_FULL, pm, 1);
+    pi += __shfl_xor_sync(PM_FULL, pi, 2);
+    pm += __shfl_xor_sync(PM_FULL, pm, 2);
+    float term = 0.0f;
+    if (valid)
+      term = __fmul_rn(xd[b], __fsub_rn(__fmul_rn(dd, (float)pi), __fmul_rn(dmin, (float)pm)));
+    int nblk = min(8, nb - (c0 >> 2));
+    for (int j = 0; j < nblk; j++) total = __fadd_rn(total, __shfl_sync(PM_FULL, term, 4 * j));
+  }
+  return total;
+}
+
+// Q6_K row . Q8x activations (planes of this row given). Per block
+// isum = sum_k sc[k] * sum_16 (q-32)*xq, term = x.d[b]*(d*isum), block order.
+__device__ __forceinline__ float row_q6k_q8x(const uint8_t *__restrict__ ql,
+                                             const uint8_t *__restrict__ qh,
+                                             const uint8_t *__restrict__ sc,
+                                             const uint8_t *__restrict__ dp, int nb,
+                                             const int8_t *__restrict__ xq,
+                                             const float *__restrict__ xd, int lane) {
+  float total = 0.0f;
+  const int n = lane >> 4, qtb = (lane >> 3) & 1, l4 = lane & 7;
+  const int vA = 128 * n + 32 * qtb + 4 * l4;  // first value of the low-nibble quad
+  for (int b = 0; b < nb; b++) {
+    uint32_t qlw = __ldg((const uint32_t *)(ql + (size_t)b * 128) + lane);
+    uint32_t qhw = __ldg((const uint32_t *)(qh + (size_t)b * 64) + n * 8 + l4);
+    uint32_t qa = (qlw & 0x0f0f0f0fu) | (((qhw >> (2 * qtb)) & 0x03030303u) << 4);
+    uint32_t qb = ((qlw >> 4) & 0x0f0f0f0fu) | (((qhw >> (2 * qtb + 4)) & 0x03030303u) << 4);
+    qa = __vsub4(qa, 0x20202020u);
+    qb = __vsub4(qb, 0x20202020u);
+    const int *xp = (const int *)(xq + (size_t)b * 256);
+    int xa = xp[vA >> 2], xb = xp[(vA + 64) >> 2];
+    const int8_t *scb = (const int8_t *)(sc + (size_t)b * 16);
+    int kA = vA >> 4;
+    int isum = (int)scb[kA] * __dp4a((int)qa, xa, 0) + (int)scb[kA + 4] * __dp4a((int)qb, xb, 0);
+    isum = pm_warp_sum_i32(isum);
+    float d = pm_f16(__ldg((const uint16_t *)(dp + (size_t)b * 2)));
+    total = __fadd_rn(total, __fmul_rn(xd[b], __fmul_rn(d, (float)isum)));
+  }
+  return total;
+}
+
+// row r of expert slot `el` of W against Q8x activations
+__device__ __forceinline__ float row_q8x(const WMat &W, int el, int r, const int8_t *xq,
+                                         const float *xd, const int32_t *xbsum, int lane) {
+  int nb = W.cols / 256;
+  if (W.type == PM_TYPE_Q4_K) {
+    const uint8_t *rowp = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * 144;
+    return row_q4k_q8x(rowp, nb, xq, xd, xbsum, lane);
+  }
+  size_t rb = (size_t)r * nb;
+  return row_q6k_q8x(W.plane[0] + (size_t)el * W.stride[0] + rb * 128,
+                     W.plane[1] + (size_t)el * W.stride[1] + rb * 64,
+                     W.plane[2] + (size_t)el * W.stride[2] + rb * 16,
+                     W.plane[3] + (size_t)el * W.stride[3] + rb * 2, nb, xq, xd, lane);
+}
+
+// any type against f32 activations; lanes take quads of a 32-value block each
+// (MXFP4: src/oss_batch.rs:774-789), f32 accumulation
+__device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const float *__restrict__ x,
+                                         int lane) {
+  float acc = 0.0f;
+  if (W.type == PM_TYPE_MXFP4) {
+    int nb = W.cols / 32;
+    const uint8_t *nib = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * 16;
+    const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * nb;
+    int w = lane & 3;
+    for (int b = lane >> 2; b < nb; b += 8) {
+      uint32_t qw = __ldg((const uint32_t *)(nib + (size_t)b * 16) + w);
+      float s = pm_e8(__ldg(scl + b));
+      const float4 x0 = *(const float4 *)(x + b * 32 + 4 * w);
+      const float4 x1 = *(const float4 *)(x + b * 32 + 16 + 4 * w);
+      float t = 0.0f;
+      t = __fmaf_rn(pm_e2m1(qw & 15), x0.x, t);
+      t = __fmaf_rn(pm_e2m1((qw >> 8) & 15), x0.y, t);
+      t = __fmaf_rn(pm_e2m1((qw >> 16) & 15), x0.z, t);
+      t = __fmaf_rn(pm_e2m1((qw >> 24) & 15), x0.w, t);
+      t = __fmaf_rn(pm_e2m1((qw >> 4) & 15), x1.x, t);
+      t = __fmaf_rn(pm_e2m1((qw >> 12) & 15), x1.y, t);
+      t = __fmaf_rn(pm_e2m1((qw >> 20) & 15), x1.z, t);
+      t = __fmaf_rn(pm_e2m1(qw >> 28), x1.w, t);
+      acc = __fmaf_rn(s, t, acc);
+    }
+  } else {
+    const uint8_t *p0 = W.plane[0] + (size_t)el * W.stride[0];
+    const uint8_t *p1 = W.plane[1] ? W.plane[1] + (size_t)el * W.stride[1] : nullptr;
+    const uint8_t *p2 = W.plane[2] ? W.plane[2] + (size_t)el * W.stride[2] : nullptr;
+    const uint8_t *p3 = W.plane[3] ? W.plane[3] + (size_t)el * W.stride[3] : nullptr;
+    int bv = W.type == PM_TYPE_Q8_0 ? 32 : 256;
+    size_t b0 = (size_t)r * (W.cols / bv);
+    for (int v = lane; v < W.cols; v += 32) {
+      float wv;
+      size_t b = b0 + v / bv;
+      int iv = v % bv;
+      if (W.type == PM_TYPE_Q4_K) wv = deq_value<PM_TYPE_Q4_K>(p0, p1, p2, p3, b, iv);
+      else if (W.type == PM_TYPE_Q6_K) wv = deq_value<PM_TYPE_Q6_K>(p0, p1, p2, p3, b, iv);
+      else wv = deq_value<PM_TYPE_Q8_0>(p0, p1, p2, p3, b, iv);
+      acc = __fmaf_rn(wv, x[v], acc);
+    }
+  }
+  return pm_warp_sum_16_1(acc);
+}
+
+// ===========================================================================
+// grouped gate/up + activation, grouped down
+// ===========================================================================
+// grid (rows/8, groups); one warp per output row, looping over the group's pairs
+__global__ void __launch_bounds__(256) k_gateup(LayerDev ly, int shared, Groups g,
+                                                const float *__restrict__ x,
+                                                const int8_t *__restrict__ xq,
+                                                const float *__restrict__ xd,
+                                                const int32_t *__restrict__ xbsum,
+                                                const float *__restrict__ wts, float *h) {
+  int a = blockIdx.y;
+  if (a >= *g.n_groups) return;
+  const WMat &G = shared ? ly.sgate : ly.gate;
+  const WMat &U = shared ? ly.sup : ly.up;
+  const int ff = G.rows, d = G.cols;
+  int lane = threadIdx.x & 31;
+  int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= ff) return;
+  int e = (int)g.expert[a];
+  int el = shared ? 0 : e - ly.first_local;
+  if (el < 0 || el >= (shared ? 1 : ly.n_local)) return;  // not held here
+  uint32_t off = g.offset[a], cnt = g.count[a];
+  const pm_layer_desc &D = ly.desc;
+  const bool fold = !shared && D.weight_fold == PM_FOLD_BEFORE_DOWN;
+  float bg = 0.0f, bu = 0.0f;
+  const bool bias = !shared && ly.bias_gate;
+  if (bias) {
+    bg = ly.bias_gate[(size_t)el * ff + r];
+    bu = ly.bias_up[(size_t)el * ff + r];
+  }
+  const int nbx = d / 256;
+  for (uint32_t i = 0; i < cnt; i++) {
+    uint32_t p = off + i;
+    uint32_t t = g.pair_token[p];
+    float gv, uv;
+    if (D.act_quant == PM_AQ_Q8X_256) {
+      const int8_t *q = xq + (size_t)t * d;
+      const float *qd = xd + (size_t)t * nbx;
+      const int32_t *qb = xbsum + (size_t)t * nbx * 8;
+      gv = row_q8x(G, el, r, q, qd, qb, lane);
+      uv = row_q8x(U, el, r, q, qd, qb, lane);
+    } else {
+      gv = row_f32(G, el, r, x + (size_t)t * d, lane);
+      uv = row_f32(U, el, r, x + (size_t)t * d, lane);
+    }
+    if (lane == 0) {
+      if (bias) {
+        gv = __fadd_rn(gv, bg);
+        uv = __fadd_rn(uv, bu);
+      }
+      float w = (fold && wts) ? wts[g.pair_src[p]] : 1.0f;
+      h[(size_t)p * ff + r] = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, w, fold && wts);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) k_down(LayerDev ly, int shared, Groups g,
+                                              const float *__restrict__ h,
+                                              const int8_t *__restrict__ hq,
+                                              const float *__restrict__ hd,
+                                              const int32_t *__restrict__ hbsum, float *eo) {
+  int a = blockIdx.y;
+  if (a >= *g.n_groups) return;
+  const WMat &Dn = shared ? ly.sdown : ly.down;
+  const int d = Dn.rows, ff = Dn.cols;
+  int lane = threadIdx.x & 31;
+  int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= d) return;
+  int e = (int)g.expert[a];
+  int el = shared ? 0 : e - ly.first_local;
+  uint32_t off = g.offset[a], cnt = g.count[a];
+  if (el < 0 || el >= (shared ? 1 : ly.n_local)) {  // not held here: zeros
+    if (lane == 0)
+      for (uint32_t i = 0; i < cnt; i++) eo[(size_t)(off + i) * d + r] = 0.0f;
+    return;
+  }
+  const pm_layer_desc &D = ly.desc;
+  float bd = (!shared && ly.bias_down) ? ly.bias_down[(size_t)el * d + r] : 0.0f;
+  const int nbh = ff / 256;
+  for (uint32_t i = 0; i < cnt; i++) {
+    uint32_t p = off + i;
+    float o;
+    if (D.act_quant == PM_AQ_Q8X_256)
+      o = row_q8x(Dn, el, r, hq + (size_t)p * ff, hd + (size_t)p * nbh,
+                  hbsum + (size_t)p * nbh * 8, lane);
+    else
+      o = row_f32(Dn, el, r, h + (size_t)p * ff, lane);
+    if (lane == 0) {
+      if (!shared && ly.bias_down) o = __fadd_rn(o, bd);  // src/oss_batch.rs:89
+      eo[(size_t)p * d + r] = o;
+    }
+  }
+}
+
+void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
+                   const float *x, const int8_t *xq, const float *xd, const int32_t *xbsum,
+                   const float *w, float *h) {
+  if (n_pairs == 0) return;
+  int ff = shared ? ly.sgate.rows : ly.gate.rows;
+  dim3 grid((ff + 7) / 8, min(g.max_groups, n_pairs));
+  KLAUNCH(L, k_gateup, grid, 256, 0, ly, (int)shared, g, x, xq, xd, xbsum, w, h);
+}
+void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
+                 const float *h, const int8_t *hq, const float *hd, const int32_t *hbsum,
+                 float *eo) {
+  if (n_pairs == 0) return;
+  int d = ly.desc.d;
+  dim3 grid((d + 7) / 8, min(g.max_groups, n_pairs));
+  KLAUNCH(L, k_down, grid, 256, 0, ly, (int)shared, g, h, hq, hd, hbsum, eo);
+}
+
+// ===========================================================================
+// combine (src/moe_kernels.rs:1798-1808): fixed k order, then the shared expert
+// ===========================================================================
+__global__ void __launch_bounds__(256) k_combine(int d, int K, int in_combine,
+                                                 const float *__restrict__ eo,
+                                                 const uint32_t *__restrict__ pair_pos,
+                                                 const float *__restrict__ w,
+                                                 const float *__restrict__ shared_out,
+                                                 const float *__restrict__ shared_logit, float *y,
+                                                 int accumulate) {
+  int t = blockIdx.y;
+  int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.0f;
+  for (int k = 0; k < K; k++) {
+    float v = eo[(size_t)pair_pos[t * K + k] * d + c];
+    if (in_combine) v = __fmul_rn(w[t * K + k], v);
+    s = __fadd_rn(s, v);
+  }
+  if (shared_out) {
+    float sv = shared_out[(size_t)t * d + c];
+    if (shared_logit)
+      sv = __fmul_rn(sv, __fdiv_rn(1.0f, __fadd_rn(1.0f, pm_exp(-shared_logit[t]))));
+    s = __fadd_rn(s, sv);
+  }
+  size_t o = (size_t)t * d + c;
+  y[o] = accumulate ? __fadd_rn(y[o], s) : s;
+}
+
+void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
+                    const float *w, const float *shared_out, const float *shared_logit, int T,
+                    float *y, bool accumulate) {
+  if (T == 0) return;
+  int d = ly.desc.d;
+  dim3 grid((d + 255) / 256, T);
+  KLAUNCH(L, k_combine, grid, 256, 0, d, ly.desc.top_k,
+          (int)(ly.desc.weight_fold == PM_FOLD_IN_COMBINE), eo, pair_pos, w, shared_out,
+          shared_logit, y, (int)accumulate);
+}
+
+// x / rms(x), unit weight; sum of squares in `dot_f32` lane order
+__global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, int T, int d,
+                                                 float eps, float *out) {
+  int lane = threadIdx.x & 31;
+  int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float *xr = x + (size_t)t * d;
+  float acc = 0.0f;
+  for (int c = lane; c < d; c += 32) acc = __fmaf_rn(xr[c], xr[c], acc);
+  float ms = __fdiv_rn(pm_warp_sum_dot(acc), (float)d);
+  float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
+  for (int c = lane; c < d; c += 32) out[(size_t)t * d + c] = __fmul_rn(xr[c], inv);
+}
+void launch_rmsnorm(const Launch &L, const float *x, int T, int d, float eps, float *out) {
+  if (T == 0) return;
+  KLAUNCH(L, k_rmsnorm, (T + 7) / 8, 256, 0, x, T, d, eps, out);
+}

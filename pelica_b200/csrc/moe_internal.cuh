@@ -1,0 +1,106 @@
+// moe_internal.cuh - device-side descriptions shared by the kernels and the C ABI.
+#pragma once
+
+#include "common.cuh"
+
+// One expert tensor family ([n_local experts][rows][cols]) in its device layout.
+//  Q4_K : plane 0 = the GGUF blocks unchanged (144 B, 16-byte aligned rows)
+//  Q6_K : plane 0 = ql (128 B/block), 1 = qh (64 B), 2 = scales (16 B),
+//         3 = d (2 B): the block's four fields split into planes so every
+//         field is aligned; 210 B/block in total, as stored (no padding)
+//  MXFP4: plane 0 = E2M1 nibbles (16 B/block), 1 = E8M0 scale bytes (1 B/block)
+//         (the reference splits gpt-oss tensors the same way, src/oss.rs:241-253)
+//  Q8_0 : plane 0 = int8 values (32 B/block), 1 = f16 scales (2 B/block)
+struct WMat {
+  int type;
+  int rows, cols;
+  uint8_t *plane[4];
+  size_t stride[4];  // bytes per expert in each plane
+};
+
+struct LayerDev {
+  pm_layer_desc desc;
+  int n_local, first_local;
+  const float *router;       // [E][d]
+  const float *logit_bias;   // [E] or null
+  const float *select_bias;  // [E] or null
+  WMat gate, up, down;
+  const float *bias_gate, *bias_up, *bias_down;  // [n_local][ff|d] or null
+  WMat sgate, sup, sdown;                        // shared expert (1 "expert")
+  const float *shared_gate_inp;                  // [d] or null
+  uint32_t *usage;                               // [E]
+};
+
+// A grouping of pairs by expert (the dispatch plan, or the trivial one-group
+// plan of the shared expert).
+struct Groups {
+  const int *n_groups;         // [1]
+  const uint32_t *expert;      // [g] global expert id
+  const uint32_t *offset;      // [g]
+  const uint32_t *count;       // [g]
+  const uint32_t *pair_token;  // [P]
+  const uint32_t *pair_src;    // [P] index t*K+k of the pair (or null)
+  int max_groups;
+};
+
+struct PlanDev {
+  int *n_active;
+  uint32_t *active, *offset, *count;  // [E]
+  uint32_t *base;                     // [E] first pair of expert e
+  uint32_t *cnt;                      // [E] scratch counters
+  uint32_t *pair_token, *pair_pos, *pair_src;  // [P]
+};
+
+// bytes of one expert's tensor in plane p
+static inline size_t wmat_plane_bytes(int type, int rows, int cols, int p) {
+  size_t nb;
+  switch (type) {
+    case PM_TYPE_Q4_K:
+      nb = (size_t)rows * (cols / 256);
+      return p == 0 ? nb * 144 : 0;
+    case PM_TYPE_Q6_K: {
+      nb = (size_t)rows * (cols / 256);
+      const size_t f[4] = {128, 64, 16, 2};
+      return nb * f[p];
+    }
+    case PM_TYPE_MXFP4:
+      nb = (size_t)rows * (cols / 32);
+      return p == 0 ? nb * 16 : (p == 1 ? nb : 0);
+    case PM_TYPE_Q8_0:
+      nb = (size_t)rows * (cols / 32);
+      return p == 0 ? nb * 32 : (p == 1 ? nb * 2 : 0);
+  }
+  return 0;
+}
+
+// ---- launchers (kernels_basic.cu) -----------------------------------------
+struct Launch {
+  cudaStream_t stream;
+  int64_t *count;  // kernels launched
+};
+
+void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t n_blocks, uint8_t *p0,
+                   uint8_t *p1, uint8_t *p2, uint8_t *p3);
+void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t n_blocks, const uint8_t *p0,
+                   const uint8_t *p1, const uint8_t *p2, const uint8_t *p3);
+void launch_dequant(const Launch &L, int type, size_t n_values, const uint8_t *p0,
+                    const uint8_t *p1, const uint8_t *p2, const uint8_t *p3, float *out);
+void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d,
+                      int32_t *bsum);
+void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits);
+void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int T, uint32_t *ids,
+                  float *w);
+void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev plan);
+void launch_iota(const Launch &L, uint32_t *p, uint32_t n);
+void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
+                   const float *x, const int8_t *xq, const float *xd, const int32_t *xbsum,
+                   const float *w, float *h);
+void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
+                 const float *h, const int8_t *hq, const float *hd, const int32_t *hbsum,
+                 float *eo);
+void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
+                    const float *w, const float *shared_out, const float *shared_logit, int T,
+                    float *y, bool accumulate);
+void launch_rmsnorm(const Launch &L, const float *x, int T, int d, float eps, float *out);
+void launch_shared_gate_logit(const Launch &L, const LayerDev &ly, const float *x, int T,
+                              float *out);

@@ -1,0 +1,74 @@
+"""Bit-exact checks of block decoding and activation quantisation on the GPU
+(through the C ABI) against the oracle."""
+import numpy as np
+import pytest
+
+from pelica_b200 import synth
+from tests.helpers import bits_equal, lcg, ref_acts, ref_q4k_blocks
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.Q8_0])
+def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
+    """Every bit pattern path: random block bytes, only the f16 scales kept finite."""
+    v, b = synth.BLOCK[ty]
+    rng = np.random.default_rng(ty)
+    nb = 257
+    raw = rng.integers(0, 256, nb * b, dtype=np.uint8).reshape(nb, b)
+    half = rng.normal(0, 0.05, (nb, 2)).astype(np.float16).view(np.uint8).reshape(nb, 4)
+    if ty == synth.Q4_K:
+        raw[:, 0:4] = half
+    elif ty == synth.Q6_K:
+        raw[:, 208:210] = half[:, :2]
+    elif ty == synth.Q8_0:
+        raw[:, 0:2] = half[:, :2]
+    else:
+        raw[:3, 0] = [0, 1, 2]  # the denormal branch of e8 (src/oss_kernels.rs:42-45)
+        raw[3, 0] = 254
+    want = oracle.dequant(ty, raw.ravel(), nb * v)
+    got = ctx.dequant(ty, raw.ravel(), nb * v)
+    assert bits_equal(got, want)
+
+
+@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4])
+def test_dequant_encoded_weights(ctx, oracle, ty):
+    rng = np.random.default_rng(1)
+    x = rng.normal(0, 0.02, 4096).astype(np.float32)
+    raw = synth.ENCODERS[ty](x)
+    assert bits_equal(ctx.dequant(ty, raw, 4096), oracle.dequant(ty, raw, 4096))
+
+
+def test_dequant_empty_and_ragged(ctx):
+    import pelica_b200 as pb
+
+    assert ctx.dequant(synth.Q4_K, np.zeros(0, np.uint8), 0).size == 0
+    with pytest.raises(pb.PelicaError):
+        ctx.dequant(synth.Q4_K, np.zeros(144, np.uint8), 100)
+    with pytest.raises(pb.PelicaError):
+        ctx.dequant(5, np.zeros(144, np.uint8), 256)
+
+
+def test_quant_act_bit_exact(ctx, oracle):
+    rng = np.random.default_rng(2)
+    cases = [rng.normal(0, 1, 2048), rng.normal(0, 1e-3, 768), np.zeros(512), rng.normal(0, 50, 7168)]
+    x = rng.normal(0, 1, 1024)
+    x[256:512] = 0.0          # an all-zero block in the middle: d = 0, q = 0
+    x[5] = 3.0
+    x[6] = -1.5 * 3.0 / 127   # lands on a .5 boundary: rounds away from zero
+    cases.append(x)
+    cases.append(ref_acts(lcg(1), 1024))  # the reference's test activations (src/ds4_cpu.rs:463)
+    for x in cases:
+        x = x.astype(np.float32)
+        q, d, bs = ctx.quant_act(x)
+        oq, od, obs = oracle.q8x(x)
+        assert np.array_equal(q, oq)
+        assert bits_equal(d, od)
+        assert np.array_equal(bs, obs)
+
+
+def test_quant_act_rejects_ragged(ctx):
+    import pelica_b200 as pb
+
+    with pytest.raises(pb.PelicaError):
+        ctx.quant_act(np.zeros(300, np.float32))

@@ -1,0 +1,224 @@
+"""Pins of the CPU oracle: the reference's own relational tests re-run on the
+restatement, exact known answers for the scalar helpers and block decoders,
+and the committed golden fixtures."""
+import os
+
+import numpy as np
+import pytest
+
+from pelica_b200 import synth
+from tests.helpers import bits_equal, lcg, ref_acts, ref_q4k_blocks
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_f16_round_trip(oracle):
+    # src/q4x.rs:3411-3420
+    for v in [0.0, 1.0, -2.5, 65504.0, 1e-5, -3.14159, 1e-8, 0.333333]:
+        h = oracle.f32_to_f16(v)
+        back = oracle.f16_to_f32(h)
+        assert abs(back - np.float32(v)) <= abs(v) * 1e-3 + 6e-8
+    assert oracle.f32_to_f16(1.0 + 1.0 / 2048.0) == 0x3C00  # ties go to even
+    assert oracle.f32_to_f16(1.0 + 3.0 / 2048.0) == 0x3C02
+
+
+def test_f16_matches_ieee(oracle):
+    bits = np.arange(0, 65536, dtype=np.uint16)
+    want = bits.view(np.float16).astype(np.float32)
+    got = np.array([oracle.f16_to_f32(int(b)) for b in bits], np.float32)
+    ok = np.isnan(want) | (want.view(np.uint32) == got.view(np.uint32))
+    assert ok.all()
+    rng = np.random.default_rng(0)
+    xs = np.concatenate([rng.normal(0, 1, 2000), rng.normal(0, 1e-6, 500), rng.normal(0, 3e4, 500)]).astype(np.float32)
+    with np.errstate(over="ignore"):
+        want16 = xs.astype(np.float16).view(np.uint16)
+    got16 = np.array([oracle.f32_to_f16(float(x)) for x in xs], np.uint16)
+    assert np.array_equal(want16, got16)
+
+
+def test_vnni_matches_scalar(oracle):
+    # src/ds4_cpu.rs:446-474 (seed 1, 4 blocks)
+    rnd = lcg(1)
+    w = ref_q4k_blocks(rnd, 4)
+    x = ref_acts(rnd, 4 * 256)
+    q, d, bs = oracle.q8x(x)
+    a = oracle.row_q4k(w, 1024, q, d, bs, "scalar")
+    f = oracle.row_q4k(w, 1024, q, d, bs, "fast")
+    assert np.float32(a).tobytes() == np.float32(f).tobytes()
+    if oracle.lib().po_have_vnni():
+        b = oracle.row_q4k(w, 1024, q, d, bs, "vnni")
+        assert abs(a - b) <= 1e-3 * max(abs(a), 1.0)
+
+
+def test_multi_matches_single(oracle):
+    # src/ds4_cpu.rs:476-503 (seed 7; 4 blocks, 3 rows, 19 tokens): bit-equal
+    rnd = lcg(7)
+    blocks, rows, toks = 4, 3, 19
+    w = ref_q4k_blocks(rnd, rows * blocks)
+    qs = [oracle.q8x(ref_acts(rnd, blocks * 256)) for _ in range(toks)]
+    for canonical in (False, True):
+        multi = oracle.q4k_rows_multi(w, rows, blocks * 256, qs, canonical=canonical)
+        for t, (q, d, bs) in enumerate(qs):
+            for r in range(rows):
+                kind = "fast" if canonical else ("vnni" if oracle.lib().po_have_vnni() else "scalar")
+                one = oracle.row_q4k(w[r * blocks * 144:(r + 1) * blocks * 144], blocks * 256, q, d, bs, kind)
+                assert np.float32(one).tobytes() == np.float32(multi[r, t]).tobytes(), (r, t)
+
+
+def test_dot_bf16_matches_dot_f32_bitwise(oracle):
+    # src/quant.rs:535-552
+    rng = np.random.default_rng(3)
+    for n in (32, 64, 2048, 2880, 104):
+        a = rng.normal(0, 1, n).astype(np.float32)
+        a_bits = (a.view(np.uint32) >> 16).astype(np.uint16)
+        a_exact = (a_bits.astype(np.uint32) << 16).view(np.float32)
+        b = rng.normal(0, 1, n).astype(np.float32)
+        assert np.float32(oracle.dot_bf16(a_bits, b)).tobytes() == np.float32(oracle.dot_f32(a_exact, b)).tobytes()
+        assert abs(oracle.dot_f32(a_exact, b) - float(a_exact.astype(np.float64) @ b.astype(np.float64))) < 1e-3
+
+
+def test_rows_match_dequant(oracle):
+    # the shape of src/q4x_cpu.rs:509-535: a quantised row equals dequantised
+    # weights . dequantised activations within 1e-3*max(|want|,1)
+    rng = np.random.default_rng(5)
+    for ty, n in ((synth.Q4_K, 1024), (synth.Q6_K, 768), (synth.Q8_0, 512)):
+        w = synth.ENCODERS[ty](rng.normal(0, 0.02, n).astype(np.float32))
+        x = rng.normal(0, 1, n).astype(np.float32)
+        wd = oracle.dequant(ty, w, n).astype(np.float64)
+        if ty == synth.Q8_0:
+            q, d = oracle.q8_32(x)
+            got = oracle.row_q8_0(w, n, q, d)
+            xd = q.astype(np.float64) * np.repeat(d, 32)
+        else:
+            q, d, bs = oracle.q8x(x)
+            got = oracle.row_q4k(w, n, q, d, bs) if ty == synth.Q4_K else oracle.row_q6k(w, n, q, d)
+            xd = q.astype(np.float64) * np.repeat(d, 256)
+        want = float(wd @ xd)
+        assert abs(got - want) <= 1e-3 * max(abs(want), 1.0)
+
+
+def test_q6k_fast_is_scalar(oracle):
+    rng = np.random.default_rng(6)
+    for _ in range(5):
+        w = rng.integers(0, 256, 3 * 210, dtype=np.uint8)
+        w[208::210] = 0x00
+        w[209::210] = 0x2C
+        q, d, _ = oracle.q8x(rng.normal(0, 1, 768).astype(np.float32))
+        a, b = oracle.row_q6k(w, 768, q, d), oracle.row_q6k(w, 768, q, d, "fast")
+        assert np.float32(a).tobytes() == np.float32(b).tobytes()
+
+
+def test_block_known_answers(oracle):
+    # Q4_K: d = 1.0 (0x3c00), dmin = 0.5 (0x3800); sub-block 0: sc 3, m 2;
+    # sub-block 5: sc 33 (needs the high bits), m 17
+    blk = np.zeros(144, np.uint8)
+    blk[0:2] = [0x00, 0x3C]
+    blk[2:4] = [0x00, 0x38]
+    s = blk[4:16]
+    s[0] = 3
+    s[4] = 2
+    s[1] = (33 >> 4) << 6          # high bits of sc[5]
+    s[5] = (17 >> 4) << 6          # high bits of m[5]
+    s[9] = (33 & 15) | ((17 & 15) << 4)
+    blk[16 + 0] = 0x07             # value 0 = 7 (sub-block 0)
+    blk[16 + 64 + 3] = 0xA0        # c=2, i=3, high nibble -> value 64*2+32+3 = 163 (sub-block 5) = 10
+    out = oracle.dequant(synth.Q4_K, blk, 256)
+    assert out[0] == 1.0 * 3 * 7 - 0.5 * 2
+    assert out[1] == -0.5 * 2
+    assert out[163] == 1.0 * 33 * 10 - 0.5 * 17
+    # Q6_K: d = 0.25 (0x3400); value 200: n=1 r=72 qt=2 l=8 -> ql byte 64+8 high nibble,
+    # qh byte 32+8 bits 4-5, scale 8+0+4 = 12
+    blk = np.zeros(210, np.uint8)
+    blk[208:210] = [0x00, 0x34]
+    blk[64 + 8] = 0xB0
+    blk[128 + 32 + 8] = 0b00100000
+    blk[192 + 12] = np.uint8(np.int8(-5).view(np.uint8))
+    out = oracle.dequant(synth.Q6_K, blk, 256)
+    assert out[200] == 0.25 * -5 * ((0xB | (2 << 4)) - 32)
+    assert out[0] == 0.0  # scale 0
+    # MXFP4: e = 129 -> 2.0; e = 1 -> 2^-127 (denormal branch); codes
+    blk = np.zeros(34, np.uint8)
+    blk[0] = 129
+    blk[1] = 0x5F  # value 0 = code 15 (-12), value 16 = code 5 (6)
+    blk[17] = 1
+    blk[18] = 0x02
+    out = oracle.dequant(synth.MXFP4, blk, 64)
+    assert out[0] == -24.0 and out[16] == 12.0
+    assert out[32] == np.float32(2.0) * np.float32(2.0 ** -127)
+    # Q8_0
+    blk = np.zeros(34, np.uint8)
+    blk[0:2] = [0x00, 0x34]
+    blk[2] = np.int8(-100).view(np.uint8)
+    out = oracle.dequant(synth.Q8_0, blk, 32)
+    assert out[0] == -25.0
+
+
+def test_q8x_known_answers(oracle):
+    x = np.zeros(512, np.float32)
+    x[0], x[1], x[2], x[40] = 2.0, -1.0, 0.0078740157, 0.5
+    q, d, bs = oracle.q8x(x)
+    assert d[0] == np.float32(2.0) / np.float32(127.0) and d[1] == 0.0
+    assert q[0] == 127 and q[1] == -64  # -63.5 rounds away from zero
+    assert q[2] == 1                    # 0.5000000 -> 1 (half away)
+    assert q[40] == 32
+    assert bs[0] == 127 - 64 + 1 and bs[1] == 32 and not bs[2:].any()
+
+
+def test_exp_and_log1p(oracle):
+    xs = np.concatenate([np.linspace(-87, 88, 3001), np.array([0.0, -0.0, 1e-8, -1e-8])]).astype(np.float32)
+    got = np.array([oracle.exp(float(x)) for x in xs], np.float64)
+    want = np.exp(xs.astype(np.float64))
+    assert np.all(np.abs(got - want) <= 3e-7 * want)
+    assert oracle.exp(-100.0) == 0.0 and np.isinf(oracle.exp(89.0))
+    xs = np.concatenate([np.logspace(-30, 9, 2000), [0.0]]).astype(np.float32)
+    got = np.array([oracle.log1p(float(x)) for x in xs], np.float64)
+    want = np.log1p(xs.astype(np.float64))
+    assert np.all(np.abs(got - want) <= 3e-7 * np.maximum(want, 1e-30) + 1e-37)
+
+
+def test_route_ties_go_low(oracle):
+    cfg = synth.C2_QWEN3.scaled(d=64, ff=256, n_exp=40, top_k=4)
+    L = oracle.Layer(oracle.LayerDesc(**cfg.desc_fields()), {"router": np.zeros((40, 64), np.float32)})
+    ids, w = L.route_logits(np.zeros((2, 40), np.float32))
+    assert ids.tolist() == [[0, 1, 2, 3]] * 2
+    assert np.allclose(w, 0.25)
+    lg = np.zeros((1, 40), np.float32)
+    lg[0, [37, 5, 33]] = 1.0
+    ids, _ = L.route_logits(lg)
+    assert ids.tolist() == [[5, 33, 37, 0]]
+
+
+def test_plan_layout(oracle):
+    ids = np.array([[3, 1], [1, 0], [3, 2], [1, 3]], np.uint32)
+    p = oracle.plan(ids, 6)
+    assert p["n_active"] == 4
+    assert p["active"][:4].tolist() == [0, 1, 2, 3]
+    assert p["count"][:4].tolist() == [1, 3, 1, 3]
+    assert p["offset"][:4].tolist() == [0, 1, 4, 5]
+    assert p["pair_token"].tolist() == [1, 0, 1, 3, 2, 0, 2, 3]
+    assert p["pair_pos"].tolist() == [5, 1, 2, 0, 6, 4, 3, 7]
+
+
+def test_fast_layer_matches_canonical(oracle):
+    cfg = synth.C2_QWEN3.scaled(d=512, ff=256, n_exp=16)
+    W = synth.make_weights(cfg, 11)
+    L = oracle.Layer(oracle.LayerDesc(**cfg.desc_fields()), W)
+    x = synth.make_activations(9, cfg.d, 12)
+    y = L.forward(x)
+    yf = L.forward_fast(x)
+    assert np.abs(y - yf).max() <= 1e-3 * np.abs(y).max()
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4"])
+def test_golden_layer_outputs(oracle, name):
+    """The committed fixtures (tests/golden/make_golden.py) pin the oracle itself."""
+    from tests.golden.make_golden import case
+
+    path = os.path.join(GOLDEN, f"layer_{name}.npz")
+    g = np.load(path)
+    cfg, W, x = case(name)
+    L = oracle.Layer(oracle.LayerDesc(**cfg.desc_fields()), W)
+    ids, w = L.route(x)
+    assert np.array_equal(ids, g["ids"])
+    assert bits_equal(w, g["w"])
+    assert bits_equal(L.forward(x), g["y"])
