@@ -250,6 +250,15 @@ PM_API int32_t pm_stack_destroy(pm_stack *stack);
 /* x[T][d] in, x_out[T][d] out (may alias); every layer: xn = x/rms(x) (unit
  * norm weight), x += moe(xn) */
 PM_API int32_t pm_stack_forward(pm_stack *stack, const float *x, int32_t T, float *x_out);
+/* mode 0 (default): one-token calls run in the persistent decode kernel when
+ * the stack's shape allows it; mode 1: the general kernels always. Both give
+ * the same bits. With device pointers a failed bounded wait of the decode
+ * kernel is reported by pm_stack_status. */
+PM_API int32_t pm_stack_set_mode(pm_stack *stack, int32_t mode);
+PM_API int32_t pm_stack_decode_kernel_available(pm_stack *stack);
+/* PM_OK, or PM_ERR_TIMEOUT when a device-side wait of an earlier call gave up
+ * (synchronises the context's stream) */
+PM_API int32_t pm_stack_status(pm_stack *stack);
 
 /* ---- synthetic weights generated on the device (benchmark set-up) ------ */
 /* fills every expert (and the router, biases, shared expert) of `layer` with

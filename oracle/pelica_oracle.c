@@ -858,10 +858,26 @@ int po_moe_forward(const po_layer *L, const float *x, int T, float *y, int accum
   return rc;
 }
 
-/* x / rms(x) with unit weight: `rms` (src/forward.rs:63-69); the sum of squares
- * is taken in dot_f32's lane order so that a 32-lane device reproduces it */
+/* x / rms(x) with unit weight: `rms` (src/forward.rs:63-69). The reference sums
+ * the squares one after another; no parallel device reproduces that order, so
+ * this glue (it is not one of the reference's hot-path functions) fixes an order
+ * a 256-thread block has: lane j of 256 takes x[j], x[j+256], ... by fma, each 32
+ * lanes are summed by xor shuffles 16,8,4,2,1, the 8 group sums one after another. */
 void po_rmsnorm(const float *x, int d, float eps, float *out) {
-  float ms = po_dot_f32(x, x, (size_t)d) / (float)d;
+  float lane[256];
+  for (int j = 0; j < 256; j++) {
+    float a = 0.0f;
+    for (int i = j; i < d; i += 256) a = fmaf(x[i], x[i], a);
+    lane[j] = a;
+  }
+  float total = 0.0f;
+  for (int g = 0; g < 8; g++) {
+    float *l = lane + 32 * g;
+    for (int off = 16; off >= 1; off >>= 1)
+      for (int i = 0; i < off; i++) l[i] = l[i] + l[i + off];
+    total = total + l[0];
+  }
+  float ms = total / (float)d;
   float inv = 1.0f / sqrtf(ms + eps);
   for (int i = 0; i < d; i++) out[i] = x[i] * inv;
 }

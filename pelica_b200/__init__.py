@@ -95,6 +95,9 @@ ABI = {
     "pm_stack_create": (C.c_int32, [_VP, C.POINTER(_VP), C.c_int32, C.c_float, C.POINTER(_VP)]),
     "pm_stack_destroy": (C.c_int32, [_VP]),
     "pm_stack_forward": (C.c_int32, [_VP, _VP, C.c_int32, _VP]),
+    "pm_stack_set_mode": (C.c_int32, [_VP, C.c_int32]),
+    "pm_stack_decode_kernel_available": (C.c_int32, [_VP]),
+    "pm_stack_status": (C.c_int32, [_VP]),
     "pm_layer_fill_synthetic": (C.c_int32, [_VP, C.c_uint64, C.c_float, C.c_float, C.c_float]),
     "pm_layer_get_expert_bias": (C.c_int32, [_VP, C.c_int32, _VP, _VP, _VP]),
     "pm_layer_get_expert": (C.c_int32, [_VP, C.c_int32, C.c_int32, _VP]),
@@ -433,3 +436,14 @@ class Stack:
 
     def forward_dev(self, x: DevBuf, T: int, out: DevBuf):
         _check(self.lib.pm_stack_forward(self.h, x.ptr, T, out.ptr))
+
+    def set_mode(self, general_only: bool):
+        """True: always the general kernels; False: one-token calls use the persistent decode kernel."""
+        _check(self.lib.pm_stack_set_mode(self.h, int(general_only)))
+
+    @property
+    def decode_kernel(self) -> bool:
+        return bool(self.lib.pm_stack_decode_kernel_available(self.h))
+
+    def status(self):
+        _check(self.lib.pm_stack_status(self.h))

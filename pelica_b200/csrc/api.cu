@@ -9,7 +9,7 @@
 #include <new>
 #include <vector>
 
-#include "moe_internal.cuh"
+#include "decode_mega.cuh"
 
 void launch_synth_blocks(const Launch &L, int type, uint8_t *raw, size_t nb, uint64_t seed,
                          float sigma);
@@ -200,6 +200,7 @@ extern "C" int32_t pm_sync(pm_ctx *c) {
   CU(cudaGetLastError());
   return PM_OK;
 }
+extern "C" int32_t pm_stack_destroy(pm_stack *s);
 extern "C" void *pm_ctx_stream(pm_ctx *c) { return c ? (void *)c->stream : nullptr; }
 extern "C" int64_t pm_ctx_launch_count(pm_ctx *c) { return c ? c->launches : 0; }
 
@@ -1099,7 +1100,65 @@ struct pm_stack {
   pm_ctx *ctx = nullptr;
   std::vector<pm_layer *> layers;
   float eps = 1e-6f;
+  int mode = 0;  // 0 = pick per call, 1 = general kernels only
+  // the one-token decode kernel (decode_mega.cu)
+  MegaPlan mega;
+  bool mega_ok = false;
+  MegaLayer *mega_layers = nullptr;
+  uint8_t *mega_buf = nullptr;  // exchange buffers + counters + error word
+  float *mega_io = nullptr;     // staged input / output token
+  unsigned long long calls = 0;
 };
+
+static int32_t stack_setup_mega(pm_stack *s) {
+  pm_ctx *c = s->ctx;
+  const pm_layer_desc &D = s->layers[0]->dev.desc;
+  for (pm_layer *ly : s->layers)
+    if (memcmp(&ly->dev.desc, &D, sizeof D) != 0) return PM_OK;  // mixed shapes: general path
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, c->device));
+  int coop = 0;
+  CU(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c->device));
+  if (!coop || prop.major < 9) return PM_OK;
+  if (!mega_plan(D, prop.multiProcessorCount, prop.sharedMemPerBlockOptin, s->mega)) return PM_OK;
+  CU(mega_prepare(s->mega.smem));
+  if (mega_max_ctas_per_sm(s->mega.smem) < 1) return PM_OK;
+  size_t L = s->layers.size();
+  std::vector<MegaLayer> ml(L);
+  for (size_t i = 0; i < L; i++) {
+    const LayerDev &dv = s->layers[i]->dev;
+    ml[i].router = dv.router;
+    ml[i].logit_bias = dv.logit_bias;
+    ml[i].select_bias = dv.select_bias;
+    ml[i].gate = dv.gate.plane[0];
+    ml[i].gate_stride = dv.gate.stride[0];
+    ml[i].up = dv.up.plane[0];
+    ml[i].up_stride = dv.up.stride[0];
+    for (int p = 0; p < 4; p++) {
+      ml[i].down[p] = dv.down.plane[p];
+      ml[i].down_stride[p] = dv.down.stride[p];
+    }
+    ml[i].usage = dv.usage;
+  }
+  CU(cudaMalloc(&s->mega_layers, L * sizeof(MegaLayer)));
+  CU(cudaMemcpy(s->mega_layers, ml.data(), L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+  size_t xb = al((size_t)D.d * 8), lb = al((size_t)D.n_exp * 8), hb = al((size_t)D.top_k * D.ff * 4);
+  size_t total = xb + lb + hb + 256;
+  CU(cudaMalloc(&s->mega_buf, total));
+  CU(cudaMemset(s->mega_buf, 0, total));
+  CU(cudaMalloc(&s->mega_io, (size_t)D.d * 4 * 2));
+  MegaParams &P = s->mega.P;
+  P.n_layers = (int)L;
+  P.layers = s->mega_layers;
+  P.eps = s->eps;
+  P.xbuf = (unsigned long long *)s->mega_buf;
+  P.lbuf = (unsigned long long *)(s->mega_buf + xb);
+  P.hbuf = (float *)(s->mega_buf + xb + lb);
+  P.hcount = (unsigned long long *)(s->mega_buf + xb + lb + hb);
+  P.err = (int *)(s->mega_buf + xb + lb + hb + 64);
+  s->mega_ok = true;
+  return PM_OK;
+}
 
 extern "C" int32_t pm_stack_create(pm_ctx *ctx, pm_layer **layers, int32_t n, float eps,
                                    pm_stack **out) {
@@ -1109,16 +1168,84 @@ extern "C" int32_t pm_stack_create(pm_ctx *ctx, pm_layer **layers, int32_t n, fl
     if (layers[i]->dev.desc.d != layers[0]->dev.desc.d)
       return fail(PM_ERR_INVALID, "layer %d: hidden size differs", i);
   }
+  CU(cudaSetDevice(ctx->device));
   pm_stack *s = new (std::nothrow) pm_stack();
   if (!s) return fail(PM_ERR_OOM, "host allocation");
   s->ctx = ctx;
   s->layers.assign(layers, layers + n);
   s->eps = eps;
+  int32_t rc = stack_setup_mega(s);
+  if (rc != PM_OK) {
+    pm_stack_destroy(s);
+    return rc;
+  }
   *out = s;
   return PM_OK;
 }
 extern "C" int32_t pm_stack_destroy(pm_stack *s) {
+  if (!s) return PM_OK;
+  cudaSetDevice(s->ctx->device);
+  cudaStreamSynchronize(s->ctx->stream);
+  if (s->mega_layers) cudaFree(s->mega_layers);
+  if (s->mega_buf) cudaFree(s->mega_buf);
+  if (s->mega_io) cudaFree(s->mega_io);
   delete s;
+  return PM_OK;
+}
+extern "C" int32_t pm_stack_set_mode(pm_stack *s, int32_t mode) {
+  if (!s || mode < 0 || mode > 1) return fail(PM_ERR_INVALID, "pm_stack_set_mode");
+  s->mode = mode;
+  return PM_OK;
+}
+extern "C" int32_t pm_stack_decode_kernel_available(pm_stack *s) { return s && s->mega_ok ? 1 : 0; }
+
+extern "C" int32_t pm_stack_status(pm_stack *s) {
+  if (!s) return fail(PM_ERR_INVALID, "pm_stack_status");
+  CU(cudaStreamSynchronize(s->ctx->stream));
+  if (!s->mega_buf) return PM_OK;
+  int err = 0;
+  CU(cudaMemcpy(&err, s->mega.P.err, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    s->mega_ok = false;
+    return fail(PM_ERR_TIMEOUT, "decode kernel: a bounded device-side wait gave up (code %d)", err);
+  }
+  return PM_OK;
+}
+
+// one token through every layer in one persistent kernel
+static int32_t stack_forward_mega(pm_stack *s, const float *x, float *x_out) {
+  pm_ctx *c = s->ctx;
+  const int d = s->layers[0]->dev.desc.d;
+  MegaParams &P = s->mega.P;
+  const float *xin = x;
+  float *xo = x_out;
+  if (!is_device_ptr(x)) {
+    CU(cudaMemcpyAsync(s->mega_io, x, (size_t)d * 4, cudaMemcpyHostToDevice, c->stream));
+    xin = s->mega_io;
+  }
+  bool out_host = !is_device_ptr(x_out);
+  if (out_host) xo = s->mega_io + d;
+  size_t L = s->layers.size();
+  s->calls++;
+  P.x_in = xin;
+  P.x_out = xo;
+  P.epoch_base = (uint32_t)(s->calls * (unsigned long long)(L + 1));
+  P.hcount_base = (s->calls - 1) * (unsigned long long)L * (unsigned long long)s->mega.grid;
+  {
+    PROF(c, PH_FUSED);
+    CU(mega_launch(s->mega, c->stream));
+    c->launches++;
+  }
+  if (out_host) {
+    CU(cudaMemcpyAsync(x_out, xo, (size_t)d * 4, cudaMemcpyDeviceToHost, c->stream));
+    int err = 0;
+    CU(cudaMemcpyAsync(&err, P.err, 4, cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    if (err) {
+      s->mega_ok = false;  // counters are no longer consistent: general kernels from now on
+      return fail(PM_ERR_TIMEOUT, "decode kernel: a bounded device-side wait gave up (code %d)", err);
+    }
+  }
   return PM_OK;
 }
 
@@ -1129,6 +1256,7 @@ extern "C" int32_t pm_stack_forward(pm_stack *s, const float *x, int32_t T, floa
   pm_ctx *c = s->ctx;
   CU(cudaSetDevice(c->device));
   for (pm_layer *ly : s->layers) TRY(layer_ready(ly, true));
+  if (T == 1 && s->mega_ok && s->mode == 0) return stack_forward_mega(s, x, x_out);
   const int d = s->layers[0]->dev.desc.d;
   size_t n = (size_t)T * d;
   size_t need = 0;

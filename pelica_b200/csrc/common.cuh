@@ -151,6 +151,27 @@ __device__ __forceinline__ float pm_warp_sum_dot(float v) {
   v = __fadd_rn(v, __shfl_xor_sync(PM_FULL, v, 1));
   return v;
 }
+// 1/rms(x), unit weight (the layer loop's glue, src/forward.rs:63-69). Sum of
+// squares in a fixed order: thread j of the first 256 takes x[j], x[j+256], ...
+// by fma, warps are summed by xor shuffles 16..1, the 8 warp sums one after
+// another. Called by every thread of a CTA of >= 256 threads; red8 = 8 floats
+// of shared memory.
+__device__ __forceinline__ float pm_rms_inv(const float *xr, int d, float eps, float *red8) {
+  int tid = threadIdx.x;
+  if (tid < 256) {
+    float acc = 0.0f;
+    for (int c = tid; c < d; c += 256) acc = __fmaf_rn(xr[c], xr[c], acc);
+    acc = pm_warp_sum_16_1(acc);
+    if ((tid & 31) == 0) red8[tid >> 5] = acc;
+  }
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 8; g++) total = __fadd_rn(total, red8[g]);
+  float ms = __fdiv_rn(total, (float)d);
+  return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
+}
+
 __device__ __forceinline__ int pm_warp_sum_i32(int v) {
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(PM_FULL, v, o);

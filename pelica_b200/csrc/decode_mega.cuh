@@ -1,0 +1,50 @@
+// decode_mega.cuh - parameters of the persistent one-token decode kernel.
+#pragma once
+
+#include "moe_internal.cuh"
+
+#define MG_NT 512
+#define MG_WARPS (MG_NT / 32)
+#define MG_GU_CHUNKS 4
+
+struct MegaLayer {
+  const float *router, *logit_bias, *select_bias;
+  const uint8_t *gate, *up;
+  size_t gate_stride, up_stride;
+  const uint8_t *down[4];
+  size_t down_stride[4];
+  uint32_t *usage;
+};
+
+struct MegaParams {
+  pm_layer_desc D;
+  int n_layers;
+  const MegaLayer *layers;
+  const float *x_in;
+  float *x_out;
+  float eps;
+  unsigned long long *xbuf;  // [d]      (value, epoch)
+  unsigned long long *lbuf;  // [E]      (logit, epoch)
+  float *hbuf;               // [K*ff]
+  unsigned long long *hcount;  // arrivals of CTAs that finished their h rows
+  unsigned long long hcount_base;
+  uint32_t epoch_base;
+  int *err;
+  // shared-memory layout (bytes from the dynamic base)
+  int rows_max, cols_max;
+  uint32_t off_gs, off_us, off_dn, off_dsm, off_xs, off_xq, off_xd, off_xbs, off_hq, off_hd,
+      off_hbs, off_rw, off_eo, off_lg, off_misc, dn_k_bytes;
+};
+
+struct MegaPlan {
+  bool ok = false;
+  int grid = 0;
+  size_t smem = 0;
+  MegaParams P{};
+};
+
+
+bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp);
+cudaError_t mega_prepare(size_t smem);
+int mega_max_ctas_per_sm(size_t smem);
+cudaError_t mega_launch(const MegaPlan &mp, cudaStream_t stream);

@@ -31,7 +31,7 @@ ROUTE_CASES = {
     "c1-softmax": synth.C1_OLMOE,
     "c2-softmax-renorm": synth.C2_QWEN3,
     "c3-selected-bias": synth.C3_GPTOSS,
-    "c4-sigmoid-groups": synth.C4_DSV3,
+    "c4-sigmoid-groups": synth.C4_DSV3.scaled(shared=0),
     "sigmoid-bias-scale": synth.C4_DSV3.scaled(n_group=0, topk_group=0, n_exp=160, shared=0),
     "sqrt-softplus": synth.C4_DSV3.scaled(gating=synth.GATE_SQRT_SOFTPLUS, n_group=0, topk_group=0, w_scale=1.5,
                                           shared=0),
