@@ -24,7 +24,8 @@
 #include "decode_mega.cuh"
 #include "route.cuh"
 
-#define MG_SPIN_LIMIT (1u << 22)
+// every cross-CTA or copy wait gives up after this long (wall time on the device)
+#define MG_WAIT_NS 2000000000ull
 
 // ---- PTX helpers -----------------------------------------------------------
 __device__ __forceinline__ uint32_t s32(const void *p) {
@@ -40,7 +41,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       " selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
       : "r"(s32(bar)), "r"(parity)
@@ -79,11 +80,22 @@ __device__ __forceinline__ int ld_volatile_i32(const int *p) {
   return v;
 }
 
-// bounded wait on an mbarrier phase; false = gave up (error word set)
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// bounded wait on an mbarrier phase (non-blocking test in a timed loop);
+// false = gave up (error word set)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
-  for (uint32_t it = 0; it < MG_SPIN_LIMIT; it++) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = now_ns();
+  for (uint32_t it = 1;; it++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023) == 1023 && ld_volatile_i32(err) != 0) return false;
+    if ((it & 255) == 0) {
+      if (ld_volatile_i32(err) != 0) return false;
+      if (now_ns() - t0 > MG_WAIT_NS) break;
+    }
   }
   atomicCAS(err, 0, 2);
   return false;
@@ -91,13 +103,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
 // bounded wait for an epoch-tagged value; false = gave up
 __device__ __forceinline__ bool wait_pair(const unsigned long long *p, uint32_t epoch, float &v,
                                           int *err) {
-  for (uint32_t it = 0; it < MG_SPIN_LIMIT; it++) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; it++) {
     unsigned long long u = ld_pair(p);
     if ((uint32_t)(u >> 32) == epoch) {
       v = __uint_as_float((uint32_t)u);
       return true;
     }
-    if ((it & 255) == 255 && ld_volatile_i32(err) != 0) return false;
+    if ((it & 63) == 63) {
+      if (ld_volatile_i32(err) != 0) return false;
+      unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > MG_WAIT_NS) break;
+    }
   }
   atomicCAS(err, 0, 1);
   return false;
@@ -304,10 +322,8 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       }
       __syncwarp();
       pm_route_warp(D, lg, ML.select_bias, lane, r_sv, r_gs, r_keep, ids, wts);
-      if (cta == 0 && lane < K && ML.usage) {
-        __syncwarp();
-        atomicAdd(&ML.usage[ids[lane]], 1u);
-      }
+      __syncwarp();  // ids[] written by lane 0
+      if (cta == 0 && lane < K && ML.usage) atomicAdd(&ML.usage[ids[lane]], 1u);
     }
     if (__syncthreads_or(dead)) { dead = true; break; }
 
@@ -379,9 +395,10 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     if (tid == 0) {
       unsigned long long want = P.hcount_base + (unsigned long long)(l + 1) * (unsigned long long)G;
       bool ok = false;
-      for (uint32_t it = 0; it < MG_SPIN_LIMIT; it++) {
+      unsigned long long t0 = now_ns();
+      for (uint32_t it = 0;; it++) {
         if (ld_acquire_u64(P.hcount) >= want) { ok = true; break; }
-        if ((it & 255) == 255 && ld_volatile_i32(P.err) != 0) break;
+        if ((it & 63) == 63 && (ld_volatile_i32(P.err) != 0 || now_ns() - t0 > MG_WAIT_NS)) break;
       }
       if (!ok) { atomicCAS(P.err, 0, 3); dead = true; }
     }
