@@ -259,6 +259,10 @@ PM_API int32_t pm_stack_decode_kernel_available(pm_stack *stack);
 /* PM_OK, or PM_ERR_TIMEOUT when a device-side wait of an earlier call gave up
  * (synchronises the context's stream) */
 PM_API int32_t pm_stack_status(pm_stack *stack);
+/* phase trace of the decode kernel (development aid): called with out == NULL
+ * it switches tracing on and returns the number of int64 entries; called with a
+ * buffer it copies the last call's SM-clock stamps: [2 CTAs][layers][8 phases]. */
+PM_API int32_t pm_stack_trace(pm_stack *stack, int64_t *out, int32_t capacity);
 
 /* ---- synthetic weights generated on the device (benchmark set-up) ------ */
 /* fills every expert (and the router, biases, shared expert) of `layer` with

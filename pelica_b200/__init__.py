@@ -98,6 +98,7 @@ ABI = {
     "pm_stack_set_mode": (C.c_int32, [_VP, C.c_int32]),
     "pm_stack_decode_kernel_available": (C.c_int32, [_VP]),
     "pm_stack_status": (C.c_int32, [_VP]),
+    "pm_stack_trace": (C.c_int32, [_VP, _VP, C.c_int32]),
     "pm_layer_fill_synthetic": (C.c_int32, [_VP, C.c_uint64, C.c_float, C.c_float, C.c_float]),
     "pm_layer_get_expert_bias": (C.c_int32, [_VP, C.c_int32, _VP, _VP, _VP]),
     "pm_layer_get_expert": (C.c_int32, [_VP, C.c_int32, C.c_int32, _VP]),
@@ -447,3 +448,16 @@ class Stack:
 
     def status(self):
         _check(self.lib.pm_stack_status(self.h))
+
+    def trace(self, enable: bool = False):
+        """Decode-kernel phase stamps (SM clocks) of the last call: array [2, layers, 8]."""
+        n = self.lib.pm_stack_trace(self.h, None, 0)
+        if n < 0:
+            _check(n)
+        if enable:
+            return None
+        out = np.zeros(n, np.int64)
+        r = self.lib.pm_stack_trace(self.h, out.ctypes.data, n)
+        if r < 0:
+            _check(r)
+        return out.reshape(2, len(self.layers), -1)

@@ -1107,6 +1107,7 @@ struct pm_stack {
   MegaLayer *mega_layers = nullptr;
   uint8_t *mega_buf = nullptr;  // exchange buffers + counters + error word
   float *mega_io = nullptr;     // staged input / output token
+  long long *mega_trace = nullptr;
   unsigned long long calls = 0;
 };
 
@@ -1189,6 +1190,7 @@ extern "C" int32_t pm_stack_destroy(pm_stack *s) {
   if (s->mega_layers) cudaFree(s->mega_layers);
   if (s->mega_buf) cudaFree(s->mega_buf);
   if (s->mega_io) cudaFree(s->mega_io);
+  if (s->mega_trace) cudaFree(s->mega_trace);
   delete s;
   return PM_OK;
 }
@@ -1198,6 +1200,23 @@ extern "C" int32_t pm_stack_set_mode(pm_stack *s, int32_t mode) {
   return PM_OK;
 }
 extern "C" int32_t pm_stack_decode_kernel_available(pm_stack *s) { return s && s->mega_ok ? 1 : 0; }
+
+extern "C" int32_t pm_stack_trace(pm_stack *s, int64_t *out, int32_t capacity) {
+  if (!s || !s->mega_ok) return fail(PM_ERR_STATE, "pm_stack_trace: no decode kernel for this stack");
+  int n = 2 * (int)s->layers.size() * MG_TRACE_PH;
+  if (!out) {  // switch tracing on
+    if (!s->mega_trace) {
+      CU(cudaMalloc(&s->mega_trace, (size_t)n * 8));
+      CU(cudaMemset(s->mega_trace, 0, (size_t)n * 8));
+    }
+    s->mega.P.trace = s->mega_trace;
+    return n;
+  }
+  if (!s->mega_trace || capacity < n) return fail(PM_ERR_INVALID, "pm_stack_trace: capacity %d < %d", capacity, n);
+  CU(cudaStreamSynchronize(s->ctx->stream));
+  CU(cudaMemcpy(out, s->mega_trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  return n;
+}
 
 extern "C" int32_t pm_stack_status(pm_stack *s) {
   if (!s) return fail(PM_ERR_INVALID, "pm_stack_status");

@@ -85,14 +85,26 @@ __device__ __forceinline__ unsigned long long now_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// bounded wait on an mbarrier phase (non-blocking test in a timed loop);
-// false = gave up (error word set)
+// blocking form with an explicit suspend-time hint: the warp sleeps in hardware
+// (no issue slots burnt) for at most `ns` before the instruction returns
+__device__ __forceinline__ bool mbar_try_wait_ns(uint64_t *bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(s32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait on an mbarrier phase: short hardware-suspended waits in a timed
+// loop; false = gave up (error word set)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = now_ns();
   for (uint32_t it = 1;; it++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255) == 0) {
+    if (mbar_try_wait_ns(bar, parity, 4000u)) return true;
+    if ((it & 15) == 0) {
       if (ld_volatile_i32(err) != 0) return false;
       if (now_ns() - t0 > MG_WAIT_NS) break;
     }
@@ -123,8 +135,10 @@ __device__ __forceinline__ bool wait_pair(const unsigned long long *p, uint32_t 
 
 // ---- Q8x of 256 values held 8 per lane (value j of the lane = element 32j+lane)
 // (`Q8x::new`, src/ds4_cpu.rs:13-35); writes q, d, bsum of the block
+// `swz`: 16-byte chunk c of the block is stored at chunk c ^ swz (so that lanes
+// reading the same chunk of 8 different blocks hit different banks)
 __device__ __forceinline__ void q8x_block_warp(const float v[8], int lane, int8_t *q, float *d,
-                                               int32_t *bsum) {
+                                               int32_t *bsum, int swz = 0) {
   float a = 0.0f;
 #pragma unroll
   for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
@@ -137,7 +151,7 @@ __device__ __forceinline__ void q8x_block_warp(const float v[8], int lane, int8_
       float f = roundf(__fmul_rn(v[j], id));
       r = (int)fminf(fmaxf(f, -127.0f), 127.0f);
     }
-    q[32 * j + lane] = (int8_t)r;
+    q[(((2 * j + (lane >> 4)) ^ swz) << 4) + (lane & 15)] = (int8_t)r;
     int s = __reduce_add_sync(PM_FULL, r);
     if (lane == 0) bsum[j] = s;
   }
@@ -145,80 +159,212 @@ __device__ __forceinline__ void q8x_block_warp(const float v[8], int lane, int8_
 }
 
 // ---- rows from shared memory (same sums and order as kernels_basic.cu) -------
-__device__ __forceinline__ float row_q4k_smem(const uint8_t *rowp, int nb, const int8_t *xq,
-                                              const float *xd, const int32_t *xbsum, int lane) {
-  float total = 0.0f;
+// Several rows at once: every row's chain is independent, so the loads, the
+// integer dots, the shuffles and the ordered float tails of NR rows overlap.
+
+// Q4_K sub-block scale/min pair (2c, 2c+1) of a block header, branch-free
+__device__ __forceinline__ void q4k_scmin_pair(const uint4 &hdr, int c, int &sc0, int &m0, int &sc1,
+                                               int &m1) {
+  // j = 2c, 2c+1.  c < 2: plain 6-bit fields of words y (scales) and z (mins);
+  // c >= 2: low nibbles from word w, high 2 bits from the top of y / z bytes.
+  int jj = (2 * c) & 3;  // byte index inside the word (0 or 2)
+  uint32_t by0 = (hdr.y >> (8 * jj)) & 0xff, by1 = (hdr.y >> (8 * jj + 8)) & 0xff;
+  uint32_t bz0 = (hdr.z >> (8 * jj)) & 0xff, bz1 = (hdr.z >> (8 * jj + 8)) & 0xff;
+  uint32_t bw0 = (hdr.w >> (8 * jj)) & 0xff, bw1 = (hdr.w >> (8 * jj + 8)) & 0xff;
+  bool hi = c >= 2;
+  sc0 = hi ? (int)((bw0 & 15) | ((by0 >> 6) << 4)) : (int)(by0 & 63);
+  m0 = hi ? (int)((bw0 >> 4) | ((bz0 >> 6) << 4)) : (int)(bz0 & 63);
+  sc1 = hi ? (int)((bw1 & 15) | ((by1 >> 6) << 4)) : (int)(by1 & 63);
+  m1 = hi ? (int)((bw1 >> 4) | ((bz1 >> 6) << 4)) : (int)(bz1 & 63);
+}
+
+template <int NR>
+__device__ __forceinline__ void rows_q4k_smem(const uint8_t *const rowp[NR], int nb,
+                                              const int8_t *const xq[NR], const float *const xd[NR],
+                                              const int32_t *const xbs[NR], int lane,
+                                              float total[NR]) {
+#pragma unroll
+  for (int r = 0; r < NR; r++) total[r] = 0.0f;
   const int nchunks = nb * 4;
+  const uint32_t M = 0x0f0f0f0fu;
   for (int c0 = 0; c0 < nchunks; c0 += 32) {
     int ci = c0 + lane;
     bool valid = ci < nchunks;
-    int b = ci >> 2, c = ci & 3;
-    int pi = 0, pm = 0;
-    float dd = 0.0f, dmin = 0.0f;
-    if (valid) {
-      const uint8_t *blk = rowp + b * 144;
-      uint4 hdr = *(const uint4 *)blk;
+    int b = valid ? (ci >> 2) : 0, c = ci & 3;
+    uint4 hdr[NR], q0[NR], q1[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+      const uint8_t *blk = rowp[r] + b * 144;
+      hdr[r] = *(const uint4 *)blk;
       const uint4 *qp = (const uint4 *)(blk + 16 + 32 * c);
-      uint4 q0 = qp[0], q1 = qp[1];
-      const int4 *xp = (const int4 *)(xq + b * 256 + 64 * c);
+      q0[r] = qp[0];
+      q1[r] = qp[1];
+    }
+    float term[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+      const int4 *xp = (const int4 *)(xq[r] + b * 256 + 64 * c);
       int4 xl0 = xp[0], xl1 = xp[1], xh0 = xp[2], xh1 = xp[3];
       int lo = 0, hi = 0;
-      const uint32_t M = 0x0f0f0f0fu;
-      lo = __dp4a((int)(q0.x & M), xl0.x, lo); hi = __dp4a((int)((q0.x >> 4) & M), xh0.x, hi);
-      lo = __dp4a((int)(q0.y & M), xl0.y, lo); hi = __dp4a((int)((q0.y >> 4) & M), xh0.y, hi);
-      lo = __dp4a((int)(q0.z & M), xl0.z, lo); hi = __dp4a((int)((q0.z >> 4) & M), xh0.z, hi);
-      lo = __dp4a((int)(q0.w & M), xl0.w, lo); hi = __dp4a((int)((q0.w >> 4) & M), xh0.w, hi);
-      lo = __dp4a((int)(q1.x & M), xl1.x, lo); hi = __dp4a((int)((q1.x >> 4) & M), xh1.x, hi);
-      lo = __dp4a((int)(q1.y & M), xl1.y, lo); hi = __dp4a((int)((q1.y >> 4) & M), xh1.y, hi);
-      lo = __dp4a((int)(q1.z & M), xl1.z, lo); hi = __dp4a((int)((q1.z >> 4) & M), xh1.z, hi);
-      lo = __dp4a((int)(q1.w & M), xl1.w, lo); hi = __dp4a((int)((q1.w >> 4) & M), xh1.w, hi);
+      lo = __dp4a((int)(q0[r].x & M), xl0.x, lo); hi = __dp4a((int)((q0[r].x >> 4) & M), xh0.x, hi);
+      lo = __dp4a((int)(q0[r].y & M), xl0.y, lo); hi = __dp4a((int)((q0[r].y >> 4) & M), xh0.y, hi);
+      lo = __dp4a((int)(q0[r].z & M), xl0.z, lo); hi = __dp4a((int)((q0[r].z >> 4) & M), xh0.z, hi);
+      lo = __dp4a((int)(q0[r].w & M), xl0.w, lo); hi = __dp4a((int)((q0[r].w >> 4) & M), xh0.w, hi);
+      lo = __dp4a((int)(q1[r].x & M), xl1.x, lo); hi = __dp4a((int)((q1[r].x >> 4) & M), xh1.x, hi);
+      lo = __dp4a((int)(q1[r].y & M), xl1.y, lo); hi = __dp4a((int)((q1[r].y >> 4) & M), xh1.y, hi);
+      lo = __dp4a((int)(q1[r].z & M), xl1.z, lo); hi = __dp4a((int)((q1[r].z >> 4) & M), xh1.z, hi);
+      lo = __dp4a((int)(q1[r].w & M), xl1.w, lo); hi = __dp4a((int)((q1[r].w >> 4) & M), xh1.w, hi);
       int sc0, m0, sc1, m1;
-      pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c, sc0, m0);
-      pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c + 1, sc1, m1);
-      pi = sc0 * lo + sc1 * hi;
-      pm = m0 * xbsum[b * 8 + 2 * c] + m1 * xbsum[b * 8 + 2 * c + 1];
-      dd = pm_f16(hdr.x);
-      dmin = pm_f16(hdr.x >> 16);
+      q4k_scmin_pair(hdr[r], c, sc0, m0, sc1, m1);
+      int pi = sc0 * lo + sc1 * hi;
+      int pm = m0 * xbs[r][b * 8 + 2 * c] + m1 * xbs[r][b * 8 + 2 * c + 1];
+      if (!valid) { pi = 0; pm = 0; }
+      pi += __shfl_xor_sync(PM_FULL, pi, 1);
+      pm += __shfl_xor_sync(PM_FULL, pm, 1);
+      pi += __shfl_xor_sync(PM_FULL, pi, 2);
+      pm += __shfl_xor_sync(PM_FULL, pm, 2);
+      float dd = pm_f16(hdr[r].x), dmin = pm_f16(hdr[r].x >> 16);
+      term[r] = __fmul_rn(xd[r][b], __fsub_rn(__fmul_rn(dd, (float)pi), __fmul_rn(dmin, (float)pm)));
     }
-    pi += __shfl_xor_sync(PM_FULL, pi, 1);
-    pm += __shfl_xor_sync(PM_FULL, pm, 1);
-    pi += __shfl_xor_sync(PM_FULL, pi, 2);
-    pm += __shfl_xor_sync(PM_FULL, pm, 2);
-    float term = 0.0f;
-    if (valid)
-      term = __fmul_rn(xd[b], __fsub_rn(__fmul_rn(dd, (float)pi), __fmul_rn(dmin, (float)pm)));
     int nblk = min(8, nb - (c0 >> 2));
-    for (int j = 0; j < nblk; j++) total = __fadd_rn(total, __shfl_sync(PM_FULL, term, 4 * j));
+    for (int j = 0; j < nblk; j++) {
+#pragma unroll
+      for (int r = 0; r < NR; r++) total[r] = __fadd_rn(total[r], __shfl_sync(PM_FULL, term[r], 4 * j));
+    }
   }
+}
+
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// Four Q4_K rows of exactly 8 blocks (2048 values) against one activation
+// vector, one WHOLE block per lane: lane = 8*row + block. The lane's block of
+// the quantised token (64 words), its 8 partial sums and its scale stay in
+// registers for the whole layer; no cross-lane reduction of the integer sums.
+// All lanes of row group g return that row's sum (block terms added in order).
+struct XBlk {
+  int x[64];
+  int bs[8];
+  float d;
+};
+__device__ __forceinline__ float row4_q4k_blk(const uint8_t *rowp, const XBlk &X, int lane) {
+  const int b = lane & 7;
+  const uint8_t *blk = rowp + b * 144;
+  const uint4 hdr = *(const uint4 *)blk;
+  const uint4 *qp = (const uint4 *)(blk + 16);
+  const uint32_t ML = 0x0f0f0f0fu, MH = 0xf0f0f0f0u;
+  int lo[4], hi[4];
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    uint4 q0 = qp[2 * c], q1 = qp[2 * c + 1];
+    int l = 0, h = 0;
+    l = __dp4a((int)(q0.x & ML), X.x[16 * c + 0], l); h = dp4a_us(q0.x & MH, X.x[16 * c + 8], h);
+    l = __dp4a((int)(q0.y & ML), X.x[16 * c + 1], l); h = dp4a_us(q0.y & MH, X.x[16 * c + 9], h);
+    l = __dp4a((int)(q0.z & ML), X.x[16 * c + 2], l); h = dp4a_us(q0.z & MH, X.x[16 * c + 10], h);
+    l = __dp4a((int)(q0.w & ML), X.x[16 * c + 3], l); h = dp4a_us(q0.w & MH, X.x[16 * c + 11], h);
+    l = __dp4a((int)(q1.x & ML), X.x[16 * c + 4], l); h = dp4a_us(q1.x & MH, X.x[16 * c + 12], h);
+    l = __dp4a((int)(q1.y & ML), X.x[16 * c + 5], l); h = dp4a_us(q1.y & MH, X.x[16 * c + 13], h);
+    l = __dp4a((int)(q1.z & ML), X.x[16 * c + 6], l); h = dp4a_us(q1.z & MH, X.x[16 * c + 14], h);
+    l = __dp4a((int)(q1.w & ML), X.x[16 * c + 7], l); h = dp4a_us(q1.w & MH, X.x[16 * c + 15], h);
+    lo[c] = l;
+    hi[c] = h >> 4;  // the high-nibble dot was accumulated 16-fold (exact)
+  }
+  // 6-bit sub-block scales and mins (`scales`, src/ds4_cpu.rs:45-57)
+  int isum = 0, msum = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    int sc, m;
+    if (j < 4) {
+      sc = (hdr.y >> (8 * j)) & 63;
+      m = (hdr.z >> (8 * j)) & 63;
+    } else {
+      uint32_t a = (hdr.w >> (8 * (j - 4))) & 0xff;
+      sc = (int)((a & 15) | ((((hdr.y >> (8 * (j - 4))) & 0xff) >> 6) << 4));
+      m = (int)((a >> 4) | ((((hdr.z >> (8 * (j - 4))) & 0xff) >> 6) << 4));
+    }
+    isum += sc * ((j & 1) ? hi[j >> 1] : lo[j >> 1]);
+    msum += m * X.bs[j];
+  }
+  float dd = pm_f16(hdr.x), dmin = pm_f16(hdr.x >> 16);
+  float term = __fmul_rn(X.d, __fsub_rn(__fmul_rn(dd, (float)isum), __fmul_rn(dmin, (float)msum)));
+  float total = 0.0f;
+  const int g0 = lane & ~7;
+#pragma unroll
+  for (int j = 0; j < 8; j++) total = __fadd_rn(total, __shfl_sync(PM_FULL, term, g0 + j));
   return total;
 }
 
-__device__ __forceinline__ float row_q6k_smem(const uint8_t *ql, const uint8_t *qh,
-                                              const uint8_t *sc, const __half *dp, int nb,
-                                              const int8_t *xq, const float *xd, int lane) {
-  float total = 0.0f;
+template <int NR>
+__device__ __forceinline__ void rows_q6k_smem(const uint8_t *const ql[NR], const uint8_t *const qh[NR],
+                                              const uint8_t *const sc[NR], const __half *const dp[NR],
+                                              int nb, const int8_t *const xq[NR],
+                                              const float *const xd[NR], int lane, float total[NR]) {
   const int n = lane >> 4, qtb = (lane >> 3) & 1, l4 = lane & 7;
   const int vA = 128 * n + 32 * qtb + 4 * l4;
+  const int kA = vA >> 4;
+#pragma unroll
+  for (int r = 0; r < NR; r++) total[r] = 0.0f;
   for (int b = 0; b < nb; b++) {
-    uint32_t qlw = ((const uint32_t *)(ql + b * 128))[lane];
-    uint32_t qhw = ((const uint32_t *)(qh + b * 64))[n * 8 + l4];
-    uint32_t qa = (qlw & 0x0f0f0f0fu) | (((qhw >> (2 * qtb)) & 0x03030303u) << 4);
-    uint32_t qb = ((qlw >> 4) & 0x0f0f0f0fu) | (((qhw >> (2 * qtb + 4)) & 0x03030303u) << 4);
-    qa = __vsub4(qa, 0x20202020u);
-    qb = __vsub4(qb, 0x20202020u);
-    const int *xp = (const int *)(xq + b * 256);
-    int xa = xp[vA >> 2], xb = xp[(vA + 64) >> 2];
-    const int8_t *scb = (const int8_t *)(sc + b * 16);
-    int kA = vA >> 4;
-    int isum = (int)scb[kA] * __dp4a((int)qa, xa, 0) + (int)scb[kA + 4] * __dp4a((int)qb, xb, 0);
-    isum = __reduce_add_sync(PM_FULL, isum);
-    float d = __half2float(dp[b]);
-    total = __fadd_rn(total, __fmul_rn(xd[b], __fmul_rn(d, (float)isum)));
+    uint32_t qlw[NR], qhw[NR];
+    int xa[NR], xb[NR], sa[NR], sb[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+      qlw[r] = ((const uint32_t *)(ql[r] + b * 128))[lane];
+      qhw[r] = ((const uint32_t *)(qh[r] + b * 64))[n * 8 + l4];
+      const int *xp = (const int *)(xq[r] + b * 256);
+      xa[r] = xp[vA >> 2];
+      xb[r] = xp[(vA + 64) >> 2];
+      const int8_t *scb = (const int8_t *)(sc[r] + b * 16);
+      sa[r] = scb[kA];
+      sb[r] = scb[kA + 4];
+    }
+    int isum[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+      uint32_t qa = (qlw[r] & 0x0f0f0f0fu) | (((qhw[r] >> (2 * qtb)) & 0x03030303u) << 4);
+      uint32_t qb = ((qlw[r] >> 4) & 0x0f0f0f0fu) | (((qhw[r] >> (2 * qtb + 4)) & 0x03030303u) << 4);
+      qa = __vsub4(qa, 0x20202020u);
+      qb = __vsub4(qb, 0x20202020u);
+      isum[r] = sa[r] * __dp4a((int)qa, xa[r], 0) + sb[r] * __dp4a((int)qb, xb[r], 0);
+    }
+#pragma unroll
+    for (int r = 0; r < NR; r++) isum[r] = __reduce_add_sync(PM_FULL, isum[r]);
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+      float d = __half2float(dp[r][b]);
+      total[r] = __fadd_rn(total[r], __fmul_rn(xd[r][b], __fmul_rn(d, (float)isum[r])));
+    }
   }
-  return total;
+}
+
+// N epoch-tagged values p[i0 + j*stride], j < N: all loads in flight at once,
+// stragglers retried one by one (bounded). false = gave up.
+template <int N>
+__device__ __forceinline__ bool poll_pairs(const unsigned long long *p, int i0, int stride, int n,
+                                           uint32_t epoch, float v[N], int *err) {
+  unsigned long long u[N];
+#pragma unroll
+  for (int j = 0; j < N; j++)
+    if (i0 + j * stride < n) u[j] = ld_pair(p + i0 + j * stride);
+  bool ok = true;
+#pragma unroll
+  for (int j = 0; j < N; j++) {
+    v[j] = 0.0f;
+    if (i0 + j * stride < n) {
+      if ((uint32_t)(u[j] >> 32) == epoch) v[j] = __uint_as_float((uint32_t)u[j]);
+      else ok = wait_pair(p + i0 + j * stride, epoch, v[j], err) && ok;
+    }
+  }
+  return ok;
 }
 
 // ---- the kernel ------------------------------------------------------------
+#define MG_GH 2  // h rows (gate+up pairs) a warp works on at once
+#define MG_DR 4  // down rows a warp works on at once
+
 __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   const pm_layer_desc &D = P.D;
@@ -230,7 +376,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   const bool dq6 = D.type_down == PM_TYPE_Q6_K;
 
   uint8_t *gs = smem + P.off_gs, *us = smem + P.off_us, *dn = smem + P.off_dn;
-  __half *dsm = (__half *)(smem + P.off_dsm);
+  uint8_t *dsm = smem + P.off_dsm;
   float *xs = (float *)(smem + P.off_xs);
   int8_t *xq = (int8_t *)(smem + P.off_xq);
   float *xd = (float *)(smem + P.off_xd);
@@ -241,24 +387,79 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   float *rw = (float *)(smem + P.off_rw);
   float *eo = (float *)(smem + P.off_eo);
   float *lg = (float *)(smem + P.off_lg);
-  // misc: mbarriers, reduction scratch, ids/weights, route scratch
   uint64_t *bar_gu = (uint64_t *)(smem + P.off_misc);  // [MG_GU_CHUNKS]
   uint64_t *bar_dn = bar_gu + MG_GU_CHUNKS;            // [PM_MAX_TOPK]
   uint64_t *bar_rw = bar_dn + PM_MAX_TOPK;             // [1]
   float *red8 = (float *)(bar_rw + 1);                 // [8]
   uint32_t *ids = (uint32_t *)(red8 + 8);              // [PM_MAX_TOPK]
   float *wts = (float *)(ids + PM_MAX_TOPK);           // [PM_MAX_TOPK]
-  int *s_dead = (int *)(wts + PM_MAX_TOPK);            // [1]
-  float *r_sv = (float *)(s_dead + 4);                 // [E] route scratch
-  float *r_gs = r_sv + PM_MAX_EXPERTS;                 // [E/2]
+  int *s_dead = (int *)(wts + PM_MAX_TOPK);            // [4]
+  float *r_sv = (float *)(s_dead + 4);                 // route scratch
+  float *r_gs = r_sv + PM_MAX_EXPERTS;
   unsigned char *r_keep = (unsigned char *)(r_gs + PM_MAX_EXPERTS / 2);
 
-  // this CTA's slices
-  const long long HR = (long long)K * ff;  // h rows of the layer: R = k*ff + j
-  const int R0 = (int)(HR * cta / G), R1 = (int)(HR * (cta + 1) / G);
+  // this CTA's slices: h rows [R0, R1) of the layer's K*ff (R = k*ff + j), and
+  // output columns [C0, C1)
+  const int HR = K * ff;
+  const int R0 = (int)((long long)HR * cta / G), R1 = (int)((long long)HR * (cta + 1) / G);
   const int C0 = (int)((long long)d * cta / G), C1 = (int)((long long)d * (cta + 1) / G);
-  const int ncols = C1 - C0;
+  const int nrows = R1 - R0, ncols = C1 - C0;
+  const int per_w = (nrows + MG_WARPS - 1) / MG_WARPS;        // h rows per warp
+  const int wpc = MG_WARPS / MG_GU_CHUNKS;                     // warps per gate/up chunk
+  const int ndown = K * ncols;
+  const int per_d = (ndown + MG_WARPS - 1) / MG_WARPS;         // down rows per warp
   const bool has_logit = cta < E;  // E <= G (checked by the host)
+
+  // the copy job of this thread (fixed for the whole call; only the expert changes)
+  //   tid  0..15 : gate/up chunk ch, segment seg (a chunk spans at most 2 experts), gate|up
+  //   tid 32..   : down, expert slot k, plane p (Q6_K: ql, qh, scales, f16 d window)
+  int job_k = -1, job_off = 0, job_dst = 0, job_bytes = 0, job_bar = 0, job_plane = 0, job_tx = 0;
+  if (tid < MG_GU_CHUNKS * 4) {
+    int ch = tid >> 2, seg = (tid >> 1) & 1, isup = tid & 1;
+    // rows of chunk ch: with 8-block rows, chunks hold whole pairs of h rows
+    const int npairs_j = (nrows + 1) >> 1, ppc_j = (npairs_j + MG_GU_CHUNKS - 1) / MG_GU_CHUNKS;
+    int ra = nbx == 8 ? min(R1, R0 + 2 * ch * ppc_j) : min(R1, R0 + ch * wpc * per_w);
+    int rb = nbx == 8 ? min(R1, R0 + 2 * (ch + 1) * ppc_j) : min(R1, R0 + (ch + 1) * wpc * per_w);
+    int ka = ra / ff;
+    int split = min(rb, (ka + 1) * ff);
+    int s0 = seg == 0 ? ra : split, s1 = seg == 0 ? split : rb;
+    job_bar = ch;
+    job_plane = isup;
+    if (seg == 0 && isup == 0) job_tx = (rb - ra) * 2 * RBG + 1;  // +1: "this thread arms the barrier"
+    if (s1 > s0) {
+      job_k = s0 / ff;
+      job_off = (s0 - job_k * ff) * RBG;
+      job_dst = (s0 - R0) * RBG;
+      job_bytes = (s1 - s0) * RBG;
+    }
+  } else if (tid >= 32 && tid < 32 + K * 4) {
+    int k = (tid - 32) >> 2, p = (tid - 32) & 3;
+    job_bar = MG_GU_CHUNKS + k;
+    job_plane = 2 + p;
+    int dwin0 = (C0 * nbh * 2) & ~15, dwin1 = ((C0 + ncols) * nbh * 2 + 15) & ~15;
+    if (dq6) {
+      const int fb[4] = {128, 64, 16, 0}, po[4] = {0, 128, 192, 0};
+      if (p == 0) job_tx = ncols * nbh * 208 + (dwin1 - dwin0) + 1;
+      if (p < 3) {
+        job_k = k;
+        job_off = C0 * nbh * fb[p];
+        job_dst = k * (int)P.dn_k_bytes + P.cols_max * nbh * po[p];
+        job_bytes = ncols * nbh * fb[p];
+      } else {
+        job_k = k;
+        job_off = dwin0;
+        job_dst = k * (int)P.dsm_k_bytes;
+        job_bytes = dwin1 - dwin0;
+      }
+    } else if (p == 0) {
+      job_tx = ncols * nbh * 144 + 1;
+      job_k = k;
+      job_off = C0 * nbh * 144;
+      job_dst = k * (int)P.dn_k_bytes;
+      job_bytes = ncols * nbh * 144;
+    }
+  }
+  const int dsm_skew = ((C0 * nbh * 2) & 15) / 2;  // halfs to skip inside the 16-byte aligned window
 
   if (tid == 0) {
     for (int i = 0; i < MG_GU_CHUNKS; i++) mbar_init(&bar_gu[i], 1);
@@ -268,28 +469,54 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // router row of layer 0
-  if (has_logit && tid == 0) {
+  if (has_logit && tid == 0) {  // router row of layer 0
     mbar_expect_tx(bar_rw, (uint32_t)d * 4);
     bulk_g2s(rw, P.layers[0].router + (size_t)cta * d, (uint32_t)d * 4, bar_rw);
   }
 
+  // layer descriptors are staged in shared memory one layer ahead (their fields
+  // would otherwise be L2-latency loads on the critical path)
+  MegaLayer *mls = (MegaLayer *)(smem + P.off_ml);
+  if (tid < (int)(sizeof(MegaLayer) / 8)) ((unsigned long long *)&mls[0])[tid] = ((const unsigned long long *)&P.layers[0])[tid];
+
+  long long *trace = nullptr;
+  if (P.trace && tid == 0 && (cta == 0 || cta == G - 1))
+    trace = P.trace + (cta == 0 ? 0 : (size_t)P.n_layers * MG_TRACE_PH);
+#define MG_TRACE(ph) do { if (trace) trace[(size_t)l * MG_TRACE_PH + (ph)] = clock64(); } while (0)
+  long long *trace_r = nullptr;  // the routing warp's own stamps
+  if (P.trace && tid == MG_NT - 32 && (cta == 0 || cta == G - 1))
+    trace_r = P.trace + (cta == 0 ? 0 : (size_t)P.n_layers * MG_TRACE_PH);
+#define MG_TRACE_R(ph) do { if (trace_r) trace_r[(size_t)l * MG_TRACE_PH + (ph)] = clock64(); } while (0)
+
   bool dead = false;
   bool copies_pending = false;
+  const bool fold = D.weight_fold == PM_FOLD_BEFORE_DOWN;
   int l = 0;
   for (; l < P.n_layers; l++) {
-    const MegaLayer &ML = P.layers[l];
+    const MegaLayer &ML = mls[l & 1];
     const uint32_t par = l & 1;
     const uint32_t ep = P.epoch_base + (uint32_t)l;  // tag of this layer's x and logits
+    MG_TRACE(0);
+    if (l + 1 < P.n_layers && tid >= 64 && tid < 64 + (int)(sizeof(MegaLayer) / 8))
+      ((unsigned long long *)&mls[(l + 1) & 1])[tid - 64] = ((const unsigned long long *)&P.layers[l + 1])[tid - 64];
 
     // ---- 1. the residual stream ----
-    for (int i = tid; i < d; i += MG_NT) {
-      float v = 0.0f;
-      if (l == 0) v = P.x_in[i];
-      else if (!wait_pair(P.xbuf + i, ep, v, P.err)) dead = true;
-      xs[i] = v;
+    {
+      float v[4];
+      for (int i0 = tid; i0 < d; i0 += 4 * MG_NT) {
+        if (l == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) v[j] = i0 + j * MG_NT < d ? P.x_in[i0 + j * MG_NT] : 0.0f;
+        } else if (!poll_pairs<4>(P.xbuf, i0, MG_NT, d, ep, v, P.err)) {
+          dead = true;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (i0 + j * MG_NT < d) xs[i0 + j * MG_NT] = v[j];
+      }
     }
     if (__syncthreads_or(dead)) { dead = true; break; }
+    MG_TRACE(1);
 
     // ---- 2. norm, Q8x of the normed token ----
     float inv = pm_rms_inv(xs, d, P.eps, red8);
@@ -297,12 +524,14 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       float v[8];
 #pragma unroll
       for (int j = 0; j < 8; j++) v[j] = __fmul_rn(xs[warp * 256 + 32 * j + lane], inv);
-      q8x_block_warp(v, lane, xq + warp * 256, xd + warp, xbs + warp * 8);
+      q8x_block_warp(v, lane, xq + warp * 256, xd + warp, xbs + warp * 8, nbx == 8 ? warp : 0);
     } else if (warp == MG_WARPS - 1) {
       // ---- 3. this CTA's router logit, then all logits, then the top-k ----
+      MG_TRACE_R(12);
       if (has_logit) {
         if (!mbar_wait(bar_rw, par, P.err)) dead = true;
         float acc = 0.0f;
+#pragma unroll 16
         for (int c = lane; c < d; c += 32) acc = __fmaf_rn(rw[c], __fmul_rn(xs[c], inv), acc);
         float s = pm_warp_sum_dot(acc);
         if (lane == 0) {
@@ -315,81 +544,109 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           bulk_g2s(rw, P.layers[l + 1].router + (size_t)cta * d, (uint32_t)d * 4, bar_rw);
         }
       }
-      for (int e = lane; e < E; e += 32) {
-        float v = 0.0f;
-        if (!wait_pair(P.lbuf + e, ep, v, P.err)) dead = true;
-        lg[e] = v;
+      MG_TRACE_R(13);
+      for (int e0 = lane; e0 < E; e0 += 4 * 32) {
+        float v[4];
+        if (!poll_pairs<4>(P.lbuf, e0, 32, E, ep, v, P.err)) dead = true;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (e0 + 32 * j < E) lg[e0 + 32 * j] = v[j];
       }
       __syncwarp();
+      MG_TRACE_R(14);
       pm_route_warp(D, lg, ML.select_bias, lane, r_sv, r_gs, r_keep, ids, wts);
-      __syncwarp();  // ids[] written by lane 0
+      __syncwarp();  // ids[] and wts[] written by lanes < K
+      MG_TRACE_R(15);
       if (cta == 0 && lane < K && ML.usage) atomicAdd(&ML.usage[ids[lane]], 1u);
     }
     if (__syncthreads_or(dead)) { dead = true; break; }
+    MG_TRACE(2);
 
     // ---- 4. bulk copies of this CTA's slices ----
-    // gate/up: chunk ch covers rows [ra, rb); a chunk spans at most two experts
-    if (tid < MG_GU_CHUNKS * 4) {
-      int ch = tid >> 2, seg = (tid >> 1) & 1, isup = tid & 1;
-      int ra = R0 + (int)((long long)(R1 - R0) * ch / MG_GU_CHUNKS);
-      int rb = R0 + (int)((long long)(R1 - R0) * (ch + 1) / MG_GU_CHUNKS);
-      int ka = ra / ff;
-      int split = min(rb, (ka + 1) * ff);  // rows [ra, split) expert slot ka, [split, rb) slot ka+1
-      int s0 = seg == 0 ? ra : split, s1 = seg == 0 ? split : rb;
-      if (seg == 0 && isup == 0) mbar_expect_tx(&bar_gu[ch], (uint32_t)(rb - ra) * 2u * (uint32_t)RBG);
-      if (s1 > s0) {
-        int k = s0 / ff, j0 = s0 - k * ff;
-        int el = (int)ids[k];
-        const uint8_t *src = (isup ? ML.up + (size_t)el * ML.up_stride : ML.gate + (size_t)el * ML.gate_stride) +
-                             (size_t)j0 * RBG;
-        uint8_t *dst = (isup ? us : gs) + (size_t)(s0 - R0) * RBG;
-        bulk_g2s(dst, src, (uint32_t)(s1 - s0) * (uint32_t)RBG, &bar_gu[ch]);
+    if (job_tx) mbar_expect_tx(&bar_gu[job_bar], (uint32_t)(job_tx - 1));  // bar_dn follows bar_gu in memory
+    if (job_bytes > 0) {
+      int el = (int)ids[job_k];
+      const uint8_t *src;
+      uint8_t *dst;
+      if (job_plane == 0) { src = ML.gate + (size_t)el * ML.gate_stride; dst = gs; }
+      else if (job_plane == 1) { src = ML.up + (size_t)el * ML.up_stride; dst = us; }
+      else {
+        int p = job_plane - 2;
+        src = ML.down[p] + (size_t)el * ML.down_stride[p];
+        dst = p == 3 ? dsm : dn;
       }
-    } else if (tid >= 32 && tid < 32 + K * 4) {
-      // down: expert slot k, plane p; columns [C0, C1)
-      int k = (tid - 32) >> 2, p = (tid - 32) & 3;
-      int el = (int)ids[k];
-      const uint32_t fb6[4] = {128, 64, 16, 0}, fb4[4] = {144, 0, 0, 0};
-      uint32_t fb = dq6 ? fb6[p] : fb4[p];
-      uint32_t tot = dq6 ? 208u : 144u;
-      if (p == 0) mbar_expect_tx(&bar_dn[k], (uint32_t)ncols * (uint32_t)nbh * tot);
-      if (fb && ncols > 0) {
-        uint32_t poff = dq6 ? (p == 0 ? 0u : p == 1 ? 128u : 192u) : 0u;  // plane offset per block unit
-        const uint8_t *src = ML.down[p] + (size_t)el * ML.down_stride[p] + (size_t)C0 * nbh * fb;
-        uint8_t *dst = dn + (size_t)k * P.dn_k_bytes + (size_t)P.cols_max * nbh * poff;
-        bulk_g2s(dst, src, (uint32_t)ncols * (uint32_t)nbh * fb, &bar_dn[k]);
-      }
+      bulk_g2s(dst + job_dst, src + job_off, (uint32_t)job_bytes, &bar_gu[job_bar]);
     }
     copies_pending = true;
-    if (dq6) {  // the f16 block scales (2 B each) by plain loads
-      int n = K * ncols * nbh;
-      for (int i = tid; i < n; i += MG_NT) {
-        int k = i / (ncols * nbh), r = i - k * (ncols * nbh);
-        int el = (int)ids[k];
-        dsm[k * P.cols_max * nbh + r] =
-            *(const __half *)(ML.down[3] + (size_t)el * ML.down_stride[3] + ((size_t)C0 * nbh + r) * 2);
-      }
-    }
+    MG_TRACE(3);
 
     // ---- 5. gate/up rows -> h ----
-    const bool fold = D.weight_fold == PM_FOLD_BEFORE_DOWN;
-    for (int r = R0 + warp; r < R1; r += MG_WARPS) {
-      int rel = r - R0;
-      // chunk of this row: the largest ch with start <= r
-      int ch = (int)(((long long)(rel + 1) * MG_GU_CHUNKS - 1) / (R1 - R0));
-      while (ch > 0 && R0 + (int)((long long)(R1 - R0) * ch / MG_GU_CHUNKS) > r) ch--;
-      while (ch + 1 < MG_GU_CHUNKS && R0 + (int)((long long)(R1 - R0) * (ch + 1) / MG_GU_CHUNKS) <= r) ch++;
-      if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[ch], par, P.err))) { dead = true; break; }
-      int k = r / ff;
-      float gv = row_q4k_smem(gs + (size_t)rel * RBG, nbx, xq, xd, xbs, lane);
-      float uv = row_q4k_smem(us + (size_t)rel * RBG, nbx, xq, xd, xbs, lane);
-      if (lane == 0) {
-        float hv = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, wts[k], fold);
-        __stcg(P.hbuf + r, hv);
+    if (nbx == 8) {
+      // pairs of h rows: lanes 0-7 gate(h0), 8-15 up(h0), 16-23 gate(h1), 24-31 up(h1)
+      XBlk X;
+      {
+        const int4 *xp = (const int4 *)(xq + 256 * (lane & 7));
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          int4 t = xp[j ^ (lane & 7)];  // chunks are stored swizzled by the block index
+          X.x[4 * j] = t.x; X.x[4 * j + 1] = t.y; X.x[4 * j + 2] = t.z; X.x[4 * j + 3] = t.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) X.bs[j] = xbs[8 * (lane & 7) + j];
+        X.d = xd[lane & 7];
+      }
+      const int npairs = (nrows + 1) >> 1;
+      const int ppc = (npairs + MG_GU_CHUNKS - 1) / MG_GU_CHUNKS;  // pairs per copy chunk
+      for (int p = warp; p < npairs; p += MG_WARPS) {
+        if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[p / ppc], par, P.err))) { dead = true; break; }
+        if (p == warp) MG_TRACE(8);
+        int rel = 2 * p + ((lane >> 4) & 1);
+        rel = min(rel, nrows - 1);
+        const uint8_t *rowp = ((lane >> 3) & 1 ? us : gs) + (size_t)rel * RBG;
+        float tot = row4_q4k_blk(rowp, X, lane);
+        float gv = __shfl_sync(PM_FULL, tot, (lane & 1) * 16);
+        float uv = __shfl_sync(PM_FULL, tot, (lane & 1) * 16 + 8);
+        int r = R0 + 2 * p + lane;
+        if (lane < 2 && r < R1) {
+          float hv = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, wts[r / ff], fold);
+          __stcg(P.hbuf + r, hv);
+        }
+      }
+    } else {
+      int ra = R0 + warp * per_w, rb = min(R1, ra + per_w);
+      if (ra < rb) {
+        if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[warp / wpc], par, P.err))) dead = true;
+      }
+      MG_TRACE(8);
+      for (int r0 = ra; r0 < rb && !dead; r0 += MG_GH) {
+        const uint8_t *rowp[2 * MG_GH];
+        const int8_t *xqp[2 * MG_GH];
+        const float *xdp[2 * MG_GH];
+        const int32_t *xbp[2 * MG_GH];
+#pragma unroll
+        for (int i = 0; i < MG_GH; i++) {
+          int rel = min(r0 + i, rb - 1) - R0;
+          rowp[2 * i] = gs + (size_t)rel * RBG;
+          rowp[2 * i + 1] = us + (size_t)rel * RBG;
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * MG_GH; i++) { xqp[i] = xq; xdp[i] = xd; xbp[i] = xbs; }
+        float tot[2 * MG_GH];
+        rows_q4k_smem<2 * MG_GH>(rowp, nbx, xqp, xdp, xbp, lane, tot);
+#pragma unroll
+        for (int i = 0; i < MG_GH; i++) {
+          int r = r0 + i;
+          if (lane == i && r < rb) {
+            float hv = pm_act(D.act, D.act_limit, D.act_alpha, tot[2 * i], tot[2 * i + 1], wts[r / ff], fold);
+            __stcg(P.hbuf + r, hv);
+          }
+        }
       }
     }
+    MG_TRACE(11);
     if (__syncthreads_or(dead)) { dead = true; break; }
     if (tid == 0) red_release_add_u64(P.hcount, 1ull);
+    MG_TRACE(4);
 
     // ---- 6. all of h, re-quantised ----
     if (tid == 0) {
@@ -403,32 +660,73 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       if (!ok) { atomicCAS(P.err, 0, 3); dead = true; }
     }
     if (__syncthreads_or(dead)) { dead = true; break; }
-    for (int b = warp; b < K * nbh; b += MG_WARPS) {
-      float v[8];
+    MG_TRACE(5);
+    for (int b0 = warp; b0 < K * nbh; b0 += 2 * MG_WARPS) {
+      int b1 = b0 + MG_WARPS;
+      float v0[8], v1[8];
 #pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = __ldcg(P.hbuf + b * 256 + 32 * j + lane);
-      q8x_block_warp(v, lane, hq + b * 256, hd + b, hbs + b * 8);
+      for (int j = 0; j < 8; j++) v0[j] = __ldcg(P.hbuf + b0 * 256 + 32 * j + lane);
+      if (b1 < K * nbh) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) v1[j] = __ldcg(P.hbuf + b1 * 256 + 32 * j + lane);
+      }
+      q8x_block_warp(v0, lane, hq + b0 * 256, hd + b0, hbs + b0 * 8);
+      if (b1 < K * nbh) q8x_block_warp(v1, lane, hq + b1 * 256, hd + b1, hbs + b1 * 8);
     }
     __syncthreads();
+    MG_TRACE(6);
 
     // ---- 7. down rows of this CTA's columns, all k; sum in k order; publish ----
-    for (int i = warp; i < K * ncols; i += MG_WARPS) {
-      int k = i / ncols, ci = i - k * ncols;
-      if (!__all_sync(PM_FULL, mbar_wait(&bar_dn[k], par, P.err))) { dead = true; break; }
-      const uint8_t *base = dn + (size_t)k * P.dn_k_bytes;
-      float o;
-      if (dq6) {
-        size_t cm = (size_t)P.cols_max * nbh;
-        o = row_q6k_smem(base + (size_t)ci * nbh * 128, base + cm * 128 + (size_t)ci * nbh * 64,
-                         base + cm * 192 + (size_t)ci * nbh * 16, dsm + k * P.cols_max * nbh + ci * nbh,
-                         nbh, hq + k * ff, hd + k * nbh, lane);
-      } else {
-        o = row_q4k_smem(base + (size_t)ci * nbh * 144, nbh, hq + k * ff, hd + k * nbh, hbs + k * nbh * 8,
-                         lane);
+    {
+      int ia = warp * per_d, ib = min(ndown, ia + per_d);
+      for (int i0 = ia; i0 < ib && !dead; i0 += MG_DR) {
+        int kk[MG_DR], cc[MG_DR];
+#pragma unroll
+        for (int r = 0; r < MG_DR; r++) {
+          int i = min(i0 + r, ib - 1);
+          kk[r] = i / ncols;
+          cc[r] = i - kk[r] * ncols;
+          if (!__all_sync(PM_FULL, mbar_wait(&bar_dn[kk[r]], par, P.err))) dead = true;
+        }
+        if (dead) break;
+        if (i0 == ia) MG_TRACE(9);
+        const int8_t *xqp[MG_DR];
+        const float *xdp[MG_DR];
+        float tot[MG_DR];
+        if (dq6) {
+          const uint8_t *ql[MG_DR], *qh[MG_DR], *sc[MG_DR];
+          const __half *dp[MG_DR];
+          size_t cm = (size_t)P.cols_max * nbh;
+#pragma unroll
+          for (int r = 0; r < MG_DR; r++) {
+            const uint8_t *base = dn + (size_t)kk[r] * P.dn_k_bytes;
+            ql[r] = base + (size_t)cc[r] * nbh * 128;
+            qh[r] = base + cm * 128 + (size_t)cc[r] * nbh * 64;
+            sc[r] = base + cm * 192 + (size_t)cc[r] * nbh * 16;
+            dp[r] = (const __half *)(dsm + (size_t)kk[r] * P.dsm_k_bytes) + dsm_skew + cc[r] * nbh;
+            xqp[r] = hq + kk[r] * ff;
+            xdp[r] = hd + kk[r] * nbh;
+          }
+          rows_q6k_smem<MG_DR>(ql, qh, sc, dp, nbh, xqp, xdp, lane, tot);
+        } else {
+          const uint8_t *rowp[MG_DR];
+          const int32_t *xbp[MG_DR];
+#pragma unroll
+          for (int r = 0; r < MG_DR; r++) {
+            rowp[r] = dn + (size_t)kk[r] * P.dn_k_bytes + (size_t)cc[r] * nbh * 144;
+            xqp[r] = hq + kk[r] * ff;
+            xdp[r] = hd + kk[r] * nbh;
+            xbp[r] = hbs + kk[r] * nbh * 8;
+          }
+          rows_q4k_smem<MG_DR>(rowp, nbh, xqp, xdp, xbp, lane, tot);
+        }
+#pragma unroll
+        for (int r = 0; r < MG_DR; r++)
+          if (lane == r && i0 + r < ib) eo[kk[r] * P.cols_max + cc[r]] = tot[r];
       }
-      if (lane == 0) eo[k * P.cols_max + ci] = o;
     }
-    copies_pending = false;  // every gate/up chunk and every down barrier was waited on
+    MG_TRACE(10);
+    copies_pending = false;  // every chunk barrier of this layer was waited on by some warp
     if (__syncthreads_or(dead)) { dead = true; copies_pending = true; break; }
     if (tid < ncols) {
       float s = 0.0f;
@@ -441,21 +739,22 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       if (l + 1 < P.n_layers) st_pair(P.xbuf + C0 + tid, xn, ep + 1);
       else P.x_out[C0 + tid] = xn;
     }
+    MG_TRACE(7);
     __syncthreads();  // eo, xs, ids are rewritten by the next layer
   }
 
   if (dead) {
     // give this CTA's own copies a bounded time to land before its shared memory goes away
     __syncthreads();
-    if (tid == 0 && copies_pending) {
+    if (tid == 0) {
       uint32_t par = l & 1;
-      for (int i = 0; i < MG_GU_CHUNKS; i++)
-        for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(&bar_gu[i], par); it++) {}
-      for (int i = 0; i < K; i++)
-        for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(&bar_dn[i], par); it++) {}
+      if (copies_pending) {
+        for (int i = 0; i < MG_GU_CHUNKS + K; i++)
+          for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(&bar_gu[i == 0 ? 0 : i], par); it++) {}
+      }
+      if (has_logit)
+        for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(bar_rw, par); it++) {}
     }
-    if (tid == 0 && has_logit)
-      for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(bar_rw, l & 1); it++) {}
     __syncthreads();
   }
 }
@@ -490,7 +789,8 @@ bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp
   uint32_t per_blk = D.type_down == PM_TYPE_Q6_K ? 208u : 144u;
   P.dn_k_bytes = up16((uint32_t)cols_max * nbh * per_blk);
   P.off_dn = take(P.dn_k_bytes * K);
-  P.off_dsm = take((uint32_t)K * cols_max * nbh * 2);
+  P.dsm_k_bytes = up16((uint32_t)cols_max * nbh * 2 + 32);
+  P.off_dsm = take(P.dsm_k_bytes * K);
   P.off_xs = take((uint32_t)d * 4);
   P.off_xq = take((uint32_t)d);
   P.off_xd = take((uint32_t)nbx * 4);
@@ -501,6 +801,7 @@ bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp
   P.off_rw = take((uint32_t)d * 4);
   P.off_eo = take((uint32_t)K * cols_max * 4);
   P.off_lg = take((uint32_t)D.n_exp * 4);
+  P.off_ml = take(2 * (uint32_t)sizeof(MegaLayer));
   P.off_misc = take(8 * (MG_GU_CHUNKS + PM_MAX_TOPK + 1) + 8 * 4 + PM_MAX_TOPK * 8 + 16 +
                     PM_MAX_EXPERTS * 4 + PM_MAX_EXPERTS * 2 + PM_MAX_EXPERTS / 2 + 64);
   mp.smem = off;

@@ -6,6 +6,7 @@
 #define MG_NT 512
 #define MG_WARPS (MG_NT / 32)
 #define MG_GU_CHUNKS 4
+#define MG_TRACE_PH 16  // trace points per layer
 
 struct MegaLayer {
   const float *router, *logit_bias, *select_bias;
@@ -30,10 +31,11 @@ struct MegaParams {
   unsigned long long hcount_base;
   uint32_t epoch_base;
   int *err;
+  long long *trace;  // optional [2][n_layers][MG_TRACE_PH] SM clocks (CTA 0 and the last CTA)
   // shared-memory layout (bytes from the dynamic base)
   int rows_max, cols_max;
   uint32_t off_gs, off_us, off_dn, off_dsm, off_xs, off_xq, off_xd, off_xbs, off_hq, off_hd,
-      off_hbs, off_rw, off_eo, off_lg, off_misc, dn_k_bytes;
+      off_hbs, off_rw, off_eo, off_lg, off_misc, off_ml, dn_k_bytes, dsm_k_bytes;
 };
 
 struct MegaPlan {

@@ -6,55 +6,65 @@
 
 #include "common.cuh"
 
-#define NPER (PM_MAX_EXPERTS / 32)
+// float -> unsigned key with the same order (finite values; -0 is folded onto
+// +0 first so that equal floats get equal keys). Maxima over keys are maxima
+// over the floats, bit for bit.
+__device__ __forceinline__ uint32_t pm_fkey(float v) {
+  uint32_t u = __float_as_uint(__fadd_rn(v, 0.0f));
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float pm_funkey(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
 
-// lane L holds experts L, L+32, ...; `lg` points at the token's E logits (any
-// address space); ssv[E], gsc[E/2], keep[E/2] are per-warp scratch in shared
-// memory (used for group-limited selection only). Lane 0 writes ids_out[K],
-// w_out[K].
-__device__ __forceinline__ void pm_route_warp(const pm_layer_desc &D, const float *lg,
-                                              const float *__restrict__ sel_bias, int lane,
-                                              float *ssv, float *gsc, unsigned char *keep,
-                                              uint32_t *ids_out, float *w_out) {
+// lane L holds experts L, L+32, ... (NP per lane, NP*32 >= E); `lg` points at the
+// token's E logits (any address space); ssv[E], gsc[E/2], keep[E/2] are per-warp
+// scratch in shared memory (used for group-limited selection only). Lane k < K
+// writes ids_out[k], w_out[k].
+template <int NP>
+__device__ __forceinline__ void pm_route_warp_n(const pm_layer_desc &D, const float *lg,
+                                                const float *__restrict__ sel_bias, int lane,
+                                                float *ssv, float *gsc, unsigned char *keep,
+                                                uint32_t *ids_out, float *w_out) {
   const int E = D.n_exp, K = D.top_k;
-  float pr[NPER], sv[NPER];
-  float mx = PM_NEG;
+  float pr[NP], sv[NP];
 #pragma unroll
-  for (int i = 0; i < NPER; i++) {
+  for (int i = 0; i < NP; i++) {
     int e = lane + 32 * i;
-    float v = e < E ? lg[e] : PM_NEG;
-    pr[i] = v;
-    mx = fmaxf(mx, v);
+    pr[i] = e < E ? lg[e] : PM_NEG;
   }
-  if (D.gating == PM_GATE_SOFTMAX_ALL) {
-    mx = pm_warp_max(mx);
+  if (D.gating == PM_GATE_SOFTMAX_ALL) {  // src/moe_kernels.rs:1023-1042
+    float mx = PM_NEG;
+#pragma unroll
+    for (int i = 0; i < NP; i++) mx = fmaxf(mx, pr[i]);
+    mx = pm_funkey(__reduce_max_sync(PM_FULL, pm_fkey(mx)));
     float sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < NPER; i++) {
-      int e = lane + 32 * i;
-      if (e < E) {
+    for (int i = 0; i < NP; i++) {
+      if (lane + 32 * i < E) {
         pr[i] = pm_exp(__fsub_rn(pr[i], mx));
         sum = __fadd_rn(sum, pr[i]);
       }
     }
     sum = pm_warp_sum_16_1(sum);
 #pragma unroll
-    for (int i = 0; i < NPER; i++) pr[i] = __fdiv_rn(pr[i], sum);
-  } else if (D.gating == PM_GATE_SIGMOID) {
+    for (int i = 0; i < NP; i++) pr[i] = __fdiv_rn(pr[i], sum);
+  } else if (D.gating == PM_GATE_SIGMOID) {  // src/moe_kernels.rs:1034
 #pragma unroll
-    for (int i = 0; i < NPER; i++)
+    for (int i = 0; i < NP; i++)
       if (lane + 32 * i < E) pr[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, pm_exp(-pr[i])));
-  } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {
+  } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {  // src/ds4.rs:1377-1379
 #pragma unroll
-    for (int i = 0; i < NPER; i++)
+    for (int i = 0; i < NP; i++)
       if (lane + 32 * i < E) {
         float v = pr[i];
         float sp = v > 20.0f ? v : pm_log1p(pm_exp(v));
         pr[i] = __fsqrt_rn(sp);
       }
   }
+  // what the selection ranks: score (+ bias) (src/moe_kernels.rs:1044-1049)
 #pragma unroll
-  for (int i = 0; i < NPER; i++) {
+  for (int i = 0; i < NP; i++) {
     int e = lane + 32 * i;
     sv[i] = e < E ? (sel_bias ? __fadd_rn(pr[i], sel_bias[e]) : pr[i]) : PM_NEG;
   }
@@ -63,7 +73,7 @@ __device__ __forceinline__ void pm_route_warp(const pm_layer_desc &D, const floa
   // lower group index)
   if (D.n_group > 0) {
 #pragma unroll
-    for (int i = 0; i < NPER; i++)
+    for (int i = 0; i < NP; i++)
       if (lane + 32 * i < E) ssv[lane + 32 * i] = sv[i];
     __syncwarp();
     const int G = D.n_group, gs = E / G;
@@ -93,66 +103,74 @@ __device__ __forceinline__ void pm_route_warp(const pm_layer_desc &D, const floa
     }
     __syncwarp();
 #pragma unroll
-    for (int i = 0; i < NPER; i++) {
+    for (int i = 0; i < NP; i++) {
       int e = lane + 32 * i;
       if (e < E && !keep[e / gs]) sv[i] = PM_NEG;
     }
   }
-  // K rounds of (max, lowest index)
-  float tw[PM_MAX_TOPK];
-  uint32_t te[PM_MAX_TOPK];
-  float wsum = 0.0f;
+  // K rounds of (max, lowest index) (src/moe_kernels.rs:1053-1067), on ordered
+  // integer keys: one warp-wide max, then the first slot/lane that holds it
+  uint32_t key[NP];
+  const uint32_t KNEG = pm_fkey(PM_NEG);
+#pragma unroll
+  for (int i = 0; i < NP; i++) key[i] = pm_fkey(sv[i]);
+  float wsum = 0.0f, w0 = 0.0f, evsum = 0.0f;
+  uint32_t my_e = 0;
+  float my_w = 0.0f, my_ev = 0.0f;
 #pragma unroll 1
   for (int k = 0; k < K; k++) {
-    float bv = PM_NEG;
-    uint32_t bi = 0xffffffffu;
+    uint32_t lk = key[0];
 #pragma unroll
-    for (int i = 0; i < NPER; i++) {
-      int e = lane + 32 * i;
-      if (e < E && (bi == 0xffffffffu || sv[i] > bv)) { bv = sv[i]; bi = (uint32_t)e; }
+    for (int i = 1; i < NP; i++) lk = max(lk, key[i]);
+    uint32_t m = __reduce_max_sync(PM_FULL, lk);
+    uint32_t e = 0;
+    float w = 0.0f;
+    bool found = false;
+#pragma unroll
+    for (int i = 0; i < NP; i++) {
+      uint32_t b = __ballot_sync(PM_FULL, key[i] == m);
+      if (!found && b != 0) {  // uniform across the warp
+        found = true;
+        int lw = __ffs((int)b) - 1;
+        e = (uint32_t)(32 * i + lw);
+        w = __shfl_sync(PM_FULL, pr[i], lw);
+        if (lane == lw) key[i] = KNEG;
+      }
     }
-    float m = pm_warp_max(bi == 0xffffffffu ? PM_NEG : bv);
-    uint32_t e = pm_warp_min_u32((bi != 0xffffffffu && bv == m) ? bi : 0xffffffffu);
-    float mine = 0.0f;
-#pragma unroll
-    for (int i = 0; i < NPER; i++)
-      if ((uint32_t)(lane + 32 * i) == e) { mine = pr[i]; sv[i] = PM_NEG; }
-    // only the owning lane has a non-zero `mine`; a shuffle fetches it exactly
-    float w = __shfl_sync(PM_FULL, mine, e & 31);
-    te[k] = e;
-    tw[k] = w;
     wsum = __fadd_rn(wsum, w);
-  }
-  if (lane == 0) {
+    float ev = 0.0f;
     if (D.gating == PM_GATE_SOFTMAX_SELECTED) {  // src/oss_kernels.rs:31-32
-      float ev[PM_MAX_TOPK];
-      float sum = 0.0f;
-      for (int k = 0; k < K; k++) {
-        ev[k] = pm_exp(__fsub_rn(tw[k], tw[0]));
-        sum = __fadd_rn(sum, ev[k]);
-      }
-      for (int k = 0; k < K; k++) {
-        float x = __fdiv_rn(ev[k], sum);
-        if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
-        tw[k] = x;
-      }
-    } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {  // src/ds4.rs:1416-1424
-      for (int k = 0; k < K; k++) {
-        float x = __fdiv_rn(tw[k], wsum);
-        if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
-        tw[k] = x;
-      }
-    } else {  // src/moe_kernels.rs:1072-1074
-      for (int k = 0; k < K; k++) {
-        float x = tw[k];
-        if (D.norm_w) x = __fdiv_rn(x, fmaxf(wsum, 6.103515625e-5f));
-        if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
-        tw[k] = x;
-      }
+      if (k == 0) w0 = w;
+      ev = pm_exp(__fsub_rn(w, w0));
+      evsum = __fadd_rn(evsum, ev);
     }
-    for (int k = 0; k < K; k++) {
-      ids_out[k] = te[k];
-      w_out[k] = tw[k];
+    if (lane == k) {
+      my_e = e;
+      my_w = w;
+      my_ev = ev;
     }
   }
+  if (lane < K) {
+    float x;
+    if (D.gating == PM_GATE_SOFTMAX_SELECTED) {
+      x = __fdiv_rn(my_ev, evsum);
+    } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {  // src/ds4.rs:1416-1424
+      x = __fdiv_rn(my_w, wsum);
+    } else {  // src/moe_kernels.rs:1072-1074
+      x = my_w;
+      if (D.norm_w) x = __fdiv_rn(x, fmaxf(wsum, 6.103515625e-5f));
+    }
+    if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
+    ids_out[lane] = my_e;
+    w_out[lane] = x;
+  }
+}
+
+__device__ __forceinline__ void pm_route_warp(const pm_layer_desc &D, const float *lg,
+                                              const float *__restrict__ sel_bias, int lane,
+                                              float *ssv, float *gsc, unsigned char *keep,
+                                              uint32_t *ids_out, float *w_out) {
+  if (D.n_exp <= 128) pm_route_warp_n<4>(D, lg, sel_bias, lane, ssv, gsc, keep, ids_out, w_out);
+  else if (D.n_exp <= 256) pm_route_warp_n<8>(D, lg, sel_bias, lane, ssv, gsc, keep, ids_out, w_out);
+  else pm_route_warp_n<16>(D, lg, sel_bias, lane, ssv, gsc, keep, ids_out, w_out);
 }
