@@ -36,7 +36,7 @@ ROUTE_CASES = {
     "sqrt-softplus": synth.C4_DSV3.scaled(gating=synth.GATE_SQRT_SOFTPLUS, n_group=0, topk_group=0, w_scale=1.5,
                                           shared=0),
     "q4x-16-of-512": synth.C2_QWEN3.scaled(gating=synth.GATE_SOFTMAX_SELECTED, n_exp=512, top_k=16, d=1024),
-    "ragged-experts": synth.C2_QWEN3.scaled(n_exp=77, top_k=5, d=96),
+    "ragged-experts": synth.C2_QWEN3.scaled(n_exp=77, top_k=5, d=256),
 }
 
 
@@ -58,7 +58,7 @@ def test_route_bit_exact(ctx, oracle, name):
 
 def test_ties_go_to_the_lower_index(ctx, oracle):
     for gating in (synth.GATE_SOFTMAX_ALL, synth.GATE_SIGMOID, synth.GATE_SOFTMAX_SELECTED):
-        cfg = synth.C2_QWEN3.scaled(n_exp=100, top_k=8, d=64, gating=gating)
+        cfg = synth.C2_QWEN3.scaled(n_exp=100, top_k=8, d=256, gating=gating)
         ol, gl = layers(oracle, ctx, cfg, 1)
         lg = np.zeros((3, 100), np.float32)
         lg[1, [99, 64, 33, 32, 2]] = 2.0
@@ -72,10 +72,10 @@ def test_ties_go_to_the_lower_index(ctx, oracle):
 
 
 def test_group_limited_ties_and_masking(ctx, oracle):
-    cfg = synth.C4_DSV3.scaled(n_exp=64, n_group=8, topk_group=2, top_k=8, d=64, shared=0, select_bias_sigma=0.0)
+    cfg = synth.C4_DSV3.scaled(n_exp=64, n_group=8, topk_group=2, top_k=8, d=256, shared=0, select_bias_sigma=0.0)
     ol, gl = layers(oracle, ctx, cfg, 2)
     lg = np.full((2, 64), -4.0, np.float32)
-    lg[0, 40:48] = 3.0       # group 5 clearly best
+    lg[0, 40:46] = 3.0       # group 5 clearly best (6 experts)
     lg[0, 8:10] = 2.0        # group 1 second (two high scores)
     lg[0, 56] = 2.5          # group 7 has one higher score but a lower top-2 sum
     # row 1: all equal -> groups 0 and 1, experts 0..7
@@ -89,7 +89,7 @@ def test_group_limited_ties_and_masking(ctx, oracle):
 
 @pytest.mark.parametrize("T,K,E", [(0, 8, 128), (1, 8, 128), (9, 4, 32), (300, 8, 128), (4096, 8, 256), (1000, 16, 512)])
 def test_plan_bit_exact(ctx, oracle, T, K, E):
-    cfg = synth.C2_QWEN3.scaled(n_exp=E, top_k=K, d=64)
+    cfg = synth.C2_QWEN3.scaled(n_exp=E, top_k=K, d=256)
     gl = pb.MoeLayer(ctx, cfg)
     rng = np.random.default_rng(T + K)
     # skewed: many experts get nothing, a few get most
@@ -112,7 +112,7 @@ def test_plan_bit_exact(ctx, oracle, T, K, E):
 
 
 def test_plan_rejects_bad_ids(ctx):
-    cfg = synth.C2_QWEN3.scaled(n_exp=16, top_k=2, d=64)
+    cfg = synth.C2_QWEN3.scaled(n_exp=16, top_k=2, d=256)
     gl = pb.MoeLayer(ctx, cfg)
     with pytest.raises(pb.PelicaError):
         gl.plan(np.array([[1, 16]], np.uint32))
