@@ -220,6 +220,25 @@ PM_API int32_t pm_router_logits(pm_layer *layer, const float *x, int32_t T, floa
 PM_API int32_t pm_route(pm_layer *layer, const float *x, int32_t T, uint32_t *ids, float *w);
 PM_API int32_t pm_route_logits(pm_layer *layer, const float *logits, int32_t T, uint32_t *ids,
                                float *w);
+/* pm_route for callers that must not allocate. No counterpart in the reference.
+ * Some hosts cannot let a library call cudaMalloc in the middle of their run:
+ * an engine that has handed all device memory to its own pool, a serving loop
+ * where the implicit device synchronisation of an allocation is a latency
+ * spike, a process under a hard memory budget. pm_route may grow the context's
+ * workspace on such a call; this variant never does. Its only scratch (the
+ * router logits) is a fixed array inside the library, sized for at most
+ * PM_ROUTE_NOALLOC_MAX_TOKENS tokens x PM_MAX_EXPERTS experts (512 KB on every
+ * GPU that loads the library, held until exit); larger T is refused with
+ * PM_ERR_LIMIT. x [T][d], ids [T][k], w [T][k] must already be DEVICE pointers.
+ * Work is queued on the context's stream and not waited for. The first call on
+ * a GPU looks up the array's device address; make that first call before any
+ * stream capture. All calls share the one array: two calls whose kernels can
+ * overlap on the GPU (different contexts of one device) race on it - order them.
+ * Nothing in it needs clearing: every logit read is written earlier in the same
+ * call. Results are the bits pm_route gives. */
+#define PM_ROUTE_NOALLOC_MAX_TOKENS 256
+PM_API int32_t pm_route_noalloc(pm_layer *layer, const float *x, int32_t T, uint32_t *ids,
+                                float *w);
 /* replaces: `plan` tail src/moe_kernels.rs:1083-1129, rows[e] src/ds4.rs:1461-1472 */
 PM_API int32_t pm_plan(pm_layer *layer, const uint32_t *ids, int32_t T, pm_plan_out *out);
 /* pair_out[P][d]: expert outputs per pair in plan order (weights folded when

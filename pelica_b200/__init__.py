@@ -87,6 +87,7 @@ ABI = {
     "pm_router_logits": (C.c_int32, [_VP, _VP, C.c_int32, _VP]),
     "pm_route": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
     "pm_route_logits": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
+    "pm_route_noalloc": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
     "pm_plan": (C.c_int32, [_VP, _VP, C.c_int32, C.POINTER(PlanOut)]),
     "pm_experts": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP, _VP]),
     "pm_combine": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32, _VP, C.c_uint32]),
@@ -369,6 +370,11 @@ class MoeLayer:
         w = np.empty((T, self.desc.top_k), np.float32)
         _check(self.lib.pm_route(self.h, _ptr(x), T, ids.ctypes.data, w.ctypes.data))
         return ids, w
+
+    def route_noalloc(self, x: DevBuf, T: int, ids: DevBuf, w: DevBuf):
+        """pm_route_noalloc: device buffers in and out, no allocation inside, at most 256 tokens;
+        queued on the context's stream (call ctx.sync() before reading the results)."""
+        _check(self.lib.pm_route_noalloc(self.h, x.ptr, T, ids.ptr, w.ptr))
 
     def route_logits(self, logits):
         logits = _f32(logits)

@@ -936,6 +936,43 @@ extern "C" int32_t pm_route(pm_layer *ly, const float *x, int32_t T, uint32_t *i
   return out_flush(c, ob, 2);
 }
 
+// ---------------------------------------------------------------------------
+// routing without any allocation
+// ---------------------------------------------------------------------------
+// Scratch for pm_route_noalloc: the router logits of up to
+// PM_ROUTE_NOALLOC_MAX_TOKENS tokens. It lives in the library image, so every
+// GPU that loads the library carries these 512 KB until the process exits.
+static __device__ __align__(256) float g_noalloc_logits[PM_ROUTE_NOALLOC_MAX_TOKENS * PM_MAX_EXPERTS];
+// The array's name is only a host-side handle; kernels need its device address,
+// which differs per GPU. Looked up once per device, with that device current.
+static float *g_noalloc_logits_dev[64] = {nullptr};
+
+extern "C" int32_t pm_route_noalloc(pm_layer *ly, const float *x, int32_t T, uint32_t *ids,
+                                    float *w) {
+  TRY(layer_ready(ly, false));
+  if (T < 0 || T > PM_ROUTE_NOALLOC_MAX_TOKENS)
+    return fail(PM_ERR_LIMIT, "pm_route_noalloc: T=%d, but its fixed scratch holds at most %d tokens "
+                              "(use pm_route for more)", T, PM_ROUTE_NOALLOC_MAX_TOKENS);
+  if (T == 0) return PM_OK;
+  if (!x || !ids || !w) return fail(PM_ERR_INVALID, "pm_route_noalloc: null argument");
+  if (!is_device_ptr(x) || !is_device_ptr(ids) || !is_device_ptr(w))
+    return fail(PM_ERR_INVALID, "pm_route_noalloc: x, ids and w must be device pointers "
+                                "(staging host buffers would need an allocation)");
+  pm_ctx *c = ly->ctx;
+  if (c->device < 0 || c->device >= 64) return fail(PM_ERR_LIMIT, "pm_route_noalloc: device index %d", c->device);
+  CU(cudaSetDevice(c->device));
+  if (!g_noalloc_logits_dev[c->device]) {  // first call on this GPU: resolve the symbol
+    float *p = nullptr;
+    CU(cudaGetSymbolAddress((void **)&p, g_noalloc_logits));
+    g_noalloc_logits_dev[c->device] = p;
+  }
+  float *logits = g_noalloc_logits_dev[c->device];
+  launch_router(c->launch(), ly->dev, x, T, logits);
+  launch_route(c->launch(), ly->dev, logits, T, ids, w);
+  CU(cudaGetLastError());
+  return PM_OK;
+}
+
 static void plan_carve(pm_ctx *c, int E, size_t P, PlanDev &pl) {
   pl.n_active = ws_take<int>(c, 1);
   pl.active = ws_take<uint32_t>(c, (size_t)E);
