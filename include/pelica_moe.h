@@ -149,6 +149,9 @@ PM_API size_t pm_type_block_values(int32_t ggml_type);
 /* ---- context ----------------------------------------------------------- */
 /* replaces: wgpu device + queue per engine (src/moe.rs:786, src/ds4_gpu.rs:568) */
 PM_API int32_t pm_ctx_create(int32_t device, pm_ctx **out);
+/* the same, ordered on a stream the caller owns (cudaStream_t; NULL = the legacy
+ * default stream), e.g. the stream its NCCL collectives are queued on */
+PM_API int32_t pm_ctx_create_on_stream(int32_t device, void *stream, pm_ctx **out);
 PM_API int32_t pm_ctx_destroy(pm_ctx *ctx);
 /* replaces: Pending::wait (src/ds4_gpu.rs:733) */
 PM_API int32_t pm_sync(pm_ctx *ctx);
@@ -246,6 +249,15 @@ PM_API int32_t pm_plan(pm_layer *layer, const uint32_t *ids, int32_t T, pm_plan_
  * `expert`/`expert_dec` src/moe_kernels.rs:1170,1423 */
 PM_API int32_t pm_experts(pm_layer *layer, const float *x, int32_t T, const uint32_t *ids,
                           const float *w, float *pair_out);
+/* expert parallelism, the serving side: row r of x [R][d] goes through expert
+ * eids[r] (which must be local to this context) with routing weight w[r];
+ * out[R][d] in row order, the same values pm_experts gives for that pair.
+ * replaces: the device side of the bridge RUN op, src/bridge.rs:412-466 */
+PM_API int32_t pm_experts_rows(pm_layer *layer, const float *x, int32_t R, const uint32_t *eids,
+                               const float *w, float *out);
+/* the shared expert alone (times its sigmoid gate, if any), out[T][d];
+ * replaces: the dense MLP ops src/moe.rs:1422-1434 */
+PM_API int32_t pm_shared(pm_layer *layer, const float *x, int32_t T, float *out);
 /* y from pair outputs; replaces `combine` src/moe_kernels.rs:1787-1813 */
 PM_API int32_t pm_combine(pm_layer *layer, const float *pair_out, const uint32_t *ids,
                           const float *w, const float *shared_out, int32_t T, float *y,

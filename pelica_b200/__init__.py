@@ -61,6 +61,7 @@ ABI = {
     "pm_type_block_bytes": (C.c_size_t, [C.c_int32]),
     "pm_type_block_values": (C.c_size_t, [C.c_int32]),
     "pm_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(_VP)]),
+    "pm_ctx_create_on_stream": (C.c_int32, [C.c_int32, _VP, C.POINTER(_VP)]),
     "pm_ctx_destroy": (C.c_int32, [_VP]),
     "pm_sync": (C.c_int32, [_VP]),
     "pm_ctx_stream": (_VP, [_VP]),
@@ -90,6 +91,8 @@ ABI = {
     "pm_route_noalloc": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
     "pm_plan": (C.c_int32, [_VP, _VP, C.c_int32, C.POINTER(PlanOut)]),
     "pm_experts": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP, _VP]),
+    "pm_experts_rows": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP, _VP]),
+    "pm_shared": (C.c_int32, [_VP, _VP, C.c_int32, _VP]),
     "pm_combine": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32, _VP, C.c_uint32]),
     "pm_dequant": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP]),
     "pm_quant_act": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP, _VP, _VP]),
@@ -177,10 +180,14 @@ def _u32(a):
 class Context:
     """One GPU: a stream, a workspace and the layers created on it."""
 
-    def __init__(self, device: int = 0):
+    def __init__(self, device: int = 0, stream=None):
+        """stream: a cudaStream_t handle (int) the caller owns, or None for a private stream."""
         self.lib = load_library()
         h = _VP()
-        _check(self.lib.pm_ctx_create(device, C.byref(h)))
+        if stream is None:
+            _check(self.lib.pm_ctx_create(device, C.byref(h)))
+        else:
+            _check(self.lib.pm_ctx_create_on_stream(device, stream, C.byref(h)))
         self.h = h.value
         self.device = device
 
@@ -401,6 +408,20 @@ class MoeLayer:
         T = x.shape[0]
         out = np.empty((T * self.desc.top_k, self.desc.d), np.float32)
         _check(self.lib.pm_experts(self.h, _ptr(x), T, _ptr(ids), _ptr(w), out.ctypes.data))
+        return out
+
+    def experts_rows(self, x, eids, w) -> np.ndarray:
+        """One expert per row (the serving side of expert parallelism)."""
+        x, eids, w = _f32(x), _u32(eids), _f32(w)
+        R = x.shape[0]
+        out = np.empty((R, self.desc.d), np.float32)
+        _check(self.lib.pm_experts_rows(self.h, _ptr(x), R, _ptr(eids), _ptr(w), out.ctypes.data))
+        return out
+
+    def shared(self, x) -> np.ndarray:
+        x = _f32(x)
+        out = np.empty((x.shape[0], self.desc.d), np.float32)
+        _check(self.lib.pm_shared(self.h, _ptr(x), x.shape[0], out.ctypes.data))
         return out
 
     def combine(self, pair_out, ids, w, shared_out=None, y=None) -> np.ndarray:

@@ -73,6 +73,7 @@ static size_t raw_bytes(int type, size_t rows, size_t cols) {
 struct pm_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
+  bool own_stream = true;
   int64_t launches = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // workspace: one region, carved per call
@@ -179,6 +180,28 @@ extern "C" int32_t pm_ctx_create(int32_t device, pm_ctx **out) {
   return PM_OK;
 }
 
+// a context whose work is ordered on a stream the caller owns (e.g. the stream
+// its collectives run on), so no cross-stream synchronisation is needed
+extern "C" int32_t pm_ctx_create_on_stream(int32_t device, void *stream, pm_ctx **out) {
+  if (!out) return fail(PM_ERR_INVALID, "pm_ctx_create_on_stream: out is null");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(PM_ERR_CUDA, "pm_ctx_create_on_stream: no CUDA device (%s); this library has no CPU path",
+                cudaGetErrorString(e));
+  if (device < 0 || device >= n) return fail(PM_ERR_INVALID, "device %d of %d", device, n);
+  CU(cudaSetDevice(device));
+  pm_ctx *c = new (std::nothrow) pm_ctx();
+  if (!c) return fail(PM_ERR_OOM, "host allocation");
+  c->device = device;
+  c->stream = (cudaStream_t)stream;
+  c->own_stream = false;
+  CU(cudaEventCreate(&c->ev0));
+  CU(cudaEventCreate(&c->ev1));
+  *out = c;
+  return PM_OK;
+}
+
 extern "C" int32_t pm_ctx_destroy(pm_ctx *c) {
   if (!c) return PM_OK;
   cudaSetDevice(c->device);
@@ -189,7 +212,7 @@ extern "C" int32_t pm_ctx_destroy(pm_ctx *c) {
   for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
-  cudaStreamDestroy(c->stream);
+  if (c->own_stream) cudaStreamDestroy(c->stream);
   delete c;
   return PM_OK;
 }
@@ -1049,6 +1072,71 @@ extern "C" int32_t pm_experts(pm_layer *ly, const float *x, int32_t T, const uin
   CU(cudaMemcpyAsync(pair_out, S.eo, P * D.d * 4, cudaMemcpyDefault, c->stream));
   CU(cudaStreamSynchronize(c->stream));
   return PM_OK;
+}
+
+// one expert per row (expert parallelism: the rows another rank dispatched here)
+extern "C" int32_t pm_experts_rows(pm_layer *ly, const float *x, int32_t R, const uint32_t *eids,
+                                   const float *w, float *out) {
+  TRY(layer_ready(ly, true));
+  TRY(check_T(R));
+  if (R == 0) return PM_OK;
+  if (!x || !eids || !w || !out) return fail(PM_ERR_INVALID, "pm_experts_rows: null argument");
+  pm_ctx *c = ly->ctx;
+  pm_layer_desc D = ly->dev.desc;
+  D.top_k = 1;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)R * D.d;
+  if (!is_device_ptr(eids)) TRY(check_ids_host(D, eids, (size_t)R));
+  TRY(ws_reserve(c, scratch_bytes(D, R) + 3 * al(n * 4) + 2 * al((size_t)R * 4)));
+  const float *xd, *wd;
+  const uint32_t *idd;
+  TRY(in_dev(c, x, n, &xd));
+  TRY(in_dev(c, eids, (size_t)R, &idd));
+  TRY(in_dev(c, w, (size_t)R, &wd));
+  OutBuf ob;
+  float *od = out_dev(c, out, n, ob);
+  Scratch S;
+  scratch_carve(c, D, R, S);
+  // the same layer seen with one expert per token; outputs are raw pair outputs
+  // (routing weight folded only where the layer folds it before down)
+  pm_layer view = *ly;
+  view.dev.desc = D;
+  view.dev.usage = nullptr;
+  launch_plan(c->launch(), view.dev, idd, R, S.plan);
+  TRY(dev_experts(&view, xd, R, S, wd));
+  LayerDev cp = view.dev;
+  cp.desc.weight_fold = PM_FOLD_BEFORE_DOWN;  // plain gather back to row order
+  launch_combine(c->launch(), cp, S.eo, S.plan.pair_pos, wd, nullptr, nullptr, R, od, false);
+  CU(cudaGetLastError());
+  return out_flush(c, &ob, 1);
+}
+
+// the shared expert alone: out[T][d] = shared(x) (times its sigmoid gate, if any)
+extern "C" int32_t pm_shared(pm_layer *ly, const float *x, int32_t T, float *out) {
+  TRY(layer_ready(ly, true));
+  TRY(check_T(T));
+  if (!ly->dev.desc.shared) return fail(PM_ERR_STATE, "pm_shared: the layer has no shared expert");
+  if (T == 0) return PM_OK;
+  if (!x || !out) return fail(PM_ERR_INVALID, "pm_shared: null argument");
+  pm_ctx *c = ly->ctx;
+  pm_layer_desc D = ly->dev.desc;
+  D.top_k = 1;
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * D.d;
+  TRY(ws_reserve(c, scratch_bytes(D, T) + 2 * al(n * 4) + al((size_t)T * 4) * 2));
+  const float *xd;
+  TRY(in_dev(c, x, n, &xd));
+  OutBuf ob;
+  float *od = out_dev(c, out, n, ob);
+  Scratch S;
+  scratch_carve(c, D, T, S);
+  TRY(dev_shared(ly, xd, T, S));
+  // y = 0 + shared * gate, through the combine kernel with no routed pairs (K = 0)
+  LayerDev cp = ly->dev;
+  cp.desc.top_k = 0;
+  launch_combine(c->launch(), cp, S.eo, S.plan.pair_pos, nullptr, S.shared_out, S.shared_logit, T, od, false);
+  CU(cudaGetLastError());
+  return out_flush(c, &ob, 1);
 }
 
 extern "C" int32_t pm_combine(pm_layer *ly, const float *pair_out, const uint32_t *ids,

@@ -1,0 +1,83 @@
+"""Expert parallelism on GPUs: the exchange of pelica_b200.ep around the C-ABI
+compute, against the unsharded layer (same bits)."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import pelica_b200 as pb
+from pelica_b200 import synth
+from tests.helpers import SMALL, bits_equal, tol_ok
+
+pytestmark = [pytest.mark.gpu, pytest.mark.timeout(600)]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("name", ["c2", "c4", "c3"])
+def test_single_rank_exchange_matches_forward(ctx, name):
+    """World size 1: every pair is 'sent' to this rank; exercises the row-serving
+    entry points (pm_experts_rows, pm_shared, pm_combine) on device pointers."""
+    import torch
+
+    from pelica_b200.ep import CudaBackend, ExpertParallelLayer
+
+    cfg = SMALL[name]
+    W = synth.make_weights(cfg, 90)
+    tctx = pb.Context(0, stream=torch.cuda.current_stream().cuda_stream)
+    layer = pb.MoeLayer(tctx, cfg).load(W)
+    ep = ExpertParallelLayer(CudaBackend(layer), cfg.n_exp)
+    x = synth.make_activations(33, cfg.d, 7)
+    want = layer.forward(x)
+    got = ep.forward(torch.from_numpy(x).cuda())
+    torch.cuda.synchronize()
+    got = got.cpu().numpy()
+    if cfg.act_quant == synth.AQ_Q8X_256:
+        assert bits_equal(got, want)
+    else:
+        assert tol_ok(got, want)
+    assert ep.forward(torch.zeros((0, cfg.d), device="cuda")).shape == (0, cfg.d)
+    layer.close()
+    tctx.close()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.parametrize("name", ["c2", "c4"])
+def test_two_gpus_match_the_unsharded_layer(ctx, tmp_path, name):
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    port = _free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "ep_gpu_worker.py"), name,
+                                       str(tmp_path)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                      text=True))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append((p.returncode, o[-2000:]))
+    assert all(rc == 0 for rc, _ in outs), outs
+    cfg = SMALL[name]
+    W = synth.make_weights(cfg, 91)
+    layer = pb.MoeLayer(ctx, cfg).load(W)
+    want = layer.forward(synth.make_activations(50, cfg.d, 6))
+    got = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(2)])
+    assert bits_equal(got, want)
+    layer.close()
