@@ -1247,8 +1247,8 @@ static int32_t stack_setup_mega(pm_stack *s) {
   CU(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c->device));
   if (!coop || prop.major < 9) return PM_OK;
   if (!mega_plan(D, prop.multiProcessorCount, prop.sharedMemPerBlockOptin, s->mega)) return PM_OK;
-  CU(mega_prepare(s->mega.smem));
-  if (mega_max_ctas_per_sm(s->mega.smem) < 1) return PM_OK;
+  CU(mega_prepare(D, s->mega.smem));
+  if (mega_max_ctas_per_sm(D, s->mega.smem) < 1) return PM_OK;
   size_t L = s->layers.size();
   std::vector<MegaLayer> ml(L);
   for (size_t i = 0; i < L; i++) {

@@ -99,8 +99,7 @@ __device__ __forceinline__ bool mbar_try_wait_ns(uint64_t *bar, uint32_t parity,
 }
 // bounded wait on an mbarrier phase: short hardware-suspended waits in a timed
 // loop; false = gave up (error word set)
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, int *err) {
   unsigned long long t0 = now_ns();
   for (uint32_t it = 1;; it++) {
     if (mbar_try_wait_ns(bar, parity, 4000u)) return true;
@@ -112,8 +111,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
   atomicCAS(err, 0, 2);
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, err);
+}
 // bounded wait for an epoch-tagged value; false = gave up
-__device__ __forceinline__ bool wait_pair(const unsigned long long *p, uint32_t epoch, float &v,
+__device__ __noinline__ bool wait_pair(const unsigned long long *p, uint32_t epoch, float &v,
                                           int *err) {
   unsigned long long t0 = 0;
   for (uint32_t it = 0;; it++) {
@@ -137,7 +140,7 @@ __device__ __forceinline__ bool wait_pair(const unsigned long long *p, uint32_t 
 // (`Q8x::new`, src/ds4_cpu.rs:13-35); writes q, d, bsum of the block
 // `swz`: 16-byte chunk c of the block is stored at chunk c ^ swz (so that lanes
 // reading the same chunk of 8 different blocks hit different banks)
-__device__ __forceinline__ void q8x_block_warp(const float v[8], int lane, int8_t *q, float *d,
+__device__ __noinline__ void q8x_block_warp(const float v[8], int lane, int8_t *q, float *d,
                                                int32_t *bsum, int swz = 0) {
   float a = 0.0f;
 #pragma unroll
@@ -365,6 +368,10 @@ __device__ __forceinline__ bool poll_pairs(const unsigned long long *p, int i0, 
 #define MG_GH 2  // h rows (gate+up pairs) a warp works on at once
 #define MG_DR 4  // down rows a warp works on at once
 
+// DQ6: down weights are Q6_K (else Q4_K); NB8: d == 2048 (8 blocks per gate/up row);
+// NP: router slots per lane (4: up to 128 experts, 8: up to 256). Compile-time so that
+// only the taken paths are in the instruction stream (the loop body must stay cache-resident).
+template <bool DQ6, bool NB8, int NP>
 __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   const pm_layer_desc &D = P.D;
@@ -373,7 +380,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nbx = d / 256, nbh = ff / 256;
   const int RBG = nbx * 144;  // bytes of a gate/up row
-  const bool dq6 = D.type_down == PM_TYPE_Q6_K;
+  constexpr bool dq6 = DQ6;
 
   uint8_t *gs = smem + P.off_gs, *us = smem + P.off_us, *dn = smem + P.off_dn;
   uint8_t *dsm = smem + P.off_dsm;
@@ -394,7 +401,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   uint32_t *ids = (uint32_t *)(red8 + 8);              // [PM_MAX_TOPK]
   float *wts = (float *)(ids + PM_MAX_TOPK);           // [PM_MAX_TOPK]
   int *s_dead = (int *)(wts + PM_MAX_TOPK);            // [4]
-  float *r_sv = (float *)(s_dead + 4);                 // route scratch
+  float *r_sv = (float *)(((uintptr_t)(s_dead + 4) + 15) & ~(uintptr_t)15);  // route scratch, 16-byte aligned
   float *r_gs = r_sv + PM_MAX_EXPERTS;
   unsigned char *r_keep = (unsigned char *)(r_gs + PM_MAX_EXPERTS / 2);
 
@@ -418,8 +425,8 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     int ch = tid >> 2, seg = (tid >> 1) & 1, isup = tid & 1;
     // rows of chunk ch: with 8-block rows, chunks hold whole pairs of h rows
     const int npairs_j = (nrows + 1) >> 1, ppc_j = (npairs_j + MG_GU_CHUNKS - 1) / MG_GU_CHUNKS;
-    int ra = nbx == 8 ? min(R1, R0 + 2 * ch * ppc_j) : min(R1, R0 + ch * wpc * per_w);
-    int rb = nbx == 8 ? min(R1, R0 + 2 * (ch + 1) * ppc_j) : min(R1, R0 + (ch + 1) * wpc * per_w);
+    int ra = NB8 ? min(R1, R0 + 2 * ch * ppc_j) : min(R1, R0 + ch * wpc * per_w);
+    int rb = NB8 ? min(R1, R0 + 2 * (ch + 1) * ppc_j) : min(R1, R0 + (ch + 1) * wpc * per_w);
     int ka = ra / ff;
     int split = min(rb, (ka + 1) * ff);
     int s0 = seg == 0 ? ra : split, s1 = seg == 0 ? split : rb;
@@ -524,38 +531,95 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       float v[8];
 #pragma unroll
       for (int j = 0; j < 8; j++) v[j] = __fmul_rn(xs[warp * 256 + 32 * j + lane], inv);
-      q8x_block_warp(v, lane, xq + warp * 256, xd + warp, xbs + warp * 8, nbx == 8 ? warp : 0);
+      q8x_block_warp(v, lane, xq + warp * 256, xd + warp, xbs + warp * 8, NB8 ? warp : 0);
     } else if (warp == MG_WARPS - 1) {
-      // ---- 3. this CTA's router logit, then all logits, then the top-k ----
-      MG_TRACE_R(12);
-      if (has_logit) {
-        if (!mbar_wait(bar_rw, par, P.err)) dead = true;
-        float acc = 0.0f;
+      // ---- 3. this CTA's router logit, then all logits, then the scores (one warp) ----
+      float *r_pr = r_sv;                          // [E] score the weight comes from
+      uint32_t *r_key = (uint32_t *)(r_sv + 160);  // [E] ordered key of what is ranked
+      float *sel_p = r_sv + 320;                   // [K] picked scores, selection order
+      uint32_t *sel_e = (uint32_t *)(r_sv + 336);  // [K] picked experts
+      {
+        MG_TRACE_R(12);
+        if (has_logit) {
+          if (!mbar_wait(bar_rw, par, P.err)) dead = true;
+          float acc = 0.0f;
 #pragma unroll 16
-        for (int c = lane; c < d; c += 32) acc = __fmaf_rn(rw[c], __fmul_rn(xs[c], inv), acc);
-        float s = pm_warp_sum_dot(acc);
-        if (lane == 0) {
-          if (ML.logit_bias) s = __fadd_rn(s, ML.logit_bias[cta]);
-          st_pair(P.lbuf + cta, s, ep);
+          for (int c = lane; c < d; c += 32) acc = __fmaf_rn(rw[c], __fmul_rn(xs[c], inv), acc);
+          float sdot = pm_warp_sum_dot(acc);
+          if (lane == 0) {
+            if (ML.logit_bias) sdot = __fadd_rn(sdot, ML.logit_bias[cta]);
+            st_pair(P.lbuf + cta, sdot, ep);
+          }
+          __syncwarp();
+          if (lane == 0 && l + 1 < P.n_layers) {  // next layer's row into the same buffer
+            mbar_expect_tx(bar_rw, (uint32_t)d * 4);
+            bulk_g2s(rw, P.layers[l + 1].router + (size_t)cta * d, (uint32_t)d * 4, bar_rw);
+          }
+        }
+        MG_TRACE_R(13);
+        for (int e0 = lane; e0 < E; e0 += 4 * 32) {
+          float v[4];
+          if (!poll_pairs<4>(P.lbuf, e0, 32, E, ep, v, P.err)) dead = true;
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            if (e0 + 32 * j < E) lg[e0 + 32 * j] = v[j];
         }
         __syncwarp();
-        if (lane == 0 && l + 1 < P.n_layers) {  // next layer's row into the same buffer
-          mbar_expect_tx(bar_rw, (uint32_t)d * 4);
-          bulk_g2s(rw, P.layers[l + 1].router + (size_t)cta * d, (uint32_t)d * 4, bar_rw);
+        MG_TRACE_R(14);
+        {
+          float pr[NP];
+          uint32_t key[NP];
+          pm_route_scores<NP>(D, lg, ML.select_bias, lane, r_sv + 352, r_gs, r_keep, pr, key);
+#pragma unroll
+          for (int i = 0; i < NP; i++)
+            if (lane + 32 * i < E) { r_pr[lane + 32 * i] = pr[i]; r_key[lane + 32 * i] = key[i]; }
         }
       }
-      MG_TRACE_R(13);
-      for (int e0 = lane; e0 < E; e0 += 4 * 32) {
-        float v[4];
-        if (!poll_pairs<4>(P.lbuf, e0, 32, E, ep, v, P.err)) dead = true;
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-          if (e0 + 32 * j < E) lg[e0 + 32 * j] = v[j];
+      MG_TRACE_R(16);
+    }
+    if (__syncthreads_or(dead)) { dead = true; break; }
+    {
+      // rank of expert e = how many experts come before it in (key descending, index
+      // ascending) order: exactly the order K rounds of (max, lowest index) pick in.
+      // Four threads per expert, each over a quarter of the keys.
+      const float *r_pr = r_sv;
+      const uint32_t *r_key = (const uint32_t *)(r_sv + 160);
+      float *sel_p = r_sv + 320;
+      uint32_t *sel_e = (uint32_t *)(r_sv + 336);
+      const int q = tid & 3;
+      const int fq = (E + 3) >> 2;
+      for (int e0 = 0; e0 < E; e0 += MG_NT / 4) {
+        int e = e0 + (tid >> 2);
+        int rank = 0, rank2 = 0;
+        if (e < E) {
+          uint32_t ke = r_key[e];
+          int fa = q * fq, fb = min(E, fa + fq);
+          for (int f = fa; f + 1 < fb; f += 2) {
+            uint32_t k0 = r_key[f], k1 = r_key[f + 1];
+            rank += (k0 > ke) || (k0 == ke && f < e);
+            rank2 += (k1 > ke) || (k1 == ke && f + 1 < e);
+          }
+          if ((fb - fa) & 1) {
+            uint32_t k0 = r_key[fb - 1];
+            rank += (k0 > ke) || (k0 == ke && fb - 1 < e);
+          }
+        }
+        rank += rank2;
+        rank += __shfl_xor_sync(PM_FULL, rank, 1);
+        rank += __shfl_xor_sync(PM_FULL, rank, 2);
+        if (q == 0 && e < E && rank < K) { sel_e[rank] = (uint32_t)e; sel_p[rank] = r_pr[e]; }
+      }
+    }
+    __syncthreads();
+    if (warp == MG_WARPS - 1) {
+      const float *sel_p = r_sv + 320;
+      const uint32_t *sel_e = (const uint32_t *)(r_sv + 336);
+      MG_TRACE_R(18);
+      if (lane < K) {
+        ids[lane] = sel_e[lane];
+        wts[lane] = pm_route_weight(D, sel_p, lane);
       }
       __syncwarp();
-      MG_TRACE_R(14);
-      pm_route_warp(D, lg, ML.select_bias, lane, r_sv, r_gs, r_keep, ids, wts);
-      __syncwarp();  // ids[] and wts[] written by lanes < K
       MG_TRACE_R(15);
       if (cta == 0 && lane < K && ML.usage) atomicAdd(&ML.usage[ids[lane]], 1u);
     }
@@ -581,7 +645,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     MG_TRACE(3);
 
     // ---- 5. gate/up rows -> h ----
-    if (nbx == 8) {
+    if (NB8) {
       // pairs of h rows: lanes 0-7 gate(h0), 8-15 up(h0), 16-23 gate(h1), 24-31 up(h1)
       XBlk X;
       {
@@ -770,7 +834,7 @@ bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp
   if (D.type_down != PM_TYPE_Q4_K && D.type_down != PM_TYPE_Q6_K) return false;
   if (D.shared || D.has_expert_bias || D.n_exp_local > 0) return false;
   if (D.n_exp > n_sm || D.top_k > PM_MAX_TOPK) return false;
-  if (D.d / 256 > MG_WARPS - 1) return false;
+  if (D.d / 256 > MG_WARPS - 4) return false;  // the last 4 warps route while the first d/256 quantise
   int G = n_sm;
   const int d = D.d, ff = D.ff, K = D.top_k;
   const int nbx = d / 256, nbh = ff / 256;
@@ -811,13 +875,24 @@ bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp
   return true;
 }
 
-cudaError_t mega_prepare(size_t smem) {
-  return cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+typedef void (*MegaKernel)(const MegaParams);
+static MegaKernel mega_kernel(const pm_layer_desc &D) {
+  bool dq6 = D.type_down == PM_TYPE_Q6_K, nb8 = D.d == 2048, big = D.n_exp > 128;
+  if (dq6) {
+    if (nb8) return big ? k_decode_mega<true, true, 8> : k_decode_mega<true, true, 4>;
+    return big ? k_decode_mega<true, false, 8> : k_decode_mega<true, false, 4>;
+  }
+  if (nb8) return big ? k_decode_mega<false, true, 8> : k_decode_mega<false, true, 4>;
+  return big ? k_decode_mega<false, false, 8> : k_decode_mega<false, false, 4>;
 }
 
-int mega_max_ctas_per_sm(size_t smem) {
+cudaError_t mega_prepare(const pm_layer_desc &D, size_t smem) {
+  return cudaFuncSetAttribute((const void *)mega_kernel(D), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
+int mega_max_ctas_per_sm(const pm_layer_desc &D, size_t smem) {
   int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode_mega, MG_NT, smem) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void *)mega_kernel(D), MG_NT, smem) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -827,6 +902,5 @@ int mega_max_ctas_per_sm(size_t smem) {
 cudaError_t mega_launch(const MegaPlan &mp, cudaStream_t stream) {
   MegaParams P = mp.P;
   void *args[] = {(void *)&P};
-  return cudaLaunchCooperativeKernel((const void *)k_decode_mega, dim3(mp.grid), dim3(MG_NT), args, mp.smem,
-                                     stream);
+  return cudaLaunchCooperativeKernel((const void *)mega_kernel(P.D), dim3(mp.grid), dim3(MG_NT), args, mp.smem, stream);
 }

@@ -6,7 +6,7 @@
 #define MG_NT 512
 #define MG_WARPS (MG_NT / 32)
 #define MG_GU_CHUNKS 4
-#define MG_TRACE_PH 16  // trace points per layer
+#define MG_TRACE_PH 20  // trace points per layer
 
 struct MegaLayer {
   const float *router, *logit_bias, *select_bias;
@@ -47,6 +47,6 @@ struct MegaPlan {
 
 
 bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp);
-cudaError_t mega_prepare(size_t smem);
-int mega_max_ctas_per_sm(size_t smem);
+cudaError_t mega_prepare(const pm_layer_desc &D, size_t smem);
+int mega_max_ctas_per_sm(const pm_layer_desc &D, size_t smem);
 cudaError_t mega_launch(const MegaPlan &mp, cudaStream_t stream);

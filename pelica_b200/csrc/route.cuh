@@ -21,13 +21,18 @@ __device__ __forceinline__ float pm_funkey(uint32_t k) {
 // token's E logits (any address space); ssv[E], gsc[E/2], keep[E/2] are per-warp
 // scratch in shared memory (used for group-limited selection only). Lane k < K
 // writes ids_out[k], w_out[k].
+// Scores of one token by one warp. lane L holds experts L, L+32, ... (NP per lane,
+// NP*32 >= E); `lg` points at the token's E logits (any address space); ssv[E],
+// gsc[E/2], keep[E/2] are per-warp scratch in shared memory (group-limited
+// selection only). Out: pr[] = the score the weight is taken from, key[] = the
+// ordered key of what the selection ranks (score + bias, masked groups lowest).
 template <int NP>
-__device__ __forceinline__ void pm_route_warp_n(const pm_layer_desc &D, const float *lg,
+__device__ __forceinline__ void pm_route_scores(const pm_layer_desc &D, const float *lg,
                                                 const float *__restrict__ sel_bias, int lane,
                                                 float *ssv, float *gsc, unsigned char *keep,
-                                                uint32_t *ids_out, float *w_out) {
-  const int E = D.n_exp, K = D.top_k;
-  float pr[NP], sv[NP];
+                                                float pr[NP], uint32_t key[NP]) {
+  const int E = D.n_exp;
+  float sv[NP];
 #pragma unroll
   for (int i = 0; i < NP; i++) {
     int e = lane + 32 * i;
@@ -108,15 +113,53 @@ __device__ __forceinline__ void pm_route_warp_n(const pm_layer_desc &D, const fl
       if (e < E && !keep[e / gs]) sv[i] = PM_NEG;
     }
   }
-  // K rounds of (max, lowest index) (src/moe_kernels.rs:1053-1067), on ordered
-  // integer keys: one warp-wide max, then the first slot/lane that holds it
-  uint32_t key[NP];
-  const uint32_t KNEG = pm_fkey(PM_NEG);
 #pragma unroll
   for (int i = 0; i < NP; i++) key[i] = pm_fkey(sv[i]);
-  float wsum = 0.0f, w0 = 0.0f, evsum = 0.0f;
+}
+
+// The routing weight of pick k = lane (< K) from the picked scores in selection
+// order sel_p[0..K) (src/moe_kernels.rs:1072-1074, src/oss_kernels.rs:31-32,
+// src/ds4.rs:1416-1424). Sums run in k order, every lane repeats them.
+__device__ __forceinline__ float pm_route_weight(const pm_layer_desc &D, const float *sel_p,
+                                                 int k) {
+  const int K = D.top_k;
+  float x;
+  if (D.gating == PM_GATE_SOFTMAX_SELECTED) {
+    float evsum = 0.0f, mine = 0.0f;
+    for (int j = 0; j < K; j++) {
+      float ev = pm_exp(__fsub_rn(sel_p[j], sel_p[0]));
+      evsum = __fadd_rn(evsum, ev);
+      if (j == k) mine = ev;
+    }
+    x = __fdiv_rn(mine, evsum);
+  } else {
+    float wsum = 0.0f;
+    for (int j = 0; j < K; j++) wsum = __fadd_rn(wsum, sel_p[j]);
+    x = sel_p[k];
+    if (D.gating == PM_GATE_SQRT_SOFTPLUS) x = __fdiv_rn(x, wsum);
+    else if (D.norm_w) x = __fdiv_rn(x, fmaxf(wsum, 6.103515625e-5f));
+  }
+  if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
+  return x;
+}
+
+// The whole routing of one token by one warp; lane k < K writes ids_out[k], w_out[k].
+// sel_p: K floats of per-warp shared scratch.
+template <int NP>
+__device__ __forceinline__ void pm_route_warp_n(const pm_layer_desc &D, const float *lg,
+                                                const float *__restrict__ sel_bias, int lane,
+                                                float *ssv, float *gsc, unsigned char *keep,
+                                                uint32_t *ids_out, float *w_out) {
+  const int K = D.top_k;
+  float pr[NP];
+  uint32_t key[NP];
+  pm_route_scores<NP>(D, lg, sel_bias, lane, ssv, gsc, keep, pr, key);
+  float *sel_p = ssv;  // the group scratch is free again
+  __syncwarp();
+  // K rounds of (max, lowest index) (src/moe_kernels.rs:1053-1067), on ordered
+  // integer keys: one warp-wide max, then the first slot/lane that holds it
+  const uint32_t KNEG = pm_fkey(PM_NEG);
   uint32_t my_e = 0;
-  float my_w = 0.0f, my_ev = 0.0f;
 #pragma unroll 1
   for (int k = 0; k < K; k++) {
     uint32_t lk = key[0];
@@ -137,32 +180,13 @@ __device__ __forceinline__ void pm_route_warp_n(const pm_layer_desc &D, const fl
         if (lane == lw) key[i] = KNEG;
       }
     }
-    wsum = __fadd_rn(wsum, w);
-    float ev = 0.0f;
-    if (D.gating == PM_GATE_SOFTMAX_SELECTED) {  // src/oss_kernels.rs:31-32
-      if (k == 0) w0 = w;
-      ev = pm_exp(__fsub_rn(w, w0));
-      evsum = __fadd_rn(evsum, ev);
-    }
-    if (lane == k) {
-      my_e = e;
-      my_w = w;
-      my_ev = ev;
-    }
+    if (lane == k) my_e = e;
+    if (lane == 0) sel_p[k] = w;
   }
+  __syncwarp();
   if (lane < K) {
-    float x;
-    if (D.gating == PM_GATE_SOFTMAX_SELECTED) {
-      x = __fdiv_rn(my_ev, evsum);
-    } else if (D.gating == PM_GATE_SQRT_SOFTPLUS) {  // src/ds4.rs:1416-1424
-      x = __fdiv_rn(my_w, wsum);
-    } else {  // src/moe_kernels.rs:1072-1074
-      x = my_w;
-      if (D.norm_w) x = __fdiv_rn(x, fmaxf(wsum, 6.103515625e-5f));
-    }
-    if (D.w_scale != 0.0f) x = __fmul_rn(x, D.w_scale);
     ids_out[lane] = my_e;
-    w_out[lane] = x;
+    w_out[lane] = pm_route_weight(D, sel_p, lane);
   }
 }
 
