@@ -155,6 +155,10 @@ PM_API int32_t pm_ctx_create_on_stream(int32_t device, void *stream, pm_ctx **ou
 PM_API int32_t pm_ctx_destroy(pm_ctx *ctx);
 /* replaces: Pending::wait (src/ds4_gpu.rs:733) */
 PM_API int32_t pm_sync(pm_ctx *ctx);
+/* expert products run on the tensor cores (tcgen05 int8, exact integer sums) when a
+ * call has at least this many tokens (default 32, the reference's TC_MIN,
+ * src/moe.rs:35; 0 = never). Both paths give the same bits. */
+PM_API int32_t pm_ctx_set_tensor_core_min_tokens(pm_ctx *ctx, int32_t min_tokens);
 /* the CUDA stream all work of this context is ordered on (cudaStream_t) */
 PM_API void *pm_ctx_stream(pm_ctx *ctx);
 /* kernels launched by this context since creation (bench bookkeeping) */

@@ -64,6 +64,7 @@ ABI = {
     "pm_ctx_create_on_stream": (C.c_int32, [C.c_int32, _VP, C.POINTER(_VP)]),
     "pm_ctx_destroy": (C.c_int32, [_VP]),
     "pm_sync": (C.c_int32, [_VP]),
+    "pm_ctx_set_tensor_core_min_tokens": (C.c_int32, [_VP, C.c_int32]),
     "pm_ctx_stream": (_VP, [_VP]),
     "pm_ctx_launch_count": (C.c_int64, [_VP]),
     "pm_timer_start": (C.c_int32, [_VP]),
@@ -198,6 +199,10 @@ class Context:
 
     def sync(self):
         _check(self.lib.pm_sync(self.h))
+
+    def set_tensor_core_min_tokens(self, n: int):
+        """Expert products use the tcgen05 kernels from n tokens per call (0 = never)."""
+        _check(self.lib.pm_ctx_set_tensor_core_min_tokens(self.h, n))
 
     @property
     def launches(self) -> int:

@@ -74,6 +74,8 @@ struct pm_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
   bool own_stream = true;
+  int *dev_err = nullptr;   // error word of kernels with bounded waits
+  int tc_min_tokens = 32;   // tensor-core expert products from this many tokens (the reference's TC_MIN, src/moe.rs:35); 0 = never
   int64_t launches = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // workspace: one region, carved per call
@@ -174,6 +176,8 @@ extern "C" int32_t pm_ctx_create(int32_t device, pm_ctx **out) {
   if (!c) return fail(PM_ERR_OOM, "pm_ctx_create: host allocation");
   c->device = device;
   CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  CU(cudaMalloc(&c->dev_err, 4));
+  CU(cudaMemset(c->dev_err, 0, 4));
   CU(cudaEventCreate(&c->ev0));
   CU(cudaEventCreate(&c->ev1));
   *out = c;
@@ -196,6 +200,8 @@ extern "C" int32_t pm_ctx_create_on_stream(int32_t device, void *stream, pm_ctx 
   c->device = device;
   c->stream = (cudaStream_t)stream;
   c->own_stream = false;
+  CU(cudaMalloc(&c->dev_err, 4));
+  CU(cudaMemset(c->dev_err, 0, 4));
   CU(cudaEventCreate(&c->ev0));
   CU(cudaEventCreate(&c->ev1));
   *out = c;
@@ -209,6 +215,7 @@ extern "C" int32_t pm_ctx_destroy(pm_ctx *c) {
   if (c->ws) cudaFree(c->ws);
   if (c->stage) cudaFree(c->stage);
   if (c->flush) cudaFree(c->flush);
+  if (c->dev_err) cudaFree(c->dev_err);
   for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
@@ -217,10 +224,25 @@ extern "C" int32_t pm_ctx_destroy(pm_ctx *c) {
   return PM_OK;
 }
 
+// the error word of kernels with bounded waits (call after a synchronisation)
+static int32_t check_dev_err(pm_ctx *c) {
+  int e = 0;
+  CU(cudaMemcpy(&e, c->dev_err, 4, cudaMemcpyDeviceToHost));
+  if (e) {
+    CU(cudaMemset(c->dev_err, 0, 4));
+    return fail(PM_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", e);
+  }
+  return PM_OK;
+}
 extern "C" int32_t pm_sync(pm_ctx *c) {
   if (!c) return fail(PM_ERR_INVALID, "pm_sync: null context");
   CU(cudaStreamSynchronize(c->stream));
   CU(cudaGetLastError());
+  return check_dev_err(c);
+}
+extern "C" int32_t pm_ctx_set_tensor_core_min_tokens(pm_ctx *c, int32_t min_tokens) {
+  if (!c || min_tokens < 0) return fail(PM_ERR_INVALID, "pm_ctx_set_tensor_core_min_tokens");
+  c->tc_min_tokens = min_tokens;
   return PM_OK;
 }
 extern "C" int32_t pm_stack_destroy(pm_stack *s);
@@ -775,9 +797,22 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   Groups g = plan_groups(S.plan, D.n_exp);
   bool q8 = D.act_quant == PM_AQ_Q8X_256;
   if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum); }
-  { PROF(c, PH_GATEUP); launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h); }
+  const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
+  {
+    PROF(c, PH_GATEUP);
+    if (tc && D.type_gate == PM_TYPE_Q4_K && D.type_up == PM_TYPE_Q4_K)
+      CU(launch_tc_q4k(L, dv, false, false, g, P, T, S.xq, S.xd, w, S.h, c->dev_err));
+    else
+      launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
+  }
   if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum); }
-  { PROF(c, PH_DOWN); launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo); }
+  {
+    PROF(c, PH_DOWN);
+    if (tc && D.type_down == PM_TYPE_Q4_K)
+      CU(launch_tc_q4k(L, dv, false, true, g, P, T, S.hq, S.hd, nullptr, S.eo, c->dev_err));
+    else
+      launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo);
+  }
   CU(cudaGetLastError());
   return PM_OK;
 }
@@ -807,9 +842,16 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   bool q8 = D.act_quant == PM_AQ_Q8X_256;
   // (S.xq holds the tokens' Q8x form already when the routed experts ran first)
   if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum);
-  launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
+  const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
+  if (use_tc && D.type_gate == PM_TYPE_Q4_K && D.type_up == PM_TYPE_Q4_K)
+    CU(launch_tc_q4k(L, dv, true, false, g, T, T, S.xq, S.xd, nullptr, S.sh, c->dev_err));
+  else
+    launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum);
-  launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
+  if (use_tc && D.type_down == PM_TYPE_Q4_K)
+    CU(launch_tc_q4k(L, dv, true, true, g, T, T, S.shq, S.shd, nullptr, S.shared_out, c->dev_err));
+  else
+    launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
   if (D.shared == PM_SHARED_SIGMOID_GATED) launch_shared_gate_logit(L, dv, x, T, S.shared_logit);
   else S.shared_logit = nullptr;
   CU(cudaGetLastError());
@@ -873,7 +915,10 @@ static int32_t out_flush(pm_ctx *c, OutBuf *obs, int n) {
       CU(cudaMemcpyAsync(obs[i].host, obs[i].dev, obs[i].bytes, cudaMemcpyDeviceToHost, c->stream));
       any = true;
     }
-  if (any) CU(cudaStreamSynchronize(c->stream));
+  if (any) {
+    CU(cudaStreamSynchronize(c->stream));
+    return check_dev_err(c);
+  }
   return PM_OK;
 }
 

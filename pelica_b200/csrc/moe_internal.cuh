@@ -98,6 +98,10 @@ void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, i
 void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
                  const float *h, const int8_t *hq, const float *hd, const int32_t *hbsum,
                  float *eo);
+// tensor-core (tcgen05 int8) form of launch_gateup / launch_down for Q4_K x Q8x (prefill_tc.cu)
+cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
+                          int n_pairs, int max_count, const int8_t *xq, const float *xd,
+                          const float *wts, float *out, int *err);
 void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
                     const float *w, const float *shared_out, const float *shared_logit, int T,
                     float *y, bool accumulate);
