@@ -800,7 +800,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   {
     PROF(c, PH_GATEUP);
-    if (tc && D.type_gate == PM_TYPE_Q4_K && D.type_up == PM_TYPE_Q4_K)
+    if (tc && D.type_gate == D.type_up)
       CU(launch_tc_q4k(L, dv, false, false, g, P, T, S.xq, S.xd, w, S.h, c->dev_err));
     else
       launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
@@ -808,7 +808,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum); }
   {
     PROF(c, PH_DOWN);
-    if (tc && D.type_down == PM_TYPE_Q4_K)
+    if (tc)
       CU(launch_tc_q4k(L, dv, false, true, g, P, T, S.hq, S.hd, nullptr, S.eo, c->dev_err));
     else
       launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo);
@@ -843,12 +843,12 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   // (S.xq holds the tokens' Q8x form already when the routed experts ran first)
   if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
-  if (use_tc && D.type_gate == PM_TYPE_Q4_K && D.type_up == PM_TYPE_Q4_K)
+  if (use_tc && D.type_gate == D.type_up)
     CU(launch_tc_q4k(L, dv, true, false, g, T, T, S.xq, S.xd, nullptr, S.sh, c->dev_err));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum);
-  if (use_tc && D.type_down == PM_TYPE_Q4_K)
+  if (use_tc)
     CU(launch_tc_q4k(L, dv, true, true, g, T, T, S.shq, S.shd, nullptr, S.shared_out, c->dev_err));
   else
     launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);

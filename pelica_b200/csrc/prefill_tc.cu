@@ -98,7 +98,11 @@ struct TcArgs {
   int *err;
 };
 
-__global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
+// WT: the weight type of the product's matrices (PM_TYPE_Q4_K: planes hi, lo, m;
+// PM_TYPE_Q6_K: four base-4 digit planes of the int8 sub-scale, see below)
+template <int WT>
+__global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
+  constexpr int NP = WT == PM_TYPE_Q6_K ? 4 : 3;  // operand planes = TMEM accumulators
   extern __shared__ __align__(128) uint8_t smem[];
   const int a = blockIdx.y;
   if (a >= *A.g.n_groups) return;
@@ -128,7 +132,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
 
   // shared memory: three A planes (hi, lo, m), B, per-row scales, per-token scales
   uint8_t *sA = smem;                                   // 3 x [16 chunks][128 rows][16 B]
-  uint8_t *sB = smem + 3 * 32768;                       // [16 chunks][npad rows][16 B]
+  uint8_t *sB = smem + NP * 32768;                      // [16 chunks][npad rows][16 B]
   float2 *sDm = (float2 *)(sB + 16 * TC_NMAX * 16);     // [128] (d, dmin) of the block
   float *sXd = (float *)(sDm + TC_M);                   // [128] x.d of the block per token
   uint64_t *bar = (uint64_t *)(sXd + TC_NMAX);
@@ -157,18 +161,28 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
   const uint32_t tmem = *tmem_slot;
 
   // instruction descriptor: D s32, A unsigned 8-bit, B signed 8-bit, both K-major
-  const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) |
+  const uint32_t idesc = (2u << 4) | ((WT == PM_TYPE_Q6_K ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) |
                          ((uint32_t)(TC_M >> 4) << 24);
   // this thread's weight row (two threads per row, one half of the block each)
   const int m = tid >> 1, hf = tid & 1;
-  const uint8_t *rowp = nullptr;
+  const uint8_t *rowp = nullptr, *rp_qh = nullptr, *rp_sc = nullptr, *rp_d = nullptr;
   {
     int r;
     const WMat *W;
     if (A.down) { r = r0 + m; W = &W0; }
     else if (m < 64) { r = r0 + m; W = &W0; }
     else { r = r0 + m - 64; W = &W1; }
-    if (r < rows) rowp = W->plane[0] + (size_t)el * W->stride[0] + (size_t)r * nb * 144;
+    if (r < rows) {
+      if (WT == PM_TYPE_Q6_K) {
+        size_t rb = (size_t)r * nb;
+        rowp = W->plane[0] + (size_t)el * W->stride[0] + rb * 128;
+        rp_qh = W->plane[1] + (size_t)el * W->stride[1] + rb * 64;
+        rp_sc = W->plane[2] + (size_t)el * W->stride[2] + rb * 16;
+        rp_d = W->plane[3] + (size_t)el * W->stride[3] + rb * 2;
+      } else {
+        rowp = W->plane[0] + (size_t)el * W->stride[0] + (size_t)r * nb * 144;
+      }
+    }
   }
   // epilogue role: TMEM lanes of this warp's quarter, half of the token columns
   const int q = warp & 3, ch = warp >> 2;
@@ -181,7 +195,47 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
   bool dead = false;
   for (int b = 0; b < nb; b++) {
     // ---- 1. operands of block b into shared memory ----
-    if (rowp) {
+    if (rowp && WT == PM_TYPE_Q6_K) {
+      // Q6_K: value = sc * (q - 32), sc int8 per 16 values (one K chunk), q 6 bits.
+      // sc = 64*a3 + 16*a2 + 4*a1 + a0 with a0..a2 in 0..3 and a3 in -2..1, so each
+      // plane (q-32)*a_i fits int8 and isum = I0 + 4*I1 + 16*I2 + 64*I3 exactly.
+      const uint8_t *ql = rowp + (size_t)b * 128 + 64 * hf;
+      const uint8_t *qh = rp_qh + (size_t)b * 64 + 32 * hf;
+      uint4 qlv[4] = {__ldg((const uint4 *)ql), __ldg((const uint4 *)(ql + 16)), __ldg((const uint4 *)(ql + 32)),
+                      __ldg((const uint4 *)(ql + 48))};
+      uint4 qhv[2] = {__ldg((const uint4 *)qh), __ldg((const uint4 *)(qh + 16))};
+      uint2 scw = __ldg((const uint2 *)(rp_sc + (size_t)b * 16 + 8 * hf));
+      if (hf == 0) sDm[m] = make_float2(pm_f16(__ldg((const uint16_t *)(rp_d + (size_t)b * 2))), 0.0f);
+#pragma unroll
+      for (int qt = 0; qt < 4; qt++) {
+#pragma unroll
+        for (int lh = 0; lh < 2; lh++) {
+          const uint4 qlw = qlv[2 * (qt & 1) + lh];
+          const uint4 qhw = qhv[lh];
+          const int si = 2 * qt + lh;
+          const int sv = (int)(int8_t)((si < 4 ? scw.x >> (8 * si) : scw.y >> (8 * (si - 4))) & 0xff);
+          const uint32_t dg[4] = {(uint32_t)sv & 3u, ((uint32_t)sv >> 2) & 3u, ((uint32_t)sv >> 4) & 3u,
+                                  (uint32_t)(sv >> 6 < 0 ? -(sv >> 6) : (sv >> 6))};
+          const bool neg3 = (sv >> 6) < 0;
+          const uint32_t ws[4] = {qlw.x, qlw.y, qlw.z, qlw.w}, hs[4] = {qhw.x, qhw.y, qhw.z, qhw.w};
+          uint32_t o[4][4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            uint32_t qv = ((ws[i] >> (qt >= 2 ? 4 : 0)) & 0x0f0f0f0fu) | (((hs[i] >> (2 * qt)) & 0x03030303u) << 4);
+#pragma unroll
+            for (int pp = 0; pp < 4; pp++) {
+              uint32_t v = __vsub4(qv * dg[pp], 0x20202020u * dg[pp]);  // (q - 32) * digit per byte
+              if (pp == 3 && neg3) v = __vneg4(v);
+              o[pp][i] = v;
+            }
+          }
+          size_t off_c = (size_t)(8 * hf + 2 * qt + lh) * (TC_M * 16) + (size_t)m * 16;
+#pragma unroll
+          for (int pp = 0; pp < 4; pp++)
+            *(uint4 *)(sA + (size_t)pp * 32768 + off_c) = make_uint4(o[pp][0], o[pp][1], o[pp][2], o[pp][3]);
+        }
+      }
+    } else if (rowp) {
       const uint8_t *blk = rowp + (size_t)b * 144;
       uint4 hdr = __ldg((const uint4 *)blk);
       if (hf == 0) sDm[m] = make_float2(pm_f16(hdr.x), pm_f16(hdr.x >> 16));
@@ -217,9 +271,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
       if (hf == 0) sDm[m] = make_float2(0.0f, 0.0f);
       for (int kc = 8 * hf; kc < 8 * hf + 8; kc++) {
         size_t o = (size_t)kc * (TC_M * 16) + (size_t)m * 16;
-        *(uint4 *)(sA + o) = make_uint4(0, 0, 0, 0);
-        *(uint4 *)(sA + 32768 + o) = make_uint4(0, 0, 0, 0);
-        *(uint4 *)(sA + 65536 + o) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int pp = 0; pp < NP; pp++) *(uint4 *)(sA + (size_t)pp * 32768 + o) = make_uint4(0, 0, 0, 0);
       }
     }
     for (int i = tid; i < npad * 16; i += TC_NT) {
@@ -246,7 +299,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
       for (int ks = 0; ks < 8; ks++) {
         uint64_t db = tc_desc(b0 + (uint32_t)ks * 2u * (uint32_t)npad * 16u, (uint32_t)npad * 16u, 128u);
 #pragma unroll
-        for (int p = 0; p < 3; p++) {
+        for (int p = 0; p < NP; p++) {
           uint64_t da = tc_desc(a0 + (uint32_t)p * 32768u + (uint32_t)ks * 2u * (TC_M * 16u), TC_M * 16u, 128u);
           tc_mma_i8(tmem + (uint32_t)p * TC_NMAX, da, db, idesc, ks > 0 ? 1u : 0u);
         }
@@ -267,14 +320,26 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
           tc_ld32(tl + (uint32_t)(0 * TC_NMAX + ecol0 + c32), vh);
           tc_ld32(tl + (uint32_t)(1 * TC_NMAX + ecol0 + c32), vl);
           tc_ld32(tl + (uint32_t)(2 * TC_NMAX + ecol0 + c32), vm);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (WT == PM_TYPE_Q6_K) {
+            uint32_t v3[32];
+            tc_ld32(tl + (uint32_t)(3 * TC_NMAX + ecol0 + c32), v3);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
-            int isum = 8 * (int)vh[i] + (int)vl[i];
-            int msum = (int)vm[i];
-            float term = __fmul_rn(sXd[ecol0 + c32 + i],
-                                   __fsub_rn(__fmul_rn(dm.x, (float)isum), __fmul_rn(dm.y, (float)msum)));
-            total[c32 + i] = __fadd_rn(total[c32 + i], term);
+            for (int i = 0; i < 32; i++) {
+              int isum = (int)vh[i] + 4 * (int)vl[i] + 16 * (int)vm[i] + 64 * (int)v3[i];
+              float term = __fmul_rn(sXd[ecol0 + c32 + i], __fmul_rn(dm.x, (float)isum));
+              total[c32 + i] = __fadd_rn(total[c32 + i], term);
+            }
+          } else {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+              int isum = 8 * (int)vh[i] + (int)vl[i];
+              int msum = (int)vm[i];
+              float term = __fmul_rn(sXd[ecol0 + c32 + i],
+                                     __fsub_rn(__fmul_rn(dm.x, (float)isum), __fmul_rn(dm.y, (float)msum)));
+              total[c32 + i] = __fadd_rn(total[c32 + i], term);
+            }
           }
         }
       }
@@ -324,15 +389,21 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc_q4k(const TcArgs A) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
-static const size_t TC_SMEM = 3 * 32768 + 16 * TC_NMAX * 16 + TC_M * 8 + TC_NMAX * 4 + 64 + TC_NMAX * 4 + 256;
+static size_t tc_smem(int planes) {
+  return (size_t)planes * 32768 + 16 * TC_NMAX * 16 + TC_M * 8 + TC_NMAX * 4 + 64 + TC_NMAX * 4 + 256;
+}
 
-// Tensor-core form of launch_gateup / launch_down for Q4_K weights and Q8x
+// Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x
 // activations. `max_count` bounds the tokens of one group (for the grid's z extent).
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
                           int n_pairs, int max_count, const int8_t *xq, const float *xd,
                           const float *wts, float *out, int *err) {
   if (n_pairs == 0) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(k_tc_q4k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+  const WMat &W = down ? (shared ? ly.sdown : ly.down) : (shared ? ly.sgate : ly.gate);
+  const bool q6 = W.type == PM_TYPE_Q6_K;
+  const size_t smem = tc_smem(q6 ? 4 : 3);
+  const void *kern = q6 ? (const void *)k_tc<PM_TYPE_Q6_K> : (const void *)k_tc<PM_TYPE_Q4_K>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   TcArgs A;
   A.ly = ly;
@@ -344,11 +415,11 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.wts = wts;
   A.out = out;
   A.err = err;
-  const WMat &W = down ? (shared ? ly.sdown : ly.down) : (shared ? ly.sgate : ly.gate);
   int row_tiles = down ? (W.rows + TC_M - 1) / TC_M : (W.rows + 63) / 64;
   int groups = g.max_groups < n_pairs ? g.max_groups : n_pairs;
   dim3 grid(row_tiles, groups, (max_count + TC_NMAX - 1) / TC_NMAX);
-  k_tc_q4k<<<grid, TC_NT, TC_SMEM, L.stream>>>(A);
+  if (q6) k_tc<PM_TYPE_Q6_K><<<grid, TC_NT, smem, L.stream>>>(A);
+  else k_tc<PM_TYPE_Q4_K><<<grid, TC_NT, smem, L.stream>>>(A);
   if (L.count) ++*L.count;
   return cudaGetLastError();
 }
