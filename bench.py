@@ -53,7 +53,116 @@ WORKLOADS = {
     "c1_prefill": ("c1", 64, "OLMoE-1B-7B-shaped single MoE layer, 64-token prefill"),
     "c3_decode": ("c3", 1, "gpt-oss-20b-shaped 24-layer MoE stack, decode batch 1"),
     "c3_prefill": ("c3", 2048, "gpt-oss-20b-shaped 24-layer MoE stack, 2048-token prefill"),
+    # expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine
+    "c4_prefill_ep": ("c4", 4096, "DeepSeek-V3-shaped expert-parallel MoE (layer subset), 4096-token prefill"),
+    "c4_decode64_ep": ("c4", 64, "DeepSeek-V3-shaped expert-parallel MoE (layer subset), decode batch 64"),
 }
+
+
+def run_ep(args, cfg, n_layers, T, desc):
+    """Expert-parallel workloads: tokens split over the ranks, experts sharded, all-to-all
+    dispatch and combine per layer; one step = T tokens through n_layers layers."""
+    import torch
+    import torch.distributed as dist
+
+    import pelica_b200 as pb
+    from pelica_b200.ep import CudaBackend, ExpertParallelLayer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = pb.Context(local, stream=torch.cuda.current_stream().cuda_stream)
+    per = cfg.n_exp // world
+    layers = []
+    for l in range(n_layers):
+        ly = pb.MoeLayer(ctx, cfg.scaled(first_local_expert=rank * per, n_exp_local=per))
+        # the replicated parts (router, biases, shared expert) come out identical on every rank:
+        # they are seeded by the layer only; the experts by (layer, first local expert)
+        ly.fill_synthetic(SEED + 7919 * l, cfg.sigma, 0.0, cfg.select_bias_sigma)
+        layers.append(ExpertParallelLayer(CudaBackend(ly), cfg.n_exp, validate=False))
+    be0 = layers[0].be
+    Tl = T // world
+    POOL = 4
+    g = torch.Generator(device="cuda").manual_seed(SEED + rank)
+    pool = [torch.randn((Tl, cfg.d), generator=g, device="cuda", dtype=torch.float32) for _ in range(POOL)]
+
+    def step(i):
+        x = pool[i % POOL].clone()
+        for L in layers:
+            L.forward(be0.rmsnorm(x), add_into=x)
+        return x
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    launches0 = ctx.launches
+    ctx.timer_start()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ms = ctx.timer_stop() / args.steps
+    barrier()
+    clk = clocks.stop() if rank == 0 else None
+    launches = ctx.launches - launches0
+    ctx.profile(True)
+    step(0)
+    phases = {k: v[0] for k, v in ctx.profile_read().items() if v[1]}
+    ctx.profile(False)
+    # e2e: host tokens in, host result out, per step
+    hx = torch.empty((Tl, cfg.d), dtype=torch.float32).pin_memory()
+    hx.copy_(pool[0].cpu())
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        x = hx.cuda(non_blocking=True)
+        for L in layers:
+            L.forward(be0.rmsnorm(x), add_into=x)
+        hy = x.cpu()
+    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    barrier()
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank == 0:
+        pk = peaks()
+        pairs = T * cfg.top_k
+        macs = 3 * cfg.d * cfg.ff * (pairs + T * (1 if cfg.shared else 0)) * n_layers  # expert products per step
+        flops = 2 * macs
+        line = {
+            "metric": "moe_tokens_per_s", "value": T / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x u4 -> i32 (tcgen05 kind::i8), f32 scales",
+            "data": "synthetic",
+            "config": {"workload": desc, "tokens_per_step": T, "layers": n_layers, "of_layers": cfg.n_layers,
+                       "hidden": cfg.d, "experts": cfg.n_exp, "experts_per_gpu": per, "top_k": cfg.top_k, "ff": cfg.ff,
+                       "parallelism": f"ep{world}", "seed": SEED,
+                       "l2": f"inputs larger than L2: {per * cfg.expert_bytes() * n_layers / 1e9:.1f} GB of experts per GPU"},
+            "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": Tl * cfg.d * 4 * world, "d2h_bytes_per_step": Tl * cfg.d * 4 * world},
+            "gpu_launches": int(launches), "clocks": clk,
+            "roofline": {"bound": "tensor", "unit": "TFLOP/s", "achieved": flops / (ms * 1e-3) / 1e12 / world,
+                         "peak": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (bf16 dense sustained; the kernel runs int8)",
+                         "frac": flops / (ms * 1e-3) / 1e12 / world / pk["bf16_tflops_sustained"], "traffic": None,
+                         "kernel": "k_tc (tcgen05 int8 grouped expert products)", "per": "GPU",
+                         "tokens_per_s_full_model": T / (ms / 1e3) * n_layers / cfg.n_layers,
+                         "phases_ms_per_step_rank0": phases},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
@@ -215,6 +324,9 @@ def main():
         run_reference(args, cfg, n_layers, T, desc)
         return
 
+    if args.workload.endswith("_ep"):
+        run_ep(args, cfg, args.layers or 2, T, desc)
+        return
     world, rank, local, dist = dist_setup(args.gpus)
     import pelica_b200 as pb
 

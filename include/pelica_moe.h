@@ -279,6 +279,8 @@ PM_API int32_t pm_quant_act(pm_ctx *ctx, int32_t mode, const float *x, size_t n,
 /* ---- layer stacks (the benchmark's unit: x <- x + moe(rmsnorm(x)) per layer) */
 /* the engines' layer loop around the FFN (src/moe.rs:1279-1440 `after` ops:
  * rmsnorm, FFN, residual add) reduced to its MoE part */
+/* out[T][d] = x / rms(x) (unit norm weight), the norm pm_stack_forward applies */
+PM_API int32_t pm_rmsnorm(pm_ctx *ctx, const float *x, int32_t T, int32_t d, float eps, float *out);
 PM_API int32_t pm_stack_create(pm_ctx *ctx, pm_layer **layers, int32_t n_layers, float eps,
                                pm_stack **out);
 PM_API int32_t pm_stack_destroy(pm_stack *stack);

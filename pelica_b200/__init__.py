@@ -97,6 +97,7 @@ ABI = {
     "pm_combine": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32, _VP, C.c_uint32]),
     "pm_dequant": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP]),
     "pm_quant_act": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP, _VP, _VP]),
+    "pm_rmsnorm": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_float, _VP]),
     "pm_stack_create": (C.c_int32, [_VP, C.POINTER(_VP), C.c_int32, C.c_float, C.POINTER(_VP)]),
     "pm_stack_destroy": (C.c_int32, [_VP]),
     "pm_stack_forward": (C.c_int32, [_VP, _VP, C.c_int32, _VP]),

@@ -712,6 +712,7 @@ struct Scratch {
   int8_t *xq; float *xd; int32_t *xbsum;
   float *h; int8_t *hq; float *hd; int32_t *hbsum;
   float *eo;
+  uint32_t *tiles;  // tile list of the tensor-core kernels
   // shared expert
   int *one; uint32_t *zero_u, *tcount, *iota;
   float *sh; int8_t *shq; float *shd; int32_t *shbsum;
@@ -726,6 +727,7 @@ static size_t scratch_bytes(const pm_layer_desc &D, int T) {
   b += al(T * d) + al(T * (d / 256 + 1) * 4) + al(T * (d / 32) * 4);
   b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 256 + 1) * 4) + al(P * (ff / 32) * 4);
   b += al(P * d * 4);
+  b += al((4 + 2 * ((size_t)(P > (size_t)T ? P : (size_t)T) / 128 + E + 1)) * 4);
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     b += al(4) + al(4) * 2 + al((size_t)T * 4);
@@ -757,6 +759,7 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
   S.hd = ws_take<float>(c, P * (ff / 256 + 1));
   S.hbsum = ws_take<int32_t>(c, P * (ff / 32));
   S.eo = ws_take<float>(c, P * d);
+  S.tiles = ws_take<uint32_t>(c, 4 + 2 * ((P > (size_t)T ? P : (size_t)T) / 128 + E + 1));
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     S.one = ws_take<int>(c, 1);
@@ -801,7 +804,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   {
     PROF(c, PH_GATEUP);
     if (tc && D.type_gate == D.type_up)
-      CU(launch_tc_q4k(L, dv, false, false, g, P, T, S.xq, S.xd, w, S.h, c->dev_err));
+      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.xq, S.xd, w, S.h, c->dev_err));
     else
       launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
   }
@@ -809,7 +812,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   {
     PROF(c, PH_DOWN);
     if (tc)
-      CU(launch_tc_q4k(L, dv, false, true, g, P, T, S.hq, S.hd, nullptr, S.eo, c->dev_err));
+      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.hq, S.hd, nullptr, S.eo, c->dev_err));
     else
       launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo);
   }
@@ -844,12 +847,12 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   if (use_tc && D.type_gate == D.type_up)
-    CU(launch_tc_q4k(L, dv, true, false, g, T, T, S.xq, S.xd, nullptr, S.sh, c->dev_err));
+    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, nullptr, S.sh, c->dev_err));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum);
   if (use_tc)
-    CU(launch_tc_q4k(L, dv, true, true, g, T, T, S.shq, S.shd, nullptr, S.shared_out, c->dev_err));
+    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, nullptr, S.shared_out, c->dev_err));
   else
     launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
   if (D.shared == PM_SHARED_SIGMOID_GATED) launch_shared_gate_logit(L, dv, x, T, S.shared_logit);
@@ -998,8 +1001,8 @@ extern "C" int32_t pm_route(pm_layer *ly, const float *x, int32_t T, uint32_t *i
   OutBuf ob[2];
   uint32_t *idd = out_dev(c, ids, P, ob[0]);
   float *wd = out_dev(c, w, P, ob[1]);
-  launch_router(c->launch(), ly->dev, xd, T, ld);
-  launch_route(c->launch(), ly->dev, ld, T, idd, wd);
+  { PROF(c, PH_ROUTER); launch_router(c->launch(), ly->dev, xd, T, ld); }
+  { PROF(c, PH_ROUTE); launch_route(c->launch(), ly->dev, ld, T, idd, wd); }
   CU(cudaGetLastError());
   return out_flush(c, ob, 2);
 }
@@ -1123,7 +1126,8 @@ extern "C" int32_t pm_experts(pm_layer *ly, const float *x, int32_t T, const uin
 extern "C" int32_t pm_experts_rows(pm_layer *ly, const float *x, int32_t R, const uint32_t *eids,
                                    const float *w, float *out) {
   TRY(layer_ready(ly, true));
-  TRY(check_T(R));
+  if (R < 0 || R > PM_MAX_TOKENS * PM_MAX_TOPK)
+    return fail(PM_ERR_LIMIT, "pm_experts_rows: R=%d outside 0..%d", R, PM_MAX_TOKENS * PM_MAX_TOPK);
   if (R == 0) return PM_OK;
   if (!x || !eids || !w || !out) return fail(PM_ERR_INVALID, "pm_experts_rows: null argument");
   pm_ctx *c = ly->ctx;
@@ -1147,7 +1151,7 @@ extern "C" int32_t pm_experts_rows(pm_layer *ly, const float *x, int32_t R, cons
   pm_layer view = *ly;
   view.dev.desc = D;
   view.dev.usage = nullptr;
-  launch_plan(c->launch(), view.dev, idd, R, S.plan);
+  { PROF(c, PH_PLAN); launch_plan(c->launch(), view.dev, idd, R, S.plan); }
   TRY(dev_experts(&view, xd, R, S, wd));
   LayerDev cp = view.dev;
   cp.desc.weight_fold = PM_FOLD_BEFORE_DOWN;  // plain gather back to row order
@@ -1261,6 +1265,24 @@ extern "C" int32_t pm_quant_act(pm_ctx *c, int32_t mode, const float *x, size_t 
   launch_quant_q8x(c->launch(), xd, 1, (int)n, qd, sd, bd);
   CU(cudaGetLastError());
   return out_flush(c, ob, 3);
+}
+
+// x / rms(x) with unit weight, the norm the stack applies before each layer
+extern "C" int32_t pm_rmsnorm(pm_ctx *c, const float *x, int32_t T, int32_t d, float eps, float *out) {
+  if (!c || !x || !out) return fail(PM_ERR_INVALID, "pm_rmsnorm: null argument");
+  TRY(check_T(T));
+  if (T == 0) return PM_OK;
+  if (d < 32 || d % 32) return fail(PM_ERR_INVALID, "pm_rmsnorm: d=%d", d);
+  CU(cudaSetDevice(c->device));
+  size_t n = (size_t)T * d;
+  TRY(ws_reserve(c, 2 * al(n * 4) + 4096));
+  const float *xd;
+  TRY(in_dev(c, x, n, &xd));
+  OutBuf ob;
+  float *od = out_dev(c, out, n, ob);
+  launch_rmsnorm(c->launch(), xd, T, d, eps, od);
+  CU(cudaGetLastError());
+  return out_flush(c, &ob, 1);
 }
 
 // ---------------------------------------------------------------------------

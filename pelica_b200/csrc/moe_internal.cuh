@@ -99,8 +99,10 @@ void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int
                  const float *h, const int8_t *hq, const float *hd, const int32_t *hbsum,
                  float *eo);
 // tensor-core (tcgen05 int8) form of launch_gateup / launch_down for Q4_K x Q8x (prefill_tc.cu)
+// tile_buf: 4 + 2 * tc_max_tiles(n_pairs, g.max_groups) words of scratch for the tile list
+int tc_max_tiles(int n_pairs, int max_groups);
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
-                          int n_pairs, int max_count, const int8_t *xq, const float *xd,
+                          int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
                           const float *wts, float *out, int *err);
 void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
                     const float *w, const float *shared_out, const float *shared_logit, int T,

@@ -86,6 +86,8 @@ __device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *er
   return false;
 }
 
+int tc_max_tiles(int n_pairs, int max_groups);
+
 struct TcArgs {
   LayerDev ly;
   int shared;      // 1: the shared expert's matrices (one group over all tokens)
@@ -96,7 +98,35 @@ struct TcArgs {
   const float *wts;      // routing weights [T*K] (gate/up with fold) or null
   float *out;            // gate/up: h [P][ff]; down: eo [P][d]
   int *err;
+  const int *n_tiles;          // [1]
+  const uint32_t *tile_group;  // [tiles] index into the groups
+  const uint32_t *tile_n0;     // [tiles] first token of the tile inside its group
 };
+
+// The (group, token tile) list of a grouping: group a contributes ceil(count/128)
+// tiles. One CTA; groups <= 512 (experts of a layer, or the one shared-expert group
+// whose count may be the whole batch).
+__global__ void __launch_bounds__(512) k_tc_tiles(Groups g, int *n_tiles, uint32_t *tile_group,
+                                                  uint32_t *tile_n0, int max_tiles) {
+  __shared__ uint32_t s[512];
+  const int a = threadIdx.x;
+  const int ng = min(*g.n_groups, 512);
+  uint32_t tc = a < ng ? (g.count[a] + TC_NMAX - 1) / TC_NMAX : 0;
+  s[a] = tc;
+  __syncthreads();
+  for (int off = 1; off < 512; off <<= 1) {
+    uint32_t v = a >= off ? s[a - off] : 0;
+    __syncthreads();
+    s[a] += v;
+    __syncthreads();
+  }
+  uint32_t first = s[a] - tc;
+  for (uint32_t i = 0; i < tc && (int)(first + i) < max_tiles; i++) {
+    tile_group[first + i] = (uint32_t)a;
+    tile_n0[first + i] = i * TC_NMAX;
+  }
+  if (a == 511) *n_tiles = min((int)s[511], max_tiles);
+}
 
 // WT: the weight type of the product's matrices (PM_TYPE_Q4_K: planes hi, lo, m;
 // PM_TYPE_Q6_K: four base-4 digit planes of the int8 sub-scale, see below)
@@ -104,8 +134,9 @@ template <int WT>
 __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   constexpr int NP = WT == PM_TYPE_Q6_K ? 4 : 3;  // operand planes = TMEM accumulators
   extern __shared__ __align__(128) uint8_t smem[];
-  const int a = blockIdx.y;
-  if (a >= *A.g.n_groups) return;
+  // blockIdx.y walks the list of (group, 128-token tile) pairs made by k_tc_tiles
+  if ((int)blockIdx.y >= *A.n_tiles) return;
+  const int a = (int)A.tile_group[blockIdx.y];
   const LayerDev &ly = A.ly;
   const WMat &W0 = A.down ? (A.shared ? ly.sdown : ly.down) : (A.shared ? ly.sgate : ly.gate);
   const WMat &W1 = A.shared ? ly.sup : ly.up;  // used by gate/up only
@@ -113,8 +144,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   const int e = (int)A.g.expert[a];
   const int el = A.shared ? 0 : e - ly.first_local;
   const uint32_t off = A.g.offset[a], cnt = A.g.count[a];
-  const int n0 = blockIdx.z * TC_NMAX;
-  if ((uint32_t)n0 >= cnt) return;
+  const int n0 = (int)A.tile_n0[blockIdx.y];
   const int nvalid = min((int)cnt - n0, TC_NMAX);
   const int npad = (nvalid + 15) & ~15;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -192,6 +222,44 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
 #pragma unroll
   for (int i = 0; i < TC_NMAX / 2; i++) total[i] = 0.0f;
 
+  // raw bytes of one block, one step ahead, in registers:
+  //   Q4_K: pf[0] header, pf[1..4] this thread's 64 quant bytes
+  //   Q6_K: pf[0..3] ql (64 B), pf[4..5] qh (32 B), pf[6] = (8 scales, f16 d)
+  //   pfb[0..7]: this thread's 16-byte pieces of the tokens' activations, pfx: a token's x.d
+  uint4 pf[7], pfb[8];
+  float pfx = 0.0f;
+  auto load_raw = [&](int bb) {
+    if (bb >= nb) return;
+    if (rowp) {
+      if (WT == PM_TYPE_Q6_K) {
+        const uint8_t *ql = rowp + (size_t)bb * 128 + 64 * hf;
+        const uint8_t *qh = rp_qh + (size_t)bb * 64 + 32 * hf;
+#pragma unroll
+        for (int j = 0; j < 4; j++) pf[j] = __ldg((const uint4 *)(ql + 16 * j));
+        pf[4] = __ldg((const uint4 *)qh);
+        pf[5] = __ldg((const uint4 *)(qh + 16));
+        uint2 scw = __ldg((const uint2 *)(rp_sc + (size_t)bb * 16 + 8 * hf));
+        pf[6] = make_uint4(scw.x, scw.y, (uint32_t)__ldg((const uint16_t *)(rp_d + (size_t)bb * 2)), 0);
+      } else {
+        const uint8_t *blk = rowp + (size_t)bb * 144;
+        pf[0] = __ldg((const uint4 *)blk);
+#pragma unroll
+        for (int j = 0; j < 4; j++) pf[1 + j] = __ldg((const uint4 *)(blk + 16 + 64 * hf + 16 * j));
+      }
+    }
+    {
+      const int row = (tid & 127) < npad ? s_tok[tid & 127] : -1;
+      const int8_t *src = A.xq + (size_t)(row < 0 ? 0 : row) * cols + (size_t)bb * 256 + (tid >> 7) * 16;
+#pragma unroll
+      for (int j = 0; j < 8; j++) pfb[j] = row >= 0 ? *(const uint4 *)(src + 32 * j) : make_uint4(0, 0, 0, 0);
+    }
+    if (tid < TC_NMAX) {
+      int row = s_tok[tid];
+      pfx = row >= 0 ? A.xd[(size_t)row * nb + bb] : 0.0f;
+    }
+  };
+  load_raw(0);
+
   bool dead = false;
   for (int b = 0; b < nb; b++) {
     // ---- 1. operands of block b into shared memory ----
@@ -199,13 +267,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       // Q6_K: value = sc * (q - 32), sc int8 per 16 values (one K chunk), q 6 bits.
       // sc = 64*a3 + 16*a2 + 4*a1 + a0 with a0..a2 in 0..3 and a3 in -2..1, so each
       // plane (q-32)*a_i fits int8 and isum = I0 + 4*I1 + 16*I2 + 64*I3 exactly.
-      const uint8_t *ql = rowp + (size_t)b * 128 + 64 * hf;
-      const uint8_t *qh = rp_qh + (size_t)b * 64 + 32 * hf;
-      uint4 qlv[4] = {__ldg((const uint4 *)ql), __ldg((const uint4 *)(ql + 16)), __ldg((const uint4 *)(ql + 32)),
-                      __ldg((const uint4 *)(ql + 48))};
-      uint4 qhv[2] = {__ldg((const uint4 *)qh), __ldg((const uint4 *)(qh + 16))};
-      uint2 scw = __ldg((const uint2 *)(rp_sc + (size_t)b * 16 + 8 * hf));
-      if (hf == 0) sDm[m] = make_float2(pm_f16(__ldg((const uint16_t *)(rp_d + (size_t)b * 2))), 0.0f);
+      const uint4 qlv[4] = {pf[0], pf[1], pf[2], pf[3]};
+      const uint4 qhv[2] = {pf[4], pf[5]};
+      const uint2 scw = make_uint2(pf[6].x, pf[6].y);
+      if (hf == 0) sDm[m] = make_float2(pm_f16(pf[6].z), 0.0f);
 #pragma unroll
       for (int qt = 0; qt < 4; qt++) {
 #pragma unroll
@@ -236,14 +301,12 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         }
       }
     } else if (rowp) {
-      const uint8_t *blk = rowp + (size_t)b * 144;
-      uint4 hdr = __ldg((const uint4 *)blk);
+      const uint4 hdr = pf[0];
       if (hf == 0) sDm[m] = make_float2(pm_f16(hdr.x), pm_f16(hdr.x >> 16));
 #pragma unroll
       for (int cc = 0; cc < 2; cc++) {
         int c = 2 * hf + cc;
-        uint4 w0 = __ldg((const uint4 *)(blk + 16 + 32 * c));
-        uint4 w1 = __ldg((const uint4 *)(blk + 16 + 32 * c + 16));
+        const uint4 w0 = pf[1 + 2 * cc], w1 = pf[2 + 2 * cc];
         int sc0, m0, sc1, m1;
         pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c, sc0, m0);
         pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c + 1, sc1, m1);
@@ -275,17 +338,15 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         for (int pp = 0; pp < NP; pp++) *(uint4 *)(sA + (size_t)pp * 32768 + o) = make_uint4(0, 0, 0, 0);
       }
     }
-    for (int i = tid; i < npad * 16; i += TC_NT) {
-      int n = i % npad, kc = i / npad;
-      int row = s_tok[n];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row >= 0) v = *(const uint4 *)(A.xq + (size_t)row * cols + (size_t)b * 256 + kc * 16);
-      *(uint4 *)(sB + (size_t)kc * (npad * 16) + (size_t)n * 16) = v;
+    if ((tid & 127) < npad) {  // thread = (token row tid & 127, chunks tid >> 7, +2, ...)
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        *(uint4 *)(sB + (size_t)((tid >> 7) + 2 * j) * (npad * 16) + (size_t)(tid & 127) * 16) = pfb[j];
     }
-    for (int n = tid; n < TC_NMAX; n += TC_NT) {
-      int row = s_tok[n];
-      sXd[n] = row >= 0 ? A.xd[(size_t)row * nb + b] : 0.0f;
-    }
+    if (tid < TC_NMAX) sXd[tid] = pfx;
+    // the next block's bytes start their trip from HBM now, and land while this
+    // block is multiplied and folded
+    load_raw(b + 1);
     // generic-proxy writes -> visible to the tensor core's (async proxy) reads
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -389,6 +450,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
+int tc_max_tiles(int n_pairs, int max_groups) {
+  int groups = max_groups < n_pairs ? max_groups : n_pairs;
+  return n_pairs / TC_NMAX + groups;
+}
 static size_t tc_smem(int planes) {
   return (size_t)planes * 32768 + 16 * TC_NMAX * 16 + TC_M * 8 + TC_NMAX * 4 + 64 + TC_NMAX * 4 + 256;
 }
@@ -396,9 +461,15 @@ static size_t tc_smem(int planes) {
 // Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x
 // activations. `max_count` bounds the tokens of one group (for the grid's z extent).
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
-                          int n_pairs, int max_count, const int8_t *xq, const float *xd,
+                          int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
                           const float *wts, float *out, int *err) {
   if (n_pairs == 0) return cudaSuccess;
+  // tile list: at most one partial tile per group plus the full ones
+  const int max_tiles = tc_max_tiles(n_pairs, g.max_groups);
+  int *n_tiles = (int *)tile_buf;
+  uint32_t *tile_group = tile_buf + 4, *tile_n0 = tile_buf + 4 + max_tiles;
+  k_tc_tiles<<<1, 512, 0, L.stream>>>(g, n_tiles, tile_group, tile_n0, max_tiles);
+  if (L.count) ++*L.count;
   const WMat &W = down ? (shared ? ly.sdown : ly.down) : (shared ? ly.sgate : ly.gate);
   const bool q6 = W.type == PM_TYPE_Q6_K;
   const size_t smem = tc_smem(q6 ? 4 : 3);
@@ -415,9 +486,11 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.wts = wts;
   A.out = out;
   A.err = err;
+  A.n_tiles = n_tiles;
+  A.tile_group = tile_group;
+  A.tile_n0 = tile_n0;
   int row_tiles = down ? (W.rows + TC_M - 1) / TC_M : (W.rows + 63) / 64;
-  int groups = g.max_groups < n_pairs ? g.max_groups : n_pairs;
-  dim3 grid(row_tiles, groups, (max_count + TC_NMAX - 1) / TC_NMAX);
+  dim3 grid(row_tiles, max_tiles);
   if (q6) k_tc<PM_TYPE_Q6_K><<<grid, TC_NT, smem, L.stream>>>(A);
   else k_tc<PM_TYPE_Q4_K><<<grid, TC_NT, smem, L.stream>>>(A);
   if (L.count) ++*L.count;

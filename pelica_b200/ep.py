@@ -80,13 +80,20 @@ class CudaBackend:
         self._check(self.lib.pm_shared(self.layer.h, self._p(x), x.shape[0], self._p(out)))
         return out
 
-    def combine(self, pair_out, ids, w, shared):
+    def combine(self, pair_out, ids, w, shared, into=None):
         T = ids.shape[0]
-        y = torch.empty((T, self.desc.d), dtype=torch.float32, device=ids.device)
+        y = into if into is not None else torch.empty((T, self.desc.d), dtype=torch.float32, device=ids.device)
         if T:
             self._check(self.lib.pm_combine(self.layer.h, self._p(pair_out), self._p(ids), self._p(w),
-                                            self._p(shared) if shared is not None else None, T, self._p(y), 0))
+                                            self._p(shared) if shared is not None else None, T, self._p(y),
+                                            1 if into is not None else 0))
         return y
+
+    def rmsnorm(self, x, eps=1e-6):
+        out = torch.empty_like(x)
+        if x.shape[0]:
+            self._check(self.lib.pm_rmsnorm(self.layer.ctx.h, self._p(x), x.shape[0], x.shape[1], eps, self._p(out)))
+        return out
 
     def _check(self, rc):
         from . import _check
@@ -97,8 +104,9 @@ class CudaBackend:
 class ExpertParallelLayer:
     """One MoE layer sharded by expert over the ranks of a process group."""
 
-    def __init__(self, backend, n_exp: int, group=None):
+    def __init__(self, backend, n_exp: int, group=None, validate: bool = True):
         self.be = backend
+        self.validate = validate  # host check of the received expert ids (two small device reads per call)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -121,8 +129,9 @@ class ExpertParallelLayer:
                                input_split_sizes=list(send_counts), group=self.group)
         return out
 
-    def forward(self, x):
-        """x [T_local, d] f32 (this rank's tokens, already normed) -> y [T_local, d]."""
+    def forward(self, x, add_into=None):
+        """x [T_local, d] f32 (this rank's tokens, already normed) -> y [T_local, d];
+        with add_into (a [T_local, d] tensor, the residual) the result is added into it."""
         be, W = self.be, self.world
         T = x.shape[0]
         ids, w = be.route(x)
@@ -148,12 +157,12 @@ class ExpertParallelLayer:
         recv_e = self._a2a(pair_e, sc, rc)
         recv_w = self._a2a(pair_w, sc, rc)
         lo = self.rank * self.per_rank
-        if recv_e.numel() and (int(recv_e.min()) < lo or int(recv_e.max()) >= lo + self.per_rank):
+        if self.validate and recv_e.numel() and (int(recv_e.min()) < lo or int(recv_e.max()) >= lo + self.per_rank):
             raise RuntimeError(f"rank {self.rank}: received a pair for an expert outside [{lo}, {lo + self.per_rank})")
         out_rows = be.experts_rows(recv_x, recv_e, recv_w)
         pair_out = self._a2a(out_rows, rc, sc)  # back: plan order of the sender
         shared = be.shared(x)
-        y = be.combine(pair_out, ids, w, shared)
+        y = be.combine(pair_out, ids, w, shared, add_into) if add_into is not None else be.combine(pair_out, ids, w, shared)
         self.last_stats = {"pairs_sent": int(P), "rows_served": int(sum(rc)),
                            "bytes_dispatched": int(P) * x.shape[1] * 4}
         return y
