@@ -167,38 +167,40 @@ void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, cons
 // ===========================================================================
 // activation quantiser: `Q8x::new` (src/ds4_cpu.rs:13-35)
 // ===========================================================================
-// one 256-thread CTA per 256-value block; warp w owns bsum[w]
+// one warp per 256-value block, 8 blocks per CTA; lane L holds values L, L+32, ...
+// so that value group j (32 consecutive values) is exactly register j across the warp
 __global__ void __launch_bounds__(256) k_quant_q8x(const float *__restrict__ x, size_t n_blocks,
                                                   int8_t *q, float *d, int32_t *bsum) {
-  __shared__ float wmax[8];
-  size_t b = blockIdx.x;
+  size_t b = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (b >= n_blocks) return;
-  int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float v = x[b * 256 + tid];
-  float a = pm_warp_max(fabsf(v));
-  if (lane == 0) wmax[warp] = a;
-  __syncthreads();
-  float amax = wmax[0];
+  int lane = threadIdx.x & 31;
+  float v[8];
 #pragma unroll
-  for (int i = 1; i < 8; i++) amax = fmaxf(amax, wmax[i]);
-  int r = 0;
-  if (amax != 0.0f) {
-    float id = __fdiv_rn(127.0f, amax);
-    float f = roundf(__fmul_rn(v, id));  // half away from zero, as f32::round
-    f = fminf(fmaxf(f, -127.0f), 127.0f);
-    r = (int)f;
+  for (int j = 0; j < 8; j++) v[j] = x[b * 256 + 32 * j + lane];
+  float a = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
+  a = pm_warp_max(a);
+  float id = a != 0.0f ? __fdiv_rn(127.0f, a) : 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    int r = 0;
+    if (a != 0.0f) {
+      float f = roundf(__fmul_rn(v[j], id));  // half away from zero, as f32::round
+      r = (int)fminf(fmaxf(f, -127.0f), 127.0f);
+    }
+    q[b * 256 + 32 * j + lane] = (int8_t)r;
+    int s = __reduce_add_sync(PM_FULL, r);
+    if (lane == 0) bsum[b * 8 + j] = s;
   }
-  q[b * 256 + tid] = (int8_t)r;
-  int s = pm_warp_sum_i32(r);
-  if (lane == 0) bsum[b * 8 + warp] = s;
-  if (tid == 0) d[b] = amax != 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+  if (lane == 0) d[b] = a != 0.0f ? __fdiv_rn(a, 127.0f) : 0.0f;
 }
 
 void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d,
                       int32_t *bsum) {
   size_t nb = rows * (size_t)(n / 256);
   if (nb == 0) return;
-  KLAUNCH(L, k_quant_q8x, (unsigned)nb, 256, 0, x, nb, q, d, bsum);
+  KLAUNCH(L, k_quant_q8x, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d, bsum);
 }
 
 // ===========================================================================

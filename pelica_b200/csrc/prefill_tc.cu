@@ -193,8 +193,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   // instruction descriptor: D s32, A unsigned 8-bit, B signed 8-bit, both K-major
   const uint32_t idesc = (2u << 4) | ((WT == PM_TYPE_Q6_K ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) |
                          ((uint32_t)(TC_M >> 4) << 24);
-  // this thread's weight row (two threads per row, one half of the block each)
-  const int m = tid >> 1, hf = tid & 1;
+  // this thread: one weight row, one half of the block
+  const int m = tid & 127, hf = tid >> 7;  // a warp = 32 consecutive rows, one half: conflict-free 16-byte stores
   const uint8_t *rowp = nullptr, *rp_qh = nullptr, *rp_sc = nullptr, *rp_d = nullptr;
   {
     int r;
