@@ -312,10 +312,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_decode", choices=list(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers")
+    ap.add_argument("--tokens", type=int, default=0, help="override the tokens per step of a workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
 
     key, T, desc = WORKLOADS[args.workload]
+    if args.tokens:
+        T, desc = args.tokens, f"{desc} [tokens per step overridden: {args.tokens}]"
     cfg = synth.CONFIGS[key]
     n_layers = args.layers or cfg.n_layers
     if args.impl == "reference":

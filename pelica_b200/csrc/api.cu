@@ -709,13 +709,13 @@ struct Scratch {
   uint32_t *ids;
   float *w;
   PlanDev plan;
-  int8_t *xq; float *xd; int32_t *xbsum;
-  float *h; int8_t *hq; float *hd; int32_t *hbsum;
+  int8_t *xq; float *xd; int32_t *xbsum; uint16_t *xbm; int32_t *xs;
+  float *h; int8_t *hq; float *hd; int32_t *hbsum; uint16_t *hbm; int32_t *hs;
   float *eo;
   uint32_t *tiles;  // tile list of the tensor-core kernels
   // shared expert
   int *one; uint32_t *zero_u, *tcount, *iota;
-  float *sh; int8_t *shq; float *shd; int32_t *shbsum;
+  float *sh; int8_t *shq; float *shd; int32_t *shbsum; uint16_t *shbm; int32_t *shs;
   float *shared_out, *shared_logit;
 };
 
@@ -724,14 +724,14 @@ static size_t scratch_bytes(const pm_layer_desc &D, int T) {
   size_t b = 0;
   b += al(T * E * 4) + al(P * 4) * 2;                  // logits, ids, w
   b += al(4) + al(E * 4) * 5 + al(P * 4) * 3;          // plan
-  b += al(T * d) + al(T * (d / 256 + 1) * 4) + al(T * (d / 32) * 4);
-  b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 256 + 1) * 4) + al(P * (ff / 32) * 4);
+  b += al(T * d) + al(T * (d / 256 + 1) * 4) * 2 + al(T * (d / 32) * 4) * 2;
+  b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 256 + 1) * 4) * 2 + al(P * (ff / 32) * 4) * 2;
   b += al(P * d * 4);
-  b += al((4 + 2 * ((size_t)(P > (size_t)T ? P : (size_t)T) / 128 + E + 1)) * 4);
+  b += al((4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1)) * 4);
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     b += al(4) + al(4) * 2 + al((size_t)T * 4);
-    b += al(T * sf * 4) + al(T * sf) + al(T * (sf / 256 + 1) * 4) + al(T * (sf / 32) * 4);
+    b += al(T * sf * 4) + al(T * sf) + al(T * (sf / 256 + 1) * 4) * 2 + al(T * (sf / 32) * 4) * 2;
     b += al(T * d * 4) + al((size_t)T * 4);
   }
   return b + 4096;
@@ -754,12 +754,16 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
   S.xq = ws_take<int8_t>(c, T * d);
   S.xd = ws_take<float>(c, T * (d / 256 + 1));
   S.xbsum = ws_take<int32_t>(c, T * (d / 32));
+  S.xbm = ws_take<uint16_t>(c, T * (d / 16));
+  S.xs = ws_take<int32_t>(c, T * (d / 256 + 1));
   S.h = ws_take<float>(c, P * ff);
   S.hq = ws_take<int8_t>(c, P * ff);
   S.hd = ws_take<float>(c, P * (ff / 256 + 1));
   S.hbsum = ws_take<int32_t>(c, P * (ff / 32));
+  S.hbm = ws_take<uint16_t>(c, P * (ff / 16));
+  S.hs = ws_take<int32_t>(c, P * (ff / 256 + 1));
   S.eo = ws_take<float>(c, P * d);
-  S.tiles = ws_take<uint32_t>(c, 4 + 2 * ((P > (size_t)T ? P : (size_t)T) / 128 + E + 1));
+  S.tiles = ws_take<uint32_t>(c, 4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1));
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     S.one = ws_take<int>(c, 1);
@@ -770,6 +774,8 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
     S.shq = ws_take<int8_t>(c, T * sf);
     S.shd = ws_take<float>(c, T * (sf / 256 + 1));
     S.shbsum = ws_take<int32_t>(c, T * (sf / 32));
+    S.shbm = ws_take<uint16_t>(c, T * (sf / 16));
+    S.shs = ws_take<int32_t>(c, T * (sf / 256 + 1));
     S.shared_out = ws_take<float>(c, T * d);
     S.shared_logit = ws_take<float>(c, (size_t)T);
   } else {
@@ -799,20 +805,20 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   int P = T * D.top_k;
   Groups g = plan_groups(S.plan, D.n_exp);
   bool q8 = D.act_quant == PM_AQ_Q8X_256;
-  if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum); }
+  if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   {
     PROF(c, PH_GATEUP);
     if (tc && D.type_gate == D.type_up)
-      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.xq, S.xd, w, S.h, c->dev_err));
+      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.xq, S.xd, S.xbm, S.xs, w, S.h, c->dev_err));
     else
       launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
   }
-  if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum); }
+  if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum, S.hbm, S.hs); }
   {
     PROF(c, PH_DOWN);
     if (tc)
-      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.hq, S.hd, nullptr, S.eo, c->dev_err));
+      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.hq, S.hd, S.hbm, S.hs, nullptr, S.eo, c->dev_err));
     else
       launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo);
   }
@@ -844,15 +850,15 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   g.max_groups = 1;
   bool q8 = D.act_quant == PM_AQ_Q8X_256;
   // (S.xq holds the tokens' Q8x form already when the routed experts ran first)
-  if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum);
+  if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   if (use_tc && D.type_gate == D.type_up)
-    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, nullptr, S.sh, c->dev_err));
+    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
-  if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum);
+  if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum, S.shbm, S.shs);
   if (use_tc)
-    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, nullptr, S.shared_out, c->dev_err));
+    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err));
   else
     launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
   if (D.shared == PM_SHARED_SIGMOID_GATED) launch_shared_gate_logit(L, dv, x, T, S.shared_logit);

@@ -170,7 +170,8 @@ void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, cons
 // one warp per 256-value block, 8 blocks per CTA; lane L holds values L, L+32, ...
 // so that value group j (32 consecutive values) is exactly register j across the warp
 __global__ void __launch_bounds__(256) k_quant_q8x(const float *__restrict__ x, size_t n_blocks,
-                                                  int8_t *q, float *d, int32_t *bsum) {
+                                                  int8_t *q, float *d, int32_t *bsum, uint16_t *bm,
+                                                  int32_t *xs) {
   size_t b = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (b >= n_blocks) return;
   int lane = threadIdx.x & 31;
@@ -182,6 +183,7 @@ __global__ void __launch_bounds__(256) k_quant_q8x(const float *__restrict__ x, 
   for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
   a = pm_warp_max(a);
   float id = a != 0.0f ? __fdiv_rn(127.0f, a) : 0.0f;
+  int tot = 0;
 #pragma unroll
   for (int j = 0; j < 8; j++) {
     int r = 0;
@@ -191,16 +193,26 @@ __global__ void __launch_bounds__(256) k_quant_q8x(const float *__restrict__ x, 
     }
     q[b * 256 + 32 * j + lane] = (int8_t)r;
     int s = __reduce_add_sync(PM_FULL, r);
-    if (lane == 0) bsum[b * 8 + j] = s;
+    tot += s;
+    if (lane == 0) {
+      bsum[b * 8 + j] = s;
+      if (bm) {  // s = 64 * (s >> 6) + (s & 63), both parts exact in f16
+        bm[b * 16 + j] = __half_as_ushort(__int2half_rn((s >> 6) * 64));
+        bm[b * 16 + 8 + j] = __half_as_ushort(__int2half_rn(s & 63));
+      }
+    }
   }
-  if (lane == 0) d[b] = a != 0.0f ? __fdiv_rn(a, 127.0f) : 0.0f;
+  if (lane == 0) {
+    d[b] = a != 0.0f ? __fdiv_rn(a, 127.0f) : 0.0f;
+    if (xs) xs[b] = tot;
+  }
 }
 
 void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d,
-                      int32_t *bsum) {
+                      int32_t *bsum, uint16_t *bm, int32_t *xs) {
   size_t nb = rows * (size_t)(n / 256);
   if (nb == 0) return;
-  KLAUNCH(L, k_quant_q8x, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d, bsum);
+  KLAUNCH(L, k_quant_q8x, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d, bsum, bm, xs);
 }
 
 // ===========================================================================

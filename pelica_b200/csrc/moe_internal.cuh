@@ -85,8 +85,11 @@ void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t n_blocks, con
                    const uint8_t *p1, const uint8_t *p2, const uint8_t *p3);
 void launch_dequant(const Launch &L, int type, size_t n_values, const uint8_t *p0,
                     const uint8_t *p1, const uint8_t *p2, const uint8_t *p3, float *out);
+// bm (optional): per block 16 f16 values, 64 * (bsum_j >> 6) for the 8 sub-blocks, then
+// bsum_j & 63: the operand the tensor-core kernel multiplies the Q4_K mins with;
+// xs (optional): per block the sum of its 256 values (the Q6_K offset term)
 void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d,
-                      int32_t *bsum);
+                      int32_t *bsum, uint16_t *bm = nullptr, int32_t *xs = nullptr);
 void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits);
 void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int T, uint32_t *ids,
                   float *w);
@@ -103,7 +106,7 @@ void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int
 int tc_max_tiles(int n_pairs, int max_groups);
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
                           int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
-                          const float *wts, float *out, int *err);
+                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err);
 void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
                     const float *w, const float *shared_out, const float *shared_logit, int T,
                     float *y, bool accumulate);

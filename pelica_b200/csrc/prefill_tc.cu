@@ -2,28 +2,32 @@
 // tensor cores (tcgen05.mma kind::i8, accumulators in TMEM), exact in the integer
 // domain of the reference's CPU path (src/ds4_cpu.rs:59-83).
 //
-// One CTA = (128 weight rows of one active expert) x (up to 128 of its tokens).
-// Per 256-value block b of the rows:
-//   1. CUDA cores unpack the Q4_K block into THREE int8 operand planes in shared
-//      memory (K-major, no swizzle, 8x16-byte core matrices):
-//        A_hi = nibble * (sc >> 3), A_lo = nibble * (sc & 7), A_m = m (per sub-block)
-//      so that with the token's int8 activations xq as the other operand
+// One CTA = (128 weight rows of one active expert) x (up to 64 of its tokens); two CTAs
+// per SM. Per 256-value block b of the rows:
+//   1. CUDA cores unpack the block into int8 operand planes in shared memory (K-major,
+//      no swizzle, 8x16-byte core matrices). Q4_K: A_hi = nibble * (sc >> 3),
+//      A_lo = nibble * (sc & 7), so that with the token's int8 activations xq
 //        isum = 8 * (A_hi . xq) + (A_lo . xq) = sum_j sc_j * sum_i nib_ji * xq_ji
-//        msum = A_m . xq                     = sum_j m_j * bsum_j
-//      are the reference's exact integer sums (6-bit scales do not fit one int8
-//      product with a nibble; two 3-bit halves do).
-//   2. one thread issues 24 tcgen05.mma (8 K-steps of 32 x 3 planes) into three TMEM
-//      accumulators and commits to an mbarrier;
+//      (6-bit scales do not fit one int8 product with a nibble; two 3-bit halves do),
+//      and msum = sum_j m_j * bsum_j comes from one K=16 f16 product (see k_tc). The
+//      tokens' activations arrive by cp.async while the previous block is folded.
+//   2. one thread issues the tcgen05.mma of the block (8 K-steps of 32 per plane) into
+//      TMEM accumulators and commits to an mbarrier;
 //   3. every warp reads its TMEM lanes (tcgen05.ld) and adds the block's float term
 //      total += x.d[b] * (d * isum - dmin * msum) in block order, as `row_scalar`.
 // Gate and up rows share a CTA (64 + 64 rows) so SwiGLU is fused in the epilogue;
 // down rows write the pair outputs. Waits are time-bounded; TMEM is freed on
 // every exit path.
+#include <cuda_fp16.h>
+
 #include "moe_internal.cuh"
 
 #define TC_NT 256
 #define TC_M 128
-#define TC_NMAX 128
+#define TC_NMAX 64
+#define TC_TMEM_COLS 256
+#define TC_RAW_Q4 (TC_M * 144)                       /* bytes of the raw staging area */
+#define TC_RAW_Q6 (TC_M * (128 + 64 + 16 + 4))
 #define TC_WAIT_NS 2000000000ull
 
 __device__ __forceinline__ uint32_t tc_s32(const void *p) {
@@ -66,13 +70,37 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t r[32]) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t r[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_c),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// global -> shared without registers (completion: cp.async.wait_all by the issuing thread)
+__device__ __forceinline__ void tc_cp16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tc_cp4(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ bool tc_bar_test(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       " selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(tc_s32(bar)), "r"(parity), "r"(20000u)
+      : "r"(tc_s32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -88,6 +116,20 @@ __device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *er
 
 int tc_max_tiles(int n_pairs, int max_groups);
 
+// Compile with -DPM_TC_TRACE to stamp the phases of CTA (0, 0) with the SM clock:
+// [thread 0 | thread 255][block][stamp]; read back with pm_debug_tc_trace.
+#ifdef PM_TC_TRACE
+__device__ unsigned long long g_tc_trace[2 * 32 * 8];
+#define TC_STAMP(b, i)                                                                         \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 255) && (b) < 32)              \
+    g_tc_trace[((tid ? 1 : 0) * 32 + (b)) * 8 + (i)] = clock64();
+extern "C" __attribute__((visibility("default"))) int pm_debug_tc_trace(unsigned long long *out) {
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));
+}
+#else
+#define TC_STAMP(b, i)
+#endif
+
 struct TcArgs {
   LayerDev ly;
   int shared;      // 1: the shared expert's matrices (one group over all tokens)
@@ -95,6 +137,8 @@ struct TcArgs {
   Groups g;
   const int8_t *xq;      // gate/up: [T][d] by token; down: [P][ff] by pair
   const float *xd;       // per row of xq: [cols/256]
+  const uint16_t *xbm;   // per row of xq: [cols/256][16] f16: 64 * (bsum_j >> 6) (8), bsum_j & 63 (8)
+  const int32_t *xs;     // per row of xq: [cols/256] sum of the block's values
   const float *wts;      // routing weights [T*K] (gate/up with fold) or null
   float *out;            // gate/up: h [P][ff]; down: eo [P][d]
   int *err;
@@ -128,13 +172,24 @@ __global__ void __launch_bounds__(512) k_tc_tiles(Groups g, int *n_tiles, uint32
   if (a == 511) *n_tiles = min((int)s[511], max_tiles);
 }
 
-// WT: the weight type of the product's matrices (PM_TYPE_Q4_K: planes hi, lo, m;
-// PM_TYPE_Q6_K: four base-4 digit planes of the int8 sub-scale, see below)
+// WT: the weight type of the product's matrices.
+//  PM_TYPE_Q4_K: u8 planes hi = nibble * (sc >> 3), lo = nibble * (sc & 7) and one
+//    kind::f16 product for the mins: A_m = (m_0..m_7, m_0..m_7) against the token's
+//    (64 * (bsum_j >> 6), bsum_j & 63) - every product and the sum (< 2^22) are exact in
+//    f32, so the accumulator holds msum = sum_j m_j * bsum_j as an integer-valued float.
+//  PM_TYPE_Q6_K: the product v = sc * (q - 32) in [-4064, 4096] is split after the
+//    multiplication: v + 4128 = 64 * th + tl with th in [1, 128], tl in [0, 63] - two u8
+//    planes, and isum = 64 * (th . xq) + (tl . xq) - 4128 * sum(xq) exactly.
+// The weight bytes of a block arrive by cp.async in row-contiguous pieces (a warp reads
+// whole 144-byte / 128-byte runs) into a raw staging area, from which each thread
+// unpacks its row. Two CTAs share an SM (<= 113 KB of shared memory, 256 of the 512 TMEM
+// columns, <= 128 registers): while one waits for its products or folds them, the other
+// unpacks.
 template <int WT>
-__global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
-  constexpr int NP = WT == PM_TYPE_Q6_K ? 4 : 3;  // operand planes = TMEM accumulators
+__global__ void __launch_bounds__(TC_NT, 2) k_tc(const TcArgs A) {
+  constexpr bool Q6 = WT == PM_TYPE_Q6_K;
   extern __shared__ __align__(128) uint8_t smem[];
-  // blockIdx.y walks the list of (group, 128-token tile) pairs made by k_tc_tiles
+  // blockIdx.y walks the list of (group, token tile) pairs made by k_tc_tiles
   if ((int)blockIdx.y >= *A.n_tiles) return;
   const int a = (int)A.tile_group[blockIdx.y];
   const LayerDev &ly = A.ly;
@@ -147,7 +202,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   const int n0 = (int)A.tile_n0[blockIdx.y];
   const int nvalid = min((int)cnt - n0, TC_NMAX);
   const int npad = (nvalid + 15) & ~15;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const bool local = el >= 0 && el < (A.shared ? 1 : ly.n_local);
   const int rows_per_cta = A.down ? TC_M : TC_M / 2;  // gate/up: 64 gate + 64 up rows
   const int r0 = blockIdx.x * rows_per_cta;
@@ -160,117 +215,191 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     return;
   }
 
-  // shared memory: three A planes (hi, lo, m), B, per-row scales, per-token scales
-  uint8_t *sA = smem;                                   // 3 x [16 chunks][128 rows][16 B]
-  uint8_t *sB = smem + NP * 32768;                      // [16 chunks][npad rows][16 B]
-  float2 *sDm = (float2 *)(sB + 16 * TC_NMAX * 16);     // [128] (d, dmin) of the block
-  float *sXd = (float *)(sDm + TC_M);                   // [128] x.d of the block per token
-  uint64_t *bar = (uint64_t *)(sXd + TC_NMAX);
+  uint8_t *sA = smem;                                          // 2 x [16 chunks][128 rows][16 B]
+  uint8_t *sAm = sA + 2 * 32768;                               // Q4_K: [2 chunks][128 rows][8 f16]
+  uint8_t *sB = sAm + (Q6 ? 0 : 2 * TC_M * 16);                // [16 chunks][npad tokens][16 B]
+  uint8_t *sBm = sB + 16 * TC_NMAX * 16;                       // Q4_K: [2 chunks][npad tokens][8 f16]
+  uint8_t *sRaw = sBm + (Q6 ? 0 : 2 * TC_NMAX * 16);           // one block of the 128 rows as stored
+  float *sXd = (float *)(sRaw + (Q6 ? TC_RAW_Q6 : TC_RAW_Q4)); // [2][64] x.d of a block per token
+  int32_t *sXs = (int32_t *)(sXd + 2 * TC_NMAX);               // Q6_K: [2][64] sum of the block's xq
+  uint64_t *bar = (uint64_t *)(sXs + (Q6 ? 2 * TC_NMAX : 0));
   uint32_t *tmem_slot = (uint32_t *)(bar + 1);
-  int *s_tok = (int *)(tmem_slot + 2);                  // [128] row of xq per token of the tile
+  int *s_dead = (int *)(tmem_slot + 1);
 
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      tc_s32(tmem_slot)),
-                 "r"(512u)
+                 "r"((uint32_t)TC_TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_s32(bar)), "r"(1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    *s_dead = 0;
   }
-  for (int n = tid; n < TC_NMAX; n += TC_NT) {
-    int row = -1;
-    if (n < nvalid) row = A.down ? (int)(off + n0 + n) : (int)A.g.pair_token[off + n0 + n];
-    s_tok[n] = row;
+
+  // ---- roles ----
+  // (1) activations: thread = (token bt, 16-byte column bp of every 64-byte group); a
+  // quarter-warp covers 8 consecutive tokens of one column: 128 contiguous bytes of
+  // shared memory, 64 contiguous bytes of a token row per four lanes
+  const int bt = (tid & 7) + 8 * warp, bp = (tid >> 3) & 3;
+  int brow = -1;
+  if (bt < nvalid) brow = A.down ? (int)(off + n0 + bt) : (int)A.g.pair_token[off + n0 + bt];
+  const uint32_t sB_a = tc_s32(sB), sBm_a = tc_s32(sBm), sXd_a = tc_s32(sXd), sXs_a = tc_s32(sXs);
+  auto issue_b = [&](int bb) {  // the tokens' block bb -> shared memory, asynchronously
+    if (bb >= nb || brow < 0) return;
+    const int8_t *src = A.xq + (size_t)brow * cols + (size_t)bb * 256 + 16 * bp;
+    const uint32_t dst = sB_a + (uint32_t)(bp * npad + bt) * 16u;
+#pragma unroll
+    for (int j = 0; j < 4; j++) tc_cp16(dst + (uint32_t)(4 * j * npad) * 16u, src + 64 * j);
+    if (bp == 0) tc_cp4(sXd_a + (uint32_t)((bb & 1) * TC_NMAX + bt) * 4u, A.xd + (size_t)brow * nb + bb);
+    if (!Q6 && bp == 1) {
+      const uint16_t *s = A.xbm + ((size_t)brow * nb + bb) * 16;
+      tc_cp16(sBm_a + (uint32_t)bt * 16u, s);
+      tc_cp16(sBm_a + (uint32_t)(npad + bt) * 16u, s + 8);
+    }
+    if (Q6 && bp == 1) tc_cp4(sXs_a + (uint32_t)((bb & 1) * TC_NMAX + bt) * 4u, A.xs + (size_t)brow * nb + bb);
+  };
+  if (bt >= nvalid && bt < npad) {  // padding tokens: zero operands, once
+#pragma unroll
+    for (int j = 0; j < 4; j++) *(uint4 *)(sB + (size_t)((bp + 4 * j) * npad + bt) * 16) = make_uint4(0, 0, 0, 0);
+    if (bp == 0) sXd[bt] = sXd[TC_NMAX + bt] = 0.0f;
+    if (!Q6 && bp == 1) {
+      *(uint4 *)(sBm + (size_t)bt * 16) = make_uint4(0, 0, 0, 0);
+      *(uint4 *)(sBm + (size_t)(npad + bt) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    if (Q6 && bp == 1) sXs[bt] = sXs[TC_NMAX + bt] = 0;
   }
+
+  // (2) weights. Global row of tile row i (gate rows, then up rows, in a gate/up tile), or
+  // -1 past the matrix; `second`: the row belongs to the up matrix
+  auto grow = [&](int i, bool &second) -> int {
+    second = !A.down && i >= 64;
+    int r = r0 + (second ? i - 64 : i);
+    return r < rows ? r : -1;
+  };
+  const uint32_t sRaw_a = tc_s32(sRaw);
+  // the block bb of the tile's rows -> the raw area, in pieces of 16 bytes, consecutive
+  // lanes on consecutive pieces of a row
+  auto issue_raw = [&](int bb) {
+    if (bb >= nb) return;
+    if (Q6) {
+      // ql: 8 pieces a row, [row][128 B], piece c at c ^ (row & 7); qh: 4 pieces a row,
+      // [row][64 B], piece c at c ^ ((row >> 1) & 3): both conflict-free for the row-per-lane
+      // reads below; sc: [row][16 B]; d: the aligned word holding the row's f16
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int i = (tid >> 3) + 32 * j, c = tid & 7;
+        bool sec;
+        const int r = grow(i, sec);
+        if (r < 0) continue;
+        const WMat &W = sec ? W1 : W0;
+        tc_cp16(sRaw_a + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)),
+                W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 128 + 16 * c);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const int i = (tid >> 2) + 64 * j, c = tid & 3;
+        bool sec;
+        const int r = grow(i, sec);
+        if (r < 0) continue;
+        const WMat &W = sec ? W1 : W0;
+        tc_cp16(sRaw_a + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)),
+                W.plane[1] + (size_t)el * W.stride[1] + ((size_t)r * nb + bb) * 64 + 16 * c);
+      }
+      {
+        const int i = tid & 127;
+        bool sec;
+        const int r = grow(i, sec);
+        if (r >= 0) {
+          const WMat &W = sec ? W1 : W0;
+          if (tid < 128)
+            tc_cp16(sRaw_a + 24576u + (uint32_t)i * 16u, W.plane[2] + (size_t)el * W.stride[2] + ((size_t)r * nb + bb) * 16);
+          else
+            tc_cp4(sRaw_a + 26624u + (uint32_t)i * 4u,
+                   (const uint8_t *)((uintptr_t)(W.plane[3] + (size_t)el * W.stride[3] + ((size_t)r * nb + bb) * 2) & ~(uintptr_t)3));
+        }
+      }
+    } else {
+      // [row][144 B]: 9 pieces a row (stride 144 B: row-per-lane 16-byte reads are conflict-free)
+#pragma unroll
+      for (int j = 0; j < 5; j++) {
+        const int p = tid + TC_NT * j;
+        if (p < TC_M * 9) {
+          const int i = p / 9, c = p - 9 * i;
+          bool sec;
+          const int r = grow(i, sec);
+          if (r >= 0) {
+            const WMat &W = sec ? W1 : W0;
+            tc_cp16(sRaw_a + (uint32_t)p * 16u, W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 144 + 16 * c);
+          }
+        }
+      }
+    }
+  };
+  issue_raw(0);
+  issue_b(0);
+
+  // unpack: thread = (row m of the tile, half hf of the block); a warp = 32 consecutive
+  // rows of one half: conflict-free 16-byte stores. The same thread folds row m's
+  // accumulators (TMEM lane m), so the row's (d, dmin) stay in registers.
+  const int m = tid & 127, hf = tid >> 7;
+  bool msec;
+  const int mrow = grow(m, msec);
+  // the f16 d of a Q6_K row sits in the low or high half of the staged word
+  const uint32_t dsel = Q6 && mrow >= 0
+                            ? (uint32_t)(((uintptr_t)((msec ? W1 : W0).plane[3] + (size_t)el * (msec ? W1 : W0).stride[3]) >> 1) & 1)
+                            : 0u;
+  if (mrow < 0) {  // rows past the matrix: zero operands, once
+    for (int kc = 8 * hf; kc < 8 * hf + 8; kc++)
+#pragma unroll
+      for (int pp = 0; pp < 2; pp++)
+        *(uint4 *)(sA + (size_t)pp * 32768 + (size_t)(kc * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
+    if (!Q6) *(uint4 *)(sAm + (size_t)(hf * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
+  }
+
+  // (3) fold: TMEM lanes of this warp's quarter (= rows m), 32 of the token columns
+  const int q = warp & 3, ch = warp >> 2;
+  const int ecol0 = ch * (TC_NMAX / 2);
+  float total[TC_NMAX / 2];
+#pragma unroll
+  for (int i = 0; i < TC_NMAX / 2; i++) total[i] = 0.0f;
+
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
-  // instruction descriptor: D s32, A unsigned 8-bit, B signed 8-bit, both K-major
-  const uint32_t idesc = (2u << 4) | ((WT == PM_TYPE_Q6_K ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) |
-                         ((uint32_t)(TC_M >> 4) << 24);
-  // this thread: one weight row, one half of the block
-  const int m = tid & 127, hf = tid >> 7;  // a warp = 32 consecutive rows, one half: conflict-free 16-byte stores
-  const uint8_t *rowp = nullptr, *rp_qh = nullptr, *rp_sc = nullptr, *rp_d = nullptr;
-  {
-    int r;
-    const WMat *W;
-    if (A.down) { r = r0 + m; W = &W0; }
-    else if (m < 64) { r = r0 + m; W = &W0; }
-    else { r = r0 + m - 64; W = &W1; }
-    if (r < rows) {
-      if (WT == PM_TYPE_Q6_K) {
-        size_t rb = (size_t)r * nb;
-        rowp = W->plane[0] + (size_t)el * W->stride[0] + rb * 128;
-        rp_qh = W->plane[1] + (size_t)el * W->stride[1] + rb * 64;
-        rp_sc = W->plane[2] + (size_t)el * W->stride[2] + rb * 16;
-        rp_d = W->plane[3] + (size_t)el * W->stride[3] + rb * 2;
-      } else {
-        rowp = W->plane[0] + (size_t)el * W->stride[0] + (size_t)r * nb * 144;
-      }
-    }
-  }
-  // epilogue role: TMEM lanes of this warp's quarter, half of the token columns
-  const int q = warp & 3, ch = warp >> 2;
-  const int erow = 32 * q + lane;                 // row of the tile this thread accumulates
-  const int ecol0 = ch * (TC_NMAX / 2);           // its 64 token columns
-  float total[TC_NMAX / 2];
-#pragma unroll
-  for (int i = 0; i < TC_NMAX / 2; i++) total[i] = 0.0f;
-
-  // raw bytes of one block, one step ahead, in registers:
-  //   Q4_K: pf[0] header, pf[1..4] this thread's 64 quant bytes
-  //   Q6_K: pf[0..3] ql (64 B), pf[4..5] qh (32 B), pf[6] = (8 scales, f16 d)
-  //   pfb[0..7]: this thread's 16-byte pieces of the tokens' activations, pfx: a token's x.d
-  uint4 pf[7], pfb[8];
-  float pfx = 0.0f;
-  auto load_raw = [&](int bb) {
-    if (bb >= nb) return;
-    if (rowp) {
-      if (WT == PM_TYPE_Q6_K) {
-        const uint8_t *ql = rowp + (size_t)bb * 128 + 64 * hf;
-        const uint8_t *qh = rp_qh + (size_t)bb * 64 + 32 * hf;
-#pragma unroll
-        for (int j = 0; j < 4; j++) pf[j] = __ldg((const uint4 *)(ql + 16 * j));
-        pf[4] = __ldg((const uint4 *)qh);
-        pf[5] = __ldg((const uint4 *)(qh + 16));
-        uint2 scw = __ldg((const uint2 *)(rp_sc + (size_t)bb * 16 + 8 * hf));
-        pf[6] = make_uint4(scw.x, scw.y, (uint32_t)__ldg((const uint16_t *)(rp_d + (size_t)bb * 2)), 0);
-      } else {
-        const uint8_t *blk = rowp + (size_t)bb * 144;
-        pf[0] = __ldg((const uint4 *)blk);
-#pragma unroll
-        for (int j = 0; j < 4; j++) pf[1 + j] = __ldg((const uint4 *)(blk + 16 + 64 * hf + 16 * j));
-      }
-    }
-    {
-      const int row = (tid & 127) < npad ? s_tok[tid & 127] : -1;
-      const int8_t *src = A.xq + (size_t)(row < 0 ? 0 : row) * cols + (size_t)bb * 256 + (tid >> 7) * 16;
-#pragma unroll
-      for (int j = 0; j < 8; j++) pfb[j] = row >= 0 ? *(const uint4 *)(src + 32 * j) : make_uint4(0, 0, 0, 0);
-    }
-    if (tid < TC_NMAX) {
-      int row = s_tok[tid];
-      pfx = row >= 0 ? A.xd[(size_t)row * nb + bb] : 0.0f;
-    }
-  };
-  load_raw(0);
+  // instruction descriptors: D s32, A u8, B s8, K-major; and the f16 one (D f32)
+  const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+  const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+  const uint64_t dA0 = tc_desc(tc_s32(sA), TC_M * 16u, 128u);
+  const uint64_t dB0 = tc_desc(sB_a, (uint32_t)npad * 16u, 128u);
+  const uint64_t dAm = tc_desc(tc_s32(sAm), TC_M * 16u, 128u);
+  const uint64_t dBm = tc_desc(sBm_a, (uint32_t)npad * 16u, 128u);
 
   bool dead = false;
   for (int b = 0; b < nb; b++) {
-    // ---- 1. operands of block b into shared memory ----
-    if (rowp && WT == PM_TYPE_Q6_K) {
-      // Q6_K: value = sc * (q - 32), sc int8 per 16 values (one K chunk), q 6 bits.
-      // sc = 64*a3 + 16*a2 + 4*a1 + a0 with a0..a2 in 0..3 and a3 in -2..1, so each
-      // plane (q-32)*a_i fits int8 and isum = I0 + 4*I1 + 16*I2 + 64*I3 exactly.
-      const uint4 qlv[4] = {pf[0], pf[1], pf[2], pf[3]};
-      const uint4 qhv[2] = {pf[4], pf[5]};
-      const uint2 scw = make_uint2(pf[6].x, pf[6].y);
-      if (hf == 0) sDm[m] = make_float2(pm_f16(pf[6].z), 0.0f);
+    TC_STAMP(b, 0)
+    // ---- 0. this block's bytes have landed (every thread's copies) ----
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+    if (*(volatile int *)s_dead) { dead = true; break; }
+    TC_STAMP(b, 1)
+    // ---- 1. weights of block b -> operand planes (the previous block's products have
+    // completed: every thread waited on their barrier) ----
+    float rd = 0.0f, rdmin = 0.0f;
+    if (mrow >= 0 && Q6) {
+      const uint8_t *rq = sRaw + m * 128, *rh = sRaw + 16384 + m * 64;
+      uint4 qlv[4], qhv[2];
+#pragma unroll
+      for (int j = 0; j < 4; j++) qlv[j] = *(const uint4 *)(rq + (((4 * hf + j) ^ (m & 7)) << 4));
+#pragma unroll
+      for (int j = 0; j < 2; j++) qhv[j] = *(const uint4 *)(rh + (((2 * hf + j) ^ ((m >> 1) & 3)) << 4));
+      const uint2 scw = *(const uint2 *)(sRaw + 24576 + m * 16 + 8 * hf);
+      const uint32_t dw = *(const uint32_t *)(sRaw + 26624 + m * 4);
+      rd = pm_f16(((((size_t)mrow * nb + b) & 1) ^ dsel) ? (dw >> 16) : (dw & 0xffffu));
 #pragma unroll
       for (int qt = 0; qt < 4; qt++) {
 #pragma unroll
@@ -279,154 +408,152 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
           const uint4 qhw = qhv[lh];
           const int si = 2 * qt + lh;
           const int sv = (int)(int8_t)((si < 4 ? scw.x >> (8 * si) : scw.y >> (8 * (si - 4))) & 0xff);
-          const uint32_t dg[4] = {(uint32_t)sv & 3u, ((uint32_t)sv >> 2) & 3u, ((uint32_t)sv >> 4) & 3u,
-                                  (uint32_t)(sv >> 6 < 0 ? -(sv >> 6) : (sv >> 6))};
-          const bool neg3 = (sv >> 6) < 0;
+          const uint32_t kk = (uint32_t)(4128 - 32 * sv) * 0x00010001u;
           const uint32_t ws[4] = {qlw.x, qlw.y, qlw.z, qlw.w}, hs[4] = {qhw.x, qhw.y, qhw.z, qhw.w};
-          uint32_t o[4][4];
+          uint32_t th[4], tl[4];
 #pragma unroll
           for (int i = 0; i < 4; i++) {
-            uint32_t qv = ((ws[i] >> (qt >= 2 ? 4 : 0)) & 0x0f0f0f0fu) | (((hs[i] >> (2 * qt)) & 0x03030303u) << 4);
-#pragma unroll
-            for (int pp = 0; pp < 4; pp++) {
-              uint32_t v = __vsub4(qv * dg[pp], 0x20202020u * dg[pp]);  // (q - 32) * digit per byte
-              if (pp == 3 && neg3) v = __vneg4(v);
-              o[pp][i] = v;
-            }
+            const uint32_t qv = ((ws[i] >> (qt >= 2 ? 4 : 0)) & 0x0f0f0f0fu) | (((hs[i] >> (2 * qt)) & 0x03030303u) << 4);
+            // two values per 32-bit product: 16-bit lanes of sv * q + (4128 - 32 sv) >= 0
+            const uint32_t ze = (qv & 0x00ff00ffu) * (uint32_t)sv + kk;
+            const uint32_t zo = ((qv >> 8) & 0x00ff00ffu) * (uint32_t)sv + kk;
+            tl[i] = __byte_perm(ze, zo, 0x6240) & 0x3f3f3f3fu;
+            th[i] = __byte_perm(ze >> 6, zo >> 6, 0x6240);
           }
-          size_t off_c = (size_t)(8 * hf + 2 * qt + lh) * (TC_M * 16) + (size_t)m * 16;
-#pragma unroll
-          for (int pp = 0; pp < 4; pp++)
-            *(uint4 *)(sA + (size_t)pp * 32768 + off_c) = make_uint4(o[pp][0], o[pp][1], o[pp][2], o[pp][3]);
+          const size_t off_c = (size_t)((8 * hf + 2 * qt + lh) * TC_M + m) * 16;
+          *(uint4 *)(sA + off_c) = make_uint4(th[0], th[1], th[2], th[3]);
+          *(uint4 *)(sA + 32768 + off_c) = make_uint4(tl[0], tl[1], tl[2], tl[3]);
         }
       }
-    } else if (rowp) {
-      const uint4 hdr = pf[0];
-      if (hf == 0) sDm[m] = make_float2(pm_f16(hdr.x), pm_f16(hdr.x >> 16));
+    } else if (mrow >= 0) {
+      const uint8_t *rp = sRaw + m * 144;
+      const uint4 hdr = *(const uint4 *)rp;
+      rd = pm_f16(hdr.x);
+      rdmin = pm_f16(hdr.x >> 16);
+      uint32_t mh[4];  // the eight mins as f16
+#pragma unroll
+      for (int jp = 0; jp < 4; jp++) {
+        int s0, m0, s1, m1;
+        pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp, s0, m0);
+        pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp + 1, s1, m1);
+        mh[jp] = (uint32_t)__half_as_ushort(__int2half_rn(m0)) | ((uint32_t)__half_as_ushort(__int2half_rn(m1)) << 16);
+      }
+      *(uint4 *)(sAm + (size_t)(hf * TC_M + m) * 16) = make_uint4(mh[0], mh[1], mh[2], mh[3]);
 #pragma unroll
       for (int cc = 0; cc < 2; cc++) {
-        int c = 2 * hf + cc;
-        const uint4 w0 = pf[1 + 2 * cc], w1 = pf[2 + 2 * cc];
+        const int c = 2 * hf + cc;
+        const uint4 w0 = *(const uint4 *)(rp + 16 + 32 * c), w1 = *(const uint4 *)(rp + 32 + 32 * c);
         int sc0, m0, sc1, m1;
         pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c, sc0, m0);
         pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c + 1, sc1, m1);
         const uint32_t M4 = 0x0f0f0f0fu;
         // sub-block 2c = low nibbles -> K chunks 4c, 4c+1 ; sub-block 2c+1 = high -> 4c+2, 4c+3
-        uint32_t lo[8] = {w0.x & M4, w0.y & M4, w0.z & M4, w0.w & M4, w1.x & M4, w1.y & M4, w1.z & M4, w1.w & M4};
-        uint32_t hi[8] = {(w0.x >> 4) & M4, (w0.y >> 4) & M4, (w0.z >> 4) & M4, (w0.w >> 4) & M4,
-                          (w1.x >> 4) & M4, (w1.y >> 4) & M4, (w1.z >> 4) & M4, (w1.w >> 4) & M4};
-        uint32_t sh0 = (uint32_t)sc0 >> 3, sl0 = (uint32_t)sc0 & 7, sh1 = (uint32_t)sc1 >> 3, sl1 = (uint32_t)sc1 & 7;
-        uint32_t mm0 = (uint32_t)m0 * 0x01010101u, mm1 = (uint32_t)m1 * 0x01010101u;
+        const uint32_t lo[8] = {w0.x & M4, w0.y & M4, w0.z & M4, w0.w & M4, w1.x & M4, w1.y & M4, w1.z & M4, w1.w & M4};
+        const uint32_t hi[8] = {(w0.x >> 4) & M4, (w0.y >> 4) & M4, (w0.z >> 4) & M4, (w0.w >> 4) & M4,
+                                (w1.x >> 4) & M4, (w1.y >> 4) & M4, (w1.z >> 4) & M4, (w1.w >> 4) & M4};
+        const uint32_t sh0 = (uint32_t)sc0 >> 3, sl0 = (uint32_t)sc0 & 7, sh1 = (uint32_t)sc1 >> 3, sl1 = (uint32_t)sc1 & 7;
 #pragma unroll
         for (int h2 = 0; h2 < 2; h2++) {
-          size_t o_lo = (size_t)(4 * c + h2) * (TC_M * 16) + (size_t)m * 16;      // chunk of sub-block 2c
-          size_t o_hi = (size_t)(4 * c + 2 + h2) * (TC_M * 16) + (size_t)m * 16;  // chunk of sub-block 2c+1
+          const size_t o_lo = (size_t)((4 * c + h2) * TC_M + m) * 16;      // chunk of sub-block 2c
+          const size_t o_hi = (size_t)((4 * c + 2 + h2) * TC_M + m) * 16;  // chunk of sub-block 2c+1
           const uint32_t *l4 = lo + 4 * h2, *h4 = hi + 4 * h2;
           *(uint4 *)(sA + o_lo) = make_uint4(l4[0] * sh0, l4[1] * sh0, l4[2] * sh0, l4[3] * sh0);
           *(uint4 *)(sA + 32768 + o_lo) = make_uint4(l4[0] * sl0, l4[1] * sl0, l4[2] * sl0, l4[3] * sl0);
-          *(uint4 *)(sA + 65536 + o_lo) = make_uint4(mm0, mm0, mm0, mm0);
           *(uint4 *)(sA + o_hi) = make_uint4(h4[0] * sh1, h4[1] * sh1, h4[2] * sh1, h4[3] * sh1);
           *(uint4 *)(sA + 32768 + o_hi) = make_uint4(h4[0] * sl1, h4[1] * sl1, h4[2] * sl1, h4[3] * sl1);
-          *(uint4 *)(sA + 65536 + o_hi) = make_uint4(mm1, mm1, mm1, mm1);
         }
       }
-    } else {  // rows past the matrix: zero operands
-      if (hf == 0) sDm[m] = make_float2(0.0f, 0.0f);
-      for (int kc = 8 * hf; kc < 8 * hf + 8; kc++) {
-        size_t o = (size_t)kc * (TC_M * 16) + (size_t)m * 16;
-#pragma unroll
-        for (int pp = 0; pp < NP; pp++) *(uint4 *)(sA + (size_t)pp * 32768 + o) = make_uint4(0, 0, 0, 0);
-      }
     }
-    if ((tid & 127) < npad) {  // thread = (token row tid & 127, chunks tid >> 7, +2, ...)
-#pragma unroll
-      for (int j = 0; j < 8; j++)
-        *(uint4 *)(sB + (size_t)((tid >> 7) + 2 * j) * (npad * 16) + (size_t)(tid & 127) * 16) = pfb[j];
-    }
-    if (tid < TC_NMAX) sXd[tid] = pfx;
-    // the next block's bytes start their trip from HBM now, and land while this
-    // block is multiplied and folded
-    load_raw(b + 1);
-    // generic-proxy writes -> visible to the tensor core's (async proxy) reads
+    TC_STAMP(b, 2)
+    // all operand writes -> visible to the tensor core; the raw area is free again
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TC_STAMP(b, 3)
 
-    // ---- 2. 8 K-steps x 3 planes ----
+    // ---- 2. 8 K-steps x 2 planes (+ the mins' one f16 product) ----
     if (tid == 0) {
-      const uint32_t a0 = tc_s32(sA), b0 = tc_s32(sB);
-#pragma unroll 1
-      for (int ks = 0; ks < 8; ks++) {
-        uint64_t db = tc_desc(b0 + (uint32_t)ks * 2u * (uint32_t)npad * 16u, (uint32_t)npad * 16u, 128u);
 #pragma unroll
-        for (int p = 0; p < NP; p++) {
-          uint64_t da = tc_desc(a0 + (uint32_t)p * 32768u + (uint32_t)ks * 2u * (TC_M * 16u), TC_M * 16u, 128u);
-          tc_mma_i8(tmem + (uint32_t)p * TC_NMAX, da, db, idesc, ks > 0 ? 1u : 0u);
-        }
+      for (int ks = 0; ks < 8; ks++) {
+        const uint64_t db = dB0 + (uint64_t)(ks * 2 * npad);
+#pragma unroll
+        for (int p = 0; p < 2; p++)
+          tc_mma_i8(tmem + (uint32_t)p * TC_NMAX, dA0 + (uint64_t)(p * 2048 + ks * 256), db, idesc, ks > 0 ? 1u : 0u);
       }
+      if (!Q6) tc_mma_f16(tmem + 2u * TC_NMAX, dAm, dBm, idesc_h, 0u);
       tc_commit(bar);
     }
+    issue_raw(b + 1);  // the next block's weight bytes start their trip from HBM now
+    TC_STAMP(b, 4)
     // ---- 3. the block's float term, in block order ----
-    if (!tc_bar_test(bar, (uint32_t)(b & 1)) && !tc_bar_wait(bar, (uint32_t)(b & 1), A.err)) dead = true;
-    if (__syncthreads_or(dead)) { dead = true; break; }
+    if (!tc_bar_test(bar, (uint32_t)(b & 1)) && !tc_bar_wait(bar, (uint32_t)(b & 1), A.err)) *(volatile int *)s_dead = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TC_STAMP(b, 5)
+    issue_b(b + 1);  // the operands are free again: the next block's activations
+    TC_STAMP(b, 6)
     {
-      const float2 dm = sDm[erow];
-      const uint32_t tl = tmem + ((uint32_t)(32 * q) << 16);
+      const uint32_t tl = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)ecol0;
+      const float *xdv = sXd + (b & 1) * TC_NMAX + ecol0;
+      const int32_t *xsv = sXs + (b & 1) * TC_NMAX + ecol0;
 #pragma unroll
-      for (int c32 = 0; c32 < TC_NMAX / 2; c32 += 32) {
-        if (ecol0 + c32 < npad) {
-          uint32_t vh[32], vl[32], vm[32];
-          tc_ld32(tl + (uint32_t)(0 * TC_NMAX + ecol0 + c32), vh);
-          tc_ld32(tl + (uint32_t)(1 * TC_NMAX + ecol0 + c32), vl);
-          tc_ld32(tl + (uint32_t)(2 * TC_NMAX + ecol0 + c32), vm);
-          if (WT == PM_TYPE_Q6_K) {
-            uint32_t v3[32];
-            tc_ld32(tl + (uint32_t)(3 * TC_NMAX + ecol0 + c32), v3);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int c16 = 0; c16 < TC_NMAX / 2; c16 += 16) {
+        if (ecol0 + c16 < npad) {
+          uint32_t v0[16], v1[16], v2[16];
+          tc_ld16(tl + (uint32_t)(0 * TC_NMAX + c16), v0);
+          tc_ld16(tl + (uint32_t)(1 * TC_NMAX + c16), v1);
+          if (!Q6) tc_ld16(tl + (uint32_t)(2 * TC_NMAX + c16), v2);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-              int isum = (int)vh[i] + 4 * (int)vl[i] + 16 * (int)vm[i] + 64 * (int)v3[i];
-              float term = __fmul_rn(sXd[ecol0 + c32 + i], __fmul_rn(dm.x, (float)isum));
-              total[c32 + i] = __fadd_rn(total[c32 + i], term);
+          for (int i4 = 0; i4 < 16; i4 += 4) {
+            const float4 x4 = *(const float4 *)(xdv + c16 + i4);
+            const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+            int ss[4] = {0, 0, 0, 0};
+            if (Q6) {
+              const int4 s4 = *(const int4 *)(xsv + c16 + i4);
+              ss[0] = s4.x; ss[1] = s4.y; ss[2] = s4.z; ss[3] = s4.w;
             }
-          } else {
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-              int isum = 8 * (int)vh[i] + (int)vl[i];
-              int msum = (int)vm[i];
-              float term = __fmul_rn(sXd[ecol0 + c32 + i],
-                                     __fsub_rn(__fmul_rn(dm.x, (float)isum), __fmul_rn(dm.y, (float)msum)));
-              total[c32 + i] = __fadd_rn(total[c32 + i], term);
+            for (int u = 0; u < 4; u++) {
+              const int i = i4 + u;
+              float term;
+              if (Q6) {
+                int isum = 64 * (int)v0[i] + (int)v1[i] - 4128 * ss[u];
+                term = __fmul_rn(xs[u], __fmul_rn(rd, (float)isum));
+              } else {
+                int isum = 8 * (int)v0[i] + (int)v1[i];
+                term = __fmul_rn(xs[u], __fsub_rn(__fmul_rn(rd, (float)isum), __fmul_rn(rdmin, __uint_as_float(v2[i]))));
+              }
+              total[c16 + i] = __fadd_rn(total[c16 + i], term);
             }
           }
         }
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();  // operands and accumulators are rewritten by the next block
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TC_STAMP(b, 7)
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncthreads();  // every fold is done: the planes' memory is free, TMEM can go
+  if (*(volatile int *)s_dead) dead = true;
 
   if (!dead) {
     if (A.down) {
-      const float bd = (!A.shared && ly.bias_down && r0 + erow < rows) ? ly.bias_down[(size_t)el * rows + r0 + erow] : 0.0f;
+      const float bd = (!A.shared && ly.bias_down && r0 + m < rows) ? ly.bias_down[(size_t)el * rows + r0 + m] : 0.0f;
 #pragma unroll
       for (int i = 0; i < TC_NMAX / 2; i++) {
         int n = ecol0 + i;
-        if (n < nvalid && r0 + erow < rows) {
+        if (n < nvalid && r0 + m < rows) {
           float o = total[i];
           if (!A.shared && ly.bias_down) o = __fadd_rn(o, bd);
-          A.out[(size_t)(off + n0 + n) * rows + r0 + erow] = o;
+          A.out[(size_t)(off + n0 + n) * rows + r0 + m] = o;
         }
       }
     } else {
       // gate rows in tile rows 0..63, up rows in 64..127: exchange through shared memory
-      float *S = (float *)sA;  // [128][129]
+      float *S = (float *)sA;  // [128][65]
 #pragma unroll
-      for (int i = 0; i < TC_NMAX / 2; i++) S[erow * (TC_NMAX + 1) + ecol0 + i] = total[i];
+      for (int i = 0; i < TC_NMAX / 2; i++) S[m * (TC_NMAX + 1) + ecol0 + i] = total[i];
       __syncthreads();
       const pm_layer_desc &D = ly.desc;
       const bool fold = !A.shared && D.weight_fold == PM_FOLD_BEFORE_DOWN && A.wts;
@@ -445,24 +572,26 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       }
     }
   }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TC_TMEM_COLS) : "memory");
 }
 
 int tc_max_tiles(int n_pairs, int max_groups) {
   int groups = max_groups < n_pairs ? max_groups : n_pairs;
   return n_pairs / TC_NMAX + groups;
 }
-static size_t tc_smem(int planes) {
-  return (size_t)planes * 32768 + 16 * TC_NMAX * 16 + TC_M * 8 + TC_NMAX * 4 + 64 + TC_NMAX * 4 + 256;
+static size_t tc_smem(bool q6) {
+  return (size_t)2 * 32768 + (q6 ? 0 : 2 * TC_M * 16) + 16 * TC_NMAX * 16 + (q6 ? 0 : 2 * TC_NMAX * 16) +
+         (q6 ? TC_RAW_Q6 : TC_RAW_Q4) + 2 * TC_NMAX * 4 + (q6 ? 2 * TC_NMAX * 4 : 0) + 16;
 }
 
 // Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x
-// activations. `max_count` bounds the tokens of one group (for the grid's z extent).
+// activations (xbm: the f16 form of the sub-block sums the quantiser writes).
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
                           int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
-                          const float *wts, float *out, int *err) {
+                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err) {
   if (n_pairs == 0) return cudaSuccess;
   // tile list: at most one partial tile per group plus the full ones
   const int max_tiles = tc_max_tiles(n_pairs, g.max_groups);
@@ -472,7 +601,7 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   if (L.count) ++*L.count;
   const WMat &W = down ? (shared ? ly.sdown : ly.down) : (shared ? ly.sgate : ly.gate);
   const bool q6 = W.type == PM_TYPE_Q6_K;
-  const size_t smem = tc_smem(q6 ? 4 : 3);
+  const size_t smem = tc_smem(q6);
   const void *kern = q6 ? (const void *)k_tc<PM_TYPE_Q6_K> : (const void *)k_tc<PM_TYPE_Q4_K>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
@@ -483,6 +612,8 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.g = g;
   A.xq = xq;
   A.xd = xd;
+  A.xbm = xbm;
+  A.xs = xs;
   A.wts = wts;
   A.out = out;
   A.err = err;
