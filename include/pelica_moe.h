@@ -77,9 +77,13 @@ enum {
 /* ---- activation arithmetic ------------------------------------------------ */
 enum {
   PM_AQ_F32 = 0,      /* f32 activations x dequantised weights (src/oss_batch.rs:767-877) */
-  PM_AQ_Q8X_256 = 1   /* int8 per 256 values, f32 scale, 8 partial sums
+  PM_AQ_Q8X_256 = 1,  /* int8 per 256 values, f32 scale, 8 partial sums
                          (`Q8x`, src/ds4_cpu.rs:7-36); the hidden vector is
                          re-quantised before down (src/ds4_cpu.rs:306-317)        */
+  PM_AQ_Q8_32 = 2     /* int8 per 32 values, f32 scale (`Q8`, src/q4x_cpu.rs:13-51)
+                         against Q8_0 weights: per block f16(d_w) * x.d * idot
+                         (src/q4x_cpu.rs:85-90); hidden vector re-quantised the
+                         same way before down (src/q4x_cpu.rs:399-440)            */
 };
 
 /* ---- where the routing weight is applied ------------------------------- */
@@ -271,8 +275,9 @@ PM_API int32_t pm_combine(pm_layer *layer, const float *pair_out, const uint32_t
 /* replaces: `deq4` src/moe_kernels.rs:63-84, `deq_row` src/q4x_cpu.rs:443-496 */
 PM_API int32_t pm_dequant(pm_ctx *ctx, int32_t ggml_type, const uint8_t *blocks,
                           size_t n_values, float *out);
-/* replaces: `Q8x::new` src/ds4_cpu.rs:13-35 ; n % 256 == 0;
- * q[n], scale[n/256], bsum[n/32] */
+/* replaces: `Q8x::new` src/ds4_cpu.rs:13-35 (mode PM_AQ_Q8X_256; n % 256 == 0;
+ * q[n], scale[n/256], bsum[n/32]) and `Q8::new` src/q4x_cpu.rs:23-37 (mode
+ * PM_AQ_Q8_32; n % 32 == 0; q[n], scale[n/32]; bsum unused, may be null) */
 PM_API int32_t pm_quant_act(pm_ctx *ctx, int32_t mode, const float *x, size_t n, int8_t *q,
                             float *scale, int32_t *bsum);
 

@@ -711,6 +711,31 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
       q8x_free(&xq);
       q8x_free(&hq);
     }
+  } else if (D->act_quant == PM_AQ_Q8_32) { /* src/q4x_cpu.rs:399-440 */
+    if (d % 32 || ff % 32) { free(h); return PM_ERR_INVALID; }
+    if (D->type_gate != PM_TYPE_Q8_0 || D->type_up != PM_TYPE_Q8_0 || D->type_down != PM_TYPE_Q8_0) {
+      free(h);
+      return PM_ERR_UNSUPPORTED;
+    }
+    int8_t *xq = (int8_t *)malloc((size_t)d), *hq = (int8_t *)malloc((size_t)ff);
+    float *xd = (float *)malloc((size_t)d / 32 * 4), *hd = (float *)malloc((size_t)ff / 32 * 4);
+    for (int t = 0; t < nt; t++) {
+      po_q8_32(xs[t], (size_t)d, xq, xd);
+      for (int j = 0; j < ff; j++) {
+        float g = po_row_q8_0(W->gate + (size_t)j * bg, (size_t)d, xq, xd);
+        float u = po_row_q8_0(W->up + (size_t)j * bu, (size_t)d, xq, xd);
+        if (W->bias_gate) g = g + W->bias_gate[j];
+        if (W->bias_up) u = u + W->bias_up[j];
+        h[j] = act_fn(D, g, u, wts ? wts[t] : 1.0f, fold);
+      }
+      po_q8_32(h, (size_t)ff, hq, hd);
+      for (int r = 0; r < d; r++) {
+        float o = po_row_q8_0(W->down + (size_t)r * bd, (size_t)ff, hq, hd);
+        if (W->bias_down) o = o + W->bias_down[r];
+        out[(size_t)t * d + r] = o;
+      }
+    }
+    free(xq); free(hq); free(xd); free(hd);
   } else if (D->act_quant == PM_AQ_F32) {
     for (int t = 0; t < nt; t++) {
       for (int j = 0; j < ff; j++) {

@@ -249,6 +249,15 @@ class Context:
         _check(self.lib.pm_dequant(self.h, ggml_type, blocks.ctypes.data, n_values, out.ctypes.data))
         return out
 
+    def quant_act_32(self, x: np.ndarray):
+        """`Q8::new` (src/q4x_cpu.rs:23-37): returns (q int8[n], d f32[n/32])."""
+        x = np.ascontiguousarray(x, np.float32).ravel()
+        n = x.size
+        q = np.empty(n, np.int8)
+        d = np.empty(n // 32, np.float32)
+        _check(self.lib.pm_quant_act(self.h, synth.AQ_Q8_32, x.ctypes.data, n, q.ctypes.data, d.ctypes.data, None))
+        return q, d
+
     def quant_act(self, x: np.ndarray):
         """`Q8x::new` (src/ds4_cpu.rs:13-35): returns (q int8[n], d f32[n/256], bsum i32[n/32])."""
         x = np.ascontiguousarray(x, np.float32).ravel()

@@ -381,6 +381,11 @@ static int32_t validate_desc(const pm_layer_desc *D) {
       if (t != PM_TYPE_Q4_K && t != PM_TYPE_Q6_K)
         return fail(PM_ERR_UNSUPPORTED, "Q8x activations pair with Q4_K / Q6_K weights only");
     if (D->shared && D->shared_ff % 256) return fail(PM_ERR_INVALID, "shared_ff %% 256");
+  } else if (D->act_quant == PM_AQ_Q8_32) {
+    if (D->d % 32 || D->ff % 32 || (D->shared && D->shared_ff % 32))
+      return fail(PM_ERR_INVALID, "32-block Q8 activations need d and ff multiples of 32 (src/q4x_cpu.rs:24)");
+    if (D->type_gate != PM_TYPE_Q8_0 || D->type_up != PM_TYPE_Q8_0 || D->type_down != PM_TYPE_Q8_0)
+      return fail(PM_ERR_UNSUPPORTED, "32-block Q8 activations pair with Q8_0 weights only");
   } else if (D->act_quant != PM_AQ_F32) {
     return fail(PM_ERR_UNSUPPORTED, "act_quant %d", D->act_quant);
   }
@@ -724,14 +729,14 @@ static size_t scratch_bytes(const pm_layer_desc &D, int T) {
   size_t b = 0;
   b += al(T * E * 4) + al(P * 4) * 2;                  // logits, ids, w
   b += al(4) + al(E * 4) * 5 + al(P * 4) * 3;          // plan
-  b += al(T * d) + al(T * (d / 256 + 1) * 4) * 2 + al(T * (d / 32) * 4) * 2;
-  b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 256 + 1) * 4) * 2 + al(P * (ff / 32) * 4) * 2;
+  b += al(T * d) + al(T * (d / 32 + 1) * 4) + al(T * (d / 256 + 1) * 4) + al(T * (d / 32) * 4) * 2;
+  b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 32 + 1) * 4) + al(P * (ff / 256 + 1) * 4) + al(P * (ff / 32) * 4) * 2;
   b += al(P * d * 4);
   b += al((4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1)) * 4);
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     b += al(4) + al(4) * 2 + al((size_t)T * 4);
-    b += al(T * sf * 4) + al(T * sf) + al(T * (sf / 256 + 1) * 4) * 2 + al(T * (sf / 32) * 4) * 2;
+    b += al(T * sf * 4) + al(T * sf) + al(T * (sf / 32 + 1) * 4) + al(T * (sf / 256 + 1) * 4) + al(T * (sf / 32) * 4) * 2;
     b += al(T * d * 4) + al((size_t)T * 4);
   }
   return b + 4096;
@@ -752,13 +757,13 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
   S.plan.pair_pos = ws_take<uint32_t>(c, P);
   S.plan.pair_src = ws_take<uint32_t>(c, P);
   S.xq = ws_take<int8_t>(c, T * d);
-  S.xd = ws_take<float>(c, T * (d / 256 + 1));
+  S.xd = ws_take<float>(c, T * (d / 32 + 1));  // per 256 values (Q8x) or per 32 (Q8)
   S.xbsum = ws_take<int32_t>(c, T * (d / 32));
   S.xbm = ws_take<uint16_t>(c, T * (d / 16));
   S.xs = ws_take<int32_t>(c, T * (d / 256 + 1));
   S.h = ws_take<float>(c, P * ff);
   S.hq = ws_take<int8_t>(c, P * ff);
-  S.hd = ws_take<float>(c, P * (ff / 256 + 1));
+  S.hd = ws_take<float>(c, P * (ff / 32 + 1));
   S.hbsum = ws_take<int32_t>(c, P * (ff / 32));
   S.hbm = ws_take<uint16_t>(c, P * (ff / 16));
   S.hs = ws_take<int32_t>(c, P * (ff / 256 + 1));
@@ -772,7 +777,7 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
     S.iota = ws_take<uint32_t>(c, (size_t)T);
     S.sh = ws_take<float>(c, T * sf);
     S.shq = ws_take<int8_t>(c, T * sf);
-    S.shd = ws_take<float>(c, T * (sf / 256 + 1));
+    S.shd = ws_take<float>(c, T * (sf / 32 + 1));
     S.shbsum = ws_take<int32_t>(c, T * (sf / 32));
     S.shbm = ws_take<uint16_t>(c, T * (sf / 16));
     S.shs = ws_take<int32_t>(c, T * (sf / 256 + 1));
@@ -804,8 +809,9 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   Launch L = c->launch();
   int P = T * D.top_k;
   Groups g = plan_groups(S.plan, D.n_exp);
-  bool q8 = D.act_quant == PM_AQ_Q8X_256;
+  bool q8 = D.act_quant == PM_AQ_Q8X_256, q32 = D.act_quant == PM_AQ_Q8_32;
   if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
+  if (q32) { PROF(c, PH_QUANT_X); launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd); }
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   {
     PROF(c, PH_GATEUP);
@@ -815,6 +821,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
       launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
   }
   if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum, S.hbm, S.hs); }
+  if (q32) { PROF(c, PH_QUANT_H); launch_quant_q8_32(L, S.h, (size_t)P, D.ff, S.hq, S.hd); }
   {
     PROF(c, PH_DOWN);
     if (tc)
@@ -848,15 +855,17 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   g.pair_token = S.iota;
   g.pair_src = nullptr;
   g.max_groups = 1;
-  bool q8 = D.act_quant == PM_AQ_Q8X_256;
+  bool q8 = D.act_quant == PM_AQ_Q8X_256, q32 = D.act_quant == PM_AQ_Q8_32;
   // (S.xq holds the tokens' Q8x form already when the routed experts ran first)
   if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs);
+  if (q32) launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   if (use_tc && D.type_gate == D.type_up)
     CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum, S.shbm, S.shs);
+  if (q32) launch_quant_q8_32(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd);
   if (use_tc)
     CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err));
   else
@@ -1256,16 +1265,25 @@ extern "C" int32_t pm_dequant(pm_ctx *c, int32_t type, const uint8_t *blocks, si
 
 extern "C" int32_t pm_quant_act(pm_ctx *c, int32_t mode, const float *x, size_t n, int8_t *q,
                                 float *scale, int32_t *bsum) {
-  if (!c || !x || !q || !scale || !bsum) return fail(PM_ERR_INVALID, "pm_quant_act: null argument");
-  if (mode != PM_AQ_Q8X_256) return fail(PM_ERR_UNSUPPORTED, "pm_quant_act: mode %d", mode);
-  if (n % 256) return fail(PM_ERR_INVALID, "pm_quant_act: n %% 256 != 0 (src/ds4_cpu.rs:15)");
+  if (!c || !x || !q || !scale) return fail(PM_ERR_INVALID, "pm_quant_act: null argument");
+  if (mode != PM_AQ_Q8X_256 && mode != PM_AQ_Q8_32) return fail(PM_ERR_UNSUPPORTED, "pm_quant_act: mode %d", mode);
+  const bool q32 = mode == PM_AQ_Q8_32;
+  if (!q32 && !bsum) return fail(PM_ERR_INVALID, "pm_quant_act: null bsum");
+  if (!q32 && n % 256) return fail(PM_ERR_INVALID, "pm_quant_act: n %% 256 != 0 (src/ds4_cpu.rs:15)");
+  if (q32 && n % 32) return fail(PM_ERR_INVALID, "pm_quant_act: n %% 32 != 0 (src/q4x_cpu.rs:24)");
   if (n == 0) return PM_OK;
   CU(cudaSetDevice(c->device));
-  TRY(ws_reserve(c, al(n * 4) + al(n) + al(n / 256 * 4) + al(n / 32 * 4) + 4096));
+  TRY(ws_reserve(c, al(n * 4) + al(n) + al(n / 32 * 4) * 2 + 4096));
   const float *xd;
   TRY(in_dev(c, x, n, &xd));
   OutBuf ob[3];
   int8_t *qd = out_dev(c, q, n, ob[0]);
+  if (q32) {
+    float *sd = out_dev(c, scale, n / 32, ob[1]);
+    launch_quant_q8_32(c->launch(), xd, 1, (int)n, qd, sd);
+    CU(cudaGetLastError());
+    return out_flush(c, ob, 2);
+  }
   float *sd = out_dev(c, scale, n / 256, ob[1]);
   int32_t *bd = out_dev(c, bsum, n / 32, ob[2]);
   launch_quant_q8x(c->launch(), xd, 1, (int)n, qd, sd, bd);

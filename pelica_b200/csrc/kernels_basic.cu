@@ -215,6 +215,31 @@ void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_
   KLAUNCH(L, k_quant_q8x, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d, bsum, bm, xs);
 }
 
+// `Q8::new` (src/q4x_cpu.rs:23-37): per 32 values amax, d = amax / 127, values rounded
+// half away from zero and clamped; an all-zero block keeps d = 0. One warp per block.
+__global__ void __launch_bounds__(256) k_quant_q8_32(const float *__restrict__ x, size_t n_blocks,
+                                                    int8_t *q, float *d) {
+  size_t b = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (b >= n_blocks) return;
+  int lane = threadIdx.x & 31;
+  float v = x[b * 32 + lane];
+  float a = pm_warp_max(fabsf(v));
+  int r = 0;
+  if (a != 0.0f) {
+    float id = __fdiv_rn(127.0f, a);
+    float f = roundf(__fmul_rn(v, id));
+    r = (int)fminf(fmaxf(f, -127.0f), 127.0f);
+  }
+  q[b * 32 + lane] = (int8_t)r;
+  if (lane == 0) d[b] = a != 0.0f ? __fdiv_rn(a, 127.0f) : 0.0f;
+}
+
+void launch_quant_q8_32(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d) {
+  size_t nb = rows * (size_t)(n / 32);
+  if (nb == 0) return;
+  KLAUNCH(L, k_quant_q8_32, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d);
+}
+
 // ===========================================================================
 // router logits: `dot_f32` order (src/quant.rs:215-236; src/ds4.rs:1376-1383)
 // ===========================================================================
@@ -488,6 +513,34 @@ __device__ __forceinline__ float row_q8x(const WMat &W, int el, int r, const int
                      W.plane[3] + (size_t)el * W.stride[3] + rb * 2, nb, xq, xd, lane);
 }
 
+// Q8_0 row . 32-block Q8 activations (src/q4x_cpu.rs:85-90): per block
+// total += f16(d_w) * x.d[b] * (float)idot, left to right, in block order. Lanes take
+// one block each; the 32 terms are then added in order.
+__device__ __forceinline__ float row_q8_0_q8(const WMat &W, int el, int r, const int8_t *__restrict__ xq,
+                                             const float *__restrict__ xd, int lane) {
+  const int nb = W.cols / 32;
+  const uint8_t *vals = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * 32;
+  const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * nb * 2;
+  float total = 0.0f;
+  for (int b0 = 0; b0 < nb; b0 += 32) {
+    const int b = b0 + lane;
+    float term = 0.0f;
+    if (b < nb) {
+      const int4 *wp = (const int4 *)(vals + (size_t)b * 32);
+      const int4 *xp = (const int4 *)(xq + (size_t)b * 32);
+      const int4 w0 = __ldg(wp), w1 = __ldg(wp + 1), x0 = xp[0], x1 = xp[1];
+      int s = 0;
+      s = __dp4a(w0.x, x0.x, s); s = __dp4a(w0.y, x0.y, s); s = __dp4a(w0.z, x0.z, s); s = __dp4a(w0.w, x0.w, s);
+      s = __dp4a(w1.x, x1.x, s); s = __dp4a(w1.y, x1.y, s); s = __dp4a(w1.z, x1.z, s); s = __dp4a(w1.w, x1.w, s);
+      const float dw = pm_f16(__ldg((const uint16_t *)(scl + (size_t)b * 2)));
+      term = __fmul_rn(__fmul_rn(dw, xd[b]), (float)s);
+    }
+    const int n = min(32, nb - b0);
+    for (int j = 0; j < n; j++) total = __fadd_rn(total, __shfl_sync(PM_FULL, term, j));
+  }
+  return total;
+}
+
 // any type against f32 activations; lanes take quads of a 32-value block each
 // (MXFP4: src/oss_batch.rs:774-789), f32 accumulation
 __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const float *__restrict__ x,
@@ -575,6 +628,11 @@ __global__ void __launch_bounds__(256) k_gateup(LayerDev ly, int shared, Groups 
       const int32_t *qb = xbsum + (size_t)t * nbx * 8;
       gv = row_q8x(G, el, r, q, qd, qb, lane);
       uv = row_q8x(U, el, r, q, qd, qb, lane);
+    } else if (D.act_quant == PM_AQ_Q8_32) {
+      const int8_t *q = xq + (size_t)t * d;
+      const float *qd = xd + (size_t)t * (d / 32);
+      gv = row_q8_0_q8(G, el, r, q, qd, lane);
+      uv = row_q8_0_q8(U, el, r, q, qd, lane);
     } else {
       gv = row_f32(G, el, r, x + (size_t)t * d, lane);
       uv = row_f32(U, el, r, x + (size_t)t * d, lane);
@@ -619,6 +677,8 @@ __global__ void __launch_bounds__(256) k_down(LayerDev ly, int shared, Groups g,
     if (D.act_quant == PM_AQ_Q8X_256)
       o = row_q8x(Dn, el, r, hq + (size_t)p * ff, hd + (size_t)p * nbh,
                   hbsum + (size_t)p * nbh * 8, lane);
+    else if (D.act_quant == PM_AQ_Q8_32)
+      o = row_q8_0_q8(Dn, el, r, hq + (size_t)p * ff, hd + (size_t)p * (ff / 32), lane);
     else
       o = row_f32(Dn, el, r, h + (size_t)p * ff, lane);
     if (lane == 0) {

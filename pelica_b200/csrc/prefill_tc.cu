@@ -1,19 +1,22 @@
 // prefill_tc.cu - grouped expert products for many tokens per expert on the 5th-gen
-// tensor cores (tcgen05.mma kind::i8, accumulators in TMEM), exact in the integer
-// domain of the reference's CPU path (src/ds4_cpu.rs:59-83).
+// tensor cores (tcgen05.mma kind::i8, operand A and the accumulators in TMEM), exact in
+// the integer domain of the reference's CPU path (src/ds4_cpu.rs:59-83).
 //
-// One CTA = (128 weight rows of one active expert) x (up to 64 of its tokens); two CTAs
-// per SM. Per 256-value block b of the rows:
-//   1. CUDA cores unpack the block into int8 operand planes in shared memory (K-major,
-//      no swizzle, 8x16-byte core matrices). Q4_K: A_hi = nibble * (sc >> 3),
+// One CTA = (128 weight rows of one active expert) x (up to 128 of its tokens): 16 worker
+// warps and one warp that issues the tensor-core instructions. Per 256-value block b of
+// the rows:
+//   1. the block's bytes arrive by cp.async in row-contiguous pieces; each worker unpacks
+//      64 values of one row into two u8 operand planes IN REGISTERS and stores them to
+//      tensor memory (tcgen05.st), where the products read operand A from: shared memory
+//      carries only the tokens' activations. Q4_K: A_hi = nibble * (sc >> 3),
 //      A_lo = nibble * (sc & 7), so that with the token's int8 activations xq
 //        isum = 8 * (A_hi . xq) + (A_lo . xq) = sum_j sc_j * sum_i nib_ji * xq_ji
-//      (6-bit scales do not fit one int8 product with a nibble; two 3-bit halves do),
-//      and msum = sum_j m_j * bsum_j comes from one K=16 f16 product (see k_tc). The
-//      tokens' activations arrive by cp.async while the previous block is folded.
-//   2. one thread issues the tcgen05.mma of the block (8 K-steps of 32 per plane) into
-//      TMEM accumulators and commits to an mbarrier;
-//   3. every warp reads its TMEM lanes (tcgen05.ld) and adds the block's float term
+//      (6-bit scales do not fit one u8 product with a nibble; two 3-bit halves do), and
+//      msum = sum_j m_j * bsum_j comes from one K=16 f16 product (see k_tc).
+//   2. the issuing warp runs the block's tcgen05.mma (8 K-steps of 32 per plane) into
+//      TMEM accumulators and commits to an mbarrier; meanwhile the workers unpack the
+//      next block into registers;
+//   3. every worker reads its TMEM lane (tcgen05.ld) and adds the block's float term
 //      total += x.d[b] * (d * isum - dmin * msum) in block order, as `row_scalar`.
 // Gate and up rows share a CTA (64 + 64 rows) so SwiGLU is fused in the epilogue;
 // down rows write the pair outputs. Waits are time-bounded; TMEM is freed on
@@ -22,12 +25,20 @@
 
 #include "moe_internal.cuh"
 
-#define TC_NT 256
+#define TC_NW 512                 /* worker threads */
+#define TC_NT (TC_NW + 32)        /* + the warp that issues the products */
 #define TC_M 128
-#define TC_NMAX 64
-#define TC_TMEM_COLS 256
+#define TC_NMAX 128
+#define TC_TMEM_COLS 512
+#define TC_ACC_HI 0u              /* TMEM columns: accumulators ... */
+#define TC_ACC_LO 128u
+#define TC_ACC_M 256u
+#define TC_A_HI 384u              /* ... and operand A: 64 columns (256 K values) a plane */
+#define TC_A_LO 448u
 #define TC_RAW_Q4 (TC_M * 144)                       /* bytes of the raw staging area */
 #define TC_RAW_Q6 (TC_M * (128 + 64 + 16 + 4))
+#define TC_RAW_STAGES_Q4 4                          /* weight blocks in flight */
+#define TC_RAW_STAGES_Q6 3
 #define TC_WAIT_NS 2000000000ull
 
 __device__ __forceinline__ uint32_t tc_s32(const void *p) {
@@ -45,39 +56,15 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t lbo, uint32
   return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)((lbo >> 4) & 0x3fff) << 16) |
          ((uint64_t)((sbo >> 4) & 0x3fff) << 32) | (1ull << 46);
 }
-__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc,
-                                          uint32_t accumulate) {
+// D[tmem_c] (+)= A[tmem_a] * B[db]: A from tensor memory (row = lane, 32-bit column c =
+// K values 4c..4c+3), B from shared memory
+__device__ __forceinline__ void tc_mma_i8_ta(uint32_t tmem_c, uint32_t tmem_a, uint64_t db, uint32_t idesc,
+                                             uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_c),
-      "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_c),
+      "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   tc_s32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t r[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t r[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
 }
 __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc,
                                            uint32_t accumulate) {
@@ -87,6 +74,29 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_c, uint64_t da, uint64_
       "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   tc_s32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t r[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld4(uint32_t taddr, uint32_t r[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t r[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 // global -> shared without registers (completion: cp.async.wait_all by the issuing thread)
 __device__ __forceinline__ void tc_cp16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -94,6 +104,11 @@ __device__ __forceinline__ void tc_cp16(uint32_t dst, const void *src) {
 __device__ __forceinline__ void tc_cp4(uint32_t dst, const void *src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
+// named barriers: 1 = operands of a block ready (workers arrive, the issuing warp waits),
+// 2 = among the workers
+__device__ __forceinline__ void tc_workers_sync() { asm volatile("bar.sync 2, %0;" ::"n"(TC_NW) : "memory"); }
+__device__ __forceinline__ void tc_ready_arrive() { asm volatile("bar.arrive 1, %0;" ::"n"(TC_NT) : "memory"); }
+__device__ __forceinline__ void tc_ready_wait() { asm volatile("bar.sync 1, %0;" ::"n"(TC_NT) : "memory"); }
 __device__ __forceinline__ bool tc_bar_test(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -104,11 +119,13 @@ __device__ __forceinline__ bool tc_bar_test(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// false after TC_WAIT_NS (or at once when an error is already recorded): the caller
+// carries on with whatever the accumulators hold and the call reports the error
 __device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *err) {
   unsigned long long t0 = tc_now();
   for (uint32_t it = 0;; it++) {
     if (tc_bar_test(bar, parity)) return true;
-    if ((it & 15) == 15 && tc_now() - t0 > TC_WAIT_NS) break;
+    if ((it & 15) == 15 && (*(volatile int *)err != 0 || tc_now() - t0 > TC_WAIT_NS)) break;
   }
   atomicCAS(err, 0, 7);
   return false;
@@ -117,11 +134,11 @@ __device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *er
 int tc_max_tiles(int n_pairs, int max_groups);
 
 // Compile with -DPM_TC_TRACE to stamp the phases of CTA (0, 0) with the SM clock:
-// [thread 0 | thread 255][block][stamp]; read back with pm_debug_tc_trace.
+// [thread 0 | thread 511][block][stamp]; read back with pm_debug_tc_trace.
 #ifdef PM_TC_TRACE
 __device__ unsigned long long g_tc_trace[2 * 32 * 8];
 #define TC_STAMP(b, i)                                                                         \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 255) && (b) < 32)              \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 511) && (b) < 32)              \
     g_tc_trace[((tid ? 1 : 0) * 32 + (b)) * 8 + (i)] = clock64();
 extern "C" __attribute__((visibility("default"))) int pm_debug_tc_trace(unsigned long long *out) {
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));
@@ -180,14 +197,18 @@ __global__ void __launch_bounds__(512) k_tc_tiles(Groups g, int *n_tiles, uint32
 //  PM_TYPE_Q6_K: the product v = sc * (q - 32) in [-4064, 4096] is split after the
 //    multiplication: v + 4128 = 64 * th + tl with th in [1, 128], tl in [0, 63] - two u8
 //    planes, and isum = 64 * (th . xq) + (tl . xq) - 4128 * sum(xq) exactly.
-// The weight bytes of a block arrive by cp.async in row-contiguous pieces (a warp reads
-// whole 144-byte / 128-byte runs) into a raw staging area, from which each thread
-// unpacks its row. Two CTAs share an SM (<= 113 KB of shared memory, 256 of the 512 TMEM
-// columns, <= 128 registers): while one waits for its products or folds them, the other
-// unpacks.
+// Memory: the weight bytes of a block arrive by cp.async in row-contiguous pieces (a warp
+// reads whole 144-byte / 128-byte runs) into one of TC_RAW_STAGES raw areas, issued that
+// many blocks ahead (HBM answers in about 2000 cycles under load; one block lasts less);
+// the tokens' int8 activations go to one of two areas, two blocks ahead. The first half
+// of the workers issues the weight copies, the second half the activation copies, so
+// that each thread's cp.async groups complete in the order they are needed.
 template <int WT>
-__global__ void __launch_bounds__(TC_NT, 2) k_tc(const TcArgs A) {
+__global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   constexpr bool Q6 = WT == PM_TYPE_Q6_K;
+  constexpr int NS = Q6 ? TC_RAW_STAGES_Q6 : TC_RAW_STAGES_Q4;
+  constexpr int RAWB = Q6 ? TC_RAW_Q6 : TC_RAW_Q4;
+  constexpr int BSTAGE = 16 * TC_NMAX * 16 + (Q6 ? 0 : 2 * TC_NMAX * 16);  // tokens' block (+ f16 sums)
   extern __shared__ __align__(128) uint8_t smem[];
   // blockIdx.y walks the list of (group, token tile) pairs made by k_tc_tiles
   if ((int)blockIdx.y >= *A.n_tiles) return;
@@ -215,18 +236,18 @@ __global__ void __launch_bounds__(TC_NT, 2) k_tc(const TcArgs A) {
     return;
   }
 
-  uint8_t *sA = smem;                                          // 2 x [16 chunks][128 rows][16 B]
-  uint8_t *sAm = sA + 2 * 32768;                               // Q4_K: [2 chunks][128 rows][8 f16]
-  uint8_t *sB = sAm + (Q6 ? 0 : 2 * TC_M * 16);                // [16 chunks][npad tokens][16 B]
-  uint8_t *sBm = sB + 16 * TC_NMAX * 16;                       // Q4_K: [2 chunks][npad tokens][8 f16]
-  uint8_t *sRaw = sBm + (Q6 ? 0 : 2 * TC_NMAX * 16);           // one block of the 128 rows as stored
-  float *sXd = (float *)(sRaw + (Q6 ? TC_RAW_Q6 : TC_RAW_Q4)); // [2][64] x.d of a block per token
-  int32_t *sXs = (int32_t *)(sXd + 2 * TC_NMAX);               // Q6_K: [2][64] sum of the block's xq
-  uint64_t *bar = (uint64_t *)(sXs + (Q6 ? 2 * TC_NMAX : 0));
+  uint8_t *sRaw = smem;                                        // [NS] blocks of the 128 rows as stored
+  float *sS = (float *)smem;                                   // (after the last block) gate/up exchange [128][129]
+  uint8_t *sB = smem + (NS * RAWB > TC_M * (TC_NMAX + 1) * 4 ? NS * RAWB : TC_M * (TC_NMAX + 1) * 4);
+                                                               // [2] x ([16 chunks][npad tokens][16 B] + Q4_K:
+                                                               //        [2 chunks][npad tokens][8 f16])
+  uint8_t *sAm = sB + 2 * BSTAGE;                              // Q4_K: [2][2 chunks][128 rows][8 f16]
+  float *sXd = (float *)(sAm + 2 * 2 * TC_M * 16);             // [4][128] x.d of a block per token
+  int32_t *sXs = (int32_t *)(sXd + 4 * TC_NMAX);               // Q6_K: [4][128] sum of the block's xq
+  uint64_t *bar = (uint64_t *)(sXs + 4 * TC_NMAX);
   uint32_t *tmem_slot = (uint32_t *)(bar + 1);
-  int *s_dead = (int *)(tmem_slot + 1);
 
-  if (warp == 0) {
+  if (warp == TC_NW / 32) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      tc_s32(tmem_slot)),
                  "r"((uint32_t)TC_TMEM_COLS)
@@ -236,345 +257,390 @@ __global__ void __launch_bounds__(TC_NT, 2) k_tc(const TcArgs A) {
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_s32(bar)), "r"(1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    *s_dead = 0;
   }
-
-  // ---- roles ----
-  // (1) activations: thread = (token bt, 16-byte column bp of every 64-byte group); a
-  // quarter-warp covers 8 consecutive tokens of one column: 128 contiguous bytes of
-  // shared memory, 64 contiguous bytes of a token row per four lanes
-  const int bt = (tid & 7) + 8 * warp, bp = (tid >> 3) & 3;
-  int brow = -1;
-  if (bt < nvalid) brow = A.down ? (int)(off + n0 + bt) : (int)A.g.pair_token[off + n0 + bt];
-  const uint32_t sB_a = tc_s32(sB), sBm_a = tc_s32(sBm), sXd_a = tc_s32(sXd), sXs_a = tc_s32(sXs);
-  auto issue_b = [&](int bb) {  // the tokens' block bb -> shared memory, asynchronously
-    if (bb >= nb || brow < 0) return;
-    const int8_t *src = A.xq + (size_t)brow * cols + (size_t)bb * 256 + 16 * bp;
-    const uint32_t dst = sB_a + (uint32_t)(bp * npad + bt) * 16u;
-#pragma unroll
-    for (int j = 0; j < 4; j++) tc_cp16(dst + (uint32_t)(4 * j * npad) * 16u, src + 64 * j);
-    if (bp == 0) tc_cp4(sXd_a + (uint32_t)((bb & 1) * TC_NMAX + bt) * 4u, A.xd + (size_t)brow * nb + bb);
-    if (!Q6 && bp == 1) {
-      const uint16_t *s = A.xbm + ((size_t)brow * nb + bb) * 16;
-      tc_cp16(sBm_a + (uint32_t)bt * 16u, s);
-      tc_cp16(sBm_a + (uint32_t)(npad + bt) * 16u, s + 8);
-    }
-    if (Q6 && bp == 1) tc_cp4(sXs_a + (uint32_t)((bb & 1) * TC_NMAX + bt) * 4u, A.xs + (size_t)brow * nb + bb);
-  };
-  if (bt >= nvalid && bt < npad) {  // padding tokens: zero operands, once
-#pragma unroll
-    for (int j = 0; j < 4; j++) *(uint4 *)(sB + (size_t)((bp + 4 * j) * npad + bt) * 16) = make_uint4(0, 0, 0, 0);
-    if (bp == 0) sXd[bt] = sXd[TC_NMAX + bt] = 0.0f;
-    if (!Q6 && bp == 1) {
-      *(uint4 *)(sBm + (size_t)bt * 16) = make_uint4(0, 0, 0, 0);
-      *(uint4 *)(sBm + (size_t)(npad + bt) * 16) = make_uint4(0, 0, 0, 0);
-    }
-    if (Q6 && bp == 1) sXs[bt] = sXs[TC_NMAX + bt] = 0;
-  }
-
-  // (2) weights. Global row of tile row i (gate rows, then up rows, in a gate/up tile), or
-  // -1 past the matrix; `second`: the row belongs to the up matrix
-  auto grow = [&](int i, bool &second) -> int {
-    second = !A.down && i >= 64;
-    int r = r0 + (second ? i - 64 : i);
-    return r < rows ? r : -1;
-  };
-  const uint32_t sRaw_a = tc_s32(sRaw);
-  // the block bb of the tile's rows -> the raw area, in pieces of 16 bytes, consecutive
-  // lanes on consecutive pieces of a row
-  auto issue_raw = [&](int bb) {
-    if (bb >= nb) return;
-    if (Q6) {
-      // ql: 8 pieces a row, [row][128 B], piece c at c ^ (row & 7); qh: 4 pieces a row,
-      // [row][64 B], piece c at c ^ ((row >> 1) & 3): both conflict-free for the row-per-lane
-      // reads below; sc: [row][16 B]; d: the aligned word holding the row's f16
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int i = (tid >> 3) + 32 * j, c = tid & 7;
-        bool sec;
-        const int r = grow(i, sec);
-        if (r < 0) continue;
-        const WMat &W = sec ? W1 : W0;
-        tc_cp16(sRaw_a + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)),
-                W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 128 + 16 * c);
-      }
-#pragma unroll
-      for (int j = 0; j < 2; j++) {
-        const int i = (tid >> 2) + 64 * j, c = tid & 3;
-        bool sec;
-        const int r = grow(i, sec);
-        if (r < 0) continue;
-        const WMat &W = sec ? W1 : W0;
-        tc_cp16(sRaw_a + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)),
-                W.plane[1] + (size_t)el * W.stride[1] + ((size_t)r * nb + bb) * 64 + 16 * c);
-      }
-      {
-        const int i = tid & 127;
-        bool sec;
-        const int r = grow(i, sec);
-        if (r >= 0) {
-          const WMat &W = sec ? W1 : W0;
-          if (tid < 128)
-            tc_cp16(sRaw_a + 24576u + (uint32_t)i * 16u, W.plane[2] + (size_t)el * W.stride[2] + ((size_t)r * nb + bb) * 16);
-          else
-            tc_cp4(sRaw_a + 26624u + (uint32_t)i * 4u,
-                   (const uint8_t *)((uintptr_t)(W.plane[3] + (size_t)el * W.stride[3] + ((size_t)r * nb + bb) * 2) & ~(uintptr_t)3));
-        }
-      }
-    } else {
-      // [row][144 B]: 9 pieces a row (stride 144 B: row-per-lane 16-byte reads are conflict-free)
-#pragma unroll
-      for (int j = 0; j < 5; j++) {
-        const int p = tid + TC_NT * j;
-        if (p < TC_M * 9) {
-          const int i = p / 9, c = p - 9 * i;
-          bool sec;
-          const int r = grow(i, sec);
-          if (r >= 0) {
-            const WMat &W = sec ? W1 : W0;
-            tc_cp16(sRaw_a + (uint32_t)p * 16u, W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 144 + 16 * c);
-          }
-        }
-      }
-    }
-  };
-  issue_raw(0);
-  issue_b(0);
-
-  // unpack: thread = (row m of the tile, half hf of the block); a warp = 32 consecutive
-  // rows of one half: conflict-free 16-byte stores. The same thread folds row m's
-  // accumulators (TMEM lane m), so the row's (d, dmin) stay in registers.
-  const int m = tid & 127, hf = tid >> 7;
-  bool msec;
-  const int mrow = grow(m, msec);
-  // the f16 d of a Q6_K row sits in the low or high half of the staged word
-  const uint32_t dsel = Q6 && mrow >= 0
-                            ? (uint32_t)(((uintptr_t)((msec ? W1 : W0).plane[3] + (size_t)el * (msec ? W1 : W0).stride[3]) >> 1) & 1)
-                            : 0u;
-  if (mrow < 0) {  // rows past the matrix: zero operands, once
-    for (int kc = 8 * hf; kc < 8 * hf + 8; kc++)
-#pragma unroll
-      for (int pp = 0; pp < 2; pp++)
-        *(uint4 *)(sA + (size_t)pp * 32768 + (size_t)(kc * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
-    if (!Q6) *(uint4 *)(sAm + (size_t)(hf * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
-  }
-
-  // (3) fold: TMEM lanes of this warp's quarter (= rows m), 32 of the token columns
-  const int q = warp & 3, ch = warp >> 2;
-  const int ecol0 = ch * (TC_NMAX / 2);
-  float total[TC_NMAX / 2];
-#pragma unroll
-  for (int i = 0; i < TC_NMAX / 2; i++) total[i] = 0.0f;
-
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  const uint32_t sB_a = tc_s32(sB), sAm_a = tc_s32(sAm);
 
-  // instruction descriptors: D s32, A u8, B s8, K-major; and the f16 one (D f32)
-  const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
-  const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
-  const uint64_t dA0 = tc_desc(tc_s32(sA), TC_M * 16u, 128u);
-  const uint64_t dB0 = tc_desc(sB_a, (uint32_t)npad * 16u, 128u);
-  const uint64_t dAm = tc_desc(tc_s32(sAm), TC_M * 16u, 128u);
-  const uint64_t dBm = tc_desc(sBm_a, (uint32_t)npad * 16u, 128u);
+  if (warp == TC_NW / 32) {
+    // ================= the issuing warp =================
+    // instruction descriptors: D s32, A u8, B s8, K-major; and the f16 one (D f32)
+    const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+    const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+    for (int b = 0; b < nb; b++) {
+      const uint32_t bs = sB_a + (uint32_t)(b & 1) * BSTAGE;
+      const uint64_t dB0 = tc_desc(bs, (uint32_t)npad * 16u, 128u);
+      tc_ready_wait();  // operand A in TMEM, the tokens' block in shared memory, accumulators read
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if ((tid & 31) == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+          const uint64_t db = dB0 + (uint64_t)(ks * 2 * npad);
+          tc_mma_i8_ta(tmem + TC_ACC_HI, tmem + TC_A_HI + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
+          tc_mma_i8_ta(tmem + TC_ACC_LO, tmem + TC_A_LO + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
+        }
+        if (!Q6)
+          tc_mma_f16(tmem + TC_ACC_M, tc_desc(sAm_a + (uint32_t)(b & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
+                     tc_desc(bs + 16 * TC_NMAX * 16, (uint32_t)npad * 16u, 128u), idesc_h, 0u);
+        tc_commit(bar);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ================= the workers =================
+    const bool raw_role = tid < TC_NW / 2;  // copies: weights (first half) / activations (second half)
+    const int ct = tid & (TC_NW / 2 - 1);   // index within the role
 
-  bool dead = false;
-  for (int b = 0; b < nb; b++) {
-    TC_STAMP(b, 0)
-    // ---- 0. this block's bytes have landed (every thread's copies) ----
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();
-    if (*(volatile int *)s_dead) { dead = true; break; }
-    TC_STAMP(b, 1)
-    // ---- 1. weights of block b -> operand planes (the previous block's products have
-    // completed: every thread waited on their barrier) ----
-    float rd = 0.0f, rdmin = 0.0f;
-    if (mrow >= 0 && Q6) {
-      const uint8_t *rq = sRaw + m * 128, *rh = sRaw + 16384 + m * 64;
-      uint4 qlv[4], qhv[2];
+    // (1) activations: thread = (tokens bt, bt + 64; 16-byte column bp of every 64-byte
+    // group); a quarter-warp covers 8 consecutive tokens of one column: 128 contiguous bytes
+    // of shared memory, 64 contiguous bytes of a token row per four lanes
+    const int bt = (ct & 7) + 8 * (ct >> 5), bp = (ct >> 3) & 3;
+    int brow[2] = {-1, -1};
+    if (!raw_role) {
 #pragma unroll
-      for (int j = 0; j < 4; j++) qlv[j] = *(const uint4 *)(rq + (((4 * hf + j) ^ (m & 7)) << 4));
+      for (int hh = 0; hh < 2; hh++) {
+        const int t = bt + 64 * hh;
+        if (t < nvalid) brow[hh] = A.down ? (int)(off + n0 + t) : (int)A.g.pair_token[off + n0 + t];
+      }
+    }
+    const uint32_t sXd_a = tc_s32(sXd), sXs_a = tc_s32(sXs);
+    auto issue_b = [&](int bb) {  // the tokens' block bb -> its area, asynchronously (one group)
+      if (bb < nb) {
+        const uint32_t bs = sB_a + (uint32_t)(bb & 1) * BSTAGE;
 #pragma unroll
-      for (int j = 0; j < 2; j++) qhv[j] = *(const uint4 *)(rh + (((2 * hf + j) ^ ((m >> 1) & 3)) << 4));
-      const uint2 scw = *(const uint2 *)(sRaw + 24576 + m * 16 + 8 * hf);
-      const uint32_t dw = *(const uint32_t *)(sRaw + 26624 + m * 4);
-      rd = pm_f16(((((size_t)mrow * nb + b) & 1) ^ dsel) ? (dw >> 16) : (dw & 0xffffu));
+        for (int hh = 0; hh < 2; hh++) {
+          if (brow[hh] < 0) continue;
+          const int t = bt + 64 * hh;
+          const int8_t *src = A.xq + (size_t)brow[hh] * cols + (size_t)bb * 256 + 16 * bp;
+          const uint32_t dst = bs + (uint32_t)(bp * npad + t) * 16u;
 #pragma unroll
-      for (int qt = 0; qt < 4; qt++) {
-#pragma unroll
-        for (int lh = 0; lh < 2; lh++) {
-          const uint4 qlw = qlv[2 * (qt & 1) + lh];
-          const uint4 qhw = qhv[lh];
-          const int si = 2 * qt + lh;
-          const int sv = (int)(int8_t)((si < 4 ? scw.x >> (8 * si) : scw.y >> (8 * (si - 4))) & 0xff);
-          const uint32_t kk = (uint32_t)(4128 - 32 * sv) * 0x00010001u;
-          const uint32_t ws[4] = {qlw.x, qlw.y, qlw.z, qlw.w}, hs[4] = {qhw.x, qhw.y, qhw.z, qhw.w};
-          uint32_t th[4], tl[4];
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const uint32_t qv = ((ws[i] >> (qt >= 2 ? 4 : 0)) & 0x0f0f0f0fu) | (((hs[i] >> (2 * qt)) & 0x03030303u) << 4);
-            // two values per 32-bit product: 16-bit lanes of sv * q + (4128 - 32 sv) >= 0
-            const uint32_t ze = (qv & 0x00ff00ffu) * (uint32_t)sv + kk;
-            const uint32_t zo = ((qv >> 8) & 0x00ff00ffu) * (uint32_t)sv + kk;
-            tl[i] = __byte_perm(ze, zo, 0x6240) & 0x3f3f3f3fu;
-            th[i] = __byte_perm(ze >> 6, zo >> 6, 0x6240);
+          for (int j = 0; j < 4; j++) tc_cp16(dst + (uint32_t)(4 * j * npad) * 16u, src + 64 * j);
+          if (bp == 0) tc_cp4(sXd_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xd + (size_t)brow[hh] * nb + bb);
+          if (!Q6 && bp == 1) {
+            const uint16_t *s = A.xbm + ((size_t)brow[hh] * nb + bb) * 16;
+            tc_cp16(bs + 16 * TC_NMAX * 16 + (uint32_t)t * 16u, s);
+            tc_cp16(bs + 16 * TC_NMAX * 16 + (uint32_t)(npad + t) * 16u, s + 8);
           }
-          const size_t off_c = (size_t)((8 * hf + 2 * qt + lh) * TC_M + m) * 16;
-          *(uint4 *)(sA + off_c) = make_uint4(th[0], th[1], th[2], th[3]);
-          *(uint4 *)(sA + 32768 + off_c) = make_uint4(tl[0], tl[1], tl[2], tl[3]);
+          if (Q6 && bp == 1) tc_cp4(sXs_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xs + (size_t)brow[hh] * nb + bb);
         }
       }
-    } else if (mrow >= 0) {
-      const uint8_t *rp = sRaw + m * 144;
-      const uint4 hdr = *(const uint4 *)rp;
-      rd = pm_f16(hdr.x);
-      rdmin = pm_f16(hdr.x >> 16);
-      uint32_t mh[4];  // the eight mins as f16
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (!raw_role) {  // padding tokens: zero operands, once, both areas
 #pragma unroll
-      for (int jp = 0; jp < 4; jp++) {
-        int s0, m0, s1, m1;
-        pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp, s0, m0);
-        pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp + 1, s1, m1);
-        mh[jp] = (uint32_t)__half_as_ushort(__int2half_rn(m0)) | ((uint32_t)__half_as_ushort(__int2half_rn(m1)) << 16);
+      for (int hh = 0; hh < 2; hh++) {
+        const int t = bt + 64 * hh;
+        if (t >= nvalid && t < npad) {
+#pragma unroll
+          for (int st = 0; st < 2; st++) {
+            uint8_t *bs = sB + st * BSTAGE;
+#pragma unroll
+            for (int j = 0; j < 4; j++) *(uint4 *)(bs + (size_t)((bp + 4 * j) * npad + t) * 16) = make_uint4(0, 0, 0, 0);
+            if (!Q6 && bp == 1) {
+              *(uint4 *)(bs + 16 * TC_NMAX * 16 + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
+              *(uint4 *)(bs + 16 * TC_NMAX * 16 + (size_t)(npad + t) * 16) = make_uint4(0, 0, 0, 0);
+            }
+          }
+          if (bp == 0)
+            for (int k = 0; k < 4; k++) sXd[k * TC_NMAX + t] = 0.0f;
+          if (Q6 && bp == 1)
+            for (int k = 0; k < 4; k++) sXs[k * TC_NMAX + t] = 0;
+        }
       }
-      *(uint4 *)(sAm + (size_t)(hf * TC_M + m) * 16) = make_uint4(mh[0], mh[1], mh[2], mh[3]);
+    }
+
+    // (2) weights. Global row of tile row i (gate rows, then up rows, in a gate/up tile), or
+    // -1 past the matrix; `second`: the row belongs to the up matrix
+    auto grow = [&](int i, bool &second) -> int {
+      second = !A.down && i >= 64;
+      int r = r0 + (second ? i - 64 : i);
+      return r < rows ? r : -1;
+    };
+    const uint32_t sRaw_a = tc_s32(sRaw);
+    // the block bb of the tile's rows -> raw area bb % NS, in pieces of 16 bytes, consecutive
+    // lanes on consecutive pieces of a row (one group)
+    auto issue_raw = [&](int bb) {
+      if (bb < nb) {
+        const uint32_t ra = sRaw_a + (uint32_t)(bb % NS) * RAWB;
+        if (Q6) {
+          // ql: 8 pieces a row, [row][128 B], piece c at c ^ (row & 7); qh: 4 pieces a row,
+          // [row][64 B], piece c at c ^ ((row >> 1) & 3): both conflict-free for the row-per-lane
+          // reads below; sc: [row][16 B]; d: the aligned word holding the row's f16
 #pragma unroll
-      for (int cc = 0; cc < 2; cc++) {
-        const int c = 2 * hf + cc;
+          for (int j = 0; j < 4; j++) {
+            const int i = (ct >> 3) + 32 * j, c = ct & 7;
+            bool sec;
+            const int r = grow(i, sec);
+            if (r < 0) continue;
+            const WMat &W = sec ? W1 : W0;
+            tc_cp16(ra + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)),
+                    W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 128 + 16 * c);
+          }
+#pragma unroll
+          for (int j = 0; j < 2; j++) {
+            const int i = (ct >> 2) + 64 * j, c = ct & 3;
+            bool sec;
+            const int r = grow(i, sec);
+            if (r < 0) continue;
+            const WMat &W = sec ? W1 : W0;
+            tc_cp16(ra + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)),
+                    W.plane[1] + (size_t)el * W.stride[1] + ((size_t)r * nb + bb) * 64 + 16 * c);
+          }
+          {
+            const int i = ct & 127;
+            bool sec;
+            const int r = grow(i, sec);
+            if (r >= 0) {
+              const WMat &W = sec ? W1 : W0;
+              if (ct < 128)
+                tc_cp16(ra + 24576u + (uint32_t)i * 16u, W.plane[2] + (size_t)el * W.stride[2] + ((size_t)r * nb + bb) * 16);
+              else
+                tc_cp4(ra + 26624u + (uint32_t)i * 4u,
+                       (const uint8_t *)((uintptr_t)(W.plane[3] + (size_t)el * W.stride[3] + ((size_t)r * nb + bb) * 2) & ~(uintptr_t)3));
+            }
+          }
+        } else {
+          // [row][144 B]: 9 pieces a row (stride 144 B: row-per-lane 16-byte reads are conflict-free)
+#pragma unroll
+          for (int j = 0; j < 5; j++) {
+            const int p = ct + (TC_NW / 2) * j;
+            if (p < TC_M * 9) {
+              const int i = p / 9, c = p - 9 * i;
+              bool sec;
+              const int r = grow(i, sec);
+              if (r >= 0) {
+                const WMat &W = sec ? W1 : W0;
+                tc_cp16(ra + (uint32_t)p * 16u, W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 144 + 16 * c);
+              }
+            }
+          }
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (raw_role) {
+#pragma unroll
+      for (int i = 0; i < NS; i++) issue_raw(i);
+    } else {
+      issue_b(0);
+      issue_b(1);
+    }
+
+    // unpack: thread = (row m of the tile, quarter `part` of the block: K values
+    // 64 part .. 64 part + 63 = TMEM columns 16 part .. 16 part + 15 of each plane). The same
+    // thread folds row m's accumulators (TMEM lane m), a quarter of the token columns, so
+    // the row's (d, dmin) stay in registers.
+    const int m = tid & 127, part = tid >> 7;
+    bool msec;
+    const int mrow = grow(m, msec);
+    // the f16 d of a Q6_K row sits in the low or high half of the staged word
+    const uint32_t dsel = Q6 && mrow >= 0
+                              ? (uint32_t)(((uintptr_t)((msec ? W1 : W0).plane[3] + (size_t)el * (msec ? W1 : W0).stride[3]) >> 1) & 1)
+                              : 0u;
+    uint32_t ah[16], al[16];  // this thread's 64 values of the two planes
+    float nrd = 0.0f, nrdmin = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) ah[i] = al[i] = 0u;
+    if (mrow < 0 && !Q6) {  // rows past the matrix: zero mins, once, both buffers
+      if (part < 2) *(uint4 *)(sAm + (size_t)(part * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
+      else *(uint4 *)(sAm + 2 * TC_M * 16 + (size_t)((part - 2) * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    // block bb of its raw area -> ah/al, nrd/nrdmin (and the mins of the row into sAm[bb & 1])
+    auto unpack = [&](int bb) {
+      if (mrow < 0) return;
+      const uint8_t *raw = sRaw + (size_t)(bb % NS) * RAWB;
+      if (Q6) {
+        const int hf = part >> 1, p2 = part & 1;
+        const uint8_t *rq = raw + m * 128, *rh = raw + 16384 + m * 64;
+        uint4 qlv[4], qhv[2];
+#pragma unroll
+        for (int j = 0; j < 4; j++) qlv[j] = *(const uint4 *)(rq + (((4 * hf + j) ^ (m & 7)) << 4));
+#pragma unroll
+        for (int j = 0; j < 2; j++) qhv[j] = *(const uint4 *)(rh + (((2 * hf + j) ^ ((m >> 1) & 3)) << 4));
+        const uint32_t scw = *(const uint32_t *)(raw + 24576 + m * 16 + 8 * hf + 4 * p2);
+        const uint32_t dw = *(const uint32_t *)(raw + 26624 + m * 4);
+        nrd = pm_f16(((((size_t)mrow * nb + bb) & 1) ^ dsel) ? (dw >> 16) : (dw & 0xffffu));
+#pragma unroll
+        for (int qq = 0; qq < 2; qq++) {
+#pragma unroll
+          for (int lh = 0; lh < 2; lh++) {
+            // 16 values: sub-block 8 hf + 2 qt + lh of the block, qt = 2 p2 + qq
+            const uint4 qlw = qlv[2 * qq + lh];
+            const uint4 qhw = qhv[lh];
+            const int sv = (int)(int8_t)((scw >> (8 * (2 * qq + lh))) & 0xff);
+            const uint32_t kk = (uint32_t)(4128 - 32 * sv) * 0x00010001u;
+            const uint32_t ws[4] = {qlw.x, qlw.y, qlw.z, qlw.w}, hs[4] = {qhw.x, qhw.y, qhw.z, qhw.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              const uint32_t qv = ((ws[i] >> (4 * p2)) & 0x0f0f0f0fu) | (((hs[i] >> (4 * p2 + 2 * qq)) & 0x03030303u) << 4);
+              // two values per 32-bit product: 16-bit lanes of sv * q + (4128 - 32 sv) >= 0
+              const uint32_t ze = (qv & 0x00ff00ffu) * (uint32_t)sv + kk;
+              const uint32_t zo = ((qv >> 8) & 0x00ff00ffu) * (uint32_t)sv + kk;
+              al[4 * (2 * qq + lh) + i] = __byte_perm(ze, zo, 0x6240) & 0x3f3f3f3fu;
+              ah[4 * (2 * qq + lh) + i] = __byte_perm(ze >> 6, zo >> 6, 0x6240);
+            }
+          }
+        }
+      } else {
+        const uint8_t *rp = raw + m * 144;
+        const uint4 hdr = *(const uint4 *)rp;
+        nrd = pm_f16(hdr.x);
+        nrdmin = pm_f16(hdr.x >> 16);
+        if (part < 2) {  // the eight mins as f16, K chunk `part` of the f16 product (both hold m_0..m_7)
+          uint32_t mh[4];
+#pragma unroll
+          for (int jp = 0; jp < 4; jp++) {
+            int s0, m0, s1, m1;
+            pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp, s0, m0);
+            pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp + 1, s1, m1);
+            mh[jp] = (uint32_t)__half_as_ushort(__int2half_rn(m0)) | ((uint32_t)__half_as_ushort(__int2half_rn(m1)) << 16);
+          }
+          *(uint4 *)(sAm + (size_t)(bb & 1) * (2 * TC_M * 16) + (size_t)(part * TC_M + m) * 16) = make_uint4(mh[0], mh[1], mh[2], mh[3]);
+        }
+        const int c = part;
         const uint4 w0 = *(const uint4 *)(rp + 16 + 32 * c), w1 = *(const uint4 *)(rp + 32 + 32 * c);
         int sc0, m0, sc1, m1;
         pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c, sc0, m0);
         pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c + 1, sc1, m1);
         const uint32_t M4 = 0x0f0f0f0fu;
-        // sub-block 2c = low nibbles -> K chunks 4c, 4c+1 ; sub-block 2c+1 = high -> 4c+2, 4c+3
+        // sub-block 2c = low nibbles -> K 64c .. 64c+31 ; sub-block 2c+1 = high -> K 64c+32 .. 64c+63
         const uint32_t lo[8] = {w0.x & M4, w0.y & M4, w0.z & M4, w0.w & M4, w1.x & M4, w1.y & M4, w1.z & M4, w1.w & M4};
         const uint32_t hi[8] = {(w0.x >> 4) & M4, (w0.y >> 4) & M4, (w0.z >> 4) & M4, (w0.w >> 4) & M4,
                                 (w1.x >> 4) & M4, (w1.y >> 4) & M4, (w1.z >> 4) & M4, (w1.w >> 4) & M4};
         const uint32_t sh0 = (uint32_t)sc0 >> 3, sl0 = (uint32_t)sc0 & 7, sh1 = (uint32_t)sc1 >> 3, sl1 = (uint32_t)sc1 & 7;
 #pragma unroll
-        for (int h2 = 0; h2 < 2; h2++) {
-          const size_t o_lo = (size_t)((4 * c + h2) * TC_M + m) * 16;      // chunk of sub-block 2c
-          const size_t o_hi = (size_t)((4 * c + 2 + h2) * TC_M + m) * 16;  // chunk of sub-block 2c+1
-          const uint32_t *l4 = lo + 4 * h2, *h4 = hi + 4 * h2;
-          *(uint4 *)(sA + o_lo) = make_uint4(l4[0] * sh0, l4[1] * sh0, l4[2] * sh0, l4[3] * sh0);
-          *(uint4 *)(sA + 32768 + o_lo) = make_uint4(l4[0] * sl0, l4[1] * sl0, l4[2] * sl0, l4[3] * sl0);
-          *(uint4 *)(sA + o_hi) = make_uint4(h4[0] * sh1, h4[1] * sh1, h4[2] * sh1, h4[3] * sh1);
-          *(uint4 *)(sA + 32768 + o_hi) = make_uint4(h4[0] * sl1, h4[1] * sl1, h4[2] * sl1, h4[3] * sl1);
+        for (int i = 0; i < 8; i++) {
+          ah[i] = lo[i] * sh0;
+          al[i] = lo[i] * sl0;
+          ah[8 + i] = hi[i] * sh1;
+          al[8 + i] = hi[i] * sl1;
         }
       }
-    }
-    TC_STAMP(b, 2)
-    // all operand writes -> visible to the tensor core; the raw area is free again
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    TC_STAMP(b, 3)
+    };
 
-    // ---- 2. 8 K-steps x 2 planes (+ the mins' one f16 product) ----
-    if (tid == 0) {
+    // (3) fold: TMEM lane m, a quarter of the tile's token columns (npad / 4: a multiple of 4)
+    const uint32_t tlane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+    const int ew = npad >> 2, ecol0 = part * ew;
+    float total[32];
 #pragma unroll
-      for (int ks = 0; ks < 8; ks++) {
-        const uint64_t db = dB0 + (uint64_t)(ks * 2 * npad);
-#pragma unroll
-        for (int p = 0; p < 2; p++)
-          tc_mma_i8(tmem + (uint32_t)p * TC_NMAX, dA0 + (uint64_t)(p * 2048 + ks * 256), db, idesc, ks > 0 ? 1u : 0u);
+    for (int i = 0; i < 32; i++) total[i] = 0.0f;
+
+    if (raw_role) asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
+    tc_workers_sync();
+    unpack(0);
+    tc_workers_sync();
+    if (raw_role) issue_raw(NS);
+
+    for (int b = 0; b < nb; b++) {
+      TC_STAMP(b, 0)
+      const float rd = nrd, rdmin = nrdmin;
+      // ---- 1. operand A of block b -> tensor memory (the previous block's products have
+      // completed: every worker waited on their barrier) ----
+      tc_st16(tlane + TC_A_HI + 16u * part, ah);
+      tc_st16(tlane + TC_A_LO + 16u * part, al);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (!raw_role) asm volatile("cp.async.wait_group 1;" ::: "memory");  // the tokens' block b has landed
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      tc_ready_arrive();
+      TC_STAMP(b, 1)
+      // ---- 2. while the products run: the next block -> registers ----
+      if (b + 1 < nb) {
+        if (raw_role) asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
+        tc_workers_sync();  // every copy of the raw block b + 1 has landed
+        unpack(b + 1);
+        tc_workers_sync();  // its raw area is free again
+        if (raw_role) issue_raw(b + 1 + NS);
       }
-      if (!Q6) tc_mma_f16(tmem + 2u * TC_NMAX, dAm, dBm, idesc_h, 0u);
-      tc_commit(bar);
-    }
-    issue_raw(b + 1);  // the next block's weight bytes start their trip from HBM now
-    TC_STAMP(b, 4)
-    // ---- 3. the block's float term, in block order ----
-    if (!tc_bar_test(bar, (uint32_t)(b & 1)) && !tc_bar_wait(bar, (uint32_t)(b & 1), A.err)) *(volatile int *)s_dead = 1;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    TC_STAMP(b, 5)
-    issue_b(b + 1);  // the operands are free again: the next block's activations
-    TC_STAMP(b, 6)
-    {
-      const uint32_t tl = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)ecol0;
-      const float *xdv = sXd + (b & 1) * TC_NMAX + ecol0;
-      const int32_t *xsv = sXs + (b & 1) * TC_NMAX + ecol0;
+      TC_STAMP(b, 2)
+      // ---- 3. the block's float term, in block order ----
+      if (!tc_bar_test(bar, (uint32_t)(b & 1))) tc_bar_wait(bar, (uint32_t)(b & 1), A.err);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      TC_STAMP(b, 3)
+      if (!raw_role) issue_b(b + 2);  // the tokens' area of block b is free again
+      TC_STAMP(b, 4)
+      {
+        const float *xdv = sXd + (b & 3) * TC_NMAX + ecol0;
+        const int32_t *xsv = sXs + (b & 3) * TC_NMAX + ecol0;
 #pragma unroll
-      for (int c16 = 0; c16 < TC_NMAX / 2; c16 += 16) {
-        if (ecol0 + c16 < npad) {
-          uint32_t v0[16], v1[16], v2[16];
-          tc_ld16(tl + (uint32_t)(0 * TC_NMAX + c16), v0);
-          tc_ld16(tl + (uint32_t)(1 * TC_NMAX + c16), v1);
-          if (!Q6) tc_ld16(tl + (uint32_t)(2 * TC_NMAX + c16), v2);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (int i4 = 0; i4 < 16; i4 += 4) {
-            const float4 x4 = *(const float4 *)(xdv + c16 + i4);
+        for (int c4 = 0; c4 < 32; c4 += 4) {
+          if (c4 < ew) {
+            uint32_t v0[4], v1[4], v2[4];
+            tc_ld4(tlane + TC_ACC_HI + (uint32_t)(ecol0 + c4), v0);
+            tc_ld4(tlane + TC_ACC_LO + (uint32_t)(ecol0 + c4), v1);
+            if (!Q6) tc_ld4(tlane + TC_ACC_M + (uint32_t)(ecol0 + c4), v2);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const float4 x4 = *(const float4 *)(xdv + c4);
             const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
             int ss[4] = {0, 0, 0, 0};
             if (Q6) {
-              const int4 s4 = *(const int4 *)(xsv + c16 + i4);
+              const int4 s4 = *(const int4 *)(xsv + c4);
               ss[0] = s4.x; ss[1] = s4.y; ss[2] = s4.z; ss[3] = s4.w;
             }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-              const int i = i4 + u;
               float term;
               if (Q6) {
-                int isum = 64 * (int)v0[i] + (int)v1[i] - 4128 * ss[u];
+                int isum = 64 * (int)v0[u] + (int)v1[u] - 4128 * ss[u];
                 term = __fmul_rn(xs[u], __fmul_rn(rd, (float)isum));
               } else {
-                int isum = 8 * (int)v0[i] + (int)v1[i];
-                term = __fmul_rn(xs[u], __fsub_rn(__fmul_rn(rd, (float)isum), __fmul_rn(rdmin, __uint_as_float(v2[i]))));
+                int isum = 8 * (int)v0[u] + (int)v1[u];
+                term = __fmul_rn(xs[u], __fsub_rn(__fmul_rn(rd, (float)isum), __fmul_rn(rdmin, __uint_as_float(v2[u]))));
               }
-              total[c16 + i] = __fadd_rn(total[c16 + i], term);
+              total[c4 + u] = __fadd_rn(total[c4 + u], term);
             }
           }
         }
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      TC_STAMP(b, 5)
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    TC_STAMP(b, 7)
-  }
-  asm volatile("cp.async.wait_all;" ::: "memory");
-  __syncthreads();  // every fold is done: the planes' memory is free, TMEM can go
-  if (*(volatile int *)s_dead) dead = true;
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    tc_workers_sync();  // the raw areas are dead: their memory carries the gate/up exchange
 
-  if (!dead) {
+    const bool dead = *(volatile int *)A.err != 0;
     if (A.down) {
-      const float bd = (!A.shared && ly.bias_down && r0 + m < rows) ? ly.bias_down[(size_t)el * rows + r0 + m] : 0.0f;
+      if (!dead) {
+        const float bd = (!A.shared && ly.bias_down && r0 + m < rows) ? ly.bias_down[(size_t)el * rows + r0 + m] : 0.0f;
 #pragma unroll
-      for (int i = 0; i < TC_NMAX / 2; i++) {
-        int n = ecol0 + i;
-        if (n < nvalid && r0 + m < rows) {
-          float o = total[i];
-          if (!A.shared && ly.bias_down) o = __fadd_rn(o, bd);
-          A.out[(size_t)(off + n0 + n) * rows + r0 + m] = o;
+        for (int i = 0; i < 32; i++) {
+          int n = ecol0 + i;
+          if (i < ew && n < nvalid && r0 + m < rows) {
+            float o = total[i];
+            if (!A.shared && ly.bias_down) o = __fadd_rn(o, bd);
+            A.out[(size_t)(off + n0 + n) * rows + r0 + m] = o;
+          }
         }
       }
     } else {
       // gate rows in tile rows 0..63, up rows in 64..127: exchange through shared memory
-      float *S = (float *)sA;  // [128][65]
 #pragma unroll
-      for (int i = 0; i < TC_NMAX / 2; i++) S[m * (TC_NMAX + 1) + ecol0 + i] = total[i];
-      __syncthreads();
+      for (int i = 0; i < 32; i++)
+        if (i < ew) sS[m * (TC_NMAX + 1) + ecol0 + i] = total[i];
+      tc_workers_sync();
       const pm_layer_desc &D = ly.desc;
       const bool fold = !A.shared && D.weight_fold == PM_FOLD_BEFORE_DOWN && A.wts;
       const bool bias = !A.shared && ly.bias_gate;
-      for (int i = tid; i < nvalid * 64; i += TC_NT) {
-        int j = i & 63, n = i >> 6;
-        if (r0 + j >= rows) continue;
-        float gv = S[j * (TC_NMAX + 1) + n], uv = S[(64 + j) * (TC_NMAX + 1) + n];
-        if (bias) {
-          gv = __fadd_rn(gv, ly.bias_gate[(size_t)el * rows + r0 + j]);
-          uv = __fadd_rn(uv, ly.bias_up[(size_t)el * rows + r0 + j]);
+      if (!dead)
+        for (int i = tid; i < nvalid * 64; i += TC_NW) {
+          int j = i & 63, n = i >> 6;
+          if (r0 + j >= rows) continue;
+          float gv = sS[j * (TC_NMAX + 1) + n], uv = sS[(64 + j) * (TC_NMAX + 1) + n];
+          if (bias) {
+            gv = __fadd_rn(gv, ly.bias_gate[(size_t)el * rows + r0 + j]);
+            uv = __fadd_rn(uv, ly.bias_up[(size_t)el * rows + r0 + j]);
+          }
+          uint32_t p = off + n0 + n;
+          float w = fold ? A.wts[A.g.pair_src[p]] : 1.0f;
+          A.out[(size_t)p * rows + r0 + j] = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, w, fold);
         }
-        uint32_t p = off + n0 + n;
-        float w = fold ? A.wts[A.g.pair_src[p]] : 1.0f;
-        A.out[(size_t)p * rows + r0 + j] = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, w, fold);
-      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0)
+  if (warp == TC_NW / 32)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TC_TMEM_COLS) : "memory");
 }
 
@@ -583,8 +649,10 @@ int tc_max_tiles(int n_pairs, int max_groups) {
   return n_pairs / TC_NMAX + groups;
 }
 static size_t tc_smem(bool q6) {
-  return (size_t)2 * 32768 + (q6 ? 0 : 2 * TC_M * 16) + 16 * TC_NMAX * 16 + (q6 ? 0 : 2 * TC_NMAX * 16) +
-         (q6 ? TC_RAW_Q6 : TC_RAW_Q4) + 2 * TC_NMAX * 4 + (q6 ? 2 * TC_NMAX * 4 : 0) + 16;
+  size_t raw = q6 ? (size_t)TC_RAW_STAGES_Q6 * TC_RAW_Q6 : (size_t)TC_RAW_STAGES_Q4 * TC_RAW_Q4;
+  size_t ex = (size_t)TC_M * (TC_NMAX + 1) * 4;  // the gate/up exchange shares the raw areas' memory
+  size_t bstage = (size_t)16 * TC_NMAX * 16 + (q6 ? 0 : 2 * TC_NMAX * 16);
+  return (raw > ex ? raw : ex) + 2 * bstage + 2 * 2 * TC_M * 16 + 4 * TC_NMAX * 4 + 4 * TC_NMAX * 4 + 16;
 }
 
 // Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x

@@ -19,7 +19,7 @@ BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), MXFP4: (32, 17)}
 
 GATE_SOFTMAX_ALL, GATE_SIGMOID, GATE_SQRT_SOFTPLUS, GATE_SOFTMAX_SELECTED = 0, 1, 2, 3
 ACT_SILU, ACT_SILU_CLAMP, ACT_OSS_GLU = 0, 1, 2
-AQ_F32, AQ_Q8X_256 = 0, 1
+AQ_F32, AQ_Q8X_256, AQ_Q8_32 = 0, 1, 2
 FOLD_BEFORE_DOWN, FOLD_IN_COMBINE = 0, 1
 SHARED_NONE, SHARED_PLAIN, SHARED_SIGMOID_GATED = 0, 1, 2
 
@@ -218,7 +218,12 @@ C4_DSV3 = Config("deepseek-v3-shaped", d=7168, ff=2048, n_exp=256, top_k=8, gati
                  w_scale=2.5, n_group=8, topk_group=4, shared=SHARED_PLAIN, shared_ff=2048, n_layers=58,
                  select_bias_sigma=0.01)
 C5_ZIPF = Config("qwen3-zipf", d=2048, ff=768, n_exp=128, top_k=8, gating=GATE_SOFTMAX_ALL, norm_w=1)
-CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF}
+# the reference's second CPU expert path (src/q4x_cpu.rs): 32-block Q8 activations against
+# Q8_0 weights, softmax over the selected logits (src/q4x.rs:2213-2231); its own test shape
+# is 2560 x 640 (src/q4x_cpu.rs:544)
+C6_Q8_0 = Config("q4x-q8_0", d=2560, ff=640, n_exp=32, top_k=8, gating=GATE_SOFTMAX_SELECTED, type_gate=Q8_0,
+                 type_up=Q8_0, type_down=Q8_0, act_quant=AQ_Q8_32)
+CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0}
 
 
 def make_weights(cfg: Config, seed: int, experts=None) -> dict:

@@ -24,12 +24,13 @@ SHAPES = {
     "c2": synth.C2_QWEN3.scaled(d=256, ff=256, n_exp=12, top_k=4),
     "c3": synth.C3_GPTOSS.scaled(d=96, ff=64, n_exp=6, top_k=2),
     "c4": synth.C4_DSV3.scaled(d=256, ff=256, n_exp=16, top_k=4, n_group=4, topk_group=2, shared_ff=256),
+    "c6": synth.C6_Q8_0.scaled(d=160, ff=96, n_exp=8, top_k=2),
 }
 
 
 def case(name):
     cfg = SHAPES[name]
-    seed = {"c1": 101, "c2": 102, "c3": 103, "c4": 104}[name]
+    seed = {"c1": 101, "c2": 102, "c3": 103, "c4": 104, "c6": 106}[name]
     W = synth.make_weights(cfg, seed)
     x = synth.make_activations(5, cfg.d, seed + 1000)
     return cfg, W, x

@@ -58,6 +58,7 @@ SMALL = {
     "c3": synth.C3_GPTOSS.scaled(d=320, ff=160, n_exp=8),
     "c4": synth.C4_DSV3.scaled(d=512, ff=256, n_exp=32, n_group=4, topk_group=2, shared_ff=256),
     "c5": synth.C5_ZIPF.scaled(d=512, ff=256, n_exp=32),
+    "c6": synth.C6_Q8_0.scaled(d=320, ff=160, n_exp=16),
 }
 
 

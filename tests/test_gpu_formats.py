@@ -67,6 +67,22 @@ def test_quant_act_bit_exact(ctx, oracle):
         assert np.array_equal(bs, obs)
 
 
+def test_quant_act_32_bit_exact(ctx, oracle):
+    """`Q8::new` (src/q4x_cpu.rs:23-37): values, scales; zero blocks, ties, clamping."""
+    rng = np.random.default_rng(12)
+    cases = [rng.standard_normal(2560).astype(np.float32), np.zeros(64, np.float32),
+             np.concatenate([np.zeros(32), np.full(32, -3.5), np.arange(32) - 15.5]).astype(np.float32),
+             (rng.standard_normal(640) * 1e-30).astype(np.float32), (rng.standard_normal(320) * 1e30).astype(np.float32)]
+    half = np.zeros(32, np.float32)  # .5 ties round away from zero
+    half[0], half[1], half[2], half[3] = 127.0, 0.5, -0.5, 1.5
+    cases.append(half)
+    for x in cases:
+        q, d = ctx.quant_act_32(x)
+        oq, od = oracle.q8_32(x)
+        assert np.array_equal(q, oq)
+        assert bits_equal(d, od)
+
+
 def test_quant_act_rejects_ragged(ctx):
     import pelica_b200 as pb
 

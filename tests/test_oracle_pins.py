@@ -209,7 +209,7 @@ def test_fast_layer_matches_canonical(oracle):
     assert np.abs(y - yf).max() <= 1e-3 * np.abs(y).max()
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6"])
 def test_golden_layer_outputs(oracle, name):
     """The committed fixtures (tests/golden/make_golden.py) pin the oracle itself."""
     from tests.golden.make_golden import case
