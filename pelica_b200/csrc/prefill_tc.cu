@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(512) k_tc_tiles(Groups g, int *n_tiles, uint32
 // Memory: the weight bytes of a block arrive by cp.async in row-contiguous pieces (a warp
 // reads whole 144-byte / 128-byte runs) into one of TC_RAW_STAGES raw areas, issued that
 // many blocks ahead (HBM answers in about 2000 cycles under load; one block lasts less);
-// the tokens' int8 activations go to one of two areas, two blocks ahead. The first half
+// the tokens' int8 activations go to one of three areas, two blocks ahead. The first half
 // of the workers issues the weight copies, the second half the activation copies, so
 // that each thread's cp.async groups complete in the order they are needed.
 template <int WT>
@@ -208,7 +208,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   constexpr bool Q6 = WT == PM_TYPE_Q6_K;
   constexpr int NS = Q6 ? TC_RAW_STAGES_Q6 : TC_RAW_STAGES_Q4;
   constexpr int RAWB = Q6 ? TC_RAW_Q6 : TC_RAW_Q4;
-  constexpr int BSTAGE = 16 * TC_NMAX * 16 + (Q6 ? 0 : 2 * TC_NMAX * 16);  // tokens' block (+ f16 sums)
+  // the tokens' block: [16 chunks][npad tokens + 1][16 B] (+ Q4_K: [2 chunks][npad + 1][8 f16]); the
+  // odd pitch lets a quarter-warp write the 8 chunks of one token without bank conflicts
+  constexpr int BMOFF = 16 * (TC_NMAX + 1) * 16;
+  constexpr int BSTAGE = BMOFF + (Q6 ? 0 : 2 * (TC_NMAX + 1) * 16);
   extern __shared__ __align__(128) uint8_t smem[];
   // blockIdx.y walks the list of (group, token tile) pairs made by k_tc_tiles
   if ((int)blockIdx.y >= *A.n_tiles) return;
@@ -239,9 +242,9 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   uint8_t *sRaw = smem;                                        // [NS] blocks of the 128 rows as stored
   float *sS = (float *)smem;                                   // (after the last block) gate/up exchange [128][129]
   uint8_t *sB = smem + (NS * RAWB > TC_M * (TC_NMAX + 1) * 4 ? NS * RAWB : TC_M * (TC_NMAX + 1) * 4);
-                                                               // [2] x ([16 chunks][npad tokens][16 B] + Q4_K:
+                                                               // [3] x ([16 chunks][npad tokens][16 B] + Q4_K:
                                                                //        [2 chunks][npad tokens][8 f16])
-  uint8_t *sAm = sB + 2 * BSTAGE;                              // Q4_K: [2][2 chunks][128 rows][8 f16]
+  uint8_t *sAm = sB + 3 * BSTAGE;                              // Q4_K: [2][2 chunks][128 rows][8 f16]
   float *sXd = (float *)(sAm + 2 * 2 * TC_M * 16);             // [4][128] x.d of a block per token
   int32_t *sXs = (int32_t *)(sXd + 4 * TC_NMAX);               // Q6_K: [4][128] sum of the block's xq
   uint64_t *bar = (uint64_t *)(sXs + 4 * TC_NMAX);
@@ -270,20 +273,20 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     for (int b = 0; b < nb; b++) {
-      const uint32_t bs = sB_a + (uint32_t)(b & 1) * BSTAGE;
-      const uint64_t dB0 = tc_desc(bs, (uint32_t)npad * 16u, 128u);
+      const uint32_t bs = sB_a + (uint32_t)(b % 3) * BSTAGE;
+      const uint64_t dB0 = tc_desc(bs, (uint32_t)(npad + 1) * 16u, 128u);
       tc_ready_wait();  // operand A in TMEM, the tokens' block in shared memory, accumulators read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if ((tid & 31) == 0) {
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
-          const uint64_t db = dB0 + (uint64_t)(ks * 2 * npad);
+          const uint64_t db = dB0 + (uint64_t)(ks * 2 * (npad + 1));
           tc_mma_i8_ta(tmem + TC_ACC_HI, tmem + TC_A_HI + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
           tc_mma_i8_ta(tmem + TC_ACC_LO, tmem + TC_A_LO + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
         }
         if (!Q6)
           tc_mma_f16(tmem + TC_ACC_M, tc_desc(sAm_a + (uint32_t)(b & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
-                     tc_desc(bs + 16 * TC_NMAX * 16, (uint32_t)npad * 16u, 128u), idesc_h, 0u);
+                     tc_desc(bs + BMOFF, (uint32_t)(npad + 1) * 16u, 128u), idesc_h, 0u);
         tc_commit(bar);
       }
       __syncwarp();
@@ -293,59 +296,56 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     const bool raw_role = tid < TC_NW / 2;  // copies: weights (first half) / activations (second half)
     const int ct = tid & (TC_NW / 2 - 1);   // index within the role
 
-    // (1) activations: thread = (tokens bt, bt + 64; 16-byte column bp of every 64-byte
-    // group); a quarter-warp covers 8 consecutive tokens of one column: 128 contiguous bytes
-    // of shared memory, 64 contiguous bytes of a token row per four lanes
-    const int bt = (ct & 7) + 8 * (ct >> 5), bp = (ct >> 3) & 3;
-    int brow[2] = {-1, -1};
+    // (1) activations: a quarter-warp copies 128 contiguous bytes of one token's row (the 8
+    // chunks of half a block: one line of global memory) per instruction; warp w of the role
+    // takes tokens 16 w .. 16 w + 15, four at a time
+    const int bc = ct & 7, bsub = (ct >> 3) & 3, bw = ct >> 5;
+    int brow[4] = {-1, -1, -1, -1};
     if (!raw_role) {
 #pragma unroll
-      for (int hh = 0; hh < 2; hh++) {
-        const int t = bt + 64 * hh;
-        if (t < nvalid) brow[hh] = A.down ? (int)(off + n0 + t) : (int)A.g.pair_token[off + n0 + t];
+      for (int i = 0; i < 4; i++) {
+        const int t = 16 * bw + 4 * i + bsub;
+        if (t < nvalid) brow[i] = A.down ? (int)(off + n0 + t) : (int)A.g.pair_token[off + n0 + t];
       }
     }
     const uint32_t sXd_a = tc_s32(sXd), sXs_a = tc_s32(sXs);
+    const uint32_t bpitch = (uint32_t)(npad + 1) * 16u;
     auto issue_b = [&](int bb) {  // the tokens' block bb -> its area, asynchronously (one group)
       if (bb < nb) {
-        const uint32_t bs = sB_a + (uint32_t)(bb & 1) * BSTAGE;
+        const uint32_t bs = sB_a + (uint32_t)(bb % 3) * BSTAGE;
 #pragma unroll
-        for (int hh = 0; hh < 2; hh++) {
-          if (brow[hh] < 0) continue;
-          const int t = bt + 64 * hh;
-          const int8_t *src = A.xq + (size_t)brow[hh] * cols + (size_t)bb * 256 + 16 * bp;
-          const uint32_t dst = bs + (uint32_t)(bp * npad + t) * 16u;
-#pragma unroll
-          for (int j = 0; j < 4; j++) tc_cp16(dst + (uint32_t)(4 * j * npad) * 16u, src + 64 * j);
-          if (bp == 0) tc_cp4(sXd_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xd + (size_t)brow[hh] * nb + bb);
-          if (!Q6 && bp == 1) {
-            const uint16_t *s = A.xbm + ((size_t)brow[hh] * nb + bb) * 16;
-            tc_cp16(bs + 16 * TC_NMAX * 16 + (uint32_t)t * 16u, s);
-            tc_cp16(bs + 16 * TC_NMAX * 16 + (uint32_t)(npad + t) * 16u, s + 8);
-          }
-          if (Q6 && bp == 1) tc_cp4(sXs_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xs + (size_t)brow[hh] * nb + bb);
+        for (int i = 0; i < 4; i++) {
+          if (brow[i] < 0) continue;
+          const int t = 16 * bw + 4 * i + bsub;
+          const int8_t *src = A.xq + (size_t)brow[i] * cols + (size_t)bb * 256 + 16 * bc;
+          const uint32_t dst = bs + (uint32_t)bc * bpitch + (uint32_t)t * 16u;
+          tc_cp16(dst, src);
+          tc_cp16(dst + 8u * bpitch, src + 128);
+          if (bc == 0) tc_cp4(sXd_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xd + (size_t)brow[i] * nb + bb);
+          if (!Q6 && (bc == 1 || bc == 2))
+            tc_cp16(bs + BMOFF + (uint32_t)(bc - 1) * bpitch + (uint32_t)t * 16u,
+                    A.xbm + ((size_t)brow[i] * nb + bb) * 16 + 8 * (bc - 1));
+          if (Q6 && bc == 1) tc_cp4(sXs_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xs + (size_t)brow[i] * nb + bb);
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    if (!raw_role) {  // padding tokens: zero operands, once, both areas
+    if (!raw_role) {  // padding tokens: zero operands, once, every area
 #pragma unroll
-      for (int hh = 0; hh < 2; hh++) {
-        const int t = bt + 64 * hh;
+      for (int i = 0; i < 4; i++) {
+        const int t = 16 * bw + 4 * i + bsub;
         if (t >= nvalid && t < npad) {
 #pragma unroll
-          for (int st = 0; st < 2; st++) {
+          for (int st = 0; st < 3; st++) {
             uint8_t *bs = sB + st * BSTAGE;
-#pragma unroll
-            for (int j = 0; j < 4; j++) *(uint4 *)(bs + (size_t)((bp + 4 * j) * npad + t) * 16) = make_uint4(0, 0, 0, 0);
-            if (!Q6 && bp == 1) {
-              *(uint4 *)(bs + 16 * TC_NMAX * 16 + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
-              *(uint4 *)(bs + 16 * TC_NMAX * 16 + (size_t)(npad + t) * 16) = make_uint4(0, 0, 0, 0);
-            }
+            *(uint4 *)(bs + (size_t)bc * bpitch + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
+            *(uint4 *)(bs + (size_t)(bc + 8) * bpitch + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
+            if (!Q6 && (bc == 1 || bc == 2))
+              *(uint4 *)(bs + BMOFF + (size_t)(bc - 1) * bpitch + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
           }
-          if (bp == 0)
+          if (bc == 0)
             for (int k = 0; k < 4; k++) sXd[k * TC_NMAX + t] = 0.0f;
-          if (Q6 && bp == 1)
+          if (Q6 && bc == 1)
             for (int k = 0; k < 4; k++) sXs[k * TC_NMAX + t] = 0;
         }
       }
@@ -545,6 +545,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       tc_ready_arrive();
+      if (!raw_role) issue_b(b + 2);  // its area was read by the products of block b - 1: free
       TC_STAMP(b, 1)
       // ---- 2. while the products run: the next block -> registers ----
       if (b + 1 < nb) {
@@ -559,7 +560,6 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       if (!tc_bar_test(bar, (uint32_t)(b & 1))) tc_bar_wait(bar, (uint32_t)(b & 1), A.err);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       TC_STAMP(b, 3)
-      if (!raw_role) issue_b(b + 2);  // the tokens' area of block b is free again
       TC_STAMP(b, 4)
       {
         const float *xdv = sXd + (b & 3) * TC_NMAX + ecol0;
@@ -651,8 +651,8 @@ int tc_max_tiles(int n_pairs, int max_groups) {
 static size_t tc_smem(bool q6) {
   size_t raw = q6 ? (size_t)TC_RAW_STAGES_Q6 * TC_RAW_Q6 : (size_t)TC_RAW_STAGES_Q4 * TC_RAW_Q4;
   size_t ex = (size_t)TC_M * (TC_NMAX + 1) * 4;  // the gate/up exchange shares the raw areas' memory
-  size_t bstage = (size_t)16 * TC_NMAX * 16 + (q6 ? 0 : 2 * TC_NMAX * 16);
-  return (raw > ex ? raw : ex) + 2 * bstage + 2 * 2 * TC_M * 16 + 4 * TC_NMAX * 4 + 4 * TC_NMAX * 4 + 16;
+  size_t bstage = (size_t)16 * (TC_NMAX + 1) * 16 + (q6 ? 0 : 2 * (TC_NMAX + 1) * 16);
+  return (raw > ex ? raw : ex) + 3 * bstage + 2 * 2 * TC_M * 16 + 4 * TC_NMAX * 4 + 4 * TC_NMAX * 4 + 16;
 }
 
 // Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x
