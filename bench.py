@@ -263,8 +263,9 @@ def cpu_sample(cfg, weights_per_layer, xs, threads):
 def run_reference(args, cfg, n_layers, T, desc):
     """--impl reference: the reference's CPU implementation of the path (the oracle's
     restatement of its fast path; the Rust original cannot be built here) on host cores."""
-    world, rank, _, _ = dist_setup(args.gpus)
-    if rank != 0:
+    # rank 0 alone runs and prints this arm; the other ranks leave without work (no process group:
+    # nothing here uses a GPU)
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     from oracle import pelica_oracle as po
 
@@ -396,8 +397,6 @@ def main():
     checksum = float(np.abs(hy).sum())
 
     # distinct experts per layer actually hit (decode: top_k; prefill: measured from usage)
-    for ly in layers[:1]:
-        pass
     if T == 1:
         distinct = cfg.top_k
     else:

@@ -110,6 +110,23 @@ __device__ __forceinline__ void pm_q4k_scmin(uint32_t w0, uint32_t w1, uint32_t 
   }
 }
 
+// all eight (scale, min) pairs of a Q4_K block at once, as bytes of four words: sub-blocks
+// 0..3 in sc03 / m03, 4..7 in sc47 / m47 (same field as pm_q4k_scmin)
+__device__ __forceinline__ void pm_q4k_scmin_packed(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t &sc03,
+                                                    uint32_t &sc47, uint32_t &m03, uint32_t &m47) {
+  sc03 = w0 & 0x3f3f3f3fu;
+  m03 = w1 & 0x3f3f3f3fu;
+  sc47 = (w2 & 0x0f0f0f0fu) | ((w0 >> 2) & 0x30303030u);
+  m47 = ((w2 >> 4) & 0x0f0f0f0fu) | ((w1 >> 2) & 0x30303030u);
+}
+// bytes (b_lo, b_hi) selected by `sel` (a __byte_perm selector placing them in the low bytes
+// of the two 16-bit lanes) as two f16 values: 0x6400 | b is 1024 + b, minus 1024 is exact
+__device__ __forceinline__ uint32_t pm_bytes_to_half2(uint32_t w, uint32_t sel) {
+  const uint32_t h = __byte_perm(w, 0u, sel) | 0x64006400u;
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half((unsigned short)0x6400)));
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+
 // `e8` (src/oss_kernels.rs:42-45): 2^(e-128)
 __device__ __forceinline__ float pm_e8(uint32_t e) {
   return e < 2 ? __uint_as_float(0x00200000u << e) : __uint_as_float((e - 1) << 23);

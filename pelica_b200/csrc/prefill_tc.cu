@@ -359,63 +359,78 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       return r < rows ? r : -1;
     };
     const uint32_t sRaw_a = tc_s32(sRaw);
-    // the block bb of the tile's rows -> raw area bb % NS, in pieces of 16 bytes, consecutive
-    // lanes on consecutive pieces of a row (one group)
+    // The pieces (16 bytes each) this thread copies per block, consecutive lanes on consecutive
+    // pieces of a row: byte offset of the piece in block 0 of its row within the expert's matrix
+    // (bit 31: the up matrix; ~0: a row past the matrix). Q4_K: 9 pieces a row, [row][144 B] (row-
+    // per-lane 16-byte reads of that pitch are conflict-free). Q6_K: ql 8 pieces a row, [row][128 B],
+    // piece c at c ^ (row & 7); qh 4 pieces a row, [row][64 B], piece c at c ^ ((row >> 1) & 3) (both
+    // conflict-free for the row-per-lane reads below); sc [row][16 B]; d: the aligned word holding
+    // the row's f16.
+    constexpr int NPC = Q6 ? 7 : 5;
+    uint32_t roff[NPC];
+#pragma unroll
+    for (int j = 0; j < NPC; j++) roff[j] = ~0u;
+    if (raw_role) {
+      if (Q6) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          bool sec;
+          const int r = grow((ct >> 3) + 32 * j, sec);
+          if (r >= 0) roff[j] = ((uint32_t)r * (uint32_t)nb * 128u + 16u * (ct & 7)) | (sec ? 0x80000000u : 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          bool sec;
+          const int r = grow((ct >> 2) + 64 * j, sec);
+          if (r >= 0) roff[4 + j] = ((uint32_t)r * (uint32_t)nb * 64u + 16u * (ct & 3)) | (sec ? 0x80000000u : 0u);
+        }
+        {
+          bool sec;
+          const int r = grow(ct & 127, sec);
+          if (r >= 0) roff[6] = ((uint32_t)r * (uint32_t)nb * (ct < 128 ? 16u : 2u)) | (sec ? 0x80000000u : 0u);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 5; j++) {
+          const int p = ct + (TC_NW / 2) * j;
+          if (p < TC_M * 9) {
+            const int i = p / 9, c = p - 9 * i;
+            bool sec;
+            const int r = grow(i, sec);
+            if (r >= 0) roff[j] = ((uint32_t)r * (uint32_t)nb * 144u + 16u * c) | (sec ? 0x80000000u : 0u);
+          }
+        }
+      }
+    }
+    auto wbase = [&](int plane, uint32_t o) -> const uint8_t * {  // the piece's matrix, plane `plane`
+      const WMat &W = (o & 0x80000000u) ? W1 : W0;
+      return W.plane[plane] + (size_t)el * W.stride[plane] + (o & 0x7fffffffu);
+    };
+    // the block bb of the tile's rows -> raw area bb % NS (one group)
     auto issue_raw = [&](int bb) {
       if (bb < nb) {
         const uint32_t ra = sRaw_a + (uint32_t)(bb % NS) * RAWB;
         if (Q6) {
-          // ql: 8 pieces a row, [row][128 B], piece c at c ^ (row & 7); qh: 4 pieces a row,
-          // [row][64 B], piece c at c ^ ((row >> 1) & 3): both conflict-free for the row-per-lane
-          // reads below; sc: [row][16 B]; d: the aligned word holding the row's f16
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const int i = (ct >> 3) + 32 * j, c = ct & 7;
-            bool sec;
-            const int r = grow(i, sec);
-            if (r < 0) continue;
-            const WMat &W = sec ? W1 : W0;
-            tc_cp16(ra + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)),
-                    W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 128 + 16 * c);
+            if (roff[j] != ~0u) tc_cp16(ra + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)), wbase(0, roff[j]) + (size_t)bb * 128);
           }
 #pragma unroll
           for (int j = 0; j < 2; j++) {
             const int i = (ct >> 2) + 64 * j, c = ct & 3;
-            bool sec;
-            const int r = grow(i, sec);
-            if (r < 0) continue;
-            const WMat &W = sec ? W1 : W0;
-            tc_cp16(ra + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)),
-                    W.plane[1] + (size_t)el * W.stride[1] + ((size_t)r * nb + bb) * 64 + 16 * c);
+            if (roff[4 + j] != ~0u)
+              tc_cp16(ra + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)), wbase(1, roff[4 + j]) + (size_t)bb * 64);
           }
-          {
+          if (roff[6] != ~0u) {
             const int i = ct & 127;
-            bool sec;
-            const int r = grow(i, sec);
-            if (r >= 0) {
-              const WMat &W = sec ? W1 : W0;
-              if (ct < 128)
-                tc_cp16(ra + 24576u + (uint32_t)i * 16u, W.plane[2] + (size_t)el * W.stride[2] + ((size_t)r * nb + bb) * 16);
-              else
-                tc_cp4(ra + 26624u + (uint32_t)i * 4u,
-                       (const uint8_t *)((uintptr_t)(W.plane[3] + (size_t)el * W.stride[3] + ((size_t)r * nb + bb) * 2) & ~(uintptr_t)3));
-            }
+            if (ct < 128) tc_cp16(ra + 24576u + (uint32_t)i * 16u, wbase(2, roff[6]) + (size_t)bb * 16);
+            else tc_cp4(ra + 26624u + (uint32_t)i * 4u, (const uint8_t *)((uintptr_t)(wbase(3, roff[6]) + (size_t)bb * 2) & ~(uintptr_t)3));
           }
         } else {
-          // [row][144 B]: 9 pieces a row (stride 144 B: row-per-lane 16-byte reads are conflict-free)
 #pragma unroll
-          for (int j = 0; j < 5; j++) {
-            const int p = ct + (TC_NW / 2) * j;
-            if (p < TC_M * 9) {
-              const int i = p / 9, c = p - 9 * i;
-              bool sec;
-              const int r = grow(i, sec);
-              if (r >= 0) {
-                const WMat &W = sec ? W1 : W0;
-                tc_cp16(ra + (uint32_t)p * 16u, W.plane[0] + (size_t)el * W.stride[0] + ((size_t)r * nb + bb) * 144 + 16 * c);
-              }
-            }
-          }
+          for (int j = 0; j < 5; j++)
+            if (roff[j] != ~0u) tc_cp16(ra + (uint32_t)(ct + (TC_NW / 2) * j) * 16u, wbase(0, roff[j]) + (size_t)bb * 144);
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
@@ -488,28 +503,22 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         const uint4 hdr = *(const uint4 *)rp;
         nrd = pm_f16(hdr.x);
         nrdmin = pm_f16(hdr.x >> 16);
-        if (part < 2) {  // the eight mins as f16, K chunk `part` of the f16 product (both hold m_0..m_7)
-          uint32_t mh[4];
-#pragma unroll
-          for (int jp = 0; jp < 4; jp++) {
-            int s0, m0, s1, m1;
-            pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp, s0, m0);
-            pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * jp + 1, s1, m1);
-            mh[jp] = (uint32_t)__half_as_ushort(__int2half_rn(m0)) | ((uint32_t)__half_as_ushort(__int2half_rn(m1)) << 16);
-          }
-          *(uint4 *)(sAm + (size_t)(bb & 1) * (2 * TC_M * 16) + (size_t)(part * TC_M + m) * 16) = make_uint4(mh[0], mh[1], mh[2], mh[3]);
-        }
+        uint32_t sc03, sc47, m03, m47;
+        pm_q4k_scmin_packed(hdr.y, hdr.z, hdr.w, sc03, sc47, m03, m47);
+        if (part < 2)  // the eight mins as f16, K chunk `part` of the f16 product (both hold m_0..m_7)
+          *(uint4 *)(sAm + (size_t)(bb & 1) * (2 * TC_M * 16) + (size_t)(part * TC_M + m) * 16) =
+              make_uint4(pm_bytes_to_half2(m03, 0x4140), pm_bytes_to_half2(m03, 0x4342),
+                         pm_bytes_to_half2(m47, 0x4140), pm_bytes_to_half2(m47, 0x4342));
         const int c = part;
         const uint4 w0 = *(const uint4 *)(rp + 16 + 32 * c), w1 = *(const uint4 *)(rp + 32 + 32 * c);
-        int sc0, m0, sc1, m1;
-        pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c, sc0, m0);
-        pm_q4k_scmin(hdr.y, hdr.z, hdr.w, 2 * c + 1, sc1, m1);
+        const uint32_t scw = ((c & 2) ? sc47 : sc03) >> (16 * (c & 1));
+        const uint32_t sc0 = scw & 0xffu, sc1 = (scw >> 8) & 0xffu;  // scales of sub-blocks 2c, 2c+1
         const uint32_t M4 = 0x0f0f0f0fu;
         // sub-block 2c = low nibbles -> K 64c .. 64c+31 ; sub-block 2c+1 = high -> K 64c+32 .. 64c+63
         const uint32_t lo[8] = {w0.x & M4, w0.y & M4, w0.z & M4, w0.w & M4, w1.x & M4, w1.y & M4, w1.z & M4, w1.w & M4};
         const uint32_t hi[8] = {(w0.x >> 4) & M4, (w0.y >> 4) & M4, (w0.z >> 4) & M4, (w0.w >> 4) & M4,
                                 (w1.x >> 4) & M4, (w1.y >> 4) & M4, (w1.z >> 4) & M4, (w1.w >> 4) & M4};
-        const uint32_t sh0 = (uint32_t)sc0 >> 3, sl0 = (uint32_t)sc0 & 7, sh1 = (uint32_t)sc1 >> 3, sl1 = (uint32_t)sc1 & 7;
+        const uint32_t sh0 = sc0 >> 3, sl0 = sc0 & 7, sh1 = sc1 >> 3, sl1 = sc1 & 7;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           ah[i] = lo[i] * sh0;
@@ -579,6 +588,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
               const int4 s4 = *(const int4 *)(xsv + c4);
               ss[0] = s4.x; ss[1] = s4.y; ss[2] = s4.z; ss[3] = s4.w;
             }
+            // (scalar on purpose: a packed mul.rn.f32x2 followed by add.rn.f32x2 comes out
+            // contracted into one fused operation, which is not the reference's rounding)
 #pragma unroll
             for (int u = 0; u < 4; u++) {
               float term;
