@@ -127,6 +127,12 @@ __device__ __forceinline__ uint32_t pm_bytes_to_half2(uint32_t w, uint32_t sel) 
   return *reinterpret_cast<const uint32_t *>(&r);
 }
 
+// four 6-bit values (bytes 0..63) minus 32 each, as signed bytes: with bit 7 set no byte
+// borrows from its neighbour, and flipping it back leaves q + 96 - 128 (mod 256) = q - 32
+__device__ __forceinline__ uint32_t pm_sub32x4(uint32_t q) {
+  return ((q | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+}
+
 // `e8` (src/oss_kernels.rs:42-45): 2^(e-128)
 __device__ __forceinline__ float pm_e8(uint32_t e) {
   return e < 2 ? __uint_as_float(0x00200000u << e) : __uint_as_float((e - 1) << 23);

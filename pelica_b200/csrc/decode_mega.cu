@@ -329,8 +329,8 @@ __device__ __forceinline__ void rows_q6k_smem(const uint8_t *const ql[NR], const
     for (int r = 0; r < NR; r++) {
       uint32_t qa = (qlw[r] & 0x0f0f0f0fu) | (((qhw[r] >> (2 * qtb)) & 0x03030303u) << 4);
       uint32_t qb = ((qlw[r] >> 4) & 0x0f0f0f0fu) | (((qhw[r] >> (2 * qtb + 4)) & 0x03030303u) << 4);
-      qa = __vsub4(qa, 0x20202020u);
-      qb = __vsub4(qb, 0x20202020u);
+      qa = pm_sub32x4(qa);
+      qb = pm_sub32x4(qb);
       isum[r] = sa[r] * __dp4a((int)qa, xa[r], 0) + sb[r] * __dp4a((int)qb, xb[r], 0);
     }
 #pragma unroll
@@ -626,21 +626,25 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     if (__syncthreads_or(dead)) { dead = true; break; }
     MG_TRACE(2);
 
-    // ---- 4. bulk copies of this CTA's slices ----
-    if (job_tx) mbar_expect_tx(&bar_gu[job_bar], (uint32_t)(job_tx - 1));  // bar_dn follows bar_gu in memory
-    if (job_bytes > 0) {
-      int el = (int)ids[job_k];
-      const uint8_t *src;
-      uint8_t *dst;
-      if (job_plane == 0) { src = ML.gate + (size_t)el * ML.gate_stride; dst = gs; }
-      else if (job_plane == 1) { src = ML.up + (size_t)el * ML.up_stride; dst = us; }
-      else {
-        int p = job_plane - 2;
-        src = ML.down[p] + (size_t)el * ML.down_stride[p];
-        dst = p == 3 ? dsm : dn;
+    // ---- 4. bulk copies of this CTA's slices: gate/up now, down once gate/up has landed
+    // (the gate/up bytes are needed first and should not share HBM with bytes needed later) ----
+    auto issue_job = [&]() {
+      if (job_tx) mbar_expect_tx(&bar_gu[job_bar], (uint32_t)(job_tx - 1));  // bar_dn follows bar_gu in memory
+      if (job_bytes > 0) {
+        int el = (int)ids[job_k];
+        const uint8_t *src;
+        uint8_t *dst;
+        if (job_plane == 0) { src = ML.gate + (size_t)el * ML.gate_stride; dst = gs; }
+        else if (job_plane == 1) { src = ML.up + (size_t)el * ML.up_stride; dst = us; }
+        else {
+          int p = job_plane - 2;
+          src = ML.down[p] + (size_t)el * ML.down_stride[p];
+          dst = p == 3 ? dsm : dn;
+        }
+        bulk_g2s(dst + job_dst, src + job_off, (uint32_t)job_bytes, &bar_gu[job_bar]);
       }
-      bulk_g2s(dst + job_dst, src + job_off, (uint32_t)job_bytes, &bar_gu[job_bar]);
-    }
+    };
+    if (tid < MG_GU_CHUNKS * 4) issue_job();
     copies_pending = true;
     MG_TRACE(3);
 
@@ -709,6 +713,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     }
     MG_TRACE(11);
     if (__syncthreads_or(dead)) { dead = true; break; }
+    if (tid >= 32) issue_job();  // the down slices (job threads 32 .. 32 + 4K)
     if (tid == 0) red_release_add_u64(P.hcount, 1ull);
     MG_TRACE(4);
 
@@ -741,7 +746,56 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     MG_TRACE(6);
 
     // ---- 7. down rows of this CTA's columns, all k; sum in k order; publish ----
-    {
+    if (dq6 && ndown * nbh <= PM_MAX_EXPERTS) {
+      // One (row, block) unit per lane: 256 six-bit values against the block of h, no
+      // cross-lane traffic. isum = sum_c sc[c] * (q_c . h_c - 32 * sum(h_c)) over the 16
+      // chunks c of 16 values (the integer sum of `row_q6k_q8x`, regrouped). Lanes walk the
+      // 16-byte pieces in a rotated order so that units 128 bytes apart hit different banks.
+      float *tmp = r_sv;  // [ndown * nbh] terms; the routing scratch is idle here
+      const size_t cm = (size_t)P.cols_max * nbh;
+      for (int u = tid; u < ndown * nbh; u += MG_NT) {
+        const int i = u / nbh, b = u - i * nbh, k = i / ncols, cc = i - k * ncols;
+        if (!mbar_wait(&bar_dn[k], par, P.err)) dead = true;
+        const uint8_t *base = dn + (size_t)k * P.dn_k_bytes;
+        const size_t rb = (size_t)cc * nbh + b;
+        const uint8_t *qlp = base + rb * 128, *qhp = base + cm * 128 + rb * 64;
+        const int8_t *scp = (const int8_t *)(base + cm * 192 + rb * 16);
+        const int8_t *xb = hq + k * ff + b * 256;
+        int isum = 0;
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+          const int pp = (p + lane) & 7, n = pp >> 2, jj = (pp >> 1) & 1, g = pp & 1;
+          const uint4 qlv = *(const uint4 *)(qlp + pp * 16);
+          const uint4 qhv = *(const uint4 *)(qhp + (2 * n + g) * 16);
+          const int clo = 8 * n + 2 * jj + g, chi = clo + 4;  // chunks of the low / high nibbles
+          const int4 xlo = *(const int4 *)(xb + clo * 16), xhi = *(const int4 *)(xb + chi * 16);
+          const int sh = 2 * jj;
+          const uint32_t qlw[4] = {qlv.x, qlv.y, qlv.z, qlv.w}, qhw[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
+          const int xl[4] = {xlo.x, xlo.y, xlo.z, xlo.w}, xh[4] = {xhi.x, xhi.y, xhi.z, xhi.w};
+          int dlo = 0, dhi = 0, slo = 0, shi = 0;  // q . h and sum(h) of the two chunks
+#pragma unroll
+          for (int w = 0; w < 4; w++) {
+            const uint32_t qa = (qlw[w] & 0x0f0f0f0fu) | (((qhw[w] >> sh) & 0x03030303u) << 4);
+            const uint32_t qb = ((qlw[w] >> 4) & 0x0f0f0f0fu) | (((qhw[w] >> (sh + 4)) & 0x03030303u) << 4);
+            dlo = __dp4a((int)qa, xl[w], dlo);
+            dhi = __dp4a((int)qb, xh[w], dhi);
+            slo = __dp4a(0x01010101, xl[w], slo);
+            shi = __dp4a(0x01010101, xh[w], shi);
+          }
+          isum += (int)scp[clo] * (dlo - 32 * slo) + (int)scp[chi] * (dhi - 32 * shi);
+        }
+        const float dd = __half2float(((const __half *)(dsm + (size_t)k * P.dsm_k_bytes))[dsm_skew + cc * nbh + b]);
+        tmp[u] = __fmul_rn(hd[k * nbh + b], __fmul_rn(dd, (float)isum));
+      }
+      MG_TRACE(9);
+      if (__syncthreads_or(dead)) { dead = true; copies_pending = true; break; }
+      for (int i = tid; i < ndown; i += MG_NT) {  // the row's terms in block order
+        float total = 0.0f;
+        for (int b = 0; b < nbh; b++) total = __fadd_rn(total, tmp[i * nbh + b]);
+        const int k = i / ncols, cc = i - k * ncols;
+        eo[k * P.cols_max + cc] = total;
+      }
+    } else {
       int ia = warp * per_d, ib = min(ndown, ia + per_d);
       for (int i0 = ia; i0 < ib && !dead; i0 += MG_DR) {
         int kk[MG_DR], cc[MG_DR];

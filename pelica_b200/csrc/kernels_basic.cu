@@ -484,8 +484,8 @@ __device__ __forceinline__ float row_q6k_q8x(const uint8_t *__restrict__ ql,
     uint32_t qhw = __ldg((const uint32_t *)(qh + (size_t)b * 64) + n * 8 + l4);
     uint32_t qa = (qlw & 0x0f0f0f0fu) | (((qhw >> (2 * qtb)) & 0x03030303u) << 4);
     uint32_t qb = ((qlw >> 4) & 0x0f0f0f0fu) | (((qhw >> (2 * qtb + 4)) & 0x03030303u) << 4);
-    qa = __vsub4(qa, 0x20202020u);
-    qb = __vsub4(qb, 0x20202020u);
+    qa = pm_sub32x4(qa);
+    qb = pm_sub32x4(qb);
     const int *xp = (const int *)(xq + (size_t)b * 256);
     int xa = xp[vA >> 2], xb = xp[(vA + 64) >> 2];
     const int8_t *scb = (const int8_t *)(sc + (size_t)b * 16);
