@@ -102,12 +102,13 @@ def run_ep(args, cfg, n_layers, T, desc):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    clocks.begin()
     launches0 = ctx.launches
     ctx.timer_start()
     for i in range(args.steps):
@@ -122,6 +123,7 @@ def run_ep(args, cfg, n_layers, T, desc):
     ctx.profile(False)
     # e2e: host tokens in, host result out, per step
     hx = torch.empty((Tl, cfg.d), dtype=torch.float32).pin_memory()
+    hy = torch.empty((Tl, cfg.d), dtype=torch.float32).pin_memory()
     hx.copy_(pool[0].cpu())
     barrier()
     t0 = time.perf_counter()
@@ -129,7 +131,8 @@ def run_ep(args, cfg, n_layers, T, desc):
         x = hx.cuda(non_blocking=True)
         for L in layers:
             L.forward(be0.rmsnorm(x), add_into=x)
-        hy = x.cpu()
+        hy.copy_(x, non_blocking=True)
+        torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
     barrier()
     if world > 1:
@@ -175,6 +178,10 @@ def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
     return per_layer * n_layers
 
 
+# (102,241,024 + 4,813,824) bytes over the 4 layers of the captured launch
+NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102241024 + 4813824) // 4
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
 
@@ -185,6 +192,7 @@ class ClockSampler:
     def __init__(self, device):
         self.device = device
         self.rows = []
+        self.first = 0
         self.proc = None
 
     def start(self):
@@ -201,6 +209,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def begin(self):
+        """The timed region starts here: earlier samples (warm-up) are dropped."""
+        self.first = len(self.rows)
+
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -210,7 +222,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
-        for r in self.rows:
+        for r in self.rows[self.first:]:
             if len(r) < 9:
                 continue
             try:
@@ -308,7 +320,7 @@ def run_reference(args, cfg, n_layers, T, desc):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_decode", choices=list(WORKLOADS))
@@ -358,13 +370,14 @@ def main():
         ctx.sync()
 
     # ---- device-resident throughput ----
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()  # (nvidia-smi needs a moment before its first sample: started ahead of the warm-up)
     for i in range(args.warmup):
         stack.forward_dev(dpool[i % POOL], T, dout)
     barrier()
     launches0 = ctx.launches
-    clocks = ClockSampler(local)
-    if rank == 0:
-        clocks.start()
+    clocks.begin()
     ctx.timer_start()
     for i in range(args.steps):
         stack.forward_dev(dpool[(args.warmup + i) % POOL], T, dout)
@@ -431,6 +444,11 @@ def main():
     }
     roof = {"bound": "hbm", "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"], "kernel": dom,
             "traffic": None}
+    if dom == "fused" and key == "c2":
+        # dram__bytes_read + dram__bytes_write of k_decode_mega from the ncu capture summarised in
+        # profiles/k_decode_mega_c2_decode.md (4 layers captured; the bytes grow with the layer count)
+        roof["traffic"] = NCU_DRAM_BYTES_PER_LAYER_C2_DECODE * (n_layers if phases["fused"][1] != prof_steps * n_layers else 1)
+        roof["traffic_source"] = "ncu capture of a 4-layer launch, scaled by layers"
     if dom in phase_bytes and dom_spans:
         per_launch_bytes = phase_bytes[dom]
         per_launch_ms = dom_ms / dom_spans
