@@ -4,7 +4,9 @@
 // Why: at batch 1 a Qwen3-30B-A3B-shaped layer reads 24.5 MB of expert blocks,
 // 3.8 us at HBM speed; a kernel launch per phase costs more than that. Here
 // every CTA walks all layers; per layer it
-//   1. collects the residual stream x (published by all CTAs, epoch-tagged),
+//   1. collects the residual stream x (published by all CTAs; one thread waits for the
+//      layer's arrival counter, then everybody reads: a poller per CTA instead of
+//      per word keeps the few L2 lines of the exchange from becoming a hot spot),
 //   2. norms it and quantises it to Q8x (`Q8x::new`, src/ds4_cpu.rs:13-35),
 //   3. computes "its" router logit in `dot_f32` order (src/quant.rs:215-236) and
 //      publishes it; collects all logits; picks the top-k (route.cuh),
@@ -57,15 +59,6 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
       "l"(src), "r"(bytes), "r"(s32(bar))
       : "memory");
 }
-__device__ __forceinline__ void st_pair(unsigned long long *p, float v, uint32_t epoch) {
-  unsigned long long u = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(u) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_pair(const unsigned long long *p) {
-  unsigned long long u;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(u) : "l"(p) : "memory");
-  return u;
-}
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
   unsigned long long u;
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(u) : "l"(p) : "memory");
@@ -73,6 +66,25 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 }
 __device__ __forceinline__ void red_release_add_u64(unsigned long long *p, unsigned long long v) {
   asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ int ld_volatile_i32(const int *p);
+__device__ __forceinline__ unsigned long long now_ns();
+// one thread waits until an arrival counter reaches `want` (bounded); false = gave up.
+// One poller per CTA: 148 loads a round trip on the counter's line, instead of every
+// thread polling its own words (tens of thousands of loads on a few lines of one L2 slice).
+__device__ __noinline__ bool wait_count(const unsigned long long *p, unsigned long long want, int *err, int code) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; it++) {
+    if (ld_acquire_u64(p) >= want) return true;
+    if ((it & 63) == 63) {
+      if (ld_volatile_i32(err) != 0) return false;
+      unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > MG_WAIT_NS) break;
+    }
+  }
+  atomicCAS(err, 0, code);
+  return false;
 }
 __device__ __forceinline__ int ld_volatile_i32(const int *p) {
   int v;
@@ -115,27 +127,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, err);
 }
-// bounded wait for an epoch-tagged value; false = gave up
-__device__ __noinline__ bool wait_pair(const unsigned long long *p, uint32_t epoch, float &v,
-                                          int *err) {
-  unsigned long long t0 = 0;
-  for (uint32_t it = 0;; it++) {
-    unsigned long long u = ld_pair(p);
-    if ((uint32_t)(u >> 32) == epoch) {
-      v = __uint_as_float((uint32_t)u);
-      return true;
-    }
-    if ((it & 63) == 63) {
-      if (ld_volatile_i32(err) != 0) return false;
-      unsigned long long t = now_ns();
-      if (t0 == 0) t0 = t;
-      else if (t - t0 > MG_WAIT_NS) break;
-    }
-  }
-  atomicCAS(err, 0, 1);
-  return false;
-}
-
 // ---- Q8x of 256 values held 8 per lane (value j of the lane = element 32j+lane)
 // (`Q8x::new`, src/ds4_cpu.rs:13-35); writes q, d, bsum of the block
 // `swz`: 16-byte chunk c of the block is stored at chunk c ^ swz (so that lanes
@@ -343,27 +334,6 @@ __device__ __forceinline__ void rows_q6k_smem(const uint8_t *const ql[NR], const
   }
 }
 
-// N epoch-tagged values p[i0 + j*stride], j < N: all loads in flight at once,
-// stragglers retried one by one (bounded). false = gave up.
-template <int N>
-__device__ __forceinline__ bool poll_pairs(const unsigned long long *p, int i0, int stride, int n,
-                                           uint32_t epoch, float v[N], int *err) {
-  unsigned long long u[N];
-#pragma unroll
-  for (int j = 0; j < N; j++)
-    if (i0 + j * stride < n) u[j] = ld_pair(p + i0 + j * stride);
-  bool ok = true;
-#pragma unroll
-  for (int j = 0; j < N; j++) {
-    v[j] = 0.0f;
-    if (i0 + j * stride < n) {
-      if ((uint32_t)(u[j] >> 32) == epoch) v[j] = __uint_as_float((uint32_t)u[j]);
-      else ok = wait_pair(p + i0 + j * stride, epoch, v[j], err) && ok;
-    }
-  }
-  return ok;
-}
-
 // ---- the kernel ------------------------------------------------------------
 #define MG_GH 2  // h rows (gate+up pairs) a warp works on at once
 #define MG_DR 4  // down rows a warp works on at once
@@ -502,26 +472,16 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   for (; l < P.n_layers; l++) {
     const MegaLayer &ML = mls[l & 1];
     const uint32_t par = l & 1;
-    const uint32_t ep = P.epoch_base + (uint32_t)l;  // tag of this layer's x and logits
     MG_TRACE(0);
     if (l + 1 < P.n_layers && tid >= 64 && tid < 64 + (int)(sizeof(MegaLayer) / 8))
       ((unsigned long long *)&mls[(l + 1) & 1])[tid - 64] = ((const unsigned long long *)&P.layers[l + 1])[tid - 64];
 
-    // ---- 1. the residual stream ----
-    {
-      float v[4];
-      for (int i0 = tid; i0 < d; i0 += 4 * MG_NT) {
-        if (l == 0) {
-#pragma unroll
-          for (int j = 0; j < 4; j++) v[j] = i0 + j * MG_NT < d ? P.x_in[i0 + j * MG_NT] : 0.0f;
-        } else if (!poll_pairs<4>(P.xbuf, i0, MG_NT, d, ep, v, P.err)) {
-          dead = true;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-          if (i0 + j * MG_NT < d) xs[i0 + j * MG_NT] = v[j];
-      }
+    // ---- 1. the residual stream (written by all CTAs at the end of the previous layer) ----
+    if (l > 0) {
+      if (tid == 0 && !wait_count(P.xcount, P.xcount_base + (unsigned long long)l * (unsigned long long)G, P.err, 1)) dead = true;
+      if (__syncthreads_or(dead)) { dead = true; break; }
     }
+    for (int i0 = tid; i0 < d; i0 += MG_NT) xs[i0] = l == 0 ? P.x_in[i0] : __ldcg(P.xbuf + i0);
     if (__syncthreads_or(dead)) { dead = true; break; }
     MG_TRACE(1);
 
@@ -548,7 +508,8 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           float sdot = pm_warp_sum_dot(acc);
           if (lane == 0) {
             if (ML.logit_bias) sdot = __fadd_rn(sdot, ML.logit_bias[cta]);
-            st_pair(P.lbuf + cta, sdot, ep);
+            __stcg(P.lbuf + cta, sdot);
+            red_release_add_u64(P.lcount, 1ull);
           }
           __syncwarp();
           if (lane == 0 && l + 1 < P.n_layers) {  // next layer's row into the same buffer
@@ -557,13 +518,9 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           }
         }
         MG_TRACE_R(13);
-        for (int e0 = lane; e0 < E; e0 += 4 * 32) {
-          float v[4];
-          if (!poll_pairs<4>(P.lbuf, e0, 32, E, ep, v, P.err)) dead = true;
-#pragma unroll
-          for (int j = 0; j < 4; j++)
-            if (e0 + 32 * j < E) lg[e0 + 32 * j] = v[j];
-        }
+        if (lane == 0 && !wait_count(P.lcount, P.lcount_base + (unsigned long long)(l + 1) * (unsigned long long)E, P.err, 2)) dead = true;
+        __syncwarp();
+        for (int e0 = lane; e0 < E; e0 += 32) lg[e0] = __ldcg(P.lbuf + e0);
         __syncwarp();
         MG_TRACE_R(14);
         {
@@ -854,11 +811,12 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
         s = __fadd_rn(s, v);
       }
       float xn = __fadd_rn(xs[C0 + tid], s);
-      if (l + 1 < P.n_layers) st_pair(P.xbuf + C0 + tid, xn, ep + 1);
+      if (l + 1 < P.n_layers) __stcg(P.xbuf + C0 + tid, xn);
       else P.x_out[C0 + tid] = xn;
     }
     MG_TRACE(7);
     __syncthreads();  // eo, xs, ids are rewritten by the next layer
+    if (tid == 0 && l + 1 < P.n_layers) red_release_add_u64(P.xcount, 1ull);
   }
 
   if (dead) {

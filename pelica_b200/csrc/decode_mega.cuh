@@ -24,12 +24,14 @@ struct MegaParams {
   const float *x_in;
   float *x_out;
   float eps;
-  unsigned long long *xbuf;  // [d]      (value, epoch)
-  unsigned long long *lbuf;  // [E]      (logit, epoch)
+  float *xbuf;               // [d]      the residual stream between layers
+  float *lbuf;               // [E]      the layer's router logits
   float *hbuf;               // [K*ff]
-  unsigned long long *hcount;  // arrivals of CTAs that finished their h rows
-  unsigned long long hcount_base;
-  uint32_t epoch_base;
+  // arrival counters (never reset: each call waits for base + its own arrivals):
+  unsigned long long *hcount;  // CTAs that finished their h rows
+  unsigned long long *xcount;  // CTAs that published their slice of the next layer's residual stream
+  unsigned long long *lcount;  // logits published
+  unsigned long long hcount_base, xcount_base, lcount_base;
   int *err;
   long long *trace;  // optional [2][n_layers][MG_TRACE_PH] SM clocks (CTA 0 and the last CTA)
   // shared-memory layout (bytes from the dynamic base)
