@@ -266,9 +266,69 @@ __global__ void __launch_bounds__(256) k_router(const float *__restrict__ wr,
   }
 }
 
+// The same sums for many tokens: a warp owns 8 experts x 8 tokens (64 accumulators a
+// lane), a CTA 64 experts x 8 tokens; the tokens' columns are staged in shared memory
+// 512 at a time. Lane L still runs, for every (token, expert), the fma chain over columns
+// L, L+32, ... in ascending order, so the result has the bits of k_router; the router
+// row is read once per 8 tokens instead of once per token.
+#define RT_TOK 8
+#define RT_EXP 8
+#define RT_CH 512
+__global__ void __launch_bounds__(256) k_router_tile(const float *__restrict__ wr,
+                                                     const float *__restrict__ bias,
+                                                     const float *__restrict__ x, int T, int E, int d,
+                                                     float *logits) {
+  __shared__ float xs[RT_TOK][RT_CH];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = blockIdx.y * RT_TOK, e0 = blockIdx.x * (8 * RT_EXP) + warp * RT_EXP;
+  float acc[RT_TOK][RT_EXP];
+#pragma unroll
+  for (int t = 0; t < RT_TOK; t++)
+#pragma unroll
+    for (int e = 0; e < RT_EXP; e++) acc[t][e] = 0.0f;
+  for (int c0 = 0; c0 < d; c0 += RT_CH) {
+    const int n = min(RT_CH, d - c0);  // a multiple of 32 (d is)
+    __syncthreads();
+    for (int i = threadIdx.x; i < RT_TOK * RT_CH; i += 256) {
+      const int t = i / RT_CH, c = i - t * RT_CH;
+      xs[t][c] = (t0 + t < T && c < n) ? x[(size_t)(t0 + t) * d + c0 + c] : 0.0f;
+    }
+    __syncthreads();
+    if (e0 < E) {
+      for (int c = lane; c < n; c += 32) {
+        float w[RT_EXP], xv[RT_TOK];
+#pragma unroll
+        for (int e = 0; e < RT_EXP; e++) w[e] = e0 + e < E ? __ldg(wr + (size_t)(e0 + e) * d + c0 + c) : 0.0f;
+#pragma unroll
+        for (int t = 0; t < RT_TOK; t++) xv[t] = xs[t][c];
+#pragma unroll
+        for (int t = 0; t < RT_TOK; t++)
+#pragma unroll
+          for (int e = 0; e < RT_EXP; e++) acc[t][e] = __fmaf_rn(w[e], xv[t], acc[t][e]);
+      }
+    }
+  }
+  if (e0 >= E) return;
+#pragma unroll
+  for (int t = 0; t < RT_TOK; t++)
+#pragma unroll
+    for (int e = 0; e < RT_EXP; e++) {
+      float s = pm_warp_sum_dot(acc[t][e]);
+      if (lane == 0 && t0 + t < T && e0 + e < E) {
+        if (bias) s = __fadd_rn(s, bias[e0 + e]);
+        logits[(size_t)(t0 + t) * E + e0 + e] = s;
+      }
+    }
+}
+
 void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits) {
   if (T == 0) return;
   int E = ly.desc.n_exp, d = ly.desc.d;
+  if (T >= RT_TOK) {
+    dim3 grid((E + 8 * RT_EXP - 1) / (8 * RT_EXP), (T + RT_TOK - 1) / RT_TOK);
+    KLAUNCH(L, k_router_tile, grid, 256, 0, ly.router, ly.logit_bias, x, T, E, d, logits);
+    return;
+  }
   dim3 grid((E + 7) / 8, T);
   KLAUNCH(L, k_router, grid, 256, (size_t)d * 4, ly.router, ly.logit_bias, x, E, d, logits);
 }
