@@ -178,8 +178,8 @@ def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
     return per_layer * n_layers
 
 
-# (102,241,024 + 4,813,824) bytes over the 4 layers of the captured launch
-NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102241024 + 4813824) // 4
+# (102,226,176 + 3,290,880) bytes over the 4 layers of the captured launch
+NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102226176 + 3290880) // 4
 
 
 class ClockSampler:
