@@ -445,8 +445,8 @@ def main():
     roof = {"bound": "hbm", "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"], "kernel": dom,
             "traffic": None}
     if dom == "fused" and key == "c2":
-        # dram__bytes_read + dram__bytes_write of k_decode_mega from the ncu capture summarised in
-        # profiles/k_decode_mega_c2_decode.md (4 layers captured; the bytes grow with the layer count)
+        # dram__bytes_read + dram__bytes_write of k_decode_mega from the committed ncu summary of the
+        # decode kernel (4 layers captured; the bytes grow with the layer count)
         roof["traffic"] = NCU_DRAM_BYTES_PER_LAYER_C2_DECODE * (n_layers if phases["fused"][1] != prof_steps * n_layers else 1)
         roof["traffic_source"] = "ncu capture of a 4-layer launch, scaled by layers"
     if dom in phase_bytes and dom_spans:
