@@ -178,6 +178,7 @@ size_t po_type_block_bytes(int t) {
     case PM_TYPE_F16: return 2;
     case PM_TYPE_BF16: return 2;
     case PM_TYPE_Q8_0: return 34;
+    case PM_TYPE_IQ4_NL: return 18;
     case PM_TYPE_Q4_K: return 144;
     case PM_TYPE_Q6_K: return 210;
     case PM_TYPE_MXFP4: return 17;
@@ -190,12 +191,16 @@ size_t po_type_block_values(int t) {
     case PM_TYPE_F16:
     case PM_TYPE_BF16: return 1;
     case PM_TYPE_Q8_0:
+    case PM_TYPE_IQ4_NL:
     case PM_TYPE_MXFP4: return 32;
     case PM_TYPE_Q4_K:
     case PM_TYPE_Q6_K: return 256;
   }
   return 0;
 }
+
+/* the IQ4_NL codebook: a constant of the format (src/iq_tables.rs:72) */
+static const int8_t KV_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
 static inline float f16le(const uint8_t *b) {
   return po_f16_to_f32((uint16_t)(b[0] | (b[1] << 8)));
@@ -254,6 +259,16 @@ int po_dequant(int t, const uint8_t *blocks, size_t n, float *out) {
         const uint8_t *blk = blocks + b * bb;
         float d = f16le(blk);
         for (int i = 0; i < 32; i++) out[b * 32 + i] = d * (float)(int8_t)blk[2 + i];
+      }
+      return 0;
+    case PM_TYPE_IQ4_NL: /* src/q4x_cpu.rs:453-461 */
+      for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = blocks + b * bb;
+        float d = f16le(blk);
+        for (int i = 0; i < 16; i++) {
+          out[b * 32 + i] = d * (float)KV_IQ4NL[blk[2 + i] & 15];
+          out[b * 32 + 16 + i] = d * (float)KV_IQ4NL[blk[2 + i] >> 4];
+        }
       }
       return 0;
     case PM_TYPE_Q4_K: /* src/moe_kernels.rs:73: dm.x * sm.x * q - dm.y * sm.y */
@@ -416,6 +431,27 @@ float po_row_q8_0(const uint8_t *w, size_t ncols, const int8_t *q, const float *
     total += f16le(blk) * d32[b] * (float)s;
   }
   return total;
+}
+
+/* src/q4x_cpu.rs:92-101 */
+float po_row_iq4nl(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
+  float total = 0.0f;
+  size_t nb = ncols / 32;
+  for (size_t b = 0; b < nb; b++) {
+    const uint8_t *blk = w + b * 18;
+    int32_t s = 0;
+    for (int i = 0; i < 16; i++) {
+      s += (int32_t)KV_IQ4NL[blk[2 + i] & 15] * (int32_t)q[32 * b + i];
+      s += (int32_t)KV_IQ4NL[blk[2 + i] >> 4] * (int32_t)q[32 * b + 16 + i];
+    }
+    total += f16le(blk) * d32[b] * (float)s;
+  }
+  return total;
+}
+
+/* a row of a 32-block type against 32-block Q8 activations (`row`, src/q4x_cpu.rs:367) */
+static float row_q8_32(int t, const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
+  return t == PM_TYPE_IQ4_NL ? po_row_iq4nl(w, ncols, q, d32) : po_row_q8_0(w, ncols, q, d32);
 }
 
 float po_row_f32(int t, const uint8_t *w, size_t ncols, const float *x) {
@@ -713,24 +749,28 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
     }
   } else if (D->act_quant == PM_AQ_Q8_32) { /* src/q4x_cpu.rs:399-440 */
     if (d % 32 || ff % 32) { free(h); return PM_ERR_INVALID; }
-    if (D->type_gate != PM_TYPE_Q8_0 || D->type_up != PM_TYPE_Q8_0 || D->type_down != PM_TYPE_Q8_0) {
-      free(h);
-      return PM_ERR_UNSUPPORTED;
+    {
+      const int ts[3] = {D->type_gate, D->type_up, D->type_down};
+      for (int i = 0; i < 3; i++)
+        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL) {
+          free(h);
+          return PM_ERR_UNSUPPORTED;
+        }
     }
     int8_t *xq = (int8_t *)malloc((size_t)d), *hq = (int8_t *)malloc((size_t)ff);
     float *xd = (float *)malloc((size_t)d / 32 * 4), *hd = (float *)malloc((size_t)ff / 32 * 4);
     for (int t = 0; t < nt; t++) {
       po_q8_32(xs[t], (size_t)d, xq, xd);
       for (int j = 0; j < ff; j++) {
-        float g = po_row_q8_0(W->gate + (size_t)j * bg, (size_t)d, xq, xd);
-        float u = po_row_q8_0(W->up + (size_t)j * bu, (size_t)d, xq, xd);
+        float g = row_q8_32(D->type_gate, W->gate + (size_t)j * bg, (size_t)d, xq, xd);
+        float u = row_q8_32(D->type_up, W->up + (size_t)j * bu, (size_t)d, xq, xd);
         if (W->bias_gate) g = g + W->bias_gate[j];
         if (W->bias_up) u = u + W->bias_up[j];
         h[j] = act_fn(D, g, u, wts ? wts[t] : 1.0f, fold);
       }
       po_q8_32(h, (size_t)ff, hq, hd);
       for (int r = 0; r < d; r++) {
-        float o = po_row_q8_0(W->down + (size_t)r * bd, (size_t)ff, hq, hd);
+        float o = row_q8_32(D->type_down, W->down + (size_t)r * bd, (size_t)ff, hq, hd);
         if (W->bias_down) o = o + W->bias_down[r];
         out[(size_t)t * d + r] = o;
       }

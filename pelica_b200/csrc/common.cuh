@@ -133,6 +133,21 @@ __device__ __forceinline__ uint32_t pm_sub32x4(uint32_t q) {
   return ((q | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
 }
 
+// the IQ4_NL codebook (src/iq_tables.rs:72), entry i in byte i of four words
+__device__ __forceinline__ int pm_iq4nl(uint32_t i) {
+  const uint32_t t[4] = {0xbfad9881u, 0xf6eaddcfu, 0x26190d01u, 0x71594535u};
+  return (int)(int8_t)(t[(i >> 2) & 3] >> (8 * (i & 3)));
+}
+// four codebook entries at once: the low nibble of each byte of `idx` selects
+__device__ __forceinline__ uint32_t pm_iq4nl_x4(uint32_t idx) {
+  const uint32_t s = idx & 0x07070707u;
+  const uint32_t sel = (s & 0xfu) | ((s >> 4) & 0xf0u) | ((s >> 8) & 0xf00u) | ((s >> 12) & 0xf000u);
+  const uint32_t lo = __byte_perm(0xbfad9881u, 0xf6eaddcfu, sel);  // entries 0..7
+  const uint32_t hi = __byte_perm(0x26190d01u, 0x71594535u, sel);  // entries 8..15
+  const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xffu;
+  return (lo & ~m) | (hi & m);
+}
+
 // `e8` (src/oss_kernels.rs:42-45): 2^(e-128)
 __device__ __forceinline__ float pm_e8(uint32_t e) {
   return e < 2 ? __uint_as_float(0x00200000u << e) : __uint_as_float((e - 1) << 23);

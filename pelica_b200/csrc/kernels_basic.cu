@@ -81,6 +81,11 @@ void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t nb, uin
       KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 34, 2, p1, p0, 0);
       break;
     }
+    case PM_TYPE_IQ4_NL: {
+      size_t n = nb * 18;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 18, 2, p1, p0, 0);
+      break;
+    }
   }
 }
 void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uint8_t *p0,
@@ -104,6 +109,12 @@ void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uin
     case PM_TYPE_Q8_0: {
       size_t n = nb * 34;
       KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 34, 2,
+              const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
+      break;
+    }
+    case PM_TYPE_IQ4_NL: {
+      size_t n = nb * 18;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 18, 2,
               const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
       break;
     }
@@ -138,6 +149,10 @@ __device__ __forceinline__ float deq_value(const uint8_t *p0, const uint8_t *p1,
     uint8_t byte = p0[b * 16 + (v & 15)];
     uint32_t c = v >= 16 ? (byte >> 4) : (byte & 15);
     return __fmul_rn(pm_e8(p1[b]), pm_e2m1(c));
+  } else if (TYPE == PM_TYPE_IQ4_NL) {  // d * codebook[index] (src/q4x_cpu.rs:453-461)
+    uint8_t byte = p0[b * 16 + (v & 15)];
+    float d = pm_f16(*(const uint16_t *)(p1 + b * 2));
+    return __fmul_rn(d, (float)pm_iq4nl(v >= 16 ? (byte >> 4) : (byte & 15)));
   } else {  // Q8_0: d*q (src/moe_kernels.rs:68)
     float d = pm_f16(*(const uint16_t *)(p1 + b * 2));
     return __fmul_rn(d, (float)(int8_t)p0[b * 32 + v]);
@@ -161,6 +176,7 @@ void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, cons
     case PM_TYPE_Q6_K: KLAUNCH(L, (k_dequant<PM_TYPE_Q6_K, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_MXFP4: KLAUNCH(L, (k_dequant<PM_TYPE_MXFP4, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_Q8_0: KLAUNCH(L, (k_dequant<PM_TYPE_Q8_0, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_IQ4_NL: KLAUNCH(L, (k_dequant<PM_TYPE_IQ4_NL, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
   }
 }
 
@@ -573,25 +589,38 @@ __device__ __forceinline__ float row_q8x(const WMat &W, int el, int r, const int
                      W.plane[3] + (size_t)el * W.stride[3] + rb * 2, nb, xq, xd, lane);
 }
 
-// Q8_0 row . 32-block Q8 activations (src/q4x_cpu.rs:85-90): per block
+// Q8_0 / IQ4_NL row . 32-block Q8 activations (src/q4x_cpu.rs:85-101): per block
 // total += f16(d_w) * x.d[b] * (float)idot, left to right, in block order. Lanes take
 // one block each; the 32 terms are then added in order.
 __device__ __forceinline__ float row_q8_0_q8(const WMat &W, int el, int r, const int8_t *__restrict__ xq,
                                              const float *__restrict__ xd, int lane) {
   const int nb = W.cols / 32;
-  const uint8_t *vals = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * 32;
+  const bool nl = W.type == PM_TYPE_IQ4_NL;
+  const uint8_t *vals = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * (nl ? 16 : 32);
   const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * nb * 2;
   float total = 0.0f;
   for (int b0 = 0; b0 < nb; b0 += 32) {
     const int b = b0 + lane;
     float term = 0.0f;
     if (b < nb) {
-      const int4 *wp = (const int4 *)(vals + (size_t)b * 32);
       const int4 *xp = (const int4 *)(xq + (size_t)b * 32);
-      const int4 w0 = __ldg(wp), w1 = __ldg(wp + 1), x0 = xp[0], x1 = xp[1];
+      const int4 x0 = xp[0], x1 = xp[1];
       int s = 0;
-      s = __dp4a(w0.x, x0.x, s); s = __dp4a(w0.y, x0.y, s); s = __dp4a(w0.z, x0.z, s); s = __dp4a(w0.w, x0.w, s);
-      s = __dp4a(w1.x, x1.x, s); s = __dp4a(w1.y, x1.y, s); s = __dp4a(w1.z, x1.z, s); s = __dp4a(w1.w, x1.w, s);
+      if (nl) {  // byte j: index of value j (low nibble) and of value j + 16 (high nibble)
+        const uint4 w = __ldg((const uint4 *)(vals + (size_t)b * 16));
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        const int xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          s = __dp4a((int)pm_iq4nl_x4(ww[i] & 0x0f0f0f0fu), xl[i], s);
+          s = __dp4a((int)pm_iq4nl_x4((ww[i] >> 4) & 0x0f0f0f0fu), xh[i], s);
+        }
+      } else {
+        const int4 *wp = (const int4 *)(vals + (size_t)b * 32);
+        const int4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+        s = __dp4a(w0.x, x0.x, s); s = __dp4a(w0.y, x0.y, s); s = __dp4a(w0.z, x0.z, s); s = __dp4a(w0.w, x0.w, s);
+        s = __dp4a(w1.x, x1.x, s); s = __dp4a(w1.y, x1.y, s); s = __dp4a(w1.z, x1.z, s); s = __dp4a(w1.w, x1.w, s);
+      }
       const float dw = pm_f16(__ldg((const uint16_t *)(scl + (size_t)b * 2)));
       term = __fmul_rn(__fmul_rn(dw, xd[b]), (float)s);
     }
@@ -632,7 +661,7 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
     const uint8_t *p1 = W.plane[1] ? W.plane[1] + (size_t)el * W.stride[1] : nullptr;
     const uint8_t *p2 = W.plane[2] ? W.plane[2] + (size_t)el * W.stride[2] : nullptr;
     const uint8_t *p3 = W.plane[3] ? W.plane[3] + (size_t)el * W.stride[3] : nullptr;
-    int bv = W.type == PM_TYPE_Q8_0 ? 32 : 256;
+    int bv = (W.type == PM_TYPE_Q8_0 || W.type == PM_TYPE_IQ4_NL) ? 32 : 256;
     size_t b0 = (size_t)r * (W.cols / bv);
     for (int v = lane; v < W.cols; v += 32) {
       float wv;
@@ -640,6 +669,7 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
       int iv = v % bv;
       if (W.type == PM_TYPE_Q4_K) wv = deq_value<PM_TYPE_Q4_K>(p0, p1, p2, p3, b, iv);
       else if (W.type == PM_TYPE_Q6_K) wv = deq_value<PM_TYPE_Q6_K>(p0, p1, p2, p3, b, iv);
+      else if (W.type == PM_TYPE_IQ4_NL) wv = deq_value<PM_TYPE_IQ4_NL>(p0, p1, p2, p3, b, iv);
       else wv = deq_value<PM_TYPE_Q8_0>(p0, p1, p2, p3, b, iv);
       acc = __fmaf_rn(wv, x[v], acc);
     }

@@ -11,6 +11,7 @@
 //  MXFP4: plane 0 = E2M1 nibbles (16 B/block), 1 = E8M0 scale bytes (1 B/block)
 //         (the reference splits gpt-oss tensors the same way, src/oss.rs:241-253)
 //  Q8_0 : plane 0 = int8 values (32 B/block), 1 = f16 scales (2 B/block)
+//  IQ4_NL: plane 0 = codebook indices (16 B/block), 1 = f16 scales (2 B/block)
 struct WMat {
   int type;
   int rows, cols;
@@ -69,6 +70,9 @@ static inline size_t wmat_plane_bytes(int type, int rows, int cols, int p) {
     case PM_TYPE_Q8_0:
       nb = (size_t)rows * (cols / 32);
       return p == 0 ? nb * 32 : (p == 1 ? nb * 2 : 0);
+    case PM_TYPE_IQ4_NL:
+      nb = (size_t)rows * (cols / 32);
+      return p == 0 ? nb * 16 : (p == 1 ? nb * 2 : 0);
   }
   return 0;
 }

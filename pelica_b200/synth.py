@@ -14,8 +14,10 @@ import dataclasses
 import numpy as np
 
 # ggml type ids (src/gguf.rs:85-121)
-F32, F16, Q8_0, Q4_K, Q6_K, BF16, MXFP4 = 0, 1, 8, 12, 14, 30, 39
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), MXFP4: (32, 17)}
+F32, F16, Q8_0, Q4_K, Q6_K, IQ4_NL, BF16, MXFP4 = 0, 1, 8, 12, 14, 20, 30, 39
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ4_NL: (32, 18), MXFP4: (32, 17)}
+# the IQ4_NL codebook, a constant of the format (src/iq_tables.rs:72)
+KV_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int8)
 
 GATE_SOFTMAX_ALL, GATE_SIGMOID, GATE_SQRT_SOFTPLUS, GATE_SOFTMAX_SELECTED = 0, 1, 2, 3
 ACT_SILU, ACT_SILU_CLAMP, ACT_OSS_GLU = 0, 1, 2
@@ -143,7 +145,28 @@ def encode_q8_0(x: np.ndarray) -> np.ndarray:
     return out.reshape(*lead, -1)
 
 
-ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0}
+def encode_iq4_nl(x: np.ndarray) -> np.ndarray:
+    """32 values -> f16 d + 16 bytes: byte j = codebook index of value j (low nibble) and of
+    value j + 16 (high nibble) (src/q4x_cpu.rs:453-461). d = amax / 127 (by the sign of the largest
+    value, so that it lands on the codebook's -127), indices = nearest codebook entry."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 32)
+    nb = xb.shape[0]
+    imax = np.abs(xb).argmax(-1)
+    vmax = xb[np.arange(nb), imax]
+    d = (vmax / -127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        t = np.where(df[:, None] != 0, xb / df[:, None], 0.0)
+    idx = np.abs(t[:, :, None] - KV_IQ4NL.astype(np.float32)[None, None, :]).argmin(-1).astype(np.uint8)
+    out = np.zeros((nb, 18), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:18] = idx[:, :16] | (idx[:, 16:] << 4)
+    return out.reshape(*lead, -1)
+
+
+ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0, IQ4_NL: encode_iq4_nl}
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:
@@ -223,7 +246,10 @@ C5_ZIPF = Config("qwen3-zipf", d=2048, ff=768, n_exp=128, top_k=8, gating=GATE_S
 # is 2560 x 640 (src/q4x_cpu.rs:544)
 C6_Q8_0 = Config("q4x-q8_0", d=2560, ff=640, n_exp=32, top_k=8, gating=GATE_SOFTMAX_SELECTED, type_gate=Q8_0,
                  type_up=Q8_0, type_down=Q8_0, act_quant=AQ_Q8_32)
-CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0}
+# the same path with the 4-bit non-linear type of the reference's Qwen3.8 down tensors
+C7_IQ4NL = C6_Q8_0.scaled(name="q4x-iq4_nl", type_gate=IQ4_NL, type_up=IQ4_NL, type_down=IQ4_NL)
+CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0,
+           "c7": C7_IQ4NL}
 
 
 def make_weights(cfg: Config, seed: int, experts=None) -> dict:

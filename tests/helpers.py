@@ -59,6 +59,7 @@ SMALL = {
     "c4": synth.C4_DSV3.scaled(d=512, ff=256, n_exp=32, n_group=4, topk_group=2, shared_ff=256),
     "c5": synth.C5_ZIPF.scaled(d=512, ff=256, n_exp=32),
     "c6": synth.C6_Q8_0.scaled(d=320, ff=160, n_exp=16),
+    "c7": synth.C7_IQ4NL.scaled(d=320, ff=160, n_exp=16, type_down=synth.Q8_0),  # mixed 32-block types
 }
 
 

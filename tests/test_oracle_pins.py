@@ -81,13 +81,13 @@ def test_rows_match_dequant(oracle):
     # the shape of src/q4x_cpu.rs:509-535: a quantised row equals dequantised
     # weights . dequantised activations within 1e-3*max(|want|,1)
     rng = np.random.default_rng(5)
-    for ty, n in ((synth.Q4_K, 1024), (synth.Q6_K, 768), (synth.Q8_0, 512)):
+    for ty, n in ((synth.Q4_K, 1024), (synth.Q6_K, 768), (synth.Q8_0, 512), (synth.IQ4_NL, 2560)):
         w = synth.ENCODERS[ty](rng.normal(0, 0.02, n).astype(np.float32))
         x = rng.normal(0, 1, n).astype(np.float32)
         wd = oracle.dequant(ty, w, n).astype(np.float64)
-        if ty == synth.Q8_0:
+        if ty in (synth.Q8_0, synth.IQ4_NL):
             q, d = oracle.q8_32(x)
-            got = oracle.row_q8_0(w, n, q, d)
+            got = oracle.row_q8_0(w, n, q, d) if ty == synth.Q8_0 else oracle.row_iq4nl(w, n, q, d)
             xd = q.astype(np.float64) * np.repeat(d, 32)
         else:
             q, d, bs = oracle.q8x(x)
@@ -151,6 +151,14 @@ def test_block_known_answers(oracle):
     blk[2] = np.int8(-100).view(np.uint8)
     out = oracle.dequant(synth.Q8_0, blk, 32)
     assert out[0] == -25.0
+    # IQ4_NL: d = 0.25; byte 0 = index 0 (low: value 0) and 15 (high: value 16); byte 15 = 8 / 7
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = [0x00, 0x34]
+    blk[2] = 0xF0
+    blk[17] = 0x78
+    out = oracle.dequant(synth.IQ4_NL, blk, 32)
+    assert out[0] == -31.75 and out[16] == 28.25 and out[15] == 0.25 and out[31] == -2.5
+    assert out[1] == -31.75  # index 0 everywhere else
 
 
 def test_q8x_known_answers(oracle):
