@@ -54,6 +54,8 @@ enum {
   PM_TYPE_Q6_K = 14,  /* 256 values / 210 B */
   PM_TYPE_IQ4_NL = 20, /* 32 values / 18 B: f16 d + 16 B of 4-bit indices into a fixed
                           non-linear codebook (src/iq_tables.rs:72, src/q4x_cpu.rs:92-101) */
+  PM_TYPE_IQ4_XS = 23, /* 256 values / 136 B: f16 d, 8 six-bit sub-scales (bias 32), indices into
+                          the IQ4_NL codebook (src/q4x_cpu.rs:102-117,462-476) */
   PM_TYPE_BF16 = 30,
   PM_TYPE_MXFP4 = 39  /* 32 values / 17 B  */
 };
@@ -83,7 +85,7 @@ enum {
                          (`Q8x`, src/ds4_cpu.rs:7-36); the hidden vector is
                          re-quantised before down (src/ds4_cpu.rs:306-317)        */
   PM_AQ_Q8_32 = 2     /* int8 per 32 values, f32 scale (`Q8`, src/q4x_cpu.rs:13-51)
-                         against Q8_0 / IQ4_NL weights: per block f16(d_w) * x.d * idot
+                         against Q8_0 / IQ4_NL / IQ4_XS weights: per block f16(d_w) * x.d * idot
                          (src/q4x_cpu.rs:85-101); hidden vector re-quantised the
                          same way before down (src/q4x_cpu.rs:399-440)            */
 };

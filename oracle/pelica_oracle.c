@@ -179,6 +179,7 @@ size_t po_type_block_bytes(int t) {
     case PM_TYPE_BF16: return 2;
     case PM_TYPE_Q8_0: return 34;
     case PM_TYPE_IQ4_NL: return 18;
+    case PM_TYPE_IQ4_XS: return 136;
     case PM_TYPE_Q4_K: return 144;
     case PM_TYPE_Q6_K: return 210;
     case PM_TYPE_MXFP4: return 17;
@@ -194,6 +195,7 @@ size_t po_type_block_values(int t) {
     case PM_TYPE_IQ4_NL:
     case PM_TYPE_MXFP4: return 32;
     case PM_TYPE_Q4_K:
+    case PM_TYPE_IQ4_XS:
     case PM_TYPE_Q6_K: return 256;
   }
   return 0;
@@ -268,6 +270,22 @@ int po_dequant(int t, const uint8_t *blocks, size_t n, float *out) {
         for (int i = 0; i < 16; i++) {
           out[b * 32 + i] = d * (float)KV_IQ4NL[blk[2 + i] & 15];
           out[b * 32 + 16 + i] = d * (float)KV_IQ4NL[blk[2 + i] >> 4];
+        }
+      }
+      return 0;
+    case PM_TYPE_IQ4_XS: /* src/q4x_cpu.rs:462-476 */
+      for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = blocks + b * bb;
+        float d = f16le(blk);
+        unsigned sh = (unsigned)blk[2] | ((unsigned)blk[3] << 8);
+        for (int ib = 0; ib < 8; ib++) {
+          int ls = ((blk[4 + ib / 2] >> (4 * (ib % 2))) & 15) | (int)(((sh >> (2 * ib)) & 3) << 4);
+          float dl = d * (float)(ls - 32);
+          for (int i = 0; i < 16; i++) {
+            uint8_t q = blk[8 + 16 * ib + i];
+            out[b * 256 + 32 * ib + i] = dl * (float)KV_IQ4NL[q & 15];
+            out[b * 256 + 32 * ib + 16 + i] = dl * (float)KV_IQ4NL[q >> 4];
+          }
         }
       }
       return 0;
@@ -449,9 +467,34 @@ float po_row_iq4nl(const uint8_t *w, size_t ncols, const int8_t *q, const float 
   return total;
 }
 
-/* a row of a 32-block type against 32-block Q8 activations (`row`, src/q4x_cpu.rs:367) */
+/* src/q4x_cpu.rs:102-117 */
+float po_row_iq4xs(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
+  float total = 0.0f;
+  size_t nb = ncols / 256;
+  for (size_t b = 0; b < nb; b++) {
+    const uint8_t *blk = w + b * 136;
+    float d = f16le(blk);
+    unsigned sh = (unsigned)blk[2] | ((unsigned)blk[3] << 8);
+    for (int ib = 0; ib < 8; ib++) {
+      int ls = ((blk[4 + ib / 2] >> (4 * (ib % 2))) & 15) | (int)(((sh >> (2 * ib)) & 3) << 4);
+      const uint8_t *qs = blk + 8 + 16 * ib;
+      size_t s = 8 * b + (size_t)ib;
+      int32_t acc = 0;
+      for (int i = 0; i < 16; i++) {
+        acc += (int32_t)KV_IQ4NL[qs[i] & 15] * (int32_t)q[32 * s + i];
+        acc += (int32_t)KV_IQ4NL[qs[i] >> 4] * (int32_t)q[32 * s + 16 + i];
+      }
+      total += d * (float)(ls - 32) * d32[s] * (float)acc;
+    }
+  }
+  return total;
+}
+
+/* a row of a type of the q4x path against 32-block Q8 activations (`row`, src/q4x_cpu.rs:367) */
 static float row_q8_32(int t, const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
-  return t == PM_TYPE_IQ4_NL ? po_row_iq4nl(w, ncols, q, d32) : po_row_q8_0(w, ncols, q, d32);
+  if (t == PM_TYPE_IQ4_NL) return po_row_iq4nl(w, ncols, q, d32);
+  if (t == PM_TYPE_IQ4_XS) return po_row_iq4xs(w, ncols, q, d32);
+  return po_row_q8_0(w, ncols, q, d32);
 }
 
 float po_row_f32(int t, const uint8_t *w, size_t ncols, const float *x) {
@@ -752,7 +795,7 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
     {
       const int ts[3] = {D->type_gate, D->type_up, D->type_down};
       for (int i = 0; i < 3; i++)
-        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL) {
+        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL && ts[i] != PM_TYPE_IQ4_XS) {
           free(h);
           return PM_ERR_UNSUPPORTED;
         }

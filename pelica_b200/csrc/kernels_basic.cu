@@ -86,6 +86,11 @@ void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t nb, uin
       KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 18, 2, p1, p0, 0);
       break;
     }
+    case PM_TYPE_IQ4_XS: {
+      size_t n = nb * 136;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 136, 8, p1, p0, 0);
+      break;
+    }
   }
 }
 void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uint8_t *p0,
@@ -115,6 +120,12 @@ void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uin
     case PM_TYPE_IQ4_NL: {
       size_t n = nb * 18;
       KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 18, 2,
+              const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
+      break;
+    }
+    case PM_TYPE_IQ4_XS: {
+      size_t n = nb * 136;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 136, 8,
               const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
       break;
     }
@@ -149,6 +160,14 @@ __device__ __forceinline__ float deq_value(const uint8_t *p0, const uint8_t *p1,
     uint8_t byte = p0[b * 16 + (v & 15)];
     uint32_t c = v >= 16 ? (byte >> 4) : (byte & 15);
     return __fmul_rn(pm_e8(p1[b]), pm_e2m1(c));
+  } else if (TYPE == PM_TYPE_IQ4_XS) {  // (d * (ls - 32)) * codebook[index] (src/q4x_cpu.rs:462-476)
+    const uint8_t *hd = p1 + b * 8;
+    const int ib = v >> 5, i = v & 31;
+    const uint32_t sh = (uint32_t)hd[2] | ((uint32_t)hd[3] << 8);
+    const int ls = (int)((hd[4 + ib / 2] >> (4 * (ib % 2))) & 15) | (int)(((sh >> (2 * ib)) & 3) << 4);
+    const float dl = __fmul_rn(pm_f16(*(const uint16_t *)hd), (float)(ls - 32));
+    const uint8_t byte = p0[b * 128 + 16 * ib + (i & 15)];
+    return __fmul_rn(dl, (float)pm_iq4nl(i >= 16 ? (byte >> 4) : (byte & 15)));
   } else if (TYPE == PM_TYPE_IQ4_NL) {  // d * codebook[index] (src/q4x_cpu.rs:453-461)
     uint8_t byte = p0[b * 16 + (v & 15)];
     float d = pm_f16(*(const uint16_t *)(p1 + b * 2));
@@ -177,6 +196,7 @@ void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, cons
     case PM_TYPE_MXFP4: KLAUNCH(L, (k_dequant<PM_TYPE_MXFP4, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_Q8_0: KLAUNCH(L, (k_dequant<PM_TYPE_Q8_0, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_IQ4_NL: KLAUNCH(L, (k_dequant<PM_TYPE_IQ4_NL, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_IQ4_XS: KLAUNCH(L, (k_dequant<PM_TYPE_IQ4_XS, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
   }
 }
 
@@ -594,10 +614,11 @@ __device__ __forceinline__ float row_q8x(const WMat &W, int el, int r, const int
 // one block each; the 32 terms are then added in order.
 __device__ __forceinline__ float row_q8_0_q8(const WMat &W, int el, int r, const int8_t *__restrict__ xq,
                                              const float *__restrict__ xd, int lane) {
-  const int nb = W.cols / 32;
-  const bool nl = W.type == PM_TYPE_IQ4_NL;
+  const int nb = W.cols / 32;  // 32-value units: a block of Q8_0 / IQ4_NL, a sub-block of IQ4_XS
+  const bool xs = W.type == PM_TYPE_IQ4_XS;
+  const bool nl = W.type == PM_TYPE_IQ4_NL || xs;
   const uint8_t *vals = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * (nl ? 16 : 32);
-  const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * nb * 2;
+  const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * (xs ? (nb / 8) * 8 : nb * 2);
   float total = 0.0f;
   for (int b0 = 0; b0 < nb; b0 += 32) {
     const int b = b0 + lane;
@@ -621,7 +642,15 @@ __device__ __forceinline__ float row_q8_0_q8(const WMat &W, int el, int r, const
         s = __dp4a(w0.x, x0.x, s); s = __dp4a(w0.y, x0.y, s); s = __dp4a(w0.z, x0.z, s); s = __dp4a(w0.w, x0.w, s);
         s = __dp4a(w1.x, x1.x, s); s = __dp4a(w1.y, x1.y, s); s = __dp4a(w1.z, x1.z, s); s = __dp4a(w1.w, x1.w, s);
       }
-      const float dw = pm_f16(__ldg((const uint16_t *)(scl + (size_t)b * 2)));
+      float dw;
+      if (xs) {  // d * (ls - 32) of sub-block b & 7 (src/q4x_cpu.rs:102-117)
+        const uint2 hd = __ldg((const uint2 *)(scl + (size_t)(b >> 3) * 8));
+        const int ib = b & 7;
+        const int ls = (int)((hd.y >> (4 * ib)) & 15) | (int)((((hd.x >> 16) >> (2 * ib)) & 3) << 4);
+        dw = __fmul_rn(pm_f16(hd.x), (float)(ls - 32));
+      } else {
+        dw = pm_f16(__ldg((const uint16_t *)(scl + (size_t)b * 2)));
+      }
       term = __fmul_rn(__fmul_rn(dw, xd[b]), (float)s);
     }
     const int n = min(32, nb - b0);
@@ -670,6 +699,7 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
       if (W.type == PM_TYPE_Q4_K) wv = deq_value<PM_TYPE_Q4_K>(p0, p1, p2, p3, b, iv);
       else if (W.type == PM_TYPE_Q6_K) wv = deq_value<PM_TYPE_Q6_K>(p0, p1, p2, p3, b, iv);
       else if (W.type == PM_TYPE_IQ4_NL) wv = deq_value<PM_TYPE_IQ4_NL>(p0, p1, p2, p3, b, iv);
+      else if (W.type == PM_TYPE_IQ4_XS) wv = deq_value<PM_TYPE_IQ4_XS>(p0, p1, p2, p3, b, iv);
       else wv = deq_value<PM_TYPE_Q8_0>(p0, p1, p2, p3, b, iv);
       acc = __fmaf_rn(wv, x[v], acc);
     }

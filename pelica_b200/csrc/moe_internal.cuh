@@ -12,6 +12,8 @@
 //         (the reference splits gpt-oss tensors the same way, src/oss.rs:241-253)
 //  Q8_0 : plane 0 = int8 values (32 B/block), 1 = f16 scales (2 B/block)
 //  IQ4_NL: plane 0 = codebook indices (16 B/block), 1 = f16 scales (2 B/block)
+//  IQ4_XS: plane 0 = codebook indices (128 B/block), 1 = the 8-byte header (f16 d, u16 high
+//          scale bits, 4 bytes of low scale nibbles)
 struct WMat {
   int type;
   int rows, cols;
@@ -73,6 +75,9 @@ static inline size_t wmat_plane_bytes(int type, int rows, int cols, int p) {
     case PM_TYPE_IQ4_NL:
       nb = (size_t)rows * (cols / 32);
       return p == 0 ? nb * 16 : (p == 1 ? nb * 2 : 0);
+    case PM_TYPE_IQ4_XS:
+      nb = (size_t)rows * (cols / 256);
+      return p == 0 ? nb * 128 : (p == 1 ? nb * 8 : 0);
   }
   return 0;
 }

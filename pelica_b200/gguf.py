@@ -28,7 +28,7 @@ _SCALAR = {T_U8: "<B", T_I8: "<b", T_U16: "<H", T_I16: "<h", T_U32: "<I", T_I32:
            T_BOOL: "<?", T_U64: "<Q", T_I64: "<q", T_F64: "<d"}
 # ggml type id -> (values per block, bytes per block) of the types this library takes
 BLOCK = {0: (1, 4), 1: (1, 2), 30: (1, 2), synth.Q8_0: (32, 34), synth.Q4_K: (256, 144), synth.Q6_K: (256, 210),
-         synth.IQ4_NL: (32, 18), synth.MXFP4: (32, 17)}
+         synth.IQ4_NL: (32, 18), synth.IQ4_XS: (256, 136), synth.MXFP4: (32, 17)}
 
 
 class GGUFError(ValueError):
@@ -196,7 +196,7 @@ def moe_config(g: GGUFFile, layer: int = 0) -> synth.Config:
         norm_w=int(bool(g.meta.get(key("expert_weights_norm"), a in ("qwen3moe", "llama", "mixtral")))),
         w_scale=float(g.meta.get(key("expert_weights_scale"), 0.0)),
         type_gate=gate.type, type_up=up.type, type_down=down.type,
-        act_quant=synth.AQ_F32 if f32_acts else (synth.AQ_Q8_32 if gate.type in (synth.Q8_0, synth.IQ4_NL) else synth.AQ_Q8X_256),
+        act_quant=synth.AQ_F32 if f32_acts else (synth.AQ_Q8_32 if gate.type in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS) else synth.AQ_Q8X_256),
         weight_fold=synth.FOLD_IN_COMBINE if f32_acts else synth.FOLD_BEFORE_DOWN,
         shared=(synth.SHARED_SIGMOID_GATED if gated else synth.SHARED_PLAIN) if shared else synth.SHARED_NONE,
         shared_ff=int(g.tensor(f"blk.{layer}.ffn_up_shexp.weight").dims[1]) if shared else 0,

@@ -14,8 +14,8 @@ import dataclasses
 import numpy as np
 
 # ggml type ids (src/gguf.rs:85-121)
-F32, F16, Q8_0, Q4_K, Q6_K, IQ4_NL, BF16, MXFP4 = 0, 1, 8, 12, 14, 20, 30, 39
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ4_NL: (32, 18), MXFP4: (32, 17)}
+F32, F16, Q8_0, Q4_K, Q6_K, IQ4_NL, IQ4_XS, BF16, MXFP4 = 0, 1, 8, 12, 14, 20, 23, 30, 39
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ4_NL: (32, 18), IQ4_XS: (256, 136), MXFP4: (32, 17)}
 # the IQ4_NL codebook, a constant of the format (src/iq_tables.rs:72)
 KV_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int8)
 
@@ -166,7 +166,40 @@ def encode_iq4_nl(x: np.ndarray) -> np.ndarray:
     return out.reshape(*lead, -1)
 
 
-ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0, IQ4_NL: encode_iq4_nl}
+def encode_iq4_xs(x: np.ndarray) -> np.ndarray:
+    """256 values -> f16 d, u16 high scale bits, 4 bytes of low scale nibbles, 128 index bytes
+    (src/q4x_cpu.rs:462-476): sub-block scale = d * (ls - 32), ls six bits; sub-block ib's byte i holds
+    the codebook index of value i (low nibble) and of value i + 16 (high nibble)."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 8, 32)
+    nb = xb.shape[0]
+    amax = np.abs(xb).max(-1)                      # [nb, 8]
+    d = (amax.max(-1) / 127.0 / 31.0).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        l = np.where(df[:, None] > 0, np.rint(amax / 127.0 / df[:, None]), 0.0)
+    l = np.clip(l, 0, 31).astype(np.int32)
+    l = np.where((amax > 0) & (l == 0), 1, l)
+    ls = (l + 32).astype(np.uint32)                # 32..63
+    dl = df[:, None] * l.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        t = np.where(dl[:, :, None] != 0, xb / dl[:, :, None], 0.0)
+    idx = np.abs(t[..., None] - KV_IQ4NL.astype(np.float32)).argmin(-1).astype(np.uint8)  # [nb, 8, 32]
+    out = np.zeros((nb, 136), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+    sh = np.zeros(nb, np.uint32)
+    for ib in range(8):
+        sh |= ((ls[:, ib] >> 4) & 3) << (2 * ib)
+        out[:, 4 + ib // 2] |= ((ls[:, ib] & 15) << (4 * (ib % 2))).astype(np.uint8)
+    out[:, 2] = (sh & 0xFF).astype(np.uint8)
+    out[:, 3] = (sh >> 8).astype(np.uint8)
+    out[:, 8:136] = (idx[:, :, :16] | (idx[:, :, 16:] << 4)).reshape(nb, 128)
+    return out.reshape(*lead, -1)
+
+
+ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0, IQ4_NL: encode_iq4_nl,
+            IQ4_XS: encode_iq4_xs}
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:
@@ -248,8 +281,9 @@ C6_Q8_0 = Config("q4x-q8_0", d=2560, ff=640, n_exp=32, top_k=8, gating=GATE_SOFT
                  type_up=Q8_0, type_down=Q8_0, act_quant=AQ_Q8_32)
 # the same path with the 4-bit non-linear type of the reference's Qwen3.8 down tensors
 C7_IQ4NL = C6_Q8_0.scaled(name="q4x-iq4_nl", type_gate=IQ4_NL, type_up=IQ4_NL, type_down=IQ4_NL)
+C8_IQ4XS = C6_Q8_0.scaled(name="q4x-iq4_xs", type_gate=IQ4_XS, type_up=IQ4_XS, type_down=IQ4_NL)
 CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0,
-           "c7": C7_IQ4NL}
+           "c7": C7_IQ4NL, "c8": C8_IQ4XS}
 
 
 def make_weights(cfg: Config, seed: int, experts=None) -> dict:

@@ -60,6 +60,7 @@ SMALL = {
     "c5": synth.C5_ZIPF.scaled(d=512, ff=256, n_exp=32),
     "c6": synth.C6_Q8_0.scaled(d=320, ff=160, n_exp=16),
     "c7": synth.C7_IQ4NL.scaled(d=320, ff=160, n_exp=16, type_down=synth.Q8_0),  # mixed 32-block types
+    "c8": synth.C8_IQ4XS.scaled(d=512, ff=160, n_exp=16),
 }
 
 

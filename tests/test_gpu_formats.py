@@ -9,7 +9,7 @@ from tests.helpers import bits_equal, lcg, ref_acts, ref_q4k_blocks
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.Q8_0, synth.IQ4_NL])
+@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS])
 def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
     """Every bit pattern path: random block bytes, only the f16 scales kept finite."""
     v, b = synth.BLOCK[ty]
@@ -21,7 +21,7 @@ def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
         raw[:, 0:4] = half
     elif ty == synth.Q6_K:
         raw[:, 208:210] = half[:, :2]
-    elif ty in (synth.Q8_0, synth.IQ4_NL):
+    elif ty in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS):
         raw[:, 0:2] = half[:, :2]
     else:
         raw[:3, 0] = [0, 1, 2]  # the denormal branch of e8 (src/oss_kernels.rs:42-45)
@@ -31,7 +31,7 @@ def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
     assert bits_equal(got, want)
 
 
-@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.IQ4_NL])
+@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.IQ4_NL, synth.IQ4_XS])
 def test_dequant_encoded_weights(ctx, oracle, ty):
     rng = np.random.default_rng(1)
     x = rng.normal(0, 0.02, 4096).astype(np.float32)
