@@ -36,6 +36,7 @@ class CudaBackend:
         self.layer = layer
         self.desc = layer.desc
         self.lib = layer.lib
+        self._plan_bufs = {}  # (T, K, device) -> the dispatch plan's output tensors, reused across calls
 
     @staticmethod
     def _p(t):
@@ -55,12 +56,15 @@ class CudaBackend:
         T, K = ids.shape
         E = self.desc.n_exp
         dev = ids.device
-        out = dict(n_active=torch.zeros(1, dtype=torch.int32, device=dev),
-                   active=torch.zeros(E, dtype=torch.int32, device=dev),
-                   offset=torch.zeros(E, dtype=torch.int32, device=dev),
-                   count=torch.zeros(E, dtype=torch.int32, device=dev),
-                   pair_token=torch.zeros(max(T * K, 1), dtype=torch.int32, device=dev),
-                   pair_pos=torch.zeros(max(T * K, 1), dtype=torch.int32, device=dev))
+        out = self._plan_bufs.get((T, K, dev))
+        if out is None:
+            out = dict(n_active=torch.zeros(1, dtype=torch.int32, device=dev),
+                       active=torch.zeros(E, dtype=torch.int32, device=dev),
+                       offset=torch.zeros(E, dtype=torch.int32, device=dev),
+                       count=torch.zeros(E, dtype=torch.int32, device=dev),
+                       pair_token=torch.zeros(max(T * K, 1), dtype=torch.int32, device=dev),
+                       pair_pos=torch.zeros(max(T * K, 1), dtype=torch.int32, device=dev))
+            self._plan_bufs[(T, K, dev)] = out
         po = PlanOut(*[out[k].data_ptr() for k in ("n_active", "active", "offset", "count", "pair_token", "pair_pos")])
         self._check(self.lib.pm_plan(self.layer.h, self._p(ids), T, C.byref(po)))
         return out["pair_token"][:T * K], out["pair_pos"][:T * K]
@@ -139,11 +143,11 @@ class ExpertParallelLayer:
         P = T * K
         pair_token, pair_pos = be.plan(ids)
         pos = pair_pos.long()
-        # per pair, in plan order: its expert and routing weight
-        pair_e = torch.empty(P, dtype=torch.int32, device=x.device)
-        pair_w = torch.empty(P, dtype=torch.float32, device=x.device)
-        pair_e[pos] = ids.reshape(-1)
-        pair_w[pos] = w.reshape(-1)
+        # per pair, in plan order: its expert and (the bits of) its routing weight, side by side
+        # so that they travel in one exchange
+        pair_ew = torch.empty((P, 2), dtype=torch.int32, device=x.device)
+        pair_ew[pos] = torch.stack((ids.reshape(-1).to(torch.int32), w.reshape(-1).view(torch.int32)), dim=1)
+        pair_e = pair_ew[:, 0]
         # plan order is ascending expert, so each destination's pairs are contiguous
         send_counts = torch.bincount(pair_e.long() // self.per_rank, minlength=W).to(torch.int64)
         if W > 1:
@@ -154,8 +158,9 @@ class ExpertParallelLayer:
         sc, rc = send_counts.tolist(), recv_counts.tolist()  # one small host read per layer call
         send_x = x.index_select(0, pair_token.long())
         recv_x = self._a2a(send_x, sc, rc)
-        recv_e = self._a2a(pair_e, sc, rc)
-        recv_w = self._a2a(pair_w, sc, rc)
+        recv_ew = self._a2a(pair_ew, sc, rc)
+        recv_e = recv_ew[:, 0].contiguous()
+        recv_w = recv_ew[:, 1].contiguous().view(torch.float32)
         lo = self.rank * self.per_rank
         if self.validate and recv_e.numel() and (int(recv_e.min()) < lo or int(recv_e.max()) >= lo + self.per_rank):
             raise RuntimeError(f"rank {self.rank}: received a pair for an expert outside [{lo}, {lo + self.per_rank})")
