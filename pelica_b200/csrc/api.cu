@@ -1332,6 +1332,18 @@ struct pm_stack {
   float *mega_io = nullptr;     // staged input / output token
   long long *mega_trace = nullptr;
   unsigned long long calls = 0;
+  // general path for a few tokens: the layer loop recorded once as a CUDA graph per token
+  // count and replayed (a decode step is a few hundred short launches: host-paced otherwise)
+  struct Graph {
+    int T;
+    uint8_t *ws;          // workspace the recorded kernels point into
+    float *gx;            // residual stream of the recorded loop
+    cudaGraphExec_t exec;
+    int64_t launches;
+  };
+  std::vector<Graph> graphs;
+  std::vector<int> seen_T;  // token counts the general path ran once already
+  bool graph_off = false;
 };
 
 static int32_t stack_setup_mega(pm_stack *s) {
@@ -1412,6 +1424,10 @@ extern "C" int32_t pm_stack_destroy(pm_stack *s) {
   if (!s) return PM_OK;
   cudaSetDevice(s->ctx->device);
   cudaStreamSynchronize(s->ctx->stream);
+  for (auto &g : s->graphs) {
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+    if (g.gx) cudaFree(g.gx);
+  }
   if (s->mega_layers) cudaFree(s->mega_layers);
   if (s->mega_buf) cudaFree(s->mega_buf);
   if (s->mega_io) cudaFree(s->mega_io);
@@ -1510,6 +1526,67 @@ extern "C" int32_t pm_stack_forward(pm_stack *s, const float *x, int32_t T, floa
     if (b > need) need = b;
   }
   TRY(ws_reserve(c, need + 3 * al(n * 4)));
+  // ---- a few tokens: replay the recorded loop ----
+  bool graphable = T <= 16 && !c->prof_on && !s->graph_off;
+  for (pm_layer *ly : s->layers) graphable = graphable && ly->dev.desc.shared == PM_SHARED_NONE;
+  if (graphable) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(c->stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      graphable = false;
+    }
+  }
+  if (graphable) {
+    pm_stack::Graph *g = nullptr;
+    for (auto &q : s->graphs)
+      if (q.T == T && q.ws == c->ws) g = &q;
+    bool seen = false;
+    for (int t : s->seen_T) seen = seen || t == T;
+    if (!g && seen) {  // second call with this token count: record
+      pm_stack::Graph q{T, c->ws, nullptr, nullptr, 0};
+      CU(cudaMalloc(&q.gx, n * 4));
+      float *xn = ws_take<float>(c, n);
+      size_t mark = c->ws_off;
+      int64_t l0 = c->launches;
+      cudaGraph_t graph = nullptr;
+      bool ok = cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+      int32_t rc = PM_OK;
+      if (ok) {
+        for (pm_layer *ly : s->layers) {
+          c->ws_off = mark;
+          Scratch S;
+          scratch_carve(c, ly->dev.desc, T, S);
+          launch_rmsnorm(c->launch(), q.gx, T, d, s->eps, xn);
+          rc = dev_forward(ly, xn, T, q.gx, true, S);
+          if (rc != PM_OK) break;
+        }
+        ok = cudaStreamEndCapture(c->stream, &graph) == cudaSuccess && rc == PM_OK && graph;
+      }
+      q.launches = c->launches - l0;
+      c->launches = l0;
+      if (ok) ok = cudaGraphInstantiate(&q.exec, graph, 0) == cudaSuccess;
+      if (graph) cudaGraphDestroy(graph);
+      if (ok) {
+        s->graphs.push_back(q);
+        g = &s->graphs.back();
+      } else {  // not recordable here: the plain loop from now on
+        cudaGetLastError();
+        cudaFree(q.gx);
+        s->graph_off = true;
+        c->ws_off = 0;
+      }
+    }
+    if (g) {
+      CU(cudaMemcpyAsync(g->gx, x, n * 4, cudaMemcpyDefault, c->stream));
+      CU(cudaGraphLaunch(g->exec, c->stream));
+      c->launches += g->launches;
+      CU(cudaMemcpyAsync(x_out, g->gx, n * 4, cudaMemcpyDefault, c->stream));
+      if (!is_device_ptr(x_out)) CU(cudaStreamSynchronize(c->stream));
+      return PM_OK;
+    }
+    if (!seen) s->seen_T.push_back(T);
+    c->ws_off = 0;
+  }
   // residual stream: in place in x_out when it is a device pointer
   float *xc = is_device_ptr(x_out) ? x_out : ws_take<float>(c, n);
   float *xn = ws_take<float>(c, n);

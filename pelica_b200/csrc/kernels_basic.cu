@@ -668,21 +668,39 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
     int nb = W.cols / 32;
     const uint8_t *nib = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * 16;
     const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * nb;
-    int w = lane & 3;
-    for (int b = lane >> 2; b < nb; b += 8) {
-      uint32_t qw = __ldg((const uint32_t *)(nib + (size_t)b * 16) + w);
-      float s = pm_e8(__ldg(scl + b));
-      const float4 x0 = *(const float4 *)(x + b * 32 + 4 * w);
-      const float4 x1 = *(const float4 *)(x + b * 32 + 16 + 4 * w);
+    // a lane takes whole blocks (16 bytes of codes, 32 activations): few, wide loads per row
+    for (int b = lane; b < nb; b += 32) {
+      const uint4 qv = __ldg((const uint4 *)(nib + (size_t)b * 16));
+      const float s = pm_e8(__ldg(scl + b));
+      const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+      const float4 *xp = (const float4 *)(x + b * 32);
+      // An E2M1 code (sign, 2 exponent bits, 1 mantissa bit) placed at bits 15, 10..9 of an f16 is
+      // that value times 2^-14 exactly (exponent 0 lands on the f16 subnormals 0 and 2^-15); the
+      // doubled table of the reference (src/moe_kernels.rs:109) is 2^15 times the f16. Two codes
+      // a word operation; the sums are exact products either way, only their order differs.
       float t = 0.0f;
-      t = __fmaf_rn(pm_e2m1(qw & 15), x0.x, t);
-      t = __fmaf_rn(pm_e2m1((qw >> 8) & 15), x0.y, t);
-      t = __fmaf_rn(pm_e2m1((qw >> 16) & 15), x0.z, t);
-      t = __fmaf_rn(pm_e2m1((qw >> 24) & 15), x0.w, t);
-      t = __fmaf_rn(pm_e2m1((qw >> 4) & 15), x1.x, t);
-      t = __fmaf_rn(pm_e2m1((qw >> 12) & 15), x1.y, t);
-      t = __fmaf_rn(pm_e2m1((qw >> 20) & 15), x1.z, t);
-      t = __fmaf_rn(pm_e2m1(qw >> 28), x1.w, t);
+#pragma unroll
+      for (int w = 0; w < 4; w++) {  // byte j of the block: value j (low nibble), value j + 16 (high)
+        const float4 x0 = xp[w], x1 = xp[4 + w];
+        const uint32_t q = qw[w];
+        const uint32_t ha = ((q << 9) & 0x0e000e00u) | ((q << 12) & 0x80008000u);   // bytes 0, 2 low
+        const uint32_t hb = ((q << 1) & 0x0e000e00u) | ((q << 4) & 0x80008000u);    // bytes 1, 3 low
+        const uint32_t hc = ((q << 5) & 0x0e000e00u) | ((q << 8) & 0x80008000u);    // bytes 0, 2 high
+        const uint32_t hd = ((q >> 3) & 0x0e000e00u) | (q & 0x80008000u);           // bytes 1, 3 high
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&ha));
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&hb));
+        const float2 fc = __half22float2(*reinterpret_cast<const __half2 *>(&hc));
+        const float2 fd = __half22float2(*reinterpret_cast<const __half2 *>(&hd));
+        t = __fmaf_rn(fa.x, x0.x, t);
+        t = __fmaf_rn(fb.x, x0.y, t);
+        t = __fmaf_rn(fa.y, x0.z, t);
+        t = __fmaf_rn(fb.y, x0.w, t);
+        t = __fmaf_rn(fc.x, x1.x, t);
+        t = __fmaf_rn(fd.x, x1.y, t);
+        t = __fmaf_rn(fc.y, x1.z, t);
+        t = __fmaf_rn(fd.y, x1.w, t);
+      }
+      t = __fmul_rn(t, 32768.0f);
       acc = __fmaf_rn(s, t, acc);
     }
   } else {
