@@ -487,11 +487,14 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
 
     // ---- 2. norm, Q8x of the normed token ----
     float inv = pm_rms_inv(xs, d, P.eps, red8);
-    if (warp < nbx) {
+    // block qb of x is quantised by a warp that does not share an issue scheduler (warp & 3)
+    // with the routing warp, which runs the layer's longest serial chain meanwhile
+    const int qb = (warp & 3) == 3 ? -1 : (warp >> 2) * 3 + (warp & 3);
+    if (qb >= 0 && qb < nbx) {
       float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = __fmul_rn(xs[warp * 256 + 32 * j + lane], inv);
-      q8x_block_warp(v, lane, xq + warp * 256, xd + warp, xbs + warp * 8, NB8 ? warp : 0);
+      for (int j = 0; j < 8; j++) v[j] = __fmul_rn(xs[qb * 256 + 32 * j + lane], inv);
+      q8x_block_warp(v, lane, xq + qb * 256, xd + qb, xbs + qb * 8, NB8 ? qb : 0);
     } else if (warp == MG_WARPS - 1) {
       // ---- 3. this CTA's router logit, then all logits, then the scores (one warp) ----
       float *r_pr = r_sv;                          // [E] score the weight comes from
