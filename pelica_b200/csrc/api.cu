@@ -1378,7 +1378,7 @@ static int32_t stack_setup_mega(pm_stack *s) {
   }
   CU(cudaMalloc(&s->mega_layers, L * sizeof(MegaLayer)));
   CU(cudaMemcpy(s->mega_layers, ml.data(), L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
-  size_t xb = al((size_t)D.d * 4), lb = al((size_t)D.n_exp * 4), hb = al((size_t)D.top_k * D.ff * 4);
+  size_t xb = al((size_t)D.d * 4), lb = al((size_t)D.n_exp * 8), hb = al((size_t)D.top_k * D.ff * 4);
   size_t total = xb + lb + hb + 512;
   CU(cudaMalloc(&s->mega_buf, total));
   CU(cudaMemset(s->mega_buf, 0, total));
@@ -1388,11 +1388,10 @@ static int32_t stack_setup_mega(pm_stack *s) {
   P.layers = s->mega_layers;
   P.eps = s->eps;
   P.xbuf = (float *)s->mega_buf;
-  P.lbuf = (float *)(s->mega_buf + xb);
+  P.lbuf = (unsigned long long *)(s->mega_buf + xb);
   P.hbuf = (float *)(s->mega_buf + xb + lb);
   P.hcount = (unsigned long long *)(s->mega_buf + xb + lb + hb);  // each counter on its own 128-byte line
   P.xcount = (unsigned long long *)(s->mega_buf + xb + lb + hb + 128);
-  P.lcount = (unsigned long long *)(s->mega_buf + xb + lb + hb + 256);
   P.err = (int *)(s->mega_buf + xb + lb + hb + 384);
   s->mega_ok = true;
   return PM_OK;
@@ -1491,7 +1490,7 @@ static int32_t stack_forward_mega(pm_stack *s, const float *x, float *x_out) {
   P.x_out = xo;
   P.hcount_base = (s->calls - 1) * (unsigned long long)L * (unsigned long long)s->mega.grid;
   P.xcount_base = (s->calls - 1) * (unsigned long long)(L - 1) * (unsigned long long)s->mega.grid;
-  P.lcount_base = (s->calls - 1) * (unsigned long long)L * (unsigned long long)P.D.n_exp;
+  P.lepoch_base = (uint32_t)((s->calls - 1) * (unsigned long long)L);
   {
     PROF(c, PH_FUSED);
     CU(mega_launch(s->mega, c->stream));

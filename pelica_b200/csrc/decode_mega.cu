@@ -9,7 +9,9 @@
 //      per word keeps the few L2 lines of the exchange from becoming a hot spot),
 //   2. norms it and quantises it to Q8x (`Q8x::new`, src/ds4_cpu.rs:13-35),
 //   3. computes "its" router logit in `dot_f32` order (src/quant.rs:215-236) and
-//      publishes it; collects all logits; picks the top-k (route.cuh),
+//      publishes it as one 64-bit word (layer epoch, float bits) with a relaxed store;
+//      the routing warp polls all E words until they carry the epoch; picks the top-k
+//      (route.cuh),
 //   4. issues bulk async copies (cp.async.bulk + mbarrier) of ITS slice of the
 //      chosen experts' gate/up rows and down rows into shared memory: the whole
 //      layer's 24.5 MB is spread over the SMs' shared memories, so HBM streams
@@ -63,6 +65,14 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
   unsigned long long u;
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(u) : "l"(p) : "memory");
   return u;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long *p) {
+  unsigned long long u;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(u) : "l"(p) : "memory");
+  return u;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ void red_release_add_u64(unsigned long long *p, unsigned long long v) {
   asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -472,6 +482,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   for (; l < P.n_layers; l++) {
     const MegaLayer &ML = mls[l & 1];
     const uint32_t par = l & 1;
+    const uint32_t lepoch = P.lepoch_base + (uint32_t)l + 1u;  // never repeats within 2^32 layers
     MG_TRACE(0);
     if (l + 1 < P.n_layers && tid >= 64 && tid < 64 + (int)(sizeof(MegaLayer) / 8))
       ((unsigned long long *)&mls[(l + 1) & 1])[tid - 64] = ((const unsigned long long *)&P.layers[l + 1])[tid - 64];
@@ -511,8 +522,9 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           float sdot = pm_warp_sum_dot(acc);
           if (lane == 0) {
             if (ML.logit_bias) sdot = __fadd_rn(sdot, ML.logit_bias[cta]);
-            __stcg(P.lbuf + cta, sdot);
-            red_release_add_u64(P.lcount, 1ull);
+            // the logit and the layer's epoch travel in one 64-bit word: a single store,
+            // no release (and its half microsecond) before it, nothing else to order
+            st_relaxed_u64(P.lbuf + cta, ((unsigned long long)lepoch << 32) | (unsigned long long)__float_as_uint(sdot));
           }
           __syncwarp();
           if (lane == 0 && l + 1 < P.n_layers) {  // next layer's row into the same buffer
@@ -521,9 +533,36 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           }
         }
         MG_TRACE_R(13);
-        if (lane == 0 && !wait_count(P.lcount, P.lcount_base + (unsigned long long)(l + 1) * (unsigned long long)E, P.err, 2)) dead = true;
-        __syncwarp();
-        for (int e0 = lane; e0 < E; e0 += 32) lg[e0] = __ldcg(P.lbuf + e0);
+        {
+          // every lane polls its own words until all of them carry this layer's epoch:
+          // one round trip after the last arrival (a counter first and the values after
+          // it were two); 32 x NP loads a CTA a round
+          bool ok = false;
+          unsigned long long t0 = 0;
+          for (uint32_t it = 0;; it++) {
+            bool all = true;
+#pragma unroll
+            for (int i = 0; i < NP; i++) {
+              int e0 = lane + 32 * i;
+              if (e0 < E) {
+                unsigned long long w = ld_relaxed_u64(P.lbuf + e0);
+                if ((uint32_t)(w >> 32) == lepoch) lg[e0] = __uint_as_float((uint32_t)w);
+                else all = false;
+              }
+            }
+            if (__all_sync(PM_FULL, all)) { ok = true; break; }
+            if ((it & 63) == 63) {
+              unsigned long long t = now_ns();
+              if (t0 == 0) t0 = t;
+              bool stop = ld_volatile_i32(P.err) != 0 || t - t0 > MG_WAIT_NS;
+              if (__any_sync(PM_FULL, stop)) break;
+            }
+          }
+          if (!ok) {
+            if (lane == 0) atomicCAS(P.err, 0, 2);
+            dead = true;
+          }
+        }
         __syncwarp();
         MG_TRACE_R(14);
         {

@@ -25,13 +25,13 @@ struct MegaParams {
   float *x_out;
   float eps;
   float *xbuf;               // [d]      the residual stream between layers
-  float *lbuf;               // [E]      the layer's router logits
+  unsigned long long *lbuf;  // [E]      the layer's router logits: (epoch << 32) | float bits
   float *hbuf;               // [K*ff]
   // arrival counters (never reset: each call waits for base + its own arrivals):
   unsigned long long *hcount;  // CTAs that finished their h rows
   unsigned long long *xcount;  // CTAs that published their slice of the next layer's residual stream
-  unsigned long long *lcount;  // logits published
-  unsigned long long hcount_base, xcount_base, lcount_base;
+  unsigned long long hcount_base, xcount_base;
+  uint32_t lepoch_base;  // epochs before this call: (calls - 1) * layers
   int *err;
   long long *trace;  // optional [2][n_layers][MG_TRACE_PH] SM clocks (CTA 0 and the last CTA)
   // shared-memory layout (bytes from the dynamic base)
