@@ -712,8 +712,16 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     }
     MG_TRACE(11);
     if (__syncthreads_or(dead)) { dead = true; break; }
-    if (tid >= 32) issue_job();  // the down slices (job threads 32 .. 32 + 4K)
-    if (tid == 0) red_release_add_u64(P.hcount, 1ull);
+    // h is published first, the down slices (job threads 32 .. 32 + 4K: warps 1 and 2) are
+    // issued after it: with 70 KB of bulk copies in flight the release took three times as long
+    if (warp == 0) {
+      if (tid == 0) red_release_add_u64(P.hcount, 1ull);
+      __syncwarp();
+      asm volatile("bar.arrive 3, 96;" ::: "memory");
+    } else if (warp <= 2) {
+      asm volatile("bar.sync 3, 96;" ::: "memory");
+      issue_job();
+    }
     MG_TRACE(4);
 
     // ---- 6. all of h, re-quantised ----
