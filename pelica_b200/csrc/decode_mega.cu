@@ -609,7 +609,29 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
         if (q == 0 && e < E && rank < K) { sel_e[rank] = (uint32_t)e; sel_p[rank] = r_pr[e]; }
       }
     }
+    // ---- 4. bulk copies of this CTA's slices: gate/up now, down once gate/up has landed
+    // (the gate/up bytes are needed first and should not share HBM with bytes needed later) ----
+    auto issue_job = [&]() {
+      if (job_tx) mbar_expect_tx(&bar_gu[job_bar], (uint32_t)(job_tx - 1));  // bar_dn follows bar_gu in memory
+      if (job_bytes > 0) {
+        // gate/up jobs go out before `ids` is written: they read the ranking's own list
+        int el = (int)(job_plane < 2 ? ((const uint32_t *)(r_sv + 336))[job_k] : ids[job_k]);
+        const uint8_t *src;
+        uint8_t *dst;
+        if (job_plane == 0) { src = ML.gate + (size_t)el * ML.gate_stride; dst = gs; }
+        else if (job_plane == 1) { src = ML.up + (size_t)el * ML.up_stride; dst = us; }
+        else {
+          int p = job_plane - 2;
+          src = ML.down[p] + (size_t)el * ML.down_stride[p];
+          dst = p == 3 ? dsm : dn;
+        }
+        bulk_g2s(dst + job_dst, src + job_off, (uint32_t)job_bytes, &bar_gu[job_bar]);
+      }
+    };
     __syncthreads();
+    // the experts are known: the gate/up copies leave now, the weights follow meanwhile
+    if (tid < MG_GU_CHUNKS * 4) issue_job();
+    copies_pending = true;
     if (warp == MG_WARPS - 1) {
       const float *sel_p = r_sv + 320;
       const uint32_t *sel_e = (const uint32_t *)(r_sv + 336);
@@ -625,26 +647,6 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     if (__syncthreads_or(dead)) { dead = true; break; }
     MG_TRACE(2);
 
-    // ---- 4. bulk copies of this CTA's slices: gate/up now, down once gate/up has landed
-    // (the gate/up bytes are needed first and should not share HBM with bytes needed later) ----
-    auto issue_job = [&]() {
-      if (job_tx) mbar_expect_tx(&bar_gu[job_bar], (uint32_t)(job_tx - 1));  // bar_dn follows bar_gu in memory
-      if (job_bytes > 0) {
-        int el = (int)ids[job_k];
-        const uint8_t *src;
-        uint8_t *dst;
-        if (job_plane == 0) { src = ML.gate + (size_t)el * ML.gate_stride; dst = gs; }
-        else if (job_plane == 1) { src = ML.up + (size_t)el * ML.up_stride; dst = us; }
-        else {
-          int p = job_plane - 2;
-          src = ML.down[p] + (size_t)el * ML.down_stride[p];
-          dst = p == 3 ? dsm : dn;
-        }
-        bulk_g2s(dst + job_dst, src + job_off, (uint32_t)job_bytes, &bar_gu[job_bar]);
-      }
-    };
-    if (tid < MG_GU_CHUNKS * 4) issue_job();
-    copies_pending = true;
     MG_TRACE(3);
 
     // ---- 5. gate/up rows -> h ----
