@@ -590,7 +590,23 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       for (int e0 = 0; e0 < E; e0 += MG_NT / 4) {
         int e = e0 + (tid >> 2);
         int rank = 0, rank2 = 0;
-        if (e < E) {
+        if (e < E && (fq & 7) == 0 && E == 4 * fq && r_key[e] != 0u) {
+          // "before e" is k_f >= ke for f < e and k_f > ke for f > e: one compare against
+          // ke - 1 or ke (ke != 0), the keys read eight at a time
+          const uint32_t ke = r_key[e], kem1 = ke - 1u;
+          const int fa = q * fq, nlo = e - fa;  // keys j < nlo of this quarter lie below e
+          for (int j = 0; j < fq; j += 8) {
+            const uint4 a = *(const uint4 *)(r_key + fa + j), b = *(const uint4 *)(r_key + fa + j + 4);
+            rank += a.x > (j + 0 < nlo ? kem1 : ke);
+            rank2 += a.y > (j + 1 < nlo ? kem1 : ke);
+            rank += a.z > (j + 2 < nlo ? kem1 : ke);
+            rank2 += a.w > (j + 3 < nlo ? kem1 : ke);
+            rank += b.x > (j + 4 < nlo ? kem1 : ke);
+            rank2 += b.y > (j + 5 < nlo ? kem1 : ke);
+            rank += b.z > (j + 6 < nlo ? kem1 : ke);
+            rank2 += b.w > (j + 7 < nlo ? kem1 : ke);
+          }
+        } else if (e < E) {
           uint32_t ke = r_key[e];
           int fa = q * fq, fb = min(E, fa + fq);
           for (int f = fa; f + 1 < fb; f += 2) {
