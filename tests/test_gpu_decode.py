@@ -39,6 +39,39 @@ def test_decode_kernel_small_shapes(ctx, oracle, name, n_layers):
         g.close()
 
 
+@pytest.mark.parametrize("n_exp", [24, 128])
+def test_decode_kernel_equal_logits_pick_lowest_indices(ctx, oracle, n_exp):
+    """Ties: rows of the router repeated (and all-zero rows) make logits equal bit for bit;
+    the pick must then go by ascending expert index, as K rounds of (max, lowest index) do.
+    128 experts take the ranking's eight-keys-at-a-time path, 24 the general one."""
+    cfg = synth.C2_QWEN3.scaled(d=512, ff=256, n_exp=n_exp)
+    ols, gls = [], []
+    for l in range(3):
+        W = synth.make_weights(cfg, 300 + l)
+        r = W["router"]
+        if l == 0:
+            r[:] = 0.0                      # every logit equal: experts 0..K-1
+        elif l == 1:
+            r[1::2] = r[0::2]               # pairs of equal logits
+        else:
+            r[n_exp // 2:] = r[: n_exp // 2]  # equal logits a quarter boundary apart
+        ols.append(oracle.Layer(oracle.LayerDesc(**cfg.desc_fields()), W))
+        gls.append(pb.MoeLayer(ctx, cfg).load(W))
+    st = pb.Stack(ctx, gls)
+    assert st.decode_kernel
+    for i in range(3):
+        x = np.random.default_rng(40 + i).normal(0, 1, (1, cfg.d)).astype(np.float32)
+        want = oracle.stack_forward(ols, 1e-6, x)
+        assert bits_equal(st.forward(x), want), i
+        st.set_mode(True)
+        assert bits_equal(st.forward(x), want)
+        st.set_mode(False)
+    st.status()
+    st.close()
+    for g in gls:
+        g.close()
+
+
 @pytest.mark.parametrize("key", ["c2", "c1"])
 def test_decode_kernel_full_shape(ctx, oracle, key):
     """Full layer shapes (Qwen3-30B-A3B: d 2048, 128 experts, ff 768, Q4_K/Q6_K;
