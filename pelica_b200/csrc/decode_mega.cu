@@ -595,7 +595,11 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           // ke - 1 or ke (ke != 0), the keys read eight at a time
           const uint32_t ke = r_key[e], kem1 = ke - 1u;
           const int fa = q * fq, nlo = e - fa;  // keys j < nlo of this quarter lie below e
-          for (int j = 0; j < fq; j += 8) {
+          // the four quarters of an expert start eight keys apart: their 32-byte reads would
+          // otherwise fall on the same banks (quarters are fq words apart) four ways
+          const int jrot = (8 * q) % fq;
+          for (int j0 = 0; j0 < fq; j0 += 8) {
+            const int j = j0 + jrot < fq ? j0 + jrot : j0 + jrot - fq;
             const uint4 a = *(const uint4 *)(r_key + fa + j), b = *(const uint4 *)(r_key + fa + j + 4);
             rank += a.x > (j + 0 < nlo ? kem1 : ke);
             rank2 += a.y > (j + 1 < nlo ? kem1 : ke);
