@@ -141,8 +141,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
 // (`Q8x::new`, src/ds4_cpu.rs:13-35); writes q, d, bsum of the block
 // `swz`: 16-byte chunk c of the block is stored at chunk c ^ swz (so that lanes
 // reading the same chunk of 8 different blocks hit different banks)
+// `fold8`: chunks 8-15 additionally swap their halves (c ^ 4), for the Q6_K down units, whose
+// lanes read chunks {0-3, 8-11} (then {4-7, 12-15}) at once: banks 0-15 twice without it
 __device__ __noinline__ void q8x_block_warp(const float v[8], int lane, int8_t *q, float *d,
-                                               int32_t *bsum, int swz = 0) {
+                                               int32_t *bsum, int swz = 0, bool fold8 = false) {
   float a = 0.0f;
 #pragma unroll
   for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
@@ -155,7 +157,8 @@ __device__ __noinline__ void q8x_block_warp(const float v[8], int lane, int8_t *
       float f = roundf(__fmul_rn(v[j], id));
       r = (int)fminf(fmaxf(f, -127.0f), 127.0f);
     }
-    q[(((2 * j + (lane >> 4)) ^ swz) << 4) + (lane & 15)] = (int8_t)r;
+    const int c = 2 * j + (lane >> 4);
+    q[(((c ^ swz) ^ (fold8 ? (c & 8) >> 1 : 0)) << 4) + (lane & 15)] = (int8_t)r;
     int s = __reduce_add_sync(PM_FULL, r);
     if (lane == 0) bsum[j] = s;
   }
@@ -478,6 +481,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
   bool dead = false;
   bool copies_pending = false;
   const bool fold = D.weight_fold == PM_FOLD_BEFORE_DOWN;
+  const bool h_fold8 = dq6 && ndown * nbh <= PM_MAX_EXPERTS;  // the Q6_K down phase works in (row, block) units
   int l = 0;
   for (; l < P.n_layers; l++) {
     const MegaLayer &ML = mls[l & 1];
@@ -768,14 +772,14 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
 #pragma unroll
         for (int j = 0; j < 8; j++) v1[j] = __ldcg(P.hbuf + b1 * 256 + 32 * j + lane);
       }
-      q8x_block_warp(v0, lane, hq + b0 * 256, hd + b0, hbs + b0 * 8);
-      if (b1 < K * nbh) q8x_block_warp(v1, lane, hq + b1 * 256, hd + b1, hbs + b1 * 8);
+      q8x_block_warp(v0, lane, hq + b0 * 256, hd + b0, hbs + b0 * 8, 0, h_fold8);
+      if (b1 < K * nbh) q8x_block_warp(v1, lane, hq + b1 * 256, hd + b1, hbs + b1 * 8, 0, h_fold8);
     }
     __syncthreads();
     MG_TRACE(6);
 
     // ---- 7. down rows of this CTA's columns, all k; sum in k order; publish ----
-    if (dq6 && ndown * nbh <= PM_MAX_EXPERTS) {
+    if (h_fold8) {
       // One (row, block) unit per lane: 256 six-bit values against the block of h, no
       // cross-lane traffic. isum = sum_c sc[c] * (q_c . h_c - 32 * sum(h_c)) over the 16
       // chunks c of 16 values (the integer sum of `row_q6k_q8x`, regrouped). Lanes walk the
@@ -797,7 +801,8 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           const uint4 qlv = *(const uint4 *)(qlp + pp * 16);
           const uint4 qhv = *(const uint4 *)(qhp + (2 * n + g) * 16);
           const int clo = 8 * n + 2 * jj + g, chi = clo + 4;  // chunks of the low / high nibbles
-          const int4 xlo = *(const int4 *)(xb + clo * 16), xhi = *(const int4 *)(xb + chi * 16);
+          // h's chunks 8-15 are stored with their halves swapped (`fold8`)
+          const int4 xlo = *(const int4 *)(xb + (clo + 4 * n) * 16), xhi = *(const int4 *)(xb + (chi - 4 * n) * 16);
           const int sh = 2 * jj;
           const uint32_t qlw[4] = {qlv.x, qlv.y, qlv.z, qlv.w}, qhw[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
           const int xl[4] = {xlo.x, xlo.y, xlo.z, xlo.w}, xh[4] = {xhi.x, xhi.y, xhi.z, xhi.w};
