@@ -797,7 +797,11 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
         int isum = 0;
 #pragma unroll
         for (int p = 0; p < 8; p++) {
-          const int pp = (p + lane) & 7, n = pp >> 2, jj = (pp >> 1) & 1, g = pp & 1;
+          // piece order per lane: a rotation of a permutation (bits 0 and 1 of the lane
+          // swapped) under which lanes 128 bytes apart in the 64-byte-a-unit qh plane, i.e.
+          // lanes of equal parity, take four different qh pieces
+          const int pl = (lane & 4) | ((lane & 1) << 1) | ((lane >> 1) & 1);
+          const int pp = (p + pl) & 7, n = pp >> 2, jj = (pp >> 1) & 1, g = pp & 1;
           const uint4 qlv = *(const uint4 *)(qlp + pp * 16);
           const uint4 qhv = *(const uint4 *)(qhp + (2 * n + g) * 16);
           const int clo = 8 * n + 2 * jj + g, chi = clo + 4;  // chunks of the low / high nibbles
