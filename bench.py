@@ -179,7 +179,7 @@ def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
 
 
 # (102,226,176 + 3,290,880) bytes over the 4 layers of the captured launch
-NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102228224 + 3646464) // 4
+NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102217472 + 3546112) // 4
 
 
 class ClockSampler:
