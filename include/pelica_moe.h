@@ -169,20 +169,6 @@ PM_API int32_t pm_sync(pm_ctx *ctx);
 PM_API int32_t pm_ctx_set_tensor_core_min_tokens(pm_ctx *ctx, int32_t min_tokens);
 /* the CUDA stream all work of this context is ordered on (cudaStream_t) */
 PM_API void *pm_ctx_stream(pm_ctx *ctx);
-/* kernels launched by this context since creation (bench bookkeeping) */
-PM_API int64_t pm_ctx_launch_count(pm_ctx *ctx);
-/* device-timed interval on the context's stream, in milliseconds */
-PM_API int32_t pm_timer_start(pm_ctx *ctx);
-PM_API int32_t pm_timer_stop(pm_ctx *ctx, float *ms);
-/* writes a buffer larger than L2 (evicts cached weights between timed runs) */
-PM_API int32_t pm_flush_l2(pm_ctx *ctx);
-/* per-phase device timing (CUDA events around each phase of the operator):
- * enable, run, then read milliseconds and span counts per phase; phase names
- * by index below pm_profile_phases(). Costs two event records per phase. */
-PM_API int32_t pm_profile_enable(pm_ctx *ctx, int32_t on);
-PM_API int32_t pm_profile_phases(void);
-PM_API const char *pm_profile_phase_name(int32_t i);
-PM_API int32_t pm_profile_read(pm_ctx *ctx, float *ms, int64_t *spans);
 /* pinned host memory for activations that cross the bus every call */
 PM_API int32_t pm_host_alloc(pm_ctx *ctx, size_t bytes, void **out);
 PM_API int32_t pm_host_free(pm_ctx *ctx, void *p);
@@ -299,17 +285,13 @@ PM_API int32_t pm_stack_forward(pm_stack *stack, const float *x, int32_t T, floa
 /* mode 0 (default): one-token calls run in the persistent decode kernel when
  * the stack's shape allows it; mode 1: the general kernels always. Both give
  * the same bits. With device pointers a failed bounded wait of the decode
- * kernel is reported by pm_stack_status. */
+ * kernel is reported by pm_stack_status. A layer whose weights are (re)loaded after the stack
+ * was created is picked up by the next pm_stack_forward. */
 PM_API int32_t pm_stack_set_mode(pm_stack *stack, int32_t mode);
 PM_API int32_t pm_stack_decode_kernel_available(pm_stack *stack);
 /* PM_OK, or PM_ERR_TIMEOUT when a device-side wait of an earlier call gave up
  * (synchronises the context's stream) */
 PM_API int32_t pm_stack_status(pm_stack *stack);
-/* phase trace of the decode kernel (development aid): called with out == NULL
- * it switches tracing on and returns the number of int64 entries; called with a
- * buffer it copies the last call's SM-clock stamps: [2 CTAs][layers][8 phases]. */
-PM_API int32_t pm_stack_trace(pm_stack *stack, int64_t *out, int32_t capacity);
-
 /* ---- synthetic weights generated on the device (benchmark set-up) ------ */
 /* fills every expert (and the router, biases, shared expert) of `layer` with
  * N(0, sigma) weights quantised to the layer's types by on-device encoders;

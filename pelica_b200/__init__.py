@@ -66,14 +66,6 @@ ABI = {
     "pm_sync": (C.c_int32, [_VP]),
     "pm_ctx_set_tensor_core_min_tokens": (C.c_int32, [_VP, C.c_int32]),
     "pm_ctx_stream": (_VP, [_VP]),
-    "pm_ctx_launch_count": (C.c_int64, [_VP]),
-    "pm_timer_start": (C.c_int32, [_VP]),
-    "pm_timer_stop": (C.c_int32, [_VP, C.POINTER(C.c_float)]),
-    "pm_flush_l2": (C.c_int32, [_VP]),
-    "pm_profile_enable": (C.c_int32, [_VP, C.c_int32]),
-    "pm_profile_phases": (C.c_int32, []),
-    "pm_profile_phase_name": (C.c_char_p, [C.c_int32]),
-    "pm_profile_read": (C.c_int32, [_VP, _VP, _VP]),
     "pm_host_alloc": (C.c_int32, [_VP, C.c_size_t, C.POINTER(_VP)]),
     "pm_host_free": (C.c_int32, [_VP, _VP]),
     "pm_dev_alloc": (C.c_int32, [_VP, C.c_size_t, C.POINTER(_VP)]),
@@ -104,12 +96,30 @@ ABI = {
     "pm_stack_set_mode": (C.c_int32, [_VP, C.c_int32]),
     "pm_stack_decode_kernel_available": (C.c_int32, [_VP]),
     "pm_stack_status": (C.c_int32, [_VP]),
-    "pm_stack_trace": (C.c_int32, [_VP, _VP, C.c_int32]),
     "pm_layer_fill_synthetic": (C.c_int32, [_VP, C.c_uint64, C.c_float, C.c_float, C.c_float]),
     "pm_layer_get_expert_bias": (C.c_int32, [_VP, C.c_int32, _VP, _VP, _VP]),
     "pm_layer_get_expert": (C.c_int32, [_VP, C.c_int32, C.c_int32, _VP]),
     "pm_layer_get_router": (C.c_int32, [_VP, _VP, _VP, _VP]),
 }
+
+# measurement and test hooks (include/pelica_moe_diag.h)
+ABI_DIAG = {
+    "pm_ctx_launch_count": (C.c_int64, [_VP]),
+    "pm_ctx_path_counts": (C.c_int32, [_VP, _VP]),
+    "pm_timer_start": (C.c_int32, [_VP]),
+    "pm_timer_stop": (C.c_int32, [_VP, C.POINTER(C.c_float)]),
+    "pm_flush_l2": (C.c_int32, [_VP]),
+    "pm_profile_enable": (C.c_int32, [_VP, C.c_int32]),
+    "pm_profile_phases": (C.c_int32, []),
+    "pm_profile_phase_name": (C.c_char_p, [C.c_int32]),
+    "pm_profile_read": (C.c_int32, [_VP, _VP, _VP]),
+    "pm_stack_trace": (C.c_int32, [_VP, _VP, C.c_int32]),
+    "pm_debug_set_wait_limit_ns": (C.c_int32, [_VP, C.c_uint64]),
+    "pm_debug_stack_fault_next_call": (C.c_int32, [_VP]),
+    "pm_debug_tc_fault_block": (C.c_int32, [_VP, C.c_int32]),
+    "pm_debug_device_free_bytes": (C.c_int32, [_VP, C.POINTER(C.c_uint64)]),
+}
+PATHS = ("general", "tensor", "decode", "multi")
 
 _lib = None
 
@@ -122,7 +132,7 @@ def load_library() -> C.CDLL:
             raise PelicaError(-5, f"{LIB_PATH} is missing: run `python -m pelica_b200.build` "
                                   "(there is no CPU fallback)")
         lib = C.CDLL(LIB_PATH)
-        for name, (res, args) in ABI.items():
+        for name, (res, args) in {**ABI, **ABI_DIAG}.items():
             fn = getattr(lib, name)  # AttributeError = a declared symbol is not exported
             fn.restype = res
             fn.argtypes = args
@@ -208,6 +218,25 @@ class Context:
     @property
     def launches(self) -> int:
         return self.lib.pm_ctx_launch_count(self.h)
+
+    def path_counts(self) -> dict:
+        """Launches of the expert-product kernels per family since the context was created."""
+        out = np.zeros(len(PATHS), np.int64)
+        _check(self.lib.pm_ctx_path_counts(self.h, out.ctypes.data))
+        return dict(zip(PATHS, (int(v) for v in out)))
+
+    def set_wait_limit_ns(self, ns: int):
+        """Test hook: the time limit of every bounded device-side wait (default 2 s)."""
+        _check(self.lib.pm_debug_set_wait_limit_ns(self.h, ns))
+
+    def tc_fault_block(self, block: int):
+        """Test hook: tensor-core kernels stop issuing products at this block (-1 = off)."""
+        _check(self.lib.pm_debug_tc_fault_block(self.h, block))
+
+    def device_free_bytes(self) -> int:
+        v = C.c_uint64()
+        _check(self.lib.pm_debug_device_free_bytes(self.h, C.byref(v)))
+        return v.value
 
     def timer_start(self):
         _check(self.lib.pm_timer_start(self.h))
@@ -328,9 +357,10 @@ class MoeLayer:
         _check(self.lib.pm_layer_get_expert(self.h, e, which, out.ctypes.data))
         return out
 
-    def get_weights(self) -> dict:
+    def get_weights(self, dense: bool = True) -> dict:
         """Everything back as the dict `load` takes (used to hand device-generated
-        weights to a checker)."""
+        weights to a checker). dense=False: per-expert lists in which experts this context
+        does not hold are one shared empty array (a shard of a large layer stays small)."""
         D = self.desc
         router = np.empty((D.n_exp, D.d), np.float32)
         lb = np.zeros(D.n_exp, np.float32)
@@ -346,7 +376,11 @@ class MoeLayer:
         for which, key in enumerate(("gate", "up", "down")):
             rows = [self.get_expert(e, which) if first <= e < first + n else None for e in range(D.n_exp)]
             size = next(r.size for r in rows if r is not None)
-            w[key] = np.stack([r if r is not None else np.zeros(size, np.uint8) for r in rows])
+            if dense:
+                w[key] = np.stack([r if r is not None else np.zeros(size, np.uint8) for r in rows])
+            else:
+                none = np.zeros(16, np.uint8)
+                w[key] = [r if r is not None else none for r in rows]
         if D.has_expert_bias:
             bg = np.zeros((D.n_exp, D.ff), np.float32)
             bu = np.zeros((D.n_exp, D.ff), np.float32)
@@ -490,6 +524,10 @@ class Stack:
 
     def status(self):
         _check(self.lib.pm_stack_status(self.h))
+
+    def fault_next_call(self):
+        """Test hook: the next decode-kernel call waits for an arrival that never comes."""
+        _check(self.lib.pm_debug_stack_fault_next_call(self.h))
 
     def trace(self, enable: bool = False):
         """Decode-kernel phase stamps (SM clocks) of the last call: array [2, layers, 8]."""

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "decode_mega.cuh"
+#include "../../include/pelica_moe_diag.h"
 
 void launch_synth_blocks(const Launch &L, int type, uint8_t *raw, size_t nb, uint64_t seed,
                          float sigma);
@@ -81,6 +82,9 @@ struct pm_ctx {
   int *dev_err = nullptr;   // error word of kernels with bounded waits
   int tc_min_tokens = 32;   // tensor-core expert products from this many tokens (the reference's TC_MIN, src/moe.rs:35); 0 = never
   int64_t launches = 0;
+  int64_t path_count[PM_PATH_N] = {0, 0, 0, 0};  // launches per expert-product path (pelica_moe_diag.h)
+  unsigned long long wait_ns = 2000000000ull;    // limit of every bounded device-side wait
+  int tc_fault_block = -1;                       // test hook: the tensor-core kernel never completes this block
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // workspace: one region, carved per call
   uint8_t *ws = nullptr;
@@ -234,6 +238,9 @@ static int32_t check_dev_err(pm_ctx *c) {
   CU(cudaMemcpy(&e, c->dev_err, 4, cudaMemcpyDeviceToHost));
   if (e) {
     CU(cudaMemset(c->dev_err, 0, 4));
+    if (e == PM_DEVERR_BAD_EXPERT_ID)
+      return fail(PM_ERR_INVALID, "an expert id in a device buffer is outside the layer's experts "
+                                  "(its pairs were left out; nothing was read or written out of bounds)");
     return fail(PM_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", e);
   }
   return PM_OK;
@@ -252,6 +259,29 @@ extern "C" int32_t pm_ctx_set_tensor_core_min_tokens(pm_ctx *c, int32_t min_toke
 extern "C" int32_t pm_stack_destroy(pm_stack *s);
 extern "C" void *pm_ctx_stream(pm_ctx *c) { return c ? (void *)c->stream : nullptr; }
 extern "C" int64_t pm_ctx_launch_count(pm_ctx *c) { return c ? c->launches : 0; }
+extern "C" int32_t pm_ctx_path_counts(pm_ctx *c, int64_t *out) {
+  if (!c || !out) return fail(PM_ERR_INVALID, "pm_ctx_path_counts: null argument");
+  for (int i = 0; i < PM_PATH_N; i++) out[i] = c->path_count[i];
+  return PM_OK;
+}
+extern "C" int32_t pm_debug_set_wait_limit_ns(pm_ctx *c, uint64_t ns) {
+  if (!c || ns == 0) return fail(PM_ERR_INVALID, "pm_debug_set_wait_limit_ns");
+  c->wait_ns = ns;
+  return PM_OK;
+}
+extern "C" int32_t pm_debug_device_free_bytes(pm_ctx *c, uint64_t *out) {
+  if (!c || !out) return fail(PM_ERR_INVALID, "pm_debug_device_free_bytes");
+  CU(cudaSetDevice(c->device));
+  size_t fr = 0, tot = 0;
+  CU(cudaMemGetInfo(&fr, &tot));
+  *out = (uint64_t)fr;
+  return PM_OK;
+}
+extern "C" int32_t pm_debug_tc_fault_block(pm_ctx *c, int32_t block) {
+  if (!c) return fail(PM_ERR_INVALID, "pm_debug_tc_fault_block");
+  c->tc_fault_block = block;
+  return PM_OK;
+}
 
 extern "C" int32_t pm_timer_start(pm_ctx *c) {
   CU(cudaEventRecord(c->ev0, c->stream));
@@ -333,6 +363,7 @@ struct pm_layer {
   std::vector<void *> owned;
   std::vector<uint8_t> expert_set;
   bool router_set = false, shared_set = false;
+  uint64_t gen = 0;  // bumped by every call that may change a device pointer or a weight (stacks re-snapshot)
   float *router_w = nullptr, *logit_bias = nullptr, *select_bias = nullptr;
   float *bias_gate = nullptr, *bias_up = nullptr, *bias_down = nullptr, *gate_inp = nullptr;
 };
@@ -503,6 +534,7 @@ extern "C" int32_t pm_layer_set_router(pm_layer *ly, const void *w, int32_t dtyp
   }
   CU(cudaStreamSynchronize(c->stream));
   ly->router_set = true;
+  ly->gen++;
   return PM_OK;
 }
 
@@ -550,6 +582,7 @@ extern "C" int32_t pm_layer_set_expert(pm_layer *ly, int32_t e, const uint8_t *g
     CU(cudaStreamSynchronize(s));
   }
   ly->expert_set[(size_t)el] = 1;
+  ly->gen++;
   return PM_OK;
 }
 
@@ -570,6 +603,7 @@ extern "C" int32_t pm_layer_set_shared(pm_layer *ly, const uint8_t *gate, const 
     dv.shared_gate_inp = ly->gate_inp;
   }
   ly->shared_set = true;
+  ly->gen++;
   return PM_OK;
 }
 
@@ -710,6 +744,7 @@ extern "C" int32_t pm_layer_fill_synthetic(pm_layer *ly, uint64_t seed, float si
   CU(cudaStreamSynchronize(c->stream));
   ly->router_set = true;
   std::fill(ly->expert_set.begin(), ly->expert_set.end(), 1);
+  ly->gen++;
   return PM_OK;
 }
 
@@ -822,19 +857,25 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   {
     PROF(c, PH_GATEUP);
-    if (tc && D.type_gate == D.type_up)
-      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.xq, S.xd, S.xbm, S.xs, w, S.h, c->dev_err));
-    else
+    if (tc && D.type_gate == D.type_up) {
+      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.xq, S.xd, S.xbm, S.xs, w, S.h, c->dev_err, c->wait_ns, c->tc_fault_block));
+      c->path_count[PM_PATH_TENSOR]++;
+    } else {
       launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
+      c->path_count[PM_PATH_GENERAL]++;
+    }
   }
   if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum, S.hbm, S.hs); }
   if (q32) { PROF(c, PH_QUANT_H); launch_quant_q8_32(L, S.h, (size_t)P, D.ff, S.hq, S.hd); }
   {
     PROF(c, PH_DOWN);
-    if (tc)
-      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.hq, S.hd, S.hbm, S.hs, nullptr, S.eo, c->dev_err));
-    else
+    if (tc) {
+      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.hq, S.hd, S.hbm, S.hs, nullptr, S.eo, c->dev_err, c->wait_ns, c->tc_fault_block));
+      c->path_count[PM_PATH_TENSOR]++;
+    } else {
       launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo);
+      c->path_count[PM_PATH_GENERAL]++;
+    }
   }
   CU(cudaGetLastError());
   return PM_OK;
@@ -868,13 +909,13 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   if (q32) launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   if (use_tc && D.type_gate == D.type_up)
-    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err));
+    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err, c->wait_ns, c->tc_fault_block));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum, S.shbm, S.shs);
   if (q32) launch_quant_q8_32(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd);
   if (use_tc)
-    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err));
+    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err, c->wait_ns, c->tc_fault_block));
   else
     launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
   if (D.shared == PM_SHARED_SIGMOID_GATED) launch_shared_gate_logit(L, dv, x, T, S.shared_logit);
@@ -891,7 +932,7 @@ static int32_t dev_forward(pm_layer *ly, const float *x, int T, float *y, bool a
   Launch L = c->launch();
   { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
   { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
-  { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan); }
+  { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan, c->dev_err); }
   TRY(dev_experts(ly, x, T, S, S.w));
   TRY(dev_shared(ly, x, T, S));
   {
@@ -1101,7 +1142,7 @@ extern "C" int32_t pm_plan(pm_layer *ly, const uint32_t *ids, int32_t T, pm_plan
   // the plan of a split call does not count towards usage[]
   LayerDev tmp = ly->dev;
   tmp.usage = nullptr;
-  launch_plan(c->launch(), tmp, idd, T, pl);
+  launch_plan(c->launch(), tmp, idd, T, pl, c->dev_err);
   CU(cudaGetLastError());
   cudaStream_t s = c->stream;
   CU(cudaMemcpyAsync(out->n_active, pl.n_active, 4, cudaMemcpyDefault, s));
@@ -1113,7 +1154,7 @@ extern "C" int32_t pm_plan(pm_layer *ly, const uint32_t *ids, int32_t T, pm_plan
     CU(cudaMemcpyAsync(out->pair_pos, pl.pair_pos, P * 4, cudaMemcpyDefault, s));
   }
   CU(cudaStreamSynchronize(s));
-  return PM_OK;
+  return check_dev_err(c);
 }
 
 extern "C" int32_t pm_experts(pm_layer *ly, const float *x, int32_t T, const uint32_t *ids,
@@ -1137,11 +1178,11 @@ extern "C" int32_t pm_experts(pm_layer *ly, const float *x, int32_t T, const uin
   scratch_carve(c, D, T, S);
   LayerDev tmp = ly->dev;
   tmp.usage = nullptr;
-  launch_plan(c->launch(), tmp, idd, T, S.plan);
+  launch_plan(c->launch(), tmp, idd, T, S.plan, c->dev_err);
   TRY(dev_experts(ly, xd, T, S, wd));
   CU(cudaMemcpyAsync(pair_out, S.eo, P * D.d * 4, cudaMemcpyDefault, c->stream));
   CU(cudaStreamSynchronize(c->stream));
-  return PM_OK;
+  return check_dev_err(c);
 }
 
 // one expert per row (expert parallelism: the rows another rank dispatched here)
@@ -1173,7 +1214,7 @@ extern "C" int32_t pm_experts_rows(pm_layer *ly, const float *x, int32_t R, cons
   pm_layer view = *ly;
   view.dev.desc = D;
   view.dev.usage = nullptr;
-  { PROF(c, PH_PLAN); launch_plan(c->launch(), view.dev, idd, R, S.plan); }
+  { PROF(c, PH_PLAN); launch_plan(c->launch(), view.dev, idd, R, S.plan, c->dev_err); }
   TRY(dev_experts(&view, xd, R, S, wd));
   LayerDev cp = view.dev;
   cp.desc.weight_fold = PM_FOLD_BEFORE_DOWN;  // plain gather back to row order
@@ -1237,7 +1278,7 @@ extern "C" int32_t pm_combine(pm_layer *ly, const float *pair_out, const uint32_
   plan_carve(c, D.n_exp, P, pl);
   LayerDev tmp = ly->dev;
   tmp.usage = nullptr;
-  launch_plan(c->launch(), tmp, idd, T, pl);
+  launch_plan(c->launch(), tmp, idd, T, pl, c->dev_err);
   launch_combine(c->launch(), ly->dev, pod, pl.pair_pos, wd, sod, nullptr, T, yd, acc);
   CU(cudaGetLastError());
   return out_flush(c, &ob, 1);
@@ -1344,21 +1385,12 @@ struct pm_stack {
   std::vector<Graph> graphs;
   std::vector<int> seen_T;  // token counts the general path ran once already
   bool graph_off = false;
+  bool fault_next = false;         // pm_debug_stack_fault_next_call
+  std::vector<uint64_t> seen_gen;  // the layers' generation counters when their pointers were last snapshot
 };
 
-static int32_t stack_setup_mega(pm_stack *s) {
-  pm_ctx *c = s->ctx;
-  const pm_layer_desc &D = s->layers[0]->dev.desc;
-  for (pm_layer *ly : s->layers)
-    if (memcmp(&ly->dev.desc, &D, sizeof D) != 0) return PM_OK;  // mixed shapes: general path
-  cudaDeviceProp prop;
-  CU(cudaGetDeviceProperties(&prop, c->device));
-  int coop = 0;
-  CU(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c->device));
-  if (!coop || prop.major < 9) return PM_OK;
-  if (!mega_plan(D, prop.multiProcessorCount, prop.sharedMemPerBlockOptin, s->mega)) return PM_OK;
-  CU(mega_prepare(D, s->mega.smem));
-  if (mega_max_ctas_per_sm(D, s->mega.smem) < 1) return PM_OK;
+// (re)writes the decode kernel's per-layer pointer table from the layers' current state
+static int32_t stack_fill_mega_layers(pm_stack *s) {
   size_t L = s->layers.size();
   std::vector<MegaLayer> ml(L);
   for (size_t i = 0; i < L; i++) {
@@ -1376,8 +1408,50 @@ static int32_t stack_setup_mega(pm_stack *s) {
     }
     ml[i].usage = dv.usage;
   }
-  CU(cudaMalloc(&s->mega_layers, L * sizeof(MegaLayer)));
   CU(cudaMemcpy(s->mega_layers, ml.data(), L * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+  return PM_OK;
+}
+
+static void stack_drop_graphs(pm_stack *s) {
+  for (auto &g : s->graphs) {
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+    if (g.gx) cudaFree(g.gx);
+  }
+  s->graphs.clear();
+  s->seen_T.clear();
+}
+
+// A layer whose weights, biases or router were (re)loaded after the stack last looked at it:
+// the decode kernel's pointer table and the recorded graphs hold the old device pointers
+// (a bias buffer, for one, is only allocated by the call that first sets it).
+static int32_t stack_refresh(pm_stack *s) {
+  bool same = s->seen_gen.size() == s->layers.size();
+  for (size_t i = 0; same && i < s->layers.size(); i++) same = s->seen_gen[i] == s->layers[i]->gen;
+  if (same) return PM_OK;
+  CU(cudaStreamSynchronize(s->ctx->stream));
+  if (s->mega_layers) TRY(stack_fill_mega_layers(s));
+  stack_drop_graphs(s);
+  s->seen_gen.resize(s->layers.size());
+  for (size_t i = 0; i < s->layers.size(); i++) s->seen_gen[i] = s->layers[i]->gen;
+  return PM_OK;
+}
+
+static int32_t stack_setup_mega(pm_stack *s) {
+  pm_ctx *c = s->ctx;
+  const pm_layer_desc &D = s->layers[0]->dev.desc;
+  for (pm_layer *ly : s->layers)
+    if (memcmp(&ly->dev.desc, &D, sizeof D) != 0) return PM_OK;  // mixed shapes: general path
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, c->device));
+  int coop = 0;
+  CU(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c->device));
+  if (!coop || prop.major < 9) return PM_OK;
+  if (!mega_plan(D, prop.multiProcessorCount, prop.sharedMemPerBlockOptin, s->mega)) return PM_OK;
+  CU(mega_prepare(D, s->mega.smem));
+  if (mega_max_ctas_per_sm(D, s->mega.smem) < 1) return PM_OK;
+  size_t L = s->layers.size();
+  CU(cudaMalloc(&s->mega_layers, L * sizeof(MegaLayer)));
+  TRY(stack_fill_mega_layers(s));
   size_t xb = al((size_t)D.d * 4), lb = al((size_t)D.n_exp * 8), hb = al((size_t)D.top_k * D.ff * 4);
   size_t total = xb + lb + hb + 512;
   CU(cudaMalloc(&s->mega_buf, total));
@@ -1416,6 +1490,7 @@ extern "C" int32_t pm_stack_create(pm_ctx *ctx, pm_layer **layers, int32_t n, fl
     pm_stack_destroy(s);
     return rc;
   }
+  for (pm_layer *ly : s->layers) s->seen_gen.push_back(ly->gen);
   *out = s;
   return PM_OK;
 }
@@ -1423,10 +1498,7 @@ extern "C" int32_t pm_stack_destroy(pm_stack *s) {
   if (!s) return PM_OK;
   cudaSetDevice(s->ctx->device);
   cudaStreamSynchronize(s->ctx->stream);
-  for (auto &g : s->graphs) {
-    if (g.exec) cudaGraphExecDestroy(g.exec);
-    if (g.gx) cudaFree(g.gx);
-  }
+  stack_drop_graphs(s);
   if (s->mega_layers) cudaFree(s->mega_layers);
   if (s->mega_buf) cudaFree(s->mega_buf);
   if (s->mega_io) cudaFree(s->mega_io);
@@ -1456,6 +1528,12 @@ extern "C" int32_t pm_stack_trace(pm_stack *s, int64_t *out, int32_t capacity) {
   CU(cudaStreamSynchronize(s->ctx->stream));
   CU(cudaMemcpy(out, s->mega_trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
   return n;
+}
+
+extern "C" int32_t pm_debug_stack_fault_next_call(pm_stack *s) {
+  if (!s || !s->mega_ok) return fail(PM_ERR_STATE, "pm_debug_stack_fault_next_call: no decode kernel for this stack");
+  s->fault_next = true;
+  return PM_OK;
 }
 
 extern "C" int32_t pm_stack_status(pm_stack *s) {
@@ -1491,10 +1569,16 @@ static int32_t stack_forward_mega(pm_stack *s, const float *x, float *x_out) {
   P.hcount_base = (s->calls - 1) * (unsigned long long)L * (unsigned long long)s->mega.grid;
   P.xcount_base = (s->calls - 1) * (unsigned long long)(L - 1) * (unsigned long long)s->mega.grid;
   P.lepoch_base = (uint32_t)((s->calls - 1) * (unsigned long long)L);
+  P.wait_ns = c->wait_ns;
+  if (s->fault_next) {  // test hook: one arrival more than the CTAs will make
+    P.hcount_base += 1;
+    s->fault_next = false;
+  }
   {
     PROF(c, PH_FUSED);
     CU(mega_launch(s->mega, c->stream));
     c->launches++;
+    c->path_count[PM_PATH_DECODE]++;
   }
   if (out_host) {
     CU(cudaMemcpyAsync(x_out, xo, (size_t)d * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -1516,6 +1600,7 @@ extern "C" int32_t pm_stack_forward(pm_stack *s, const float *x, int32_t T, floa
   pm_ctx *c = s->ctx;
   CU(cudaSetDevice(c->device));
   for (pm_layer *ly : s->layers) TRY(layer_ready(ly, true));
+  TRY(stack_refresh(s));
   if (T == 1 && s->mega_ok && s->mode == 0) return stack_forward_mega(s, x, x_out);
   const int d = s->layers[0]->dev.desc.d;
   size_t n = (size_t)T * d;

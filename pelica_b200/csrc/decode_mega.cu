@@ -28,8 +28,7 @@
 #include "decode_mega.cuh"
 #include "route.cuh"
 
-// every cross-CTA or copy wait gives up after this long (wall time on the device)
-#define MG_WAIT_NS 2000000000ull
+// every cross-CTA or copy wait gives up after MegaParams::wait_ns (wall time on the device)
 
 // ---- PTX helpers -----------------------------------------------------------
 __device__ __forceinline__ uint32_t s32(const void *p) {
@@ -82,7 +81,7 @@ __device__ __forceinline__ unsigned long long now_ns();
 // one thread waits until an arrival counter reaches `want` (bounded); false = gave up.
 // One poller per CTA: 148 loads a round trip on the counter's line, instead of every
 // thread polling its own words (tens of thousands of loads on a few lines of one L2 slice).
-__device__ __noinline__ bool wait_count(const unsigned long long *p, unsigned long long want, int *err, int code) {
+__device__ __noinline__ bool wait_count(const unsigned long long *p, unsigned long long want, int *err, int code, unsigned long long wait_ns) {
   unsigned long long t0 = 0;
   for (uint32_t it = 0;; it++) {
     if (ld_acquire_u64(p) >= want) return true;
@@ -90,7 +89,7 @@ __device__ __noinline__ bool wait_count(const unsigned long long *p, unsigned lo
       if (ld_volatile_i32(err) != 0) return false;
       unsigned long long t = now_ns();
       if (t0 == 0) t0 = t;
-      else if (t - t0 > MG_WAIT_NS) break;
+      else if (t - t0 > wait_ns) break;
     }
   }
   atomicCAS(err, 0, code);
@@ -121,21 +120,21 @@ __device__ __forceinline__ bool mbar_try_wait_ns(uint64_t *bar, uint32_t parity,
 }
 // bounded wait on an mbarrier phase: short hardware-suspended waits in a timed
 // loop; false = gave up (error word set)
-__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, int *err) {
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, int *err, unsigned long long wait_ns) {
   unsigned long long t0 = now_ns();
   for (uint32_t it = 1;; it++) {
     if (mbar_try_wait_ns(bar, parity, 4000u)) return true;
     if ((it & 15) == 0) {
       if (ld_volatile_i32(err) != 0) return false;
-      if (now_ns() - t0 > MG_WAIT_NS) break;
+      if (now_ns() - t0 > wait_ns) break;
     }
   }
   atomicCAS(err, 0, 2);
   return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, unsigned long long wait_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, err);
+  return mbar_wait_slow(bar, parity, err, wait_ns);
 }
 // ---- Q8x of 256 values held 8 per lane (value j of the lane = element 32j+lane)
 // (`Q8x::new`, src/ds4_cpu.rs:13-35); writes q, d, bsum of the block
@@ -493,7 +492,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
 
     // ---- 1. the residual stream (written by all CTAs at the end of the previous layer) ----
     if (l > 0) {
-      if (tid == 0 && !wait_count(P.xcount, P.xcount_base + (unsigned long long)l * (unsigned long long)G, P.err, 1)) dead = true;
+      if (tid == 0 && !wait_count(P.xcount, P.xcount_base + (unsigned long long)l * (unsigned long long)G, P.err, 1, P.wait_ns)) dead = true;
       if (__syncthreads_or(dead)) { dead = true; break; }
     }
     for (int i0 = tid; i0 < d; i0 += MG_NT) xs[i0] = l == 0 ? P.x_in[i0] : __ldcg(P.xbuf + i0);
@@ -519,7 +518,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       {
         MG_TRACE_R(12);
         if (has_logit) {
-          if (!mbar_wait(bar_rw, par, P.err)) dead = true;
+          if (!mbar_wait(bar_rw, par, P.err, P.wait_ns)) dead = true;
           float acc = 0.0f;
 #pragma unroll 16
           for (int c = lane; c < d; c += 32) acc = __fmaf_rn(rw[c], __fmul_rn(xs[c], inv), acc);
@@ -558,7 +557,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
             if ((it & 63) == 63) {
               unsigned long long t = now_ns();
               if (t0 == 0) t0 = t;
-              bool stop = ld_volatile_i32(P.err) != 0 || t - t0 > MG_WAIT_NS;
+              bool stop = ld_volatile_i32(P.err) != 0 || t - t0 > P.wait_ns;
               if (__any_sync(PM_FULL, stop)) break;
             }
           }
@@ -691,7 +690,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       const int npairs = (nrows + 1) >> 1;
       const int ppc = (npairs + MG_GU_CHUNKS - 1) / MG_GU_CHUNKS;  // pairs per copy chunk
       for (int p = warp; p < npairs; p += MG_WARPS) {
-        if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[p / ppc], par, P.err))) { dead = true; break; }
+        if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[p / ppc], par, P.err, P.wait_ns))) { dead = true; break; }
         if (p == warp) MG_TRACE(8);
         int rel = 2 * p + ((lane >> 4) & 1);
         rel = min(rel, nrows - 1);
@@ -708,7 +707,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     } else {
       int ra = R0 + warp * per_w, rb = min(R1, ra + per_w);
       if (ra < rb) {
-        if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[warp / wpc], par, P.err))) dead = true;
+        if (!__all_sync(PM_FULL, mbar_wait(&bar_gu[warp / wpc], par, P.err, P.wait_ns))) dead = true;
       }
       MG_TRACE(8);
       for (int r0 = ra; r0 < rb && !dead; r0 += MG_GH) {
@@ -757,7 +756,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       unsigned long long t0 = now_ns();
       for (uint32_t it = 0;; it++) {
         if (ld_acquire_u64(P.hcount) >= want) { ok = true; break; }
-        if ((it & 63) == 63 && (ld_volatile_i32(P.err) != 0 || now_ns() - t0 > MG_WAIT_NS)) break;
+        if ((it & 63) == 63 && (ld_volatile_i32(P.err) != 0 || now_ns() - t0 > P.wait_ns)) break;
       }
       if (!ok) { atomicCAS(P.err, 0, 3); dead = true; }
     }
@@ -788,7 +787,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
       const size_t cm = (size_t)P.cols_max * nbh;
       for (int u = tid; u < ndown * nbh; u += MG_NT) {
         const int i = u / nbh, b = u - i * nbh, k = i / ncols, cc = i - k * ncols;
-        if (!mbar_wait(&bar_dn[k], par, P.err)) dead = true;
+        if (!mbar_wait(&bar_dn[k], par, P.err, P.wait_ns)) dead = true;
         const uint8_t *base = dn + (size_t)k * P.dn_k_bytes;
         const size_t rb = (size_t)cc * nbh + b;
         const uint8_t *qlp = base + rb * 128, *qhp = base + cm * 128 + rb * 64;
@@ -842,7 +841,7 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
           int i = min(i0 + r, ib - 1);
           kk[r] = i / ncols;
           cc[r] = i - kk[r] * ncols;
-          if (!__all_sync(PM_FULL, mbar_wait(&bar_dn[kk[r]], par, P.err))) dead = true;
+          if (!__all_sync(PM_FULL, mbar_wait(&bar_dn[kk[r]], par, P.err, P.wait_ns))) dead = true;
         }
         if (dead) break;
         if (i0 == ia) MG_TRACE(9);
@@ -905,12 +904,15 @@ __global__ void __launch_bounds__(MG_NT, 1) k_decode_mega(const MegaParams P) {
     __syncthreads();
     if (tid == 0) {
       uint32_t par = l & 1;
+      // (one time bound for the whole drain, the same as every other wait's: a barrier that was
+      // never armed for this layer has nothing in flight and is simply given up on)
+      const unsigned long long t0 = now_ns();
       if (copies_pending) {
         for (int i = 0; i < MG_GU_CHUNKS + K; i++)
-          for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(&bar_gu[i == 0 ? 0 : i], par); it++) {}
+          while (!mbar_try_wait_ns(&bar_gu[i], par, 2000u) && now_ns() - t0 < P.wait_ns) {}
       }
       if (has_logit)
-        for (uint32_t it = 0; it < (1u << 16) && !mbar_try_wait(bar_rw, par); it++) {}
+        while (!mbar_try_wait_ns(bar_rw, par, 2000u) && now_ns() - t0 < P.wait_ns) {}
     }
     __syncthreads();
   }

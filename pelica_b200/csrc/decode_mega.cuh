@@ -33,6 +33,7 @@ struct MegaParams {
   unsigned long long hcount_base, xcount_base;
   uint32_t lepoch_base;  // epochs before this call: (calls - 1) * layers
   int *err;
+  unsigned long long wait_ns;  // limit of every bounded wait
   long long *trace;  // optional [2][n_layers][MG_TRACE_PH] SM clocks (CTA 0 and the last CTA)
   // shared-memory layout (bytes from the dynamic base)
   int rows_max, cols_max;

@@ -418,9 +418,21 @@ __global__ void k_plan_zero(uint32_t *cnt, int E) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < E) cnt[i] = 0;
 }
-__global__ void k_plan_count(const uint32_t *__restrict__ ids, int P, uint32_t *cnt) {
+// An expert id outside [0, E) (a caller's device buffer, or a peer's message under expert
+// parallelism) is never used as an index: its pair is left out of every expert's list, its
+// pair_pos becomes PM_PAIR_NONE (read as a zero row by combine) and the context's error word
+// is set so that the call reports PM_ERR_INVALID at its next synchronisation.
+__global__ void k_plan_count(const uint32_t *__restrict__ ids, int P, int E, uint32_t *cnt,
+                             uint32_t *pair_pos, int *err) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < P) atomicAdd(&cnt[ids[i]], 1u);
+  if (i >= P) return;
+  uint32_t e = ids[i];
+  if (e < (uint32_t)E) {
+    atomicAdd(&cnt[e], 1u);
+  } else {
+    pair_pos[i] = PM_PAIR_NONE;
+    if (err) atomicCAS(err, 0, PM_DEVERR_BAD_EXPERT_ID);
+  }
 }
 // single CTA of 512 threads: exclusive scans over the experts
 __global__ void __launch_bounds__(512) k_plan_scan(PlanDev pl, int E, uint32_t *usage) {
@@ -491,10 +503,10 @@ __global__ void __launch_bounds__(256) k_plan_place(const uint32_t *__restrict__
   }
 }
 
-void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev pl) {
+void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev pl, int *err) {
   int E = ly.desc.n_exp, K = ly.desc.top_k, P = T * K;
   KLAUNCH(L, k_plan_zero, (E + 255) / 256, 256, 0, pl.cnt, E);
-  if (P > 0) KLAUNCH(L, k_plan_count, (P + 255) / 256, 256, 0, ids, P, pl.cnt);
+  if (P > 0) KLAUNCH(L, k_plan_count, (P + 255) / 256, 256, 0, ids, P, E, pl.cnt, pl.pair_pos, err);
   KLAUNCH(L, k_plan_scan, 1, 512, 0, pl, E, ly.usage);
   if (P > 0) KLAUNCH(L, k_plan_place, E, 256, 0, ids, P, K, pl);
 }
@@ -858,7 +870,8 @@ __global__ void __launch_bounds__(256) k_combine(int d, int K, int in_combine,
   if (c >= d) return;
   float s = 0.0f;
   for (int k = 0; k < K; k++) {
-    float v = eo[(size_t)pair_pos[t * K + k] * d + c];
+    const uint32_t p = pair_pos[t * K + k];
+    float v = p == PM_PAIR_NONE ? 0.0f : eo[(size_t)p * d + c];  // a pair whose expert id was refused
     if (in_combine) v = __fmul_rn(w[t * K + k], v);
     s = __fadd_rn(s, v);
   }

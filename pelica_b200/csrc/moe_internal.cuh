@@ -34,6 +34,11 @@ struct LayerDev {
   uint32_t *usage;                               // [E]
 };
 
+// pair_pos of a pair whose expert id was refused by the plan (combine reads a zero row)
+#define PM_PAIR_NONE 0xffffffffu
+// values of a context's device error word (0 = none; 1..99 = a bounded wait gave up)
+#define PM_DEVERR_BAD_EXPERT_ID 100
+
 // A grouping of pairs by expert (the dispatch plan, or the trivial one-group
 // plan of the shared expert).
 struct Groups {
@@ -103,7 +108,8 @@ void launch_quant_q8_32(const Launch &L, const float *x, size_t rows, int n, int
 void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits);
 void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int T, uint32_t *ids,
                   float *w);
-void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev plan);
+// err: the context's error word (an expert id outside the layer is reported there, never used)
+void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev plan, int *err);
 void launch_iota(const Launch &L, uint32_t *p, uint32_t n);
 void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
                    const float *x, const int8_t *xq, const float *xd, const int32_t *xbsum,
@@ -116,7 +122,8 @@ void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int
 int tc_max_tiles(int n_pairs, int max_groups);
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
                           int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
-                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err);
+                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err,
+                          unsigned long long wait_ns, int fault_block);
 void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
                     const float *w, const float *shared_out, const float *shared_logit, int T,
                     float *y, bool accumulate);

@@ -39,7 +39,6 @@
 #define TC_RAW_Q6 (TC_M * (128 + 64 + 16 + 4))
 #define TC_RAW_STAGES_Q4 4                          /* weight blocks in flight */
 #define TC_RAW_STAGES_Q6 3
-#define TC_WAIT_NS 2000000000ull
 
 __device__ __forceinline__ uint32_t tc_s32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -119,13 +118,13 @@ __device__ __forceinline__ bool tc_bar_test(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// false after TC_WAIT_NS (or at once when an error is already recorded): the caller
+// false after the wait limit (or at once when an error is already recorded): the caller
 // carries on with whatever the accumulators hold and the call reports the error
-__device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *err) {
+__device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *err, unsigned long long wait_ns) {
   unsigned long long t0 = tc_now();
   for (uint32_t it = 0;; it++) {
     if (tc_bar_test(bar, parity)) return true;
-    if ((it & 15) == 15 && (*(volatile int *)err != 0 || tc_now() - t0 > TC_WAIT_NS)) break;
+    if ((it & 15) == 15 && (*(volatile int *)err != 0 || tc_now() - t0 > wait_ns)) break;
   }
   atomicCAS(err, 0, 7);
   return false;
@@ -159,6 +158,8 @@ struct TcArgs {
   const float *wts;      // routing weights [T*K] (gate/up with fold) or null
   float *out;            // gate/up: h [P][ff]; down: eo [P][d]
   int *err;
+  unsigned long long wait_ns;  // limit of the workers' wait for a block's products
+  int fault_block;             // test hook: no products are issued or signalled from this block on (-1 = off)
   const int *n_tiles;          // [1]
   const uint32_t *tile_group;  // [tiles] index into the groups
   const uint32_t *tile_n0;     // [tiles] first token of the tile inside its group
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       const uint64_t dB0 = tc_desc(bs, (uint32_t)(npad + 1) * 16u, 128u);
       tc_ready_wait();  // operand A in TMEM, the tokens' block in shared memory, accumulators read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if ((tid & 31) == 0) {
+      if ((tid & 31) == 0 && !(A.fault_block >= 0 && b >= A.fault_block)) {
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
           const uint64_t db = dB0 + (uint64_t)(ks * 2 * (npad + 1));
@@ -566,7 +567,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       }
       TC_STAMP(b, 2)
       // ---- 3. the block's float term, in block order ----
-      if (!tc_bar_test(bar, (uint32_t)(b & 1))) tc_bar_wait(bar, (uint32_t)(b & 1), A.err);
+      if (!tc_bar_test(bar, (uint32_t)(b & 1))) tc_bar_wait(bar, (uint32_t)(b & 1), A.err, A.wait_ns);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       TC_STAMP(b, 3)
       TC_STAMP(b, 4)
@@ -670,7 +671,8 @@ static size_t tc_smem(bool q6) {
 // activations (xbm: the f16 form of the sub-block sums the quantiser writes).
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
                           int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
-                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err) {
+                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err,
+                          unsigned long long wait_ns, int fault_block) {
   if (n_pairs == 0) return cudaSuccess;
   // tile list: at most one partial tile per group plus the full ones
   const int max_tiles = tc_max_tiles(n_pairs, g.max_groups);
@@ -696,6 +698,8 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.wts = wts;
   A.out = out;
   A.err = err;
+  A.wait_ns = wait_ns;
+  A.fault_block = fault_block;
   A.n_tiles = n_tiles;
   A.tile_group = tile_group;
   A.tile_n0 = tile_n0;

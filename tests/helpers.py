@@ -70,3 +70,14 @@ def make_pair(po, pb, ctx, cfg, seed):
     ol = po.Layer(po.LayerDesc(**cfg.desc_fields()), W)
     gl = pb.MoeLayer(ctx, cfg).load(W)
     return ol, gl, W
+
+
+def device_pair(po, pb, ctx, cfg, seed):
+    """A layer whose weights are generated on the GPU (any size, seconds) and read back for
+    the CPU checker: (oracle layer, CUDA layer). Only the experts the context holds are
+    read back (cfg.n_exp_local), so a shard of a full-width layer stays a few hundred MB."""
+    gl = pb.MoeLayer(ctx, cfg).fill_synthetic(seed, cfg.sigma, cfg.sigma if cfg.logit_bias else 0.0,
+                                              cfg.select_bias_sigma)
+    W = gl.get_weights(dense=False)
+    ol = po.Layer(po.LayerDesc(**cfg.desc_fields()), W)
+    return ol, gl

@@ -13,8 +13,8 @@ from pelica_b200 import build, synth
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    src = open(os.path.join(ROOT, "include", "pelica_moe.h")).read()
+def declared_symbols(header="pelica_moe.h"):
+    src = open(os.path.join(ROOT, "include", header)).read()
     return sorted(set(re.findall(r"PM_API[^;(]*?\b(pm_\w+)\s*\(", src)))
 
 
@@ -22,12 +22,23 @@ def test_header_and_binding_agree():
     names = declared_symbols()
     assert len(names) >= 30
     assert set(names) == set(pb.ABI), set(names) ^ set(pb.ABI)
+    diag = declared_symbols("pelica_moe_diag.h")
+    assert set(diag) == set(pb.ABI_DIAG), set(diag) ^ set(pb.ABI_DIAG)
+    assert not set(diag) & set(names)
+
+
+def test_boundary_header_cites_the_reference():
+    """Every entry point of the boundary header sits under a comment that names the reference
+    code it replaces or serves (src/...), except the documented addition without a counterpart."""
+    src = open(os.path.join(ROOT, "include", "pelica_moe.h")).read()
+    assert "src/ds4_cpu.rs:297" in src and "src/moe.rs:1377-1437" in src
+    assert "No counterpart in the reference" in src  # pm_route_noalloc
 
 
 def test_library_exports_every_declared_symbol():
     build.build_library()
     lib = ctypes.CDLL(pb.LIB_PATH)
-    for name in declared_symbols():
+    for name in declared_symbols() + declared_symbols("pelica_moe_diag.h"):
         assert hasattr(lib, name), name
     pb.load_library()
     assert b"sm_100a" in pb.load_library().pm_version()

@@ -17,9 +17,15 @@ def test_tensor_core_path_matches_oracle_and_general(ctx, oracle, name, T):
     ol, gl, _ = make_pair(oracle, pb, ctx, cfg, 31)
     x = synth.make_activations(T, cfg.d, 400 + T)
     ctx.set_tensor_core_min_tokens(32)
+    c0 = ctx.path_counts()
     tc = gl.forward(x)
+    c1 = ctx.path_counts()
+    # which kernels served the call: gate/up and down of the routed experts (and of the shared one)
+    assert c1["tensor"] - c0["tensor"] >= 2 and c1["general"] == c0["general"]
     ctx.set_tensor_core_min_tokens(0)
     general = gl.forward(x)
+    c2 = ctx.path_counts()
+    assert c2["tensor"] == c1["tensor"] and c2["general"] - c1["general"] >= 2
     ctx.set_tensor_core_min_tokens(32)
     assert bits_equal(tc, general)
     assert bits_equal(tc, ol.forward(x))

@@ -117,3 +117,28 @@ def test_plan_rejects_bad_ids(ctx):
     with pytest.raises(pb.PelicaError):
         gl.plan(np.array([[1, 16]], np.uint32))
     gl.close()
+
+
+def test_bf16_router_weights(ctx, oracle):
+    """A router stored as bf16 (GLM's `router_scores`, src/forward.rs:117): the logits are the
+    reference's `dot_bf16` (src/quant.rs:282-304), bit for bit, which in turn equals `dot_f32`
+    over the widened values."""
+    cfg = synth.C4_DSV3.scaled(n_group=0, topk_group=0, n_exp=64, d=1024, shared=0)
+    rng = np.random.default_rng(17)
+    r32 = synth.bf16_round(rng.normal(0, cfg.sigma, (cfg.n_exp, cfg.d)).astype(np.float32))
+    bits = np.ascontiguousarray((r32.view(np.uint32) >> 16).astype(np.uint16))
+    sb = rng.normal(0, cfg.select_bias_sigma, cfg.n_exp).astype(np.float32)
+    gl = pb.MoeLayer(ctx, cfg)
+    pb._check(gl.lib.pm_layer_set_router(gl.h, bits.ctypes.data, synth.BF16, None, sb.ctypes.data))
+    ol = oracle.Layer(oracle.LayerDesc(**cfg.desc_fields()), {"router": r32, "select_bias": sb})
+    for T in (1, 9, 70):
+        x = synth.make_activations(T, cfg.d, 500 + T)
+        lg = gl.router_logits(x)
+        for t in (0, T - 1):
+            for e in (0, 13, cfg.n_exp - 1):
+                assert np.float32(oracle.dot_bf16(bits[e], x[t])).view(np.uint32) == lg[t, e].view(np.uint32)
+        assert bits_equal(lg, ol.router_logits(x))
+        ids_o, w_o = ol.route(x)
+        ids_g, w_g = gl.route(x)
+        assert np.array_equal(ids_g, ids_o) and bits_equal(w_g, w_o)
+    gl.close()

@@ -37,8 +37,12 @@ def test_route_noalloc_matches_route_twice(ctx, cfg):
         dx = ctx.alloc(x.nbytes).upload(x)
         dids = ctx.alloc(T * K * 4)
         dw = ctx.alloc(T * K * 4)
+        free0 = ctx.device_free_bytes()
         ly.route_noalloc(dx, T, dids, dw)
         ctx.sync()
+        free1 = ctx.device_free_bytes()
+        # nothing was allocated (or freed) by the call: the device's free memory is unchanged
+        assert free0 == free1
         got_ids = dids.download(np.uint32, (T, K))
         got_w = dw.download(np.float32, (T, K))
         assert np.array_equal(got_ids, want_ids)
