@@ -238,7 +238,9 @@ class Layer:
 
     def __init__(self, desc: LayerDesc, weights: dict):
         self.desc = desc
-        self.w = {k: (np.ascontiguousarray(v) if v is not None else None) for k, v in weights.items()}
+        # a tensor family may also come as a per-expert list of byte arrays (a shard of a large layer)
+        self.w = {k: ([np.ascontiguousarray(a) for a in v] if isinstance(v, list) else
+                      np.ascontiguousarray(v) if v is not None else None) for k, v in weights.items()}
         w = self.w
         E = desc.n_exp
         self._experts = (ExpertW * E)()

@@ -5,8 +5,10 @@
 
 #define MG_NT 512
 #define MG_WARPS (MG_NT / 32)
+#define MG_CW (MG_WARPS - 1)  // warps that run gate/up passes; the last warp routes and issues the down copies
 #define MG_GU_CHUNKS 4
-#define MG_TRACE_PH 20  // trace points per layer
+#define MG_TRACE_PH 16        // stamps per layer
+#define MG_TRACE_CTAS 3       // CTA 0, the middle one and the last one are traced
 
 struct MegaLayer {
   const float *router, *logit_bias, *select_bias;
@@ -24,21 +26,21 @@ struct MegaParams {
   const float *x_in;
   float *x_out;
   float eps;
-  float *xbuf;               // [d]      the residual stream between layers
-  unsigned long long *lbuf;  // [E]      the layer's router logits: (epoch << 32) | float bits
-  float *hbuf;               // [K*ff]
-  // arrival counters (never reset: each call waits for base + its own arrivals):
-  unsigned long long *hcount;  // CTAs that finished their h rows
-  unsigned long long *xcount;  // CTAs that published their slice of the next layer's residual stream
-  unsigned long long hcount_base, xcount_base;
-  uint32_t lepoch_base;  // epochs before this call: (calls - 1) * layers
+  // The three all-CTA exchanges of a layer. Every word is (epoch << 32) | float bits, written
+  // with one relaxed 64-bit store and polled by its readers until it carries the layer's epoch:
+  // no counter, no release fence. Two buffers each, alternating by layer.
+  unsigned long long *xw;  // [2][d]    the residual stream entering a layer
+  unsigned long long *lw;  // [2][E]    the layer's router logits
+  unsigned long long *hw;  // [2][K*ff] the layer's hidden values (activation applied, weight folded)
+  uint32_t epoch_base;     // epochs used by earlier calls: (calls - 1) * layers
+  uint32_t fault;          // test hook: XORed into the epoch the readers of h expect in layer 0
   int *err;
   unsigned long long wait_ns;  // limit of every bounded wait
-  long long *trace;  // optional [2][n_layers][MG_TRACE_PH] SM clocks (CTA 0 and the last CTA)
+  unsigned long long *trace;   // optional [MG_TRACE_CTAS][n_layers][MG_TRACE_PH] global-timer stamps (ns)
   // shared-memory layout (bytes from the dynamic base)
   int rows_max, cols_max;
   uint32_t off_gs, off_us, off_dn, off_dsm, off_xs, off_xq, off_xd, off_xbs, off_hq, off_hd,
-      off_hbs, off_rw, off_eo, off_lg, off_misc, off_ml, dn_k_bytes, dsm_k_bytes;
+      off_hbs, off_rw, off_tmp, off_lg, off_misc, off_ml, dn_k_bytes, dsm_k_bytes;
 };
 
 struct MegaPlan {
@@ -47,7 +49,6 @@ struct MegaPlan {
   size_t smem = 0;
   MegaParams P{};
 };
-
 
 bool mega_plan(const pm_layer_desc &D, int n_sm, size_t smem_optin, MegaPlan &mp);
 cudaError_t mega_prepare(const pm_layer_desc &D, size_t smem);

@@ -85,14 +85,20 @@ def test_expert_ids_in_device_buffers_are_range_checked(ctx, oracle):
     assert e.value.code == -1
     # device ids: the plan kernels leave the pairs out and flag the call
     dbad = ctx.alloc(bad.nbytes).upload(bad)
-    with pytest.raises(pb.PelicaError) as e:
-        gl.plan(dbad)
-    assert e.value.code == -1
+    E = cfg.n_exp
+    r = dict(n_active=np.zeros(1, np.int32), active=np.zeros(E, np.uint32), offset=np.zeros(E, np.uint32),
+             count=np.zeros(E, np.uint32), pair_token=np.zeros(T * K, np.uint32), pair_pos=np.zeros(T * K, np.uint32))
+    po_ = pb.PlanOut(*[r[k].ctypes.data for k in ("n_active", "active", "offset", "count", "pair_token", "pair_pos")])
+    import ctypes
+
+    assert gl.lib.pm_plan(gl.h, dbad.ptr, T, ctypes.byref(po_)) == -1
+    assert int(r["count"].sum()) == T * K - 2           # the two bad pairs are in no expert's list
+    assert (r["pair_pos"].reshape(T, K)[[3, 7], [2, 0]] == 0xFFFFFFFF).all()
     dx = ctx.alloc(x.nbytes).upload(x)
     dw = ctx.alloc(w.nbytes).upload(w)
-    with pytest.raises(pb.PelicaError) as e:
-        gl.experts(dx, dbad, dw)
-    assert e.value.code == -1
+    out = np.zeros((T * K, cfg.d), np.float32)
+    assert gl.lib.pm_experts(gl.h, dx.ptr, T, dbad.ptr, dw.ptr, out.ctypes.data) == -1
+    assert b"outside the layer" in gl.lib.pm_last_error()
     # the context is intact and the error does not stick
     assert bits_equal(gl.forward(x), ol.forward(x))
     ctx.sync()
