@@ -530,7 +530,7 @@ class Stack:
         _check(self.lib.pm_debug_stack_fault_next_call(self.h))
 
     def trace(self, enable: bool = False):
-        """Decode-kernel phase stamps (SM clocks) of the last call: array [2, layers, 8]."""
+        """Decode-kernel phase stamps (global timer, ns) of the last call: array [CTAs, layers, 16]."""
         n = self.lib.pm_stack_trace(self.h, None, 0)
         if n < 0:
             _check(n)
@@ -540,4 +540,4 @@ class Stack:
         r = self.lib.pm_stack_trace(self.h, out.ctypes.data, n)
         if r < 0:
             _check(r)
-        return out.reshape(2, len(self.layers), -1)
+        return out.reshape(len(out) // (len(self.layers) * 16), len(self.layers), 16)

@@ -19,7 +19,7 @@ NVCC_FLAGS = [
     "-fmad=false",            # fused multiply-adds only where __fmaf_rn is written
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "--expt-relaxed-constexpr",
-]
+] + os.environ.get("PM_EXTRA_NVCC", "").split()
 
 
 def _nvcc() -> str:

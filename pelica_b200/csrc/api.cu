@@ -1371,7 +1371,8 @@ struct pm_stack {
   MegaLayer *mega_layers = nullptr;
   uint8_t *mega_buf = nullptr;  // exchange buffers + counters + error word
   float *mega_io = nullptr;     // staged input / output token
-  long long *mega_trace = nullptr;
+  size_t mega_buf_bytes = 0, mega_xw_bytes = 0;
+  unsigned long long *mega_trace = nullptr;
   unsigned long long calls = 0;
   // general path for a few tokens: the layer loop recorded once as a CUDA graph per token
   // count and replayed (a decode step is a few hundred short launches: host-paced otherwise)
@@ -1452,8 +1453,10 @@ static int32_t stack_setup_mega(pm_stack *s) {
   size_t L = s->layers.size();
   CU(cudaMalloc(&s->mega_layers, L * sizeof(MegaLayer)));
   TRY(stack_fill_mega_layers(s));
-  size_t xb = al((size_t)D.d * 4), lb = al((size_t)D.n_exp * 8), hb = al((size_t)D.top_k * D.ff * 4);
-  size_t total = xb + lb + hb + 512;
+  // the three exchanges, two buffers each, of 64-bit (epoch, value) words; epoch 0 = never written
+  size_t xb = al((size_t)D.d * 16), lb = al((size_t)D.n_exp * 16), hb = al((size_t)D.top_k * D.ff * 16);
+  size_t fb = al(128 + (size_t)(D.top_k * D.ff / 256) * 128);  // the counters, a 128-byte line each
+  size_t total = xb + lb + hb + fb + 512;
   CU(cudaMalloc(&s->mega_buf, total));
   CU(cudaMemset(s->mega_buf, 0, total));
   CU(cudaMalloc(&s->mega_io, (size_t)D.d * 4 * 2));
@@ -1461,12 +1464,14 @@ static int32_t stack_setup_mega(pm_stack *s) {
   P.n_layers = (int)L;
   P.layers = s->mega_layers;
   P.eps = s->eps;
-  P.xbuf = (float *)s->mega_buf;
-  P.lbuf = (unsigned long long *)(s->mega_buf + xb);
-  P.hbuf = (float *)(s->mega_buf + xb + lb);
-  P.hcount = (unsigned long long *)(s->mega_buf + xb + lb + hb);  // each counter on its own 128-byte line
-  P.xcount = (unsigned long long *)(s->mega_buf + xb + lb + hb + 128);
-  P.err = (int *)(s->mega_buf + xb + lb + hb + 384);
+  P.xw = (unsigned long long *)s->mega_buf;
+  P.lw = (unsigned long long *)(s->mega_buf + xb);
+  P.hw = (unsigned long long *)(s->mega_buf + xb + lb);
+  P.xcount = (unsigned long long *)(s->mega_buf + xb + lb + hb);
+  P.hcount = (unsigned long long *)(s->mega_buf + xb + lb + hb + 128);
+  P.err = (int *)(s->mega_buf + xb + lb + hb + fb + 256);
+  s->mega_buf_bytes = total;
+  s->mega_xw_bytes = xb + lb + hb;
   s->mega_ok = true;
   return PM_OK;
 }
@@ -1515,7 +1520,7 @@ extern "C" int32_t pm_stack_decode_kernel_available(pm_stack *s) { return s && s
 
 extern "C" int32_t pm_stack_trace(pm_stack *s, int64_t *out, int32_t capacity) {
   if (!s || !s->mega_ok) return fail(PM_ERR_STATE, "pm_stack_trace: no decode kernel for this stack");
-  int n = 2 * (int)s->layers.size() * MG_TRACE_PH;
+  int n = s->mega.grid * (int)s->layers.size() * MG_TRACE_PH;
   if (!out) {  // switch tracing on
     if (!s->mega_trace) {
       CU(cudaMalloc(&s->mega_trace, (size_t)n * 8));
@@ -1566,12 +1571,17 @@ static int32_t stack_forward_mega(pm_stack *s, const float *x, float *x_out) {
   s->calls++;
   P.x_in = xin;
   P.x_out = xo;
-  P.hcount_base = (s->calls - 1) * (unsigned long long)L * (unsigned long long)s->mega.grid;
-  P.xcount_base = (s->calls - 1) * (unsigned long long)(L - 1) * (unsigned long long)s->mega.grid;
-  P.lepoch_base = (uint32_t)((s->calls - 1) * (unsigned long long)L);
+  // epochs of this call: base + 1 .. base + L (32 bits; the words are cleared before they could repeat)
+  if ((s->calls * (unsigned long long)L) >> 32 != ((s->calls - 1) * (unsigned long long)L) >> 32) {
+    CU(cudaMemsetAsync(s->mega_buf, 0, s->mega_xw_bytes, c->stream));  // (the words only: the counters never repeat)
+  }
+  P.epoch_base = (uint32_t)((s->calls - 1) * (unsigned long long)L);
+  P.count_base = (s->calls - 1) * (unsigned long long)L;
+  P.xcount_base = (s->calls - 1) * (unsigned long long)(L - 1);
   P.wait_ns = c->wait_ns;
-  if (s->fault_next) {  // test hook: one arrival more than the CTAs will make
-    P.hcount_base += 1;
+  P.fault = 0;
+  if (s->fault_next) {  // test hook: the readers of h expect an epoch nobody writes
+    P.fault = 1u;
     s->fault_next = false;
   }
   {
