@@ -759,6 +759,7 @@ struct Scratch {
   int8_t *xq; float *xd; int32_t *xbsum; uint16_t *xbm; int32_t *xs;
   float *h; int8_t *hq; float *hd; int32_t *hbsum; uint16_t *hbm; int32_t *hs;
   float *eo;
+  uint16_t *xhl, *hhl;  // MXFP4 tensor-core path: bf16 (hi, lo) split of x [2][T*d] and of h [2][P*ff]
   uint32_t *tiles;  // tile list of the tensor-core kernels
   // shared expert
   int *one; uint32_t *zero_u, *tcount, *iota;
@@ -774,6 +775,7 @@ static size_t scratch_bytes(const pm_layer_desc &D, int T) {
   b += al(T * d) + al(T * (d / 32 + 1) * 4) + al(T * (d / 256 + 1) * 4) + al(T * (d / 32) * 4) * 2;
   b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 32 + 1) * 4) + al(P * (ff / 256 + 1) * 4) + al(P * (ff / 32) * 4) * 2;
   b += al(P * d * 4);
+  if (D.act_quant == PM_AQ_F32 && D.type_gate == PM_TYPE_MXFP4) b += al(T * d * 4) + al(P * ff * 4);
   b += al((4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1)) * 4);
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
@@ -810,6 +812,11 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
   S.hbm = ws_take<uint16_t>(c, P * (ff / 16));
   S.hs = ws_take<int32_t>(c, P * (ff / 256 + 1));
   S.eo = ws_take<float>(c, P * d);
+  S.xhl = S.hhl = nullptr;
+  if (D.act_quant == PM_AQ_F32 && D.type_gate == PM_TYPE_MXFP4) {
+    S.xhl = ws_take<uint16_t>(c, 2 * T * d);
+    S.hhl = ws_take<uint16_t>(c, 2 * P * ff);
+  }
   S.tiles = ws_take<uint32_t>(c, 4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1));
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
@@ -855,6 +862,31 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
   if (q32) { PROF(c, PH_QUANT_X); launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd); }
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
+  // MXFP4 weights with f32 activations: the bf16 tensor-core kernels (tolerance parity, not bits)
+  const bool tcmx = D.act_quant == PM_AQ_F32 && D.type_gate == PM_TYPE_MXFP4 && D.type_up == PM_TYPE_MXFP4 &&
+                    D.type_down == PM_TYPE_MXFP4 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens && S.xhl;
+  if (tcmx) {
+    const size_t nx = (size_t)T * D.d, nh = (size_t)P * D.ff;
+    {
+      PROF(c, PH_QUANT_X);
+      launch_split_bf16(L, x, nx, S.xhl, S.xhl + nx);
+    }
+    {
+      PROF(c, PH_GATEUP);
+      CU(launch_tc_mx(L, dv, false, g, P, S.tiles, S.xhl, S.xhl + nx, w, S.h, c->dev_err, c->wait_ns));
+    }
+    {
+      PROF(c, PH_QUANT_H);
+      launch_split_bf16(L, S.h, nh, S.hhl, S.hhl + nh);
+    }
+    {
+      PROF(c, PH_DOWN);
+      CU(launch_tc_mx(L, dv, true, g, P, S.tiles, S.hhl, S.hhl + nh, nullptr, S.eo, c->dev_err, c->wait_ns));
+    }
+    c->path_count[PM_PATH_TENSOR] += 2;
+    CU(cudaGetLastError());
+    return PM_OK;
+  }
   {
     PROF(c, PH_GATEUP);
     if (tc && D.type_gate == D.type_up) {

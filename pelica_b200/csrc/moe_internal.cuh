@@ -124,6 +124,12 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
                           int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
                           const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err,
                           unsigned long long wait_ns, int fault_block);
+// tensor-core (tcgen05 bf16) form for MXFP4 weights and f32 activations given as their bf16
+// (hi, lo) split (prefill_mx.cu); launch_split_bf16 makes the split: hi[n], lo[n] bf16
+void launch_split_bf16(const Launch &L, const float *x, size_t n, void *hi, void *lo);
+cudaError_t launch_tc_mx(const Launch &L, const LayerDev &ly, bool down, Groups g, int n_pairs, uint32_t *tile_buf,
+                         const void *xhi, const void *xlo, const float *wts, float *out, int *err,
+                         unsigned long long wait_ns);
 void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
                     const float *w, const float *shared_out, const float *shared_logit, int T,
                     float *y, bool accumulate);

@@ -656,6 +656,11 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TC_TMEM_COLS) : "memory");
 }
 
+void launch_tc_tiles(const Launch &L, Groups g, int *n_tiles, uint32_t *tile_group, uint32_t *tile_n0, int max_tiles) {
+  k_tc_tiles<<<1, 512, 0, L.stream>>>(g, n_tiles, tile_group, tile_n0, max_tiles);
+  if (L.count) ++*L.count;
+}
+
 int tc_max_tiles(int n_pairs, int max_groups) {
   int groups = max_groups < n_pairs ? max_groups : n_pairs;
   return n_pairs / TC_NMAX + groups;

@@ -50,7 +50,11 @@ def test_c3_full_width_layer(ctx, oracle, T):
     ids, w = gl.route(x)
     ids_o, w_o = ol.route(x)
     assert np.array_equal(ids, ids_o) and bits_equal(w, w_o)
+    before = ctx.path_counts()
     got = gl.forward(x)
+    after = ctx.path_counts()
+    if T >= 32:  # 90 blocks a row: 45 K chunks of the bf16 tensor-core kernel
+        assert after["tensor"] - before["tensor"] >= 2
     want = ol.forward(x)
     assert tol_ok(got, want), float(np.abs(got - want).max())
     gl.close()

@@ -54,3 +54,31 @@ def test_tensor_core_path_full_width_rows(ctx, oracle):
     x = synth.make_activations(150, cfg.d, 10)
     assert bits_equal(gl.forward(x), ol.forward(x))
     gl.close()
+
+
+@pytest.mark.parametrize("T", [32, 77, 300])
+def test_mxfp4_tensor_core_path(ctx, oracle, T):
+    """MXFP4 weights with f32 activations (the gpt-oss path) on the bf16 tensor-core kernels:
+    the activations are split hi + lo into two bf16 operands, so parity is the layer tolerance
+    (1e-3 relative + 1e-4 of the RMS), against the oracle and against the general f32 kernels.
+    The reduced shape has ff = 160: the down products end in a chunk of a single 32-value block."""
+    from tests.helpers import tol_ok
+
+    cfg = SMALL["c3"]
+    ol, gl, _ = make_pair(oracle, pb, ctx, cfg, 35)
+    x = synth.make_activations(T, cfg.d, 700 + T)
+    ctx.set_tensor_core_min_tokens(32)
+    c0 = ctx.path_counts()
+    tc = gl.forward(x)
+    c1 = ctx.path_counts()
+    assert c1["tensor"] - c0["tensor"] >= 2 and c1["general"] == c0["general"]
+    ctx.set_tensor_core_min_tokens(0)
+    general = gl.forward(x)
+    ctx.set_tensor_core_min_tokens(32)
+    want = ol.forward(x)
+    assert tol_ok(general, want)
+    assert tol_ok(tc, want), float(np.abs(tc - want).max())
+    # the split leaves 2^-17 of each activation behind: far inside the tolerance
+    rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
+    assert float(np.abs(tc.astype(np.float64) - want).max()) < 2e-4 * rms + 1e-3 * float(np.abs(want).max())
+    gl.close()
