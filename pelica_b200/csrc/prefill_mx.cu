@@ -73,7 +73,7 @@ __device__ __forceinline__ void mx_cp16(uint32_t dst, const void *src) {
 __device__ __forceinline__ bool mx_bar_test(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       " selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
       : "r"(mx_s32(bar)), "r"(parity)
@@ -107,17 +107,35 @@ void launch_split_bf16(const Launch &L, const float *x, size_t n, void *hi, void
   if (L.count) ++*L.count;
 }
 
-// eight E2M1 codes (a word's nibbles 0..7 of bytes j.. : low nibbles or high nibbles already
-// isolated as 4 bytes in `c4`, one code in the low nibble of each byte) times 2^(e-128) as
-// four bf16 pairs is done two codes at a time below. One code: magnitude m = c & 7 is
-// {0,1,2,3,4,6,8,12}[m] = (1 + (m & 1) / 2) * 2^(m >> 1) for m >= 2, 1 for m = 1; times the
-// scale 2^(e-128) its bf16 pattern is ((e - 1) << 7) + (m >= 2 ? m << 6 : 0), zero for m = 0.
-__device__ __forceinline__ uint32_t mx_code_bf16(uint32_t c, uint32_t base) {
-  const uint32_t m = c & 7u;
-  uint32_t v = base + (m >= 2u ? (m << 6) : 0u);
-  if (m == 0u) v = 0u;
-  return v | ((c & 8u) << 12);
+// Four E2M1 codes (one in the low nibble of each byte of c4) -> the four bf16 patterns of
+// code * 2^(e-128), as two words (codes 0,1 and 2,3), by byte-table look-ups (prmt): the low
+// and the high byte of the offset {0, 0, 128, 192, 256, 320, 384, 448}[m] that magnitude m adds to
+// the scale's own pattern `base2` ((e - 1) << 7 in both halves), the sign into bit 15, and a
+// mask that zeroes the lanes with m = 0.
+__device__ __forceinline__ void mx_decode4(uint32_t c4, uint32_t base2, uint32_t &w01, uint32_t &w23) {
+  const uint32_t m = c4 & 0x07070707u;
+  const uint32_t sel = (m & 0x7u) | ((m >> 4) & 0x70u) | ((m >> 8) & 0x700u) | ((m >> 12) & 0x7000u);
+  const uint32_t lo = __byte_perm(0xc0800000u, 0xc0804000u, sel);
+  const uint32_t hi = __byte_perm(0x00000000u, 0x01010101u, sel);
+  const uint32_t nz = __byte_perm(0xffffff00u, 0xffffffffu, sel);
+  const uint32_t hs = hi | ((c4 & 0x08080808u) << 4);
+  const uint32_t d01 = __byte_perm(lo, hs, 0x5140), d23 = __byte_perm(lo, hs, 0x7362);
+  w01 = (d01 + base2) & __byte_perm(nz, nz, 0x1100);
+  w23 = (d23 + base2) & __byte_perm(nz, nz, 0x3322);
 }
+
+// Compile with -DPM_MX_TRACE to stamp the phases of CTA (0, 0) with the SM clock:
+// [worker thread 0 | issuing thread][chunk][stamp]; read back with pm_debug_mx_trace.
+#ifdef PM_MX_TRACE
+__device__ unsigned long long g_mx_trace[2 * 64 * 8];
+#define MX_STAMP(who, kc, i)                                                                   \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && (kc) < 64) g_mx_trace[(((who) * 64) + (kc)) * 8 + (i)] = clock64();
+extern "C" __attribute__((visibility("default"))) int pm_debug_mx_trace(unsigned long long *out) {
+  return (int)cudaMemcpyFromSymbol(out, g_mx_trace, sizeof(g_mx_trace));
+}
+#else
+#define MX_STAMP(who, kc, i)
+#endif
 
 struct MxArgs {
   LayerDev ly;
@@ -186,23 +204,32 @@ __global__ void __launch_bounds__(MX_NT, 1) k_tc_mx(const MxArgs A) {
     // ================= the issuing warp =================
     // instruction descriptor: D f32, A and B bf16, both K-major, N = npad, M = 128
     const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MX_M >> 4) << 24);
+    const uint64_t da0 = mx_desc(sStage_a, MX_M * 16u, 128u);
+    const uint64_t dbh0 = mx_desc(sStage_a + MX_A_BYTES, bpitch, 128u);
     for (int kc = 0; kc < nkc; kc++) {
       const int s = kc % MX_ST;
       // full[s]: named barrier 1 + s (workers arrive, this warp waits)
       asm volatile("bar.sync %0, %1;" ::"r"(1 + s), "n"(MX_NT) : "memory");
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if ((tid & 31) == 0) {
-        const uint32_t sa = sStage_a + (uint32_t)s * MX_STAGE;
+        MX_STAMP(1, kc, 0)
+        // (descriptors of stage s, step ks = those of stage 0, step 0 plus the byte offset >> 4 in
+        // the address field: shared memory addresses stay below 2^18)
+        const uint32_t so = (uint32_t)s * MX_STAGE;
         const int ksteps = min(4, (cols - kc * MX_KC) / 16);  // (a trailing single block: 2 steps)
-        for (int ks = 0; ks < ksteps; ks++) {
-          const uint64_t da = mx_desc(sa + (uint32_t)(2 * ks) * (MX_M * 16u), MX_M * 16u, 128u);
-          const uint64_t dbh = mx_desc(sa + MX_A_BYTES + (uint32_t)(2 * ks) * bpitch, bpitch, 128u);
-          const uint64_t dbl = mx_desc(sa + MX_A_BYTES + MX_B_BYTES + (uint32_t)(2 * ks) * bpitch, bpitch, 128u);
-          mx_mma(tmem, da, dbh, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
-          mx_mma(tmem, da, dbl, idesc, 1u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+          if (ks < ksteps) {
+            const uint64_t da = da0 + ((so + (uint32_t)(2 * ks) * (MX_M * 16u)) >> 4);
+            const uint64_t dbh = dbh0 + ((so + (uint32_t)(2 * ks) * bpitch) >> 4);
+            const uint64_t dbl = dbh + (MX_B_BYTES >> 4);
+            mx_mma(tmem, da, dbh, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
+            mx_mma(tmem, da, dbl, idesc, 1u);
+          }
         }
         mx_commit(&bar_empty[s]);
         if (kc == nkc - 1) mx_commit(bar_done);
+        MX_STAMP(1, kc, 1)
       }
       __syncwarp();
     }
@@ -217,22 +244,32 @@ __global__ void __launch_bounds__(MX_NT, 1) k_tc_mx(const MxArgs A) {
       brow[i] = t < nvalid ? (A.down ? (int)(off + n0 + t) : (int)A.g.pair_token[off + n0 + t]) : -1;
     }
     const int bc = tid & 7;
-    auto issue_b = [&](int kc) {  // the tokens' chunk kc -> its stage, asynchronously (one group)
-      if (kc < nkc) {
-        const uint32_t sb = sStage_a + (uint32_t)(kc % MX_ST) * MX_STAGE + MX_A_BYTES;
-        const int k0 = kc * MX_KC + 8 * bc;
-        if (k0 < cols) {
+    // (through registers: 16-byte cp.async moves about 21 bytes a cycle per SM, a chunk's 32 KB of
+    // activations would take three times as long as its products)
+    uint4 breg[4];
+    auto load_b = [&](int kc) {  // the tokens' chunk kc -> registers
+      const int k0 = kc * MX_KC + 8 * bc;
+      const bool on = kc < nkc && k0 < cols;
 #pragma unroll
-          for (int i = 0; i < 2; i++) {
-            if (brow[i] < 0) continue;
-            const int t = (tid >> 3) + 64 * i;
-            const uint32_t dst = sb + (uint32_t)bc * bpitch + (uint32_t)t * 16u;
-            mx_cp16(dst, A.xhi + (size_t)brow[i] * cols + k0);
-            mx_cp16(dst + MX_B_BYTES, A.xlo + (size_t)brow[i] * cols + k0);
-          }
+      for (int i = 0; i < 2; i++) {
+        if (on && brow[i] >= 0) {
+          breg[2 * i] = __ldg((const uint4 *)(A.xhi + (size_t)brow[i] * cols + k0));
+          breg[2 * i + 1] = __ldg((const uint4 *)(A.xlo + (size_t)brow[i] * cols + k0));
         }
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto store_b = [&](int kc) {  // registers -> chunk kc's stage
+      if (kc >= nkc) return;
+      uint8_t *sb = sStage + (size_t)(kc % MX_ST) * MX_STAGE + MX_A_BYTES;
+      if (kc * MX_KC + 8 * bc >= cols) return;
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        if (brow[i] < 0) continue;
+        const int t = (tid >> 3) + 64 * i;
+        uint8_t *dst = sb + (size_t)bc * bpitch + (size_t)t * 16;
+        *(uint4 *)dst = breg[2 * i];
+        *(uint4 *)(dst + MX_B_BYTES) = breg[2 * i + 1];
+      }
     };
     // padding tokens (and, in a trailing half chunk, the missing K): zero operands, once
 #pragma unroll
@@ -267,22 +304,16 @@ __global__ void __launch_bounds__(MX_NT, 1) k_tc_mx(const MxArgs A) {
         rsc = 0;
       }
     };
-    auto store_a = [&](int kc) {
+    auto store_a = [&](int kc, const uint2 raw, const uint32_t rsc) {  // (the bytes loaded one chunk earlier)
       uint8_t *sa = sStage + (size_t)(kc % MX_ST) * MX_STAGE;
-      // (e < 2: the scale's own subnormal branch, src/oss_kernels.rs:42-45; decoded through f32)
+      // (e < 2, the scale's own subnormal branch, src/oss_kernels.rs:42-45, and scales near the top of the range: decoded through f32)
       uint32_t lo4[4], hi4[4];
-      if (rsc >= 2u || (raw.x | raw.y) == 0u) {
-        const uint32_t base = (rsc - 1u) << 7;
-        const uint32_t w[2] = {raw.x, raw.y};
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-#pragma unroll
-          for (int p = 0; p < 2; p++) {  // bytes 2p, 2p+1 of word j: two values a 32-bit result
-            const uint32_t b0 = (w[j] >> (16 * p)) & 0xffu, b1 = (w[j] >> (16 * p + 8)) & 0xffu;
-            lo4[2 * j + p] = mx_code_bf16(b0 & 15u, base) | (mx_code_bf16(b1 & 15u, base) << 16);
-            hi4[2 * j + p] = mx_code_bf16(b0 >> 4, base) | (mx_code_bf16(b1 >> 4, base) << 16);
-          }
-        }
+      if ((rsc >= 2u && rsc < 250u) || (raw.x | raw.y) == 0u) {
+        const uint32_t base2 = ((rsc - 1u) << 7) * 0x00010001u;
+        mx_decode4(raw.x, base2, lo4[0], lo4[1]);
+        mx_decode4(raw.y, base2, lo4[2], lo4[3]);
+        mx_decode4(raw.x >> 4, base2, hi4[0], hi4[1]);
+        mx_decode4(raw.y >> 4, base2, hi4[2], hi4[3]);
       } else {
         const float s = pm_e8(rsc);
         const uint32_t w[2] = {raw.x, raw.y};
@@ -300,37 +331,38 @@ __global__ void __launch_bounds__(MX_NT, 1) k_tc_mx(const MxArgs A) {
       *(uint4 *)(sa + (size_t)(4 * b2 + 2 + hh) * (MX_M * 16) + (size_t)m * 16) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
     };
 
-    issue_b(0);
-    issue_b(1);
+    // chunk 0's activations directly, chunk 1's and the weight bytes of chunk 0 in registers
+    // (one chunk ahead: two chunks ahead, with twice the registers, measured slower)
+    load_b(0);
+    store_b(0);
+    load_b(1);
     load_a(0);
     bool dead = false;
     for (int kc = 0; kc < nkc; kc++) {
       const int s = kc % MX_ST;
-      // the stage chunk kc + 2 goes to held chunk kc + 2 - MX_ST: its products must be done
-      if (kc + 2 >= MX_ST && kc + 2 < nkc) {
-        const int kp = kc + 2 - MX_ST;  // (completion number kp / MX_ST of that stage's barrier)
+      if (tid == 0) { MX_STAMP(0, kc, 0) }
+      // chunk kc + 1's activations (in registers since the last round) go to the stage that held
+      // chunk kc + 1 - MX_ST: its products must be done
+      if (kc + 1 >= MX_ST && kc + 1 < nkc) {
+        const int kp = kc + 1 - MX_ST;  // (completion number kp / MX_ST of that stage's barrier)
         if (!dead && !mx_bar_wait(&bar_empty[kp % MX_ST], (uint32_t)((kp / MX_ST) & 1), A.err, A.wait_ns)) dead = true;
       }
-      issue_b(kc + 2);
-      // this chunk's stage held chunk kc - MX_ST: waited for two iterations ago (as kc + 2 then)
+      if (tid == 0) { MX_STAMP(0, kc, 1) }
+      store_b(kc + 1);
+      load_b(kc + 2);
+      if (tid == 0) { MX_STAMP(0, kc, 2) }
+      // this chunk's own stage held chunk kc - MX_ST: waited for in the last round (as kc + 1 then).
+      // The next chunk's weight bytes are requested before this chunk's are decoded.
       const uint2 raw_now = raw;
       const uint32_t rsc_now = rsc;
       load_a(kc + 1);
-      {
-        const uint2 keep = raw;
-        const uint32_t keeps = rsc;
-        raw = raw_now;
-        rsc = rsc_now;
-        store_a(kc);
-        raw = keep;
-        rsc = keeps;
-      }
-      asm volatile("cp.async.wait_group 2;" ::: "memory");  // the tokens' chunk kc has landed
+      store_a(kc, raw_now, rsc_now);
+      if (tid == 0) { MX_STAMP(0, kc, 3) }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("bar.arrive %0, %1;" ::"r"(1 + s), "n"(MX_NT) : "memory");
+      if (tid == 0) { MX_STAMP(0, kc, 5) }
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
     // ---- epilogue: all products done -> TMEM lane m, a quarter of the token columns ----
     if (!mx_bar_test(bar_done, 0)) mx_bar_wait(bar_done, 0, A.err, A.wait_ns);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
