@@ -42,7 +42,8 @@ enum {
   PM_ERR_OOM = -4,         /* device or pinned allocation failed            */
   PM_ERR_STATE = -5,       /* weights missing, layer not finalised ...      */
   PM_ERR_TIMEOUT = -6,     /* a bounded device-side wait gave up            */
-  PM_ERR_LIMIT = -7        /* a size beyond a documented fixed maximum      */
+  PM_ERR_LIMIT = -7,       /* a size beyond a documented fixed maximum      */
+  PM_ERR_COMM = -8         /* the collective library is missing or reported an error */
 };
 
 /* ---- ggml tensor type ids (src/gguf.rs:85-121) ------------------------- */
@@ -145,6 +146,7 @@ typedef struct pm_plan_out {
 typedef struct pm_ctx pm_ctx;
 typedef struct pm_layer pm_layer;
 typedef struct pm_stack pm_stack;
+typedef struct pm_ep pm_ep;
 
 /* ---- library ----------------------------------------------------------- */
 PM_API const char *pm_last_error(void);
@@ -260,6 +262,35 @@ PM_API int32_t pm_shared(pm_layer *layer, const float *x, int32_t T, float *out)
 PM_API int32_t pm_combine(pm_layer *layer, const float *pair_out, const uint32_t *ids,
                           const float *w, const float *shared_out, int32_t T, float *y,
                           uint32_t flags);
+
+/* ---- expert parallelism: experts sharded over the GPUs of a node ----------------------
+ * replaces: the bridge, Pelica's only expert-offload mechanism: `RUN` sends activations and
+ * per-expert (token, weight) rows to the machine that holds the experts and gets the summed
+ * outputs back (src/bridge.rs:412-466, host side `Remote::start/finish/fail`
+ * src/bridge.rs:730-786, callers src/ds4.rs:1527-1552,1695-1713). Here the transport is NCCL
+ * (grouped ncclSend/ncclRecv on the context's stream, NVLink/NVSwitch), one rank per GPU:
+ * expert e lives on rank e / (n_exp / world); router, selection bias and shared expert are
+ * replicated; tokens are data-parallel. NCCL is bound at run time (dlopen of libnccl.so.2).
+ * Failure behaviour: a missing library or a failed NCCL call is PM_ERR_COMM (also the
+ * asynchronous errors NCCL reports, polled by every call); a rank that never enters the call
+ * shows as PM_ERR_TIMEOUT on the others after pm_ep_set_timeout_ms (default 60 s), as the
+ * bridge's callers fall back when a link fails (src/ds4.rs:1706-1710). */
+/* 128 bytes identifying a new communicator: rank 0 calls this and hands the bytes to the other
+ * ranks by its own means (a file, a socket, its launcher) */
+PM_API int32_t pm_ep_unique_id(uint8_t *out128);
+/* collective: every rank calls it with the same id; the context's GPU joins the communicator */
+PM_API int32_t pm_ep_init(pm_ctx *ctx, const uint8_t *unique_id128, int32_t rank, int32_t world, pm_ep **out);
+PM_API int32_t pm_ep_destroy(pm_ep *ep);
+PM_API int32_t pm_ep_set_timeout_ms(pm_ep *ep, int64_t ms);
+/* collective: y[T][d] = the layer's output for this rank's T tokens (x, y device pointers; T may
+ * differ per rank and may be 0). The layer must have been created with first_local_expert =
+ * rank * n_exp / world and n_exp_local = n_exp / world. Same values as pm_moe_forward on a
+ * layer that holds every expert. Work is queued on the context's stream; the call waits on the
+ * host once, for the ranks' pair counts. flags: PM_FWD_ACCUMULATE. */
+PM_API int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *layer, const float *x, int32_t T, float *y, uint32_t flags);
+/* the last call's traffic: out[4] = rows sent, rows received, bytes sent, bytes received
+ * (to and from other ranks; rows that stay on the rank are not counted) */
+PM_API int32_t pm_ep_last_stats(pm_ep *ep, uint64_t *out);
 
 /* ---- format checks (bit-exact against the reference arithmetic) -------- */
 /* replaces: `deq4` src/moe_kernels.rs:63-84, `deq_row` src/q4x_cpu.rs:443-496 */

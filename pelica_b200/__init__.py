@@ -87,6 +87,12 @@ ABI = {
     "pm_experts_rows": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP, _VP]),
     "pm_shared": (C.c_int32, [_VP, _VP, C.c_int32, _VP]),
     "pm_combine": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32, _VP, C.c_uint32]),
+    "pm_ep_unique_id": (C.c_int32, [_VP]),
+    "pm_ep_init": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.POINTER(_VP)]),
+    "pm_ep_destroy": (C.c_int32, [_VP]),
+    "pm_ep_set_timeout_ms": (C.c_int32, [_VP, C.c_int64]),
+    "pm_moe_forward_ep": (C.c_int32, [_VP, _VP, _VP, C.c_int32, _VP, C.c_uint32]),
+    "pm_ep_last_stats": (C.c_int32, [_VP, _VP]),
     "pm_dequant": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP]),
     "pm_quant_act": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP, _VP, _VP]),
     "pm_rmsnorm": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_float, _VP]),
@@ -541,3 +547,56 @@ class Stack:
         if r < 0:
             _check(r)
         return out.reshape(len(out) // (len(self.layers) * 16), len(self.layers), 16)
+
+
+def ep_unique_id() -> bytes:
+    """128 bytes naming a new expert-parallel communicator (rank 0 makes them, every rank passes them
+    to ExpertParallel)."""
+    buf = (C.c_uint8 * 128)()
+    _check(load_library().pm_ep_unique_id(buf))
+    return bytes(buf)
+
+
+class ExpertParallel:
+    """One rank of an expert-parallel group (pm_ep_*): experts sharded over the ranks' GPUs,
+    NCCL dispatch and combine inside the library."""
+
+    def __init__(self, ctx: Context, unique_id: bytes, rank: int, world: int):
+        self.ctx = ctx
+        self.lib = ctx.lib
+        self.rank, self.world = rank, world
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        h = _VP()
+        _check(self.lib.pm_ep_init(ctx.h, buf, rank, world, C.byref(h)))
+        self.h = h.value
+
+    def close(self):
+        if self.h:
+            self.lib.pm_ep_destroy(self.h)
+            self.h = None
+
+    def set_timeout_ms(self, ms: int):
+        _check(self.lib.pm_ep_set_timeout_ms(self.h, ms))
+
+    def forward_dev(self, layer: MoeLayer, x, T: int, y, accumulate: bool = False):
+        """x, y: device pointers (DevBuf or int) of [T, d] f32."""
+        xp = x.ptr if isinstance(x, DevBuf) else x
+        yp = y.ptr if isinstance(y, DevBuf) else y
+        _check(self.lib.pm_moe_forward_ep(self.h, layer.h, xp, T, yp, PM_FWD_ACCUMULATE if accumulate else 0))
+
+    def forward(self, layer: MoeLayer, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        T, d = x.shape
+        dx = self.ctx.alloc(max(x.nbytes, 4)).upload(x) if T else self.ctx.alloc(4)
+        dy = self.ctx.alloc(max(x.nbytes, 4))
+        self.forward_dev(layer, dx, T, dy)
+        self.ctx.sync()
+        out = dy.download(np.float32, (T, d)) if T else np.zeros((0, d), np.float32)
+        dx.free()
+        dy.free()
+        return out
+
+    def last_stats(self) -> dict:
+        out = np.zeros(4, np.uint64)
+        _check(self.lib.pm_ep_last_stats(self.h, out.ctypes.data))
+        return dict(rows_sent=int(out[0]), rows_received=int(out[1]), bytes_sent=int(out[2]), bytes_received=int(out[3]))

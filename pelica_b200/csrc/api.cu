@@ -851,7 +851,9 @@ static Groups plan_groups(const PlanDev &pl, int E) {
 }
 
 // routed experts: x (and its Q8x form) -> eo[P][d]
-static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, const float *w) {
+// prequant: S.xq / S.xd / S.xbsum (and their derived forms) already hold the rows' quantised
+// form (rows received from another rank arrive quantised)
+static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, const float *w, bool prequant = false) {
   pm_ctx *c = ly->ctx;
   const LayerDev &dv = ly->dev;
   const pm_layer_desc &D = dv.desc;
@@ -859,8 +861,8 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   int P = T * D.top_k;
   Groups g = plan_groups(S.plan, D.n_exp);
   bool q8 = D.act_quant == PM_AQ_Q8X_256, q32 = D.act_quant == PM_AQ_Q8_32;
-  if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
-  if (q32) { PROF(c, PH_QUANT_X); launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd); }
+  if (q8 && !prequant) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
+  if (q32 && !prequant) { PROF(c, PH_QUANT_X); launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd); }
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   // MXFP4 weights with f32 activations: the bf16 tensor-core kernels (tolerance parity, not bits)
   const bool tcmx = D.act_quant == PM_AQ_F32 && D.type_gate == PM_TYPE_MXFP4 && D.type_up == PM_TYPE_MXFP4 &&
@@ -1730,4 +1732,338 @@ extern "C" int32_t pm_stack_forward(pm_stack *s, const float *x, int32_t T, floa
     CU(cudaStreamSynchronize(c->stream));
   }
   return PM_OK;
+}
+
+
+// ---------------------------------------------------------------------------
+// expert parallelism over NCCL (one rank per GPU; experts sharded by rank)
+// ---------------------------------------------------------------------------
+// NCCL is bound at run time (dlopen), so the library loads on hosts without it and a process
+// that already carries an NCCL (a framework's) shares that copy. Only the calls below are used.
+#include <dlfcn.h>
+
+#include <chrono>
+
+typedef struct ncclComm *pm_ncclComm_t;
+typedef struct { char internal[128]; } pm_ncclUniqueId;
+enum { PM_NCCL_INT8 = 0, PM_NCCL_UINT8 = 1, PM_NCCL_INT32 = 2, PM_NCCL_UINT32 = 3, PM_NCCL_FLOAT32 = 7 };
+struct NcclApi {
+  void *handle = nullptr;
+  int (*GetUniqueId)(pm_ncclUniqueId *) = nullptr;
+  int (*CommInitRank)(pm_ncclComm_t *, int, pm_ncclUniqueId, int) = nullptr;
+  int (*CommDestroy)(pm_ncclComm_t) = nullptr;
+  int (*CommAbort)(pm_ncclComm_t) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  int (*Send)(const void *, size_t, int, int, pm_ncclComm_t, cudaStream_t) = nullptr;
+  int (*Recv)(void *, size_t, int, int, pm_ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void *, void *, size_t, int, pm_ncclComm_t, cudaStream_t) = nullptr;
+  int (*CommGetAsyncError)(pm_ncclComm_t, int *) = nullptr;
+  const char *(*GetErrorString)(int) = nullptr;
+};
+static NcclApi g_nccl;
+
+static int32_t nccl_load() {
+  if (g_nccl.handle) return PM_OK;
+  void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return fail(PM_ERR_COMM, "NCCL is not available: %s", dlerror());
+  NcclApi a;
+  a.handle = h;
+#define PM_NCCL_SYM(field, name)                                                     \
+  do {                                                                               \
+    *(void **)(&a.field) = dlsym(h, name);                                           \
+    if (!a.field) return fail(PM_ERR_COMM, "NCCL symbol %s is missing", name);       \
+  } while (0)
+  PM_NCCL_SYM(GetUniqueId, "ncclGetUniqueId");
+  PM_NCCL_SYM(CommInitRank, "ncclCommInitRank");
+  PM_NCCL_SYM(CommDestroy, "ncclCommDestroy");
+  PM_NCCL_SYM(CommAbort, "ncclCommAbort");
+  PM_NCCL_SYM(GroupStart, "ncclGroupStart");
+  PM_NCCL_SYM(GroupEnd, "ncclGroupEnd");
+  PM_NCCL_SYM(Send, "ncclSend");
+  PM_NCCL_SYM(Recv, "ncclRecv");
+  PM_NCCL_SYM(AllGather, "ncclAllGather");
+  PM_NCCL_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+  PM_NCCL_SYM(GetErrorString, "ncclGetErrorString");
+#undef PM_NCCL_SYM
+  g_nccl = a;
+  return PM_OK;
+}
+#define NC(call)                                                                                  \
+  do {                                                                                            \
+    int r_ = (call);                                                                              \
+    if (r_ != 0) return fail(PM_ERR_COMM, "%s: %s (%s:%d)", #call, g_nccl.GetErrorString(r_), __FILE__, __LINE__); \
+  } while (0)
+
+struct pm_ep {
+  pm_ctx *ctx = nullptr;   // the rank's context: routing, the rank's own tokens, the exchanges' stream
+  pm_ctx *sub = nullptr;   // a second workspace on the same stream: the rows received from the other ranks
+  pm_ncclComm_t comm = nullptr;
+  int rank = 0, world = 1;
+  int32_t *d_cnt = nullptr;  // [W] pairs this rank sends to each rank, then [W*W] everybody's
+  int32_t *h_cnt = nullptr;  // pinned copy of the [W*W] table
+  cudaEvent_t ev = nullptr;
+  int64_t timeout_ms = 60000;  // host watchdog on the counts (a peer that never enters the call)
+  uint64_t stats[4] = {0, 0, 0, 0};  // last call: rows sent, rows received, bytes sent, bytes received
+};
+
+extern "C" int32_t pm_ep_unique_id(uint8_t *out) {
+  if (!out) return fail(PM_ERR_INVALID, "pm_ep_unique_id: null argument");
+  TRY(nccl_load());
+  pm_ncclUniqueId id;
+  NC(g_nccl.GetUniqueId(&id));
+  memcpy(out, id.internal, 128);
+  return PM_OK;
+}
+
+extern "C" int32_t pm_ep_destroy(pm_ep *ep) {
+  if (!ep) return PM_OK;
+  cudaSetDevice(ep->ctx->device);
+  cudaError_t q = cudaStreamQuery(ep->ctx->stream);
+  if (ep->comm) {
+    // work still queued behind a peer that never came: abort instead of waiting for it
+    if (q == cudaErrorNotReady) g_nccl.CommAbort(ep->comm);
+    else g_nccl.CommDestroy(ep->comm);
+  }
+  cudaGetLastError();
+  if (ep->sub) {
+    if (ep->sub->ws) cudaFree(ep->sub->ws);
+    delete ep->sub;
+  }
+  if (ep->d_cnt) cudaFree(ep->d_cnt);
+  if (ep->h_cnt) cudaFreeHost(ep->h_cnt);
+  if (ep->ev) cudaEventDestroy(ep->ev);
+  delete ep;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_ep_init(pm_ctx *ctx, const uint8_t *unique_id, int32_t rank, int32_t world, pm_ep **out) {
+  if (!ctx || !unique_id || !out || world < 1 || world > 64 || rank < 0 || rank >= world)
+    return fail(PM_ERR_INVALID, "pm_ep_init: bad argument (rank %d of %d)", rank, world);
+  TRY(nccl_load());
+  CU(cudaSetDevice(ctx->device));
+  pm_ep *ep = new (std::nothrow) pm_ep();
+  if (!ep) return fail(PM_ERR_OOM, "host allocation");
+  ep->ctx = ctx;
+  ep->rank = rank;
+  ep->world = world;
+  ep->sub = new (std::nothrow) pm_ctx();
+  if (!ep->sub) { delete ep; return fail(PM_ERR_OOM, "host allocation"); }
+  ep->sub->device = ctx->device;
+  ep->sub->stream = ctx->stream;
+  ep->sub->own_stream = false;
+  ep->sub->dev_err = ctx->dev_err;
+  cudaError_t e = cudaMalloc(&ep->d_cnt, (size_t)(world + world * world) * 4);
+  if (e == cudaSuccess) e = cudaHostAlloc((void **)&ep->h_cnt, (size_t)world * world * 4, cudaHostAllocDefault);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ep->ev, cudaEventDisableTiming);
+  if (e != cudaSuccess) {
+    pm_ep_destroy(ep);
+    return fail(PM_ERR_CUDA, "pm_ep_init: %s", cudaGetErrorString(e));
+  }
+  pm_ncclUniqueId id;
+  memcpy(id.internal, unique_id, 128);
+  int r = g_nccl.CommInitRank(&ep->comm, world, id, rank);
+  if (r != 0) {
+    ep->comm = nullptr;
+    pm_ep_destroy(ep);
+    return fail(PM_ERR_COMM, "ncclCommInitRank: %s", g_nccl.GetErrorString(r));
+  }
+  *out = ep;
+  return PM_OK;
+}
+
+extern "C" int32_t pm_ep_set_timeout_ms(pm_ep *ep, int64_t ms) {
+  if (!ep || ms < 1) return fail(PM_ERR_INVALID, "pm_ep_set_timeout_ms");
+  ep->timeout_ms = ms;
+  return PM_OK;
+}
+extern "C" int32_t pm_ep_last_stats(pm_ep *ep, uint64_t *out) {
+  if (!ep || !out) return fail(PM_ERR_INVALID, "pm_ep_last_stats");
+  for (int i = 0; i < 4; i++) out[i] = ep->stats[i];
+  return PM_OK;
+}
+
+static int32_t ep_comm_ok(pm_ep *ep) {
+  int ae = 0;
+  NC(g_nccl.CommGetAsyncError(ep->comm, &ae));
+  if (ae != 0) return fail(PM_ERR_COMM, "NCCL reported an asynchronous error: %s", g_nccl.GetErrorString(ae));
+  return PM_OK;
+}
+
+// y[T][d] for this rank's T tokens; the layer holds experts [rank * E / W, (rank + 1) * E / W).
+// Per call: route and plan the rank's tokens; every rank learns every rank's per-destination pair
+// counts (one small all-gather, read by the host while the shared expert runs); the pairs' rows go
+// to the ranks that hold their experts in their quantised wire form (Q8x: int8 + scales + group
+// sums, 3.5 times fewer bytes than f32; sender-side quantisation is the same pure function the
+// receiver would apply) together with (expert, weight); the rows received run through the local
+// experts; the outputs travel back and are combined in k order with the shared expert's.
+extern "C" int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *ly, const float *x, int32_t T, float *y, uint32_t flags) {
+  if (!ep || !ly) return fail(PM_ERR_INVALID, "pm_moe_forward_ep: null argument");
+  TRY(layer_ready(ly, true));
+  TRY(check_T(T));
+  pm_ctx *c = ep->ctx;
+  if (ly->ctx != c) return fail(PM_ERR_INVALID, "pm_moe_forward_ep: the layer belongs to another context");
+  const LayerDev &dv = ly->dev;
+  const pm_layer_desc &D = dv.desc;
+  const int W = ep->world, rank = ep->rank, E = D.n_exp, K = D.top_k, d = D.d;
+  if (E % W) return fail(PM_ERR_INVALID, "%d experts do not split over %d ranks", E, W);
+  const int per = E / W;
+  if (dv.first_local != rank * per || dv.n_local != per)
+    return fail(PM_ERR_INVALID, "rank %d of %d must hold experts [%d, %d); the layer holds [%d, %d)", rank, W, rank * per,
+                (rank + 1) * per, dv.first_local, dv.first_local + dv.n_local);
+  if (T > 0 && (!x || !y || !is_device_ptr(x) || !is_device_ptr(y)))
+    return fail(PM_ERR_INVALID, "pm_moe_forward_ep: x and y must be device pointers");
+  CU(cudaSetDevice(c->device));
+  const bool q8 = D.act_quant == PM_AQ_Q8X_256;
+  const size_t P = (size_t)T * K;
+  const int nd = q8 ? d / 256 : 0, nbs = q8 ? d / 32 : 0;
+  const size_t row_bytes = q8 ? (size_t)d : (size_t)d * 4;  // wire form of a row: int8 (Q8x) or f32
+  Launch L = c->launch();
+
+  // ---- this rank's tokens: route, plan, counts ----
+  TRY(ws_reserve(c, scratch_bytes(D, T > 0 ? T : 1) + al(P * row_bytes) + al(P * (nd + 1) * 4) + al(P * (nbs + 1) * 4) +
+                        al(P * 8) + 4096));
+  Scratch S;
+  scratch_carve(c, D, T > 0 ? T : 1, S);
+  uint8_t *srows = ws_take<uint8_t>(c, P * row_bytes);
+  float *sd = ws_take<float>(c, P * (size_t)(nd + 1));
+  int32_t *sbs = ws_take<int32_t>(c, P * (size_t)(nbs + 1));
+  uint32_t *smeta = ws_take<uint32_t>(c, P * 2);
+  if (T > 0) {
+    { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
+    { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
+  }
+  { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan, c->dev_err); }
+  launch_ep_rank_counts(L, S.plan.cnt, E, W, ep->d_cnt);
+  NC(g_nccl.AllGather(ep->d_cnt, ep->d_cnt + W, (size_t)W, PM_NCCL_INT32, ep->comm, c->stream));
+  CU(cudaMemcpyAsync(ep->h_cnt, ep->d_cnt + W, (size_t)W * W * 4, cudaMemcpyDeviceToHost, c->stream));
+  CU(cudaEventRecord(ep->ev, c->stream));
+  // ---- meanwhile on the GPU: the rows' wire form and the shared expert ----
+  if (T > 0) {
+    if (q8) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
+    launch_ep_pack(L, (int)P, (int)row_bytes, nd, nbs, q8 ? (const void *)S.xq : (const void *)x, S.xd, S.xbsum,
+                   S.plan.pair_token, S.plan.pair_src, S.ids, S.w, srows, sd, sbs, smeta);
+    TRY(dev_shared(ly, x, T, S));
+  }
+  // ---- the host learns the counts (bounded: a peer that never enters the call shows here) ----
+  {
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+      cudaError_t q = cudaEventQuery(ep->ev);
+      if (q == cudaSuccess) break;
+      if (q != cudaErrorNotReady) return fail(PM_ERR_CUDA, "pm_moe_forward_ep: %s", cudaGetErrorString(q));
+      TRY(ep_comm_ok(ep));
+      if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > ep->timeout_ms)
+        return fail(PM_ERR_TIMEOUT, "pm_moe_forward_ep: the ranks' pair counts did not arrive within %lld ms "
+                                    "(a rank that did not enter the call?)", (long long)ep->timeout_ms);
+    }
+  }
+  std::vector<size_t> scnt(W), soff(W), rcnt(W), roff(W);
+  size_t R = 0, so = 0;
+  for (int j = 0; j < W; j++) {
+    scnt[j] = (size_t)ep->h_cnt[rank * W + j];
+    rcnt[j] = (size_t)ep->h_cnt[j * W + rank];
+    soff[j] = so;
+    roff[j] = R;
+    so += scnt[j];
+    R += rcnt[j];
+  }
+  if (so != P) return fail(PM_ERR_STATE, "pm_moe_forward_ep: %zu pairs planned, %zu counted", P, so);
+  if (R > (size_t)PM_MAX_TOKENS * PM_MAX_TOPK) return fail(PM_ERR_LIMIT, "pm_moe_forward_ep: %zu rows received", R);
+
+  // ---- the rows this rank serves: a second workspace (its size is only known now) ----
+  pm_ctx *sc = ep->sub;
+  sc->prof_on = false;
+  pm_layer_desc D1 = D;
+  D1.top_k = 1;
+  const size_t Rr = R > 0 ? R : 1;
+  TRY(ws_reserve(sc, scratch_bytes(D1, (int)Rr) + al(Rr * row_bytes) + al(Rr * 8) + 2 * al(Rr * 4) + al(Rr * (size_t)d * 4) + 4096));
+  Scratch RS;
+  scratch_carve(sc, D1, (int)Rr, RS);
+  uint8_t *rrows = q8 ? (uint8_t *)RS.xq : ws_take<uint8_t>(sc, Rr * row_bytes);
+  uint32_t *rmeta = ws_take<uint32_t>(sc, Rr * 2);
+  uint32_t *reid = ws_take<uint32_t>(sc, Rr);
+  float *rw = ws_take<float>(sc, Rr);
+  float *orows = ws_take<float>(sc, Rr * (size_t)d);
+
+  // ---- dispatch ----
+  {
+    PROF(c, PH_FUSED);
+    NC(g_nccl.GroupStart());
+    for (int j = 0; j < W; j++) {
+      if (j == rank) continue;
+      if (scnt[j]) {
+        NC(g_nccl.Send(srows + soff[j] * row_bytes, scnt[j] * row_bytes, PM_NCCL_UINT8, j, ep->comm, c->stream));
+        NC(g_nccl.Send(smeta + soff[j] * 2, scnt[j] * 2, PM_NCCL_UINT32, j, ep->comm, c->stream));
+        if (q8) {
+          NC(g_nccl.Send(sd + soff[j] * nd, scnt[j] * nd, PM_NCCL_FLOAT32, j, ep->comm, c->stream));
+          NC(g_nccl.Send(sbs + soff[j] * nbs, scnt[j] * nbs, PM_NCCL_INT32, j, ep->comm, c->stream));
+        }
+      }
+      if (rcnt[j]) {
+        NC(g_nccl.Recv(rrows + roff[j] * row_bytes, rcnt[j] * row_bytes, PM_NCCL_UINT8, j, ep->comm, c->stream));
+        NC(g_nccl.Recv(rmeta + roff[j] * 2, rcnt[j] * 2, PM_NCCL_UINT32, j, ep->comm, c->stream));
+        if (q8) {
+          NC(g_nccl.Recv(RS.xd + roff[j] * nd, rcnt[j] * nd, PM_NCCL_FLOAT32, j, ep->comm, c->stream));
+          NC(g_nccl.Recv(RS.xbsum + roff[j] * nbs, rcnt[j] * nbs, PM_NCCL_INT32, j, ep->comm, c->stream));
+        }
+      }
+    }
+    NC(g_nccl.GroupEnd());
+    if (scnt[rank]) {  // the pairs that stay on this rank
+      const size_t o = soff[rank], r0 = roff[rank], n = scnt[rank];
+      CU(cudaMemcpyAsync(rrows + r0 * row_bytes, srows + o * row_bytes, n * row_bytes, cudaMemcpyDeviceToDevice, c->stream));
+      CU(cudaMemcpyAsync(rmeta + r0 * 2, smeta + o * 2, n * 8, cudaMemcpyDeviceToDevice, c->stream));
+      if (q8) {
+        CU(cudaMemcpyAsync(RS.xd + r0 * nd, sd + o * nd, n * nd * 4, cudaMemcpyDeviceToDevice, c->stream));
+        CU(cudaMemcpyAsync(RS.xbsum + r0 * nbs, sbs + o * nbs, n * nbs * 4, cudaMemcpyDeviceToDevice, c->stream));
+      }
+    }
+  }
+  // ---- the local experts over the received rows ----
+  if (R > 0) {
+    Launch SL = sc->launch();
+    launch_ep_unmeta(SL, (int)R, rmeta, dv.first_local, dv.n_local, reid, rw, c->dev_err);
+    if (q8) launch_q8x_aux(SL, R * (size_t)nd, RS.xbsum, RS.xbm, RS.xs);
+    pm_layer view = *ly;
+    view.ctx = sc;
+    view.dev.desc = D1;
+    view.dev.usage = nullptr;
+    sc->tc_min_tokens = c->tc_min_tokens;
+    sc->wait_ns = c->wait_ns;
+    launch_plan(SL, view.dev, reid, (int)R, RS.plan, c->dev_err);
+    TRY(dev_experts(&view, q8 ? nullptr : (const float *)rrows, (int)R, RS, rw, q8));
+    LayerDev cp = view.dev;
+    cp.desc.weight_fold = PM_FOLD_BEFORE_DOWN;  // plain gather back to row order
+    launch_combine(SL, cp, RS.eo, RS.plan.pair_pos, rw, nullptr, nullptr, (int)R, orows, false);
+    for (int i = 0; i < PM_PATH_N; i++) { c->path_count[i] += sc->path_count[i]; sc->path_count[i] = 0; }
+    c->launches += sc->launches;
+    sc->launches = 0;
+  }
+  // ---- the outputs go home (they arrive in the sender's plan order: S.eo is what combine takes) ----
+  {
+    PROF(c, PH_FUSED);
+    NC(g_nccl.GroupStart());
+    for (int j = 0; j < W; j++) {
+      if (j == rank) continue;
+      if (rcnt[j]) NC(g_nccl.Send(orows + roff[j] * d, rcnt[j] * (size_t)d, PM_NCCL_FLOAT32, j, ep->comm, c->stream));
+      if (scnt[j]) NC(g_nccl.Recv(S.eo + soff[j] * d, scnt[j] * (size_t)d, PM_NCCL_FLOAT32, j, ep->comm, c->stream));
+    }
+    NC(g_nccl.GroupEnd());
+    if (scnt[rank])
+      CU(cudaMemcpyAsync(S.eo + soff[rank] * d, orows + roff[rank] * d, scnt[rank] * (size_t)d * 4, cudaMemcpyDeviceToDevice,
+                         c->stream));
+  }
+  if (T > 0) {
+    PROF(c, PH_COMBINE);
+    launch_combine(L, dv, S.eo, S.plan.pair_pos, S.w, S.shared_out, S.shared_logit, T, y, (flags & PM_FWD_ACCUMULATE) != 0);
+  }
+  CU(cudaGetLastError());
+  ep->stats[0] = P - scnt[rank];
+  ep->stats[1] = R - rcnt[rank];
+  const size_t per_row = row_bytes + 8 + (size_t)nd * 4 + (size_t)nbs * 4;
+  ep->stats[2] = (P - scnt[rank]) * per_row + (R - rcnt[rank]) * (size_t)d * 4;
+  ep->stats[3] = (R - rcnt[rank]) * per_row + (P - scnt[rank]) * (size_t)d * 4;
+  return ep_comm_ok(ep);
 }

@@ -909,3 +909,89 @@ void launch_rmsnorm(const Launch &L, const float *x, int T, int d, float eps, fl
   if (T == 0) return;
   KLAUNCH(L, k_rmsnorm, T, 256, 0, x, T, d, eps, out);
 }
+
+// ===========================================================================
+// expert parallelism: the wire records of a dispatch (replaces the body of the
+// bridge RUN message, src/bridge.rs:412-466: activations and (expert, weight) rows)
+// ===========================================================================
+// pairs routed to each rank's experts: cnt[e] summed over the rank's E / W experts
+__global__ void k_ep_rank_counts(const uint32_t *__restrict__ cnt, int E, int W, int32_t *out) {
+  int r = threadIdx.x;
+  if (r >= W) return;
+  int per = E / W, s = 0;
+  for (int e = r * per; e < (r + 1) * per; e++) s += (int)cnt[e];
+  out[r] = s;
+}
+void launch_ep_rank_counts(const Launch &L, const uint32_t *cnt, int E, int W, int32_t *out) {
+  KLAUNCH(L, k_ep_rank_counts, 1, 64, 0, cnt, E, W, out);
+}
+
+// one CTA per pair p (dispatch-plan order: ascending expert, so every destination rank's
+// pairs are contiguous): the token's row in its wire form and the pair's (expert, weight)
+__global__ void __launch_bounds__(256) k_ep_pack(int P, int row_bytes, int nd, int nbs, const uint8_t *__restrict__ rows,
+                                                 const float *__restrict__ xd, const int32_t *__restrict__ xbs,
+                                                 const uint32_t *__restrict__ pair_token,
+                                                 const uint32_t *__restrict__ pair_src, const uint32_t *__restrict__ ids,
+                                                 const float *__restrict__ w, uint8_t *srows, float *sd, int32_t *sbs,
+                                                 uint32_t *smeta) {
+  const int p = blockIdx.x;
+  if (p >= P) return;
+  const uint32_t t = pair_token[p];
+  const uint4 *src = (const uint4 *)(rows + (size_t)t * row_bytes);
+  uint4 *dst = (uint4 *)(srows + (size_t)p * row_bytes);
+  for (int i = threadIdx.x; i < row_bytes / 16; i += 256) dst[i] = src[i];
+  for (int i = threadIdx.x; i < nd; i += 256) sd[(size_t)p * nd + i] = xd[(size_t)t * nd + i];
+  for (int i = threadIdx.x; i < nbs; i += 256) sbs[(size_t)p * nbs + i] = xbs[(size_t)t * nbs + i];
+  if (threadIdx.x == 0) {
+    const uint32_t s = pair_src[p];
+    smeta[2 * p] = ids[s];
+    smeta[2 * p + 1] = __float_as_uint(w[s]);
+  }
+}
+void launch_ep_pack(const Launch &L, int P, int row_bytes, int nd, int nbs, const void *rows, const float *xd,
+                    const int32_t *xbs, const uint32_t *pair_token, const uint32_t *pair_src, const uint32_t *ids,
+                    const float *w, void *srows, float *sd, int32_t *sbs, uint32_t *smeta) {
+  if (P == 0) return;
+  KLAUNCH(L, k_ep_pack, P, 256, 0, P, row_bytes, nd, nbs, (const uint8_t *)rows, xd, xbs, pair_token, pair_src, ids, w,
+          (uint8_t *)srows, sd, sbs, smeta);
+}
+
+// received (expert, weight) records -> expert ids and weights; an expert this rank does not
+// hold is reported through the error word (and mapped to the rank's first expert so that
+// nothing indexes out of its planes)
+__global__ void k_ep_unmeta(int R, const uint32_t *__restrict__ meta, int first, int n_local, uint32_t *eids, float *w,
+                            int *err) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  uint32_t e = meta[2 * r];
+  if (e < (uint32_t)first || e >= (uint32_t)(first + n_local)) {
+    atomicCAS(err, 0, PM_DEVERR_BAD_EXPERT_ID);
+    e = (uint32_t)first;
+  }
+  eids[r] = e;
+  w[r] = __uint_as_float(meta[2 * r + 1]);
+}
+void launch_ep_unmeta(const Launch &L, int R, const uint32_t *meta, int first, int n_local, uint32_t *eids, float *w,
+                      int *err) {
+  if (R == 0) return;
+  KLAUNCH(L, k_ep_unmeta, (R + 255) / 256, 256, 0, R, meta, first, n_local, eids, w, err);
+}
+
+// the two derived forms of the 8 group sums of a Q8x block that the tensor-core kernels read
+// (k_quant_q8x writes them when it quantises; received rows carry the sums only)
+__global__ void k_q8x_aux(size_t n_blocks, const int32_t *__restrict__ bsum, uint16_t *bm, int32_t *xs) {
+  size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n_blocks) return;
+  int tot = 0;
+  for (int j = 0; j < 8; j++) {
+    const int s = bsum[b * 8 + j];
+    tot += s;
+    bm[b * 16 + j] = __half_as_ushort(__int2half_rn((s >> 6) * 64));
+    bm[b * 16 + 8 + j] = __half_as_ushort(__int2half_rn(s & 63));
+  }
+  xs[b] = tot;
+}
+void launch_q8x_aux(const Launch &L, size_t n_blocks, const int32_t *bsum, uint16_t *bm, int32_t *xs) {
+  if (n_blocks == 0) return;
+  KLAUNCH(L, k_q8x_aux, (unsigned)((n_blocks + 255) / 256), 256, 0, n_blocks, bsum, bm, xs);
+}

@@ -130,6 +130,15 @@ void launch_split_bf16(const Launch &L, const float *x, size_t n, void *hi, void
 cudaError_t launch_tc_mx(const Launch &L, const LayerDev &ly, bool down, Groups g, int n_pairs, uint32_t *tile_buf,
                          const void *xhi, const void *xlo, const float *wts, float *out, int *err,
                          unsigned long long wait_ns);
+// expert parallelism (kernels_basic.cu): per-rank pair counts, the wire records of a dispatch,
+// the received (expert, weight) records, the derived forms of received Q8x group sums
+void launch_ep_rank_counts(const Launch &L, const uint32_t *cnt, int E, int W, int32_t *out);
+void launch_ep_pack(const Launch &L, int P, int row_bytes, int nd, int nbs, const void *rows, const float *xd,
+                    const int32_t *xbs, const uint32_t *pair_token, const uint32_t *pair_src, const uint32_t *ids,
+                    const float *w, void *srows, float *sd, int32_t *sbs, uint32_t *smeta);
+void launch_ep_unmeta(const Launch &L, int R, const uint32_t *meta, int first, int n_local, uint32_t *eids, float *w,
+                      int *err);
+void launch_q8x_aux(const Launch &L, size_t n_blocks, const int32_t *bsum, uint16_t *bm, int32_t *xs);
 void launch_combine(const Launch &L, const LayerDev &ly, const float *eo, const uint32_t *pair_pos,
                     const float *w, const float *shared_out, const float *shared_logit, int T,
                     float *y, bool accumulate);

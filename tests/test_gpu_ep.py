@@ -81,3 +81,69 @@ def test_two_gpus_match_the_unsharded_layer(ctx, tmp_path, name):
     got = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(2)])
     assert bits_equal(got, want)
     layer.close()
+
+
+# ---- the same through the C ABI (pm_ep_*: NCCL inside the library) ----
+
+@pytest.mark.parametrize("name", ["c2", "c4", "c3"])
+@pytest.mark.parametrize("T", [0, 5, 70])
+def test_c_abi_single_rank(ctx, name, T):
+    """World size 1 through pm_moe_forward_ep: the whole pipeline (counts all-gather, wire
+    records, the second workspace for served rows, combine) with every pair staying on the rank.
+    Q8x layers: the same bits as pm_moe_forward; f32 layers: the layer tolerance (70 tokens take
+    the tensor-core kernels on both sides)."""
+    cfg = SMALL[name]
+    W = synth.make_weights(cfg, 92)
+    layer = pb.MoeLayer(ctx, cfg).load(W)
+    ep = pb.ExpertParallel(ctx, pb.ep_unique_id(), 0, 1)
+    x = synth.make_activations(T, cfg.d, 8) if T else np.zeros((0, cfg.d), np.float32)
+    got = ep.forward(layer, x)
+    want = layer.forward(x)
+    if cfg.act_quant == synth.AQ_Q8X_256:
+        assert bits_equal(got, want)
+    else:
+        assert tol_ok(got, want)
+    st = ep.last_stats()
+    assert st["rows_sent"] == 0 and st["bytes_sent"] == 0  # nothing leaves a world of one
+    # a layer that does not hold the rank's shard is refused
+    other = pb.MoeLayer(ctx, cfg.scaled(first_local_expert=0, n_exp_local=cfg.n_exp // 2)).load(W)
+    with pytest.raises(pb.PelicaError) as e:
+        ep.forward(other, x)
+    assert e.value.code == -1
+    other.close()
+    ep.close()
+    layer.close()
+
+
+@pytest.mark.parametrize("name", ["c2", "c4"])
+def test_c_abi_two_gpus_match_the_unsharded_layer(ctx, tmp_path, name):
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    T_total = 90  # 45 tokens a rank: the tensor-core kernels serve the received rows
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "ep_c_worker.py"), name, str(tmp_path),
+                                       str(r), "2", str(T_total)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append((p.returncode, o[-2000:]))
+    assert all(rc == 0 for rc, _ in outs), outs
+    cfg = SMALL[name]
+    W = synth.make_weights(cfg, 91)
+    layer = pb.MoeLayer(ctx, cfg).load(W)
+    want = layer.forward(synth.make_activations(T_total, cfg.d, 6))
+    got = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(2)])
+    assert bits_equal(got, want)
+    st = [np.load(tmp_path / f"stats{r}.npy") for r in range(2)]
+    assert int(st[0][0]) == int(st[1][1]) and int(st[1][0]) == int(st[0][1])  # rows sent by one = received by the other
+    assert int(st[0][0]) > 0
+    layer.close()
