@@ -2,9 +2,9 @@
 """Benchmark of the MoE hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2_decode|c2_prefill|c1_decode|c3_decode|c4_layers_decode] [--layers L]
+                    [--workload NAME] [--layers L] [--tokens T] [--no-cpu] [--no-ep]
 
-Default workload (N=1): the Qwen3-30B-A3B-shaped 48-layer MoE stack, decode at batch 1
+Default workload (`c2_decode`): the Qwen3-30B-A3B-shaped 48-layer MoE stack, decode at batch 1
 (hidden 2048, 128 experts, softmax top-8 renormalised, ff 768, gate/up Q4_K, down Q6_K,
 synthetic N(0,0.02) weights generated on the device, residual add + RMS norm between
 layers). A step is one token through all layers.
@@ -13,8 +13,15 @@ layers). A step is one token through all layers.
            library's stream).
 `e2e`    : tokens/s through the C-ABI call with pinned HOST buffers: host->device copy of
            the activation and device->host read of the result inside the timed region.
-At N>1 every rank runs its own replica of the stack on its own tokens (the path shards by
-token with no data-path collective at these shapes); the value is the aggregate.
+`ep`     : (default workload, every N) the sharded path on the same ranks: the
+           DeepSeek-V3-shaped expert-parallel layer subset, 4096-token prefill through
+           pm_moe_forward_ep (NCCL dispatch and combine inside the library).
+At N>1 every rank runs its own replica of the default stack on its own tokens (the path
+shards by token with no data-path collective at these shapes); the value is the aggregate.
+
+Other workloads: c2_prefill, c1_decode, c1_prefill, c3_decode, c3_prefill, c5_sweep (one
+Zipf-routed layer over 1..8192 tokens), c4_prefill_ep, c4_decode64_ep, c4_decode1_ep
+(expert-parallel, run under torchrun for N>1).
 
 One JSON line is printed by rank 0.
 """
@@ -35,6 +42,15 @@ from pelica_b200 import synth  # noqa: E402
 
 SEED = 0xC0FFEE
 
+# Libraries below (the collective library for one) may print to standard output; the one JSON
+# line is the only thing this program may write there. Everything else goes to standard error.
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line: dict):
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -53,137 +69,18 @@ WORKLOADS = {
     "c1_prefill": ("c1", 64, "OLMoE-1B-7B-shaped single MoE layer, 64-token prefill"),
     "c3_decode": ("c3", 1, "gpt-oss-20b-shaped 24-layer MoE stack, decode batch 1"),
     "c3_prefill": ("c3", 2048, "gpt-oss-20b-shaped 24-layer MoE stack, 2048-token prefill"),
-    # expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine
+    "c5_sweep": ("c5", 512, "Qwen3-30B-A3B-shaped single layer, Zipf(1.2) routing, token batch swept 1..8192"),
+    # expert-parallel: experts sharded over the ranks, NCCL dispatch/combine inside the library
     "c4_prefill_ep": ("c4", 4096, "DeepSeek-V3-shaped expert-parallel MoE (layer subset), 4096-token prefill"),
     "c4_decode64_ep": ("c4", 64, "DeepSeek-V3-shaped expert-parallel MoE (layer subset), decode batch 64"),
+    "c4_decode1_ep": ("c4", 1, "DeepSeek-V3-shaped expert-parallel MoE (layer subset), decode batch 1"),
 }
-
-
-def run_ep(args, cfg, n_layers, T, desc):
-    """Expert-parallel workloads: tokens split over the ranks, experts sharded, all-to-all
-    dispatch and combine per layer; one step = T tokens through n_layers layers."""
-    import torch
-    import torch.distributed as dist
-
-    import pelica_b200 as pb
-    from pelica_b200.ep import CudaBackend, ExpertParallelLayer
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ctx = pb.Context(local, stream=torch.cuda.current_stream().cuda_stream)
-    per = cfg.n_exp // world
-    layers = []
-    for l in range(n_layers):
-        ly = pb.MoeLayer(ctx, cfg.scaled(first_local_expert=rank * per, n_exp_local=per))
-        # the replicated parts (router, biases, shared expert) come out identical on every rank:
-        # they are seeded by the layer only; the experts by (layer, first local expert)
-        ly.fill_synthetic(SEED + 7919 * l, cfg.sigma, 0.0, cfg.select_bias_sigma)
-        layers.append(ExpertParallelLayer(CudaBackend(ly), cfg.n_exp, validate=False))
-    be0 = layers[0].be
-    Tl = T // world
-    POOL = 4
-    g = torch.Generator(device="cuda").manual_seed(SEED + rank)
-    pool = [torch.randn((Tl, cfg.d), generator=g, device="cuda", dtype=torch.float32) for _ in range(POOL)]
-
-    def step(i):
-        x = pool[i % POOL].clone()
-        for L in layers:
-            L.forward(be0.rmsnorm(x), add_into=x)
-        return x
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    clocks = ClockSampler(local)
-    if rank == 0:
-        clocks.start()
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    clocks.begin()
-    launches0 = ctx.launches
-    ctx.timer_start()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    ms = ctx.timer_stop() / args.steps
-    barrier()
-    clk = clocks.stop() if rank == 0 else None
-    launches = ctx.launches - launches0
-    ctx.profile(True)
-    step(0)
-    phases = {k: v[0] for k, v in ctx.profile_read().items() if v[1]}
-    ctx.profile(False)
-    # e2e: host tokens in, host result out, per step
-    hx = torch.empty((Tl, cfg.d), dtype=torch.float32).pin_memory()
-    hy = torch.empty((Tl, cfg.d), dtype=torch.float32).pin_memory()
-    hx.copy_(pool[0].cpu())
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        x = hx.cuda(non_blocking=True)
-        for L in layers:
-            L.forward(be0.rmsnorm(x), add_into=x)
-        hy.copy_(x, non_blocking=True)
-        torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
-    barrier()
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
-    if rank == 0:
-        pk = peaks()
-        pairs = T * cfg.top_k
-        macs = 3 * cfg.d * cfg.ff * (pairs + T * (1 if cfg.shared else 0)) * n_layers  # expert products per step
-        flops = 2 * macs
-        line = {
-            "metric": "moe_tokens_per_s", "value": T / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x u4 -> i32 (tcgen05 kind::i8), f32 scales",
-            "data": "synthetic",
-            "config": {"workload": desc, "tokens_per_step": T, "layers": n_layers, "of_layers": cfg.n_layers,
-                       "hidden": cfg.d, "experts": cfg.n_exp, "experts_per_gpu": per, "top_k": cfg.top_k, "ff": cfg.ff,
-                       "parallelism": f"ep{world}", "seed": SEED,
-                       "l2": f"inputs larger than L2: {per * cfg.expert_bytes() * n_layers / 1e9:.1f} GB of experts per GPU"},
-            "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": Tl * cfg.d * 4 * world, "d2h_bytes_per_step": Tl * cfg.d * 4 * world},
-            "gpu_launches": int(launches), "clocks": clk,
-            "roofline": {"bound": "tensor", "unit": "TFLOP/s", "achieved": flops / (ms * 1e-3) / 1e12 / world,
-                         "peak": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (bf16 dense sustained; the kernel runs int8)",
-                         "frac": flops / (ms * 1e-3) / 1e12 / world / pk["bf16_tflops_sustained"], "traffic": None,
-                         "kernel": "k_tc (tcgen05 int8 grouped expert products)", "per": "GPU",
-                         "tokens_per_s_full_model": T / (ms / 1e3) * n_layers / cfg.n_layers,
-                         "phases_ms_per_step_rank0": phases},
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-
-
-def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
-    """Bytes one step must move: the distinct experts hit (gate+up+down blocks, biases), the
-    router, the shared expert, and the activations in and out, per layer."""
-    per_layer = distinct_experts_per_layer * cfg.expert_bytes() + cfg.n_exp * cfg.d * 4 + 2 * T * cfg.d * 4
-    if cfg.shared:
-        sh = cfg.scaled(ff=cfg.shared_ff, has_expert_bias=0)
-        per_layer += sh.expert_bytes()
-    return per_layer * n_layers
-
-
-# (102,226,176 + 3,290,880) bytes over the 4 layers of the captured launch
-NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102217472 + 3546112) // 4
+# workloads whose dominant kernels are bound by the tensor pipe (the rest: HBM)
+TENSOR_BOUND = {"c3_prefill", "c4_prefill_ep"}
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs (read-only)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -198,7 +95,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -215,7 +112,7 @@ class ClockSampler:
 
     def stop(self):
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -237,7 +134,7 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def dist_setup(n_gpus):
+def dist_setup():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -252,6 +149,164 @@ def dist_setup(n_gpus):
     return world, rank, local, dist
 
 
+def share_bytes(dist, rank, local, payload, n):
+    """rank 0's `payload` (n bytes) on every rank (torch.distributed as plumbing)."""
+    if dist is None:
+        return payload
+    import torch
+
+    t = torch.zeros(n, dtype=torch.uint8, device=f"cuda:{local}")
+    if rank == 0:
+        t.copy_(torch.frombuffer(bytearray(payload), dtype=torch.uint8))
+    dist.broadcast(t, 0)
+    return bytes(t.cpu().numpy().tobytes())
+
+
+def max_over_ranks(dist, local, values):
+    if dist is None:
+        return list(values)
+    import torch
+
+    t = torch.tensor(list(values), device=f"cuda:{local}", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+# ---------------------------------------------------------------------------
+# the sharded path: expert parallelism through pm_moe_forward_ep
+# ---------------------------------------------------------------------------
+def ep_measure(pb, ctx, dist, world, rank, local, cfg, n_layers, T, steps, warmup):
+    """T tokens (split over the ranks) through n_layers expert-parallel layers per step:
+    x += moe(rmsnorm(x)) per layer. Returns the record rank 0 reports."""
+    import ctypes as C
+
+    per = cfg.n_exp // world
+    uid = share_bytes(dist, rank, local, pb.ep_unique_id() if rank == 0 else b"", 128)
+    ep = pb.ExpertParallel(ctx, uid, rank, world)
+    layers = []
+    for l in range(n_layers):
+        ly = pb.MoeLayer(ctx, cfg.scaled(first_local_expert=rank * per, n_exp_local=per))
+        # the replicated parts (router, biases, shared expert) come out identical on every rank:
+        # they are seeded by the layer only; the experts by (layer, first local expert)
+        ly.fill_synthetic(SEED + 7919 * l, cfg.sigma, 0.0, cfg.select_bias_sigma)
+        layers.append(ly)
+    Tl = T * (rank + 1) // world - T * rank // world
+    d = cfg.d
+    POOL = 4
+    rng = np.random.default_rng(SEED + rank)
+    pool = [ctx.alloc(max(Tl, 1) * d * 4).upload(rng.normal(0, 1, (max(Tl, 1), d)).astype(np.float32)) for _ in range(POOL)]
+    xb = ctx.alloc(max(Tl, 1) * d * 4)
+    xn = ctx.alloc(max(Tl, 1) * d * 4)
+    lib = ctx.lib
+
+    def step(src):
+        pb._check(lib.pm_copy(ctx.h, xb.ptr, src, max(Tl, 1) * d * 4))
+        for ly in layers:
+            if Tl:
+                pb._check(lib.pm_rmsnorm(ctx.h, xb.ptr, Tl, d, C.c_float(1e-6), xn.ptr))
+            ep.forward_dev(ly, xn, Tl, xb, accumulate=True)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+        ctx.sync()
+
+    for i in range(warmup):
+        step(pool[i % POOL].ptr)
+    barrier()
+    launches0 = ctx.launches
+    ctx.timer_start()
+    for i in range(steps):
+        step(pool[(warmup + i) % POOL].ptr)
+    ms = ctx.timer_stop() / steps
+    barrier()
+    launches = (ctx.launches - launches0) / steps
+    stats = ep.last_stats()
+    ctx.profile(True)
+    step(pool[0].ptr)
+    phases = {k: v[0] for k, v in ctx.profile_read().items() if v[1]}
+    ctx.profile(False)
+    # end to end: host tokens in, host result out, every step
+    hx = ctx.pinned((max(Tl, 1), d))
+    hy = ctx.pinned((max(Tl, 1), d))
+    hx[:] = 0.5
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        step(hx.ctypes.data)
+        pb._check(lib.pm_copy(ctx.h, hy.ctypes.data, xb.ptr, max(Tl, 1) * d * 4))
+    e2e_ms = (time.perf_counter() - t0) / steps * 1e3
+    barrier()
+    ms, e2e_ms = max_over_ranks(dist, local, [ms, e2e_ms])
+    pk = peaks()
+    pairs = T * cfg.top_k
+    flops = 2 * 3 * d * cfg.ff * (pairs + T * (1 if cfg.shared else 0)) * n_layers
+    exch = phases.get("fused", 0.0)
+    rec = {
+        "workload": f"DeepSeek-V3-shaped expert-parallel MoE, {n_layers} of {cfg.n_layers} layers, {T} tokens per step",
+        "tokens_per_s": T / (ms / 1e3), "ms_per_step": ms, "n_gpus": world, "experts_per_gpu": per,
+        "tokens_per_step": T, "layers": n_layers,
+        "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4},
+        "gpu_launches_per_step_rank0": launches,
+        "rank0_phases_ms_per_step": phases,
+        "rank0_exchange_ms_per_step": exch, "rank0_kernel_ms_per_step": sum(phases.values()) - exch,
+        "rank0_wire_bytes_per_layer": {"sent": stats["bytes_sent"], "received": stats["bytes_received"],
+                                       "rows_sent": stats["rows_sent"], "rows_received": stats["rows_received"]},
+        "roofline": {"bound": "tensor", "unit": "TFLOP/s", "achieved": flops / (ms * 1e-3) / 1e12 / world,
+                     "peak": pk["bf16_tflops_sustained"],
+                     "peak_source": pk["source"] + " (bf16 dense sustained; the kernels run int8)",
+                     "frac": flops / (ms * 1e-3) / 1e12 / world / pk["bf16_tflops_sustained"], "per": "GPU",
+                     "kernel": "k_tc (tcgen05 int8 grouped expert products)"},
+        "tokens_per_s_full_model": T / (ms / 1e3) * n_layers / cfg.n_layers,
+        "scaling": "strong",
+    }
+    for b in pool + [xb, xn]:
+        b.free()
+    ep.close()
+    for ly in layers:
+        ly.close()
+    return rec
+
+
+def run_ep(args, cfg, n_layers, T, desc):
+    """The expert-parallel workloads as the bench's own line."""
+    world, rank, local, dist = dist_setup()
+    import pelica_b200 as pb
+
+    ctx = pb.Context(local)
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+        clocks.begin()
+    rec = ep_measure(pb, ctx, dist, world, rank, local, cfg, n_layers, T, args.steps, args.warmup)
+    clk = clocks.stop() if rank == 0 else None
+    if rank == 0:
+        line = {
+            "metric": "moe_tokens_per_s", "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x u4 -> i32 (tcgen05 kind::i8), f32 scales",
+            "data": "synthetic",
+            "config": {"workload": desc, "tokens_per_step": T, "layers": n_layers, "of_layers": cfg.n_layers,
+                       "hidden": cfg.d, "experts": cfg.n_exp, "experts_per_gpu": rec["experts_per_gpu"],
+                       "top_k": cfg.top_k, "ff": cfg.ff, "parallelism": f"ep{world}", "seed": SEED,
+                       "l2": f"inputs larger than L2: {rec['experts_per_gpu'] * cfg.expert_bytes() * n_layers / 1e9:.1f} GB "
+                             "of experts per GPU"},
+            "e2e": rec["e2e"], "gpu_launches": int(rec["gpu_launches_per_step_rank0"] * args.steps), "clocks": clk,
+            "roofline": dict(rec["roofline"], traffic=None),
+            "ep": {k: rec[k] for k in ("rank0_phases_ms_per_step", "rank0_exchange_ms_per_step", "rank0_kernel_ms_per_step",
+                                       "rank0_wire_bytes_per_layer", "tokens_per_s_full_model")},
+        }
+        emit(line)
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# the reference arm and the CPU baseline: the oracle's restatement of the reference's CPU path
+# ---------------------------------------------------------------------------
 def cpu_sample(cfg, weights_per_layer, xs, threads):
     """The reference's CPU path (restated, AVX-512 VNNI, threaded as the reference threads
     it) on a bounded sample: the given layers x the given tokens, one token at a time
@@ -259,8 +314,7 @@ def cpu_sample(cfg, weights_per_layer, xs, threads):
     from oracle import pelica_oracle as po
 
     layers = [po.Layer(po.LayerDesc(**cfg.desc_fields()), W) for W in weights_per_layer]
-    # warm-up
-    layers[0].forward_fast(xs[:1], threads)
+    layers[0].forward_fast(xs[:1], threads)  # warm-up
     t0 = time.perf_counter()
     n = 0
     for x in xs:
@@ -270,6 +324,12 @@ def cpu_sample(cfg, weights_per_layer, xs, threads):
             h = h + L.forward_fast(xn, threads)
             n += 1
     return (time.perf_counter() - t0) / n, h
+
+
+def weight_gbs(cfg, n_layers, tok_s, T):
+    """GB/s of expert + router bytes the CPU path streams at `tok_s` (decode: top_k experts a token)."""
+    per_layer = min(cfg.n_exp, T * cfg.top_k) * cfg.expert_bytes() + cfg.n_exp * cfg.d * 4
+    return per_layer * n_layers * (tok_s / T) / 1e9
 
 
 def run_reference(args, cfg, n_layers, T, desc):
@@ -283,9 +343,8 @@ def run_reference(args, cfg, n_layers, T, desc):
 
     threads = os.cpu_count() or 1
     sample_layers = min(2, n_layers)
-    sub = cfg
-    Ws = [synth.make_weights(sub, SEED + l) for l in range(sample_layers)]
-    layers = [po.Layer(po.LayerDesc(**sub.desc_fields()), W) for W in Ws]
+    Ws = [synth.make_weights(cfg, SEED + l) for l in range(sample_layers)]
+    layers = [po.Layer(po.LayerDesc(**cfg.desc_fields()), W) for W in Ws]
     rng = np.random.default_rng(SEED)
     tok = max(1, T)
 
@@ -308,25 +367,106 @@ def run_reference(args, cfg, n_layers, T, desc):
         "impl": "reference", "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 x u4/u6 -> i32, f32 scales", "data": "synthetic",
-        "config": {"workload": desc, "tokens_per_step": tok, "layers": n_layers},
+        "config": {"workload": desc, "tokens_per_step": tok, "layers": n_layers, "hidden": cfg.d, "experts": cfg.n_exp,
+                   "top_k": cfg.top_k, "ff": cfg.ff, "parallelism": "host cores", "seed": SEED},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "weight_gb_per_s": weight_gbs(cfg, n_layers, value, tok),
                          "sample": f"{sample_layers} of {n_layers} layers per step (numpy-encoded weights), "
                                    f"time scaled x{n_layers / sample_layers:g}; AVX-512 VNNI={bool(po.lib().po_have_vnni())}"},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
+    """Bytes one step must move: the distinct experts hit (gate+up+down blocks, biases), the
+    router, the shared expert, and the activations in and out, per layer."""
+    per_layer = distinct_experts_per_layer * cfg.expert_bytes() + cfg.n_exp * cfg.d * 4 + 2 * T * cfg.d * 4
+    if cfg.shared:
+        sh = cfg.scaled(ff=cfg.shared_ff, has_expert_bias=0)
+        per_layer += sh.expert_bytes()
+    return per_layer * n_layers
+
+
+# dram__bytes_read + dram__bytes_write of k_decode_mega in an ncu capture of a 4-layer launch
+# (profiles/k_decode_mega_c2_decode.md), per layer
+NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102217472 + 3546112) // 4
+
+
+def run_sweep(args, cfg, desc):
+    """C5: one Zipf-routed layer, the token batch swept; which kernel family served each size."""
+    import pelica_b200 as pb
+
+    ctx = pb.Context(0)
+    ly = pb.MoeLayer(ctx, cfg).fill_synthetic(SEED, cfg.sigma, 0.0, 0.0)
+    router = np.empty((cfg.n_exp, cfg.d), np.float32)
+    pb._check(ly.lib.pm_layer_get_router(ly.h, router.ctypes.data, None, None))
+    # (strength 0.6: the pair counts' log-log slope over the 64 most popular experts comes out at -1.2
+    # under top-8 selection of N(0, 0.9) logits; 8 experts are pushed to never win)
+    bias = synth.zipf_router_bias(cfg.n_exp, 3, s=1.2, dead=8, strength=0.6)
+    pb._check(ly.lib.pm_layer_set_router(ly.h, router.ctypes.data, synth.F32, bias.ctypes.data, None))
+    st = pb.Stack(ctx, [ly])
+    pk = peaks()
+    out = []
+    for T in (1, 8, 64, 512, 4096, 8192):
+        x = synth.make_activations(T, cfg.d, 11 + T)
+        ids, _ = ly.route(x)
+        distinct = int(len(np.unique(ids)))
+        counts = np.bincount(ids.ravel(), minlength=cfg.n_exp)
+        dx = ctx.alloc(x.nbytes).upload(x)
+        dy = ctx.alloc(x.nbytes)
+        reps = max(3, min(200, 2000 // T))
+        for _ in range(3):
+            ly.forward_dev(dx, T, dy)
+        ctx.sync()
+        p0 = ctx.path_counts()
+        l0 = ctx.launches
+        ctx.timer_start()
+        for _ in range(reps):
+            ctx.flush_l2()  # the same layer every repetition: evict its weights between calls
+            ly.forward_dev(dx, T, dy)
+        ms_all = ctx.timer_stop()
+        ctx.timer_start()
+        for _ in range(reps):
+            ctx.flush_l2()
+        ms_flush = ctx.timer_stop()
+        ms = (ms_all - ms_flush) / reps
+        p1 = ctx.path_counts()
+        byt = algorithmic_bytes_per_step(cfg, 1, T, distinct)
+        flops = 2 * 3 * cfg.d * cfg.ff * T * cfg.top_k
+        out.append({"tokens": T, "ms": ms, "tokens_per_s": T / (ms / 1e3), "distinct_experts": distinct,
+                    "max_tokens_on_one_expert": int(counts.max()), "experts_without_tokens": int((counts == 0).sum()),
+                    "kernels": {k: (p1[k] - p0[k]) // reps for k in p1 if p1[k] != p0[k]},
+                    "launches": (ctx.launches - l0) // reps,
+                    "hbm_frac": byt / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                    "tensor_frac": flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"]})
+        dx.free()
+        dy.free()
+    mid = out[3]
+    line = {"metric": "moe_tokens_per_s", "value": mid["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": 3, "ms_per_step": mid["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 x u4 -> i32, f32 scales", "data": "synthetic",
+            "config": {"workload": desc, "value_is": "the 512-token point", "layers": 1, "hidden": cfg.d, "experts": cfg.n_exp,
+                       "top_k": cfg.top_k, "ff": cfg.ff, "l2": "L2 flushed between repetitions (the flush is timed "
+                       "separately and subtracted)", "seed": SEED},
+            "sweep": out}
+    emit(line)
+    st.close()
+    ly.close()
+    ctx.close()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_decode", choices=list(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers")
     ap.add_argument("--tokens", type=int, default=0, help="override the tokens per step of a workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel record of the default workload")
     args = ap.parse_args()
 
     key, T, desc = WORKLOADS[args.workload]
@@ -339,11 +479,17 @@ def main():
             args.steps = 20  # each CPU step is a bounded sample; keep the arm within minutes
         run_reference(args, cfg, n_layers, T, desc)
         return
-
     if args.workload.endswith("_ep"):
+        if args.steps > 50:
+            args.steps = 20
         run_ep(args, cfg, args.layers or 2, T, desc)
         return
-    world, rank, local, dist = dist_setup(args.gpus)
+    if args.workload == "c5_sweep":
+        run_sweep(args, cfg, desc)
+        return
+    if T > 1 and args.steps > 50:
+        args.steps = 20  # prompt-sized steps take milliseconds each
+    world, rank, local, dist = dist_setup()
     import pelica_b200 as pb
 
     ctx = pb.Context(local)
@@ -357,7 +503,7 @@ def main():
     d = cfg.d
 
     # a pool of distinct inputs: consecutive steps route differently
-    POOL = 64
+    POOL = 64 if T == 1 else 4
     rng = np.random.default_rng(SEED + rank)
     pool = rng.normal(0, 1, (POOL, T, d)).astype(np.float32)
     dpool = [ctx.alloc(T * d * 4).upload(pool[i]) for i in range(POOL)]
@@ -388,11 +534,11 @@ def main():
 
     # ---- per-phase timing of the same steps (roofline of the dominant kernel) ----
     ctx.profile(True)
-    for i in range(min(args.steps, 50)):
+    prof_steps = min(args.steps, 50)
+    for i in range(prof_steps):
         stack.forward_dev(dpool[i % POOL], T, dout)
     phases = ctx.profile_read()
     ctx.profile(False)
-    prof_steps = min(args.steps, 50)
 
     # ---- end to end through the C ABI with pinned host buffers ----
     hx = ctx.pinned((T, d))
@@ -409,22 +555,23 @@ def main():
     barrier()
     checksum = float(np.abs(hy).sum())
 
-    # distinct experts per layer actually hit (decode: top_k; prefill: measured from usage)
+    # distinct experts per layer actually hit (decode: top_k; prefill: measured on layer 0)
     if T == 1:
         distinct = cfg.top_k
     else:
         ids, _ = layers[0].route(synth.make_activations(T, d, 1))
         distinct = len(np.unique(ids))
 
-    ms_step = ms / args.steps
-    if dist is not None:
-        import torch
+    ms_step, e2e_ms = max_over_ranks(dist, local, [ms / args.steps, e2e_s / args.steps * 1e3])
 
-        t = torch.tensor([ms_step, e2e_s / args.steps * 1e3], device=f"cuda:{local}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_ms = t.tolist()
-    else:
-        e2e_ms = e2e_s / args.steps * 1e3
+    # ---- the sharded path on the same ranks (default workload only) ----
+    ep_rec = None
+    if args.workload == "c2_decode" and not args.no_ep:
+        try:
+            c4 = synth.CONFIGS["c4"]
+            ep_rec = ep_measure(pb, ctx, dist, world, rank, local, c4, 2, 4096, 5, 3)
+        except Exception as e:  # the record is an addition: never lose the line to it
+            ep_rec = {"failed": repr(e)}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -434,39 +581,53 @@ def main():
     value = world * T / (ms_step / 1e3)
     e2e_value = world * T / (e2e_ms / 1e3)
     bytes_step = algorithmic_bytes_per_step(cfg, n_layers, T, distinct)
+    flops_step = 2 * 3 * d * cfg.ff * T * cfg.top_k * n_layers
     # the dominant phase of the step
     dom = max(phases, key=lambda k: phases[k][0])
     dom_ms, dom_spans = phases[dom]
-    phase_bytes = {
-        "gateup": distinct * (synth.row_bytes(cfg.type_gate, d) + synth.row_bytes(cfg.type_up, d)) * cfg.ff,
-        "down": distinct * synth.row_bytes(cfg.type_down, cfg.ff) * d,
-        "fused": bytes_step / n_layers if phases.get("fused", (0, 0))[1] == prof_steps * n_layers else bytes_step,
-    }
-    roof = {"bound": "hbm", "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"], "kernel": dom,
-            "traffic": None}
-    if dom == "fused" and key == "c2":
-        # dram__bytes_read + dram__bytes_write of k_decode_mega from the committed ncu summary of the
-        # decode kernel (4 layers captured; the bytes grow with the layer count)
-        roof["traffic"] = NCU_DRAM_BYTES_PER_LAYER_C2_DECODE * (n_layers if phases["fused"][1] != prof_steps * n_layers else 1)
-        roof["traffic_source"] = "ncu capture of a 4-layer launch, scaled by layers"
-    if dom in phase_bytes and dom_spans:
-        per_launch_bytes = phase_bytes[dom]
-        per_launch_ms = dom_ms / dom_spans
-        roof["achieved"] = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
-        roof["bytes_per_launch"] = per_launch_bytes
-        roof["ms_per_launch"] = per_launch_ms
+    phases_ms = {k: v[0] / prof_steps for k, v in phases.items() if v[1]}
+    if args.workload in TENSOR_BOUND:
+        # the expert products (gate/up + down phases) against the sustained bf16 peak
+        prod_ms = phases_ms.get("gateup", 0.0) + phases_ms.get("down", 0.0)
+        ach = flops_step / (prod_ms * 1e-3) / 1e12 if prod_ms else 0.0
+        roof = {"bound": "tensor", "unit": "TFLOP/s", "peak": pk["bf16_tflops_sustained"],
+                "peak_source": pk["source"] + " (bf16 dense sustained)", "kernel": "gateup + down (k_tc_mx, tcgen05 bf16)",
+                "achieved": ach, "frac": ach / pk["bf16_tflops_sustained"], "flops_per_step": flops_step,
+                "ms_of_the_products_per_step": prod_ms, "traffic": None,
+                "note": "useful flops (2 x 3 x d x ff x pairs); the kernel runs every product twice (activations "
+                        "split hi + lo into two bf16 operands), so its tensor work is twice this"}
     else:
-        roof["achieved"] = bytes_step / (ms_step * 1e-3) / 1e9
-    roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["whole_step"] = {"achieved": bytes_step / (ms_step * 1e-3) / 1e9,
-                          "frac": bytes_step / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"],
-                          "bytes_per_step": bytes_step}
-    roof["phases_ms_per_step"] = {k: v[0] / prof_steps for k, v in phases.items() if v[1]}
+        phase_bytes = {
+            "gateup": distinct * (synth.row_bytes(cfg.type_gate, d) + synth.row_bytes(cfg.type_up, d)) * cfg.ff,
+            "down": distinct * synth.row_bytes(cfg.type_down, cfg.ff) * d,
+            "fused": bytes_step / n_layers if phases.get("fused", (0, 0))[1] == prof_steps * n_layers else bytes_step,
+        }
+        roof = {"bound": "hbm", "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"], "kernel": dom,
+                "traffic": None}
+        if dom == "fused" and key == "c2":
+            roof["kernel"] = "k_decode_mega (one launch per token)"
+            roof["traffic"] = NCU_DRAM_BYTES_PER_LAYER_C2_DECODE * (n_layers if phases["fused"][1] != prof_steps * n_layers else 1)
+            roof["traffic_source"] = "ncu capture of a 4-layer launch, scaled by layers"
+        if dom in phase_bytes and dom_spans:
+            per_launch_bytes = phase_bytes[dom]
+            per_launch_ms = dom_ms / dom_spans
+            roof["achieved"] = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
+            roof["bytes_per_launch"] = per_launch_bytes
+            roof["ms_per_launch"] = per_launch_ms
+        else:
+            roof["achieved"] = bytes_step / (ms_step * 1e-3) / 1e9
+        roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["whole_step"] = {"hbm_gbs": bytes_step / (ms_step * 1e-3) / 1e9,
+                          "hbm_frac": bytes_step / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], "bytes_per_step": bytes_step,
+                          "tflops": flops_step / (ms_step * 1e-3) / 1e12}
+    roof["phases_ms_per_step"] = phases_ms
+    if clk and clk.get("sm_mhz"):
+        roof["ms_per_step_x_sm_mhz"] = ms_step * clk["sm_mhz"]
 
     line = {
         "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 x u4/u6 -> i32, f32 scales" if cfg.act_quant else "f32 x mxfp4",
+        "vs_baseline": None, "dtype": "int8 x u4/u6 -> i32, f32 scales" if cfg.act_quant else "f32 x mxfp4 (bf16 hi+lo on the tensor cores from 32 tokens)",
         "data": "synthetic",
         "config": {"workload": desc, "tokens_per_step": T, "layers": n_layers, "hidden": d, "experts": cfg.n_exp,
                    "top_k": cfg.top_k, "ff": cfg.ff, "l2": f"inputs larger than L2: {bytes_step / 1e6:.0f} MB of "
@@ -475,9 +636,12 @@ def main():
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": T * d * 4,
                 "d2h_bytes_per_step": T * d * 4, "checksum": checksum},
         "gpu_launches": int(launches),
+        "kernel_families": ctx.path_counts(),
         "clocks": clk,
         "roofline": roof,
     }
+    if ep_rec is not None:
+        line["ep"] = ep_rec
 
     # ---- CPU baseline on a bounded sample of the same workload (rank 0, N=1) ----
     if world == 1 and not args.no_cpu:
@@ -513,11 +677,12 @@ def main():
                 cpu_tok_s = T / (sec * n_layers)
                 sample = f"{T} tokens x {sl} of {n_layers} layers, scaled to {n_layers} layers"
             line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                    "sample": sample, "avx512_vnni": bool(po.lib().po_have_vnni())}
+                                    "sample": sample, "avx512_vnni": bool(po.lib().po_have_vnni()),
+                                    "weight_gb_per_s": weight_gbs(cfg, n_layers, cpu_tok_s, T)}
         except Exception as e:  # the baseline is a reported figure; never lose the GPU line to it
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"failed: {e!r}"}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if dist is not None:
         dist.destroy_process_group()
 

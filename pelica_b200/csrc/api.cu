@@ -1798,7 +1798,8 @@ static int32_t nccl_load() {
 
 struct pm_ep {
   pm_ctx *ctx = nullptr;   // the rank's context: routing, the rank's own tokens, the exchanges' stream
-  pm_ctx *sub = nullptr;   // a second workspace on the same stream: the rows received from the other ranks
+  uint8_t *ws2 = nullptr;  // a second workspace (swapped in for the rows received from the other ranks,
+  size_t ws2_cap = 0;      // whose number is only known in mid-call, when the first one is in use)
   pm_ncclComm_t comm = nullptr;
   int rank = 0, world = 1;
   int32_t *d_cnt = nullptr;  // [W] pairs this rank sends to each rank, then [W*W] everybody's
@@ -1827,10 +1828,7 @@ extern "C" int32_t pm_ep_destroy(pm_ep *ep) {
     else g_nccl.CommDestroy(ep->comm);
   }
   cudaGetLastError();
-  if (ep->sub) {
-    if (ep->sub->ws) cudaFree(ep->sub->ws);
-    delete ep->sub;
-  }
+  if (ep->ws2) cudaFree(ep->ws2);
   if (ep->d_cnt) cudaFree(ep->d_cnt);
   if (ep->h_cnt) cudaFreeHost(ep->h_cnt);
   if (ep->ev) cudaEventDestroy(ep->ev);
@@ -1848,12 +1846,6 @@ extern "C" int32_t pm_ep_init(pm_ctx *ctx, const uint8_t *unique_id, int32_t ran
   ep->ctx = ctx;
   ep->rank = rank;
   ep->world = world;
-  ep->sub = new (std::nothrow) pm_ctx();
-  if (!ep->sub) { delete ep; return fail(PM_ERR_OOM, "host allocation"); }
-  ep->sub->device = ctx->device;
-  ep->sub->stream = ctx->stream;
-  ep->sub->own_stream = false;
-  ep->sub->dev_err = ctx->dev_err;
   cudaError_t e = cudaMalloc(&ep->d_cnt, (size_t)(world + world * world) * 4);
   if (e == cudaSuccess) e = cudaHostAlloc((void **)&ep->h_cnt, (size_t)world * world * 4, cudaHostAllocDefault);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ep->ev, cudaEventDisableTiming);
@@ -1972,20 +1964,26 @@ extern "C" int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *ly, const float *x, in
   if (so != P) return fail(PM_ERR_STATE, "pm_moe_forward_ep: %zu pairs planned, %zu counted", P, so);
   if (R > (size_t)PM_MAX_TOKENS * PM_MAX_TOPK) return fail(PM_ERR_LIMIT, "pm_moe_forward_ep: %zu rows received", R);
 
-  // ---- the rows this rank serves: a second workspace (its size is only known now) ----
-  pm_ctx *sc = ep->sub;
-  sc->prof_on = false;
+  // ---- the rows this rank serves: the second workspace is swapped in (its size is only known
+  // now, and what was carved from the first one is still in use) ----
+  struct WsSwap {
+    pm_ctx *c;
+    pm_ep *ep;
+    size_t off;
+    WsSwap(pm_ctx *c_, pm_ep *e_) : c(c_), ep(e_), off(c_->ws_off) { std::swap(c->ws, ep->ws2); std::swap(c->ws_cap, ep->ws2_cap); }
+    ~WsSwap() { std::swap(c->ws, ep->ws2); std::swap(c->ws_cap, ep->ws2_cap); c->ws_off = off; }
+  } ws_swap(c, ep);
   pm_layer_desc D1 = D;
   D1.top_k = 1;
   const size_t Rr = R > 0 ? R : 1;
-  TRY(ws_reserve(sc, scratch_bytes(D1, (int)Rr) + al(Rr * row_bytes) + al(Rr * 8) + 2 * al(Rr * 4) + al(Rr * (size_t)d * 4) + 4096));
+  TRY(ws_reserve(c, scratch_bytes(D1, (int)Rr) + al(Rr * row_bytes) + al(Rr * 8) + 2 * al(Rr * 4) + al(Rr * (size_t)d * 4) + 4096));
   Scratch RS;
-  scratch_carve(sc, D1, (int)Rr, RS);
-  uint8_t *rrows = q8 ? (uint8_t *)RS.xq : ws_take<uint8_t>(sc, Rr * row_bytes);
-  uint32_t *rmeta = ws_take<uint32_t>(sc, Rr * 2);
-  uint32_t *reid = ws_take<uint32_t>(sc, Rr);
-  float *rw = ws_take<float>(sc, Rr);
-  float *orows = ws_take<float>(sc, Rr * (size_t)d);
+  scratch_carve(c, D1, (int)Rr, RS);
+  uint8_t *rrows = q8 ? (uint8_t *)RS.xq : ws_take<uint8_t>(c, Rr * row_bytes);
+  uint32_t *rmeta = ws_take<uint32_t>(c, Rr * 2);
+  uint32_t *reid = ws_take<uint32_t>(c, Rr);
+  float *rw = ws_take<float>(c, Rr);
+  float *orows = ws_take<float>(c, Rr * (size_t)d);
 
   // ---- dispatch ----
   {
@@ -2023,23 +2021,16 @@ extern "C" int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *ly, const float *x, in
   }
   // ---- the local experts over the received rows ----
   if (R > 0) {
-    Launch SL = sc->launch();
-    launch_ep_unmeta(SL, (int)R, rmeta, dv.first_local, dv.n_local, reid, rw, c->dev_err);
-    if (q8) launch_q8x_aux(SL, R * (size_t)nd, RS.xbsum, RS.xbm, RS.xs);
+    launch_ep_unmeta(L, (int)R, rmeta, dv.first_local, dv.n_local, reid, rw, c->dev_err);
+    if (q8) launch_q8x_aux(L, R * (size_t)nd, RS.xbsum, RS.xbm, RS.xs);
     pm_layer view = *ly;
-    view.ctx = sc;
     view.dev.desc = D1;
     view.dev.usage = nullptr;
-    sc->tc_min_tokens = c->tc_min_tokens;
-    sc->wait_ns = c->wait_ns;
-    launch_plan(SL, view.dev, reid, (int)R, RS.plan, c->dev_err);
+    { PROF(c, PH_PLAN); launch_plan(L, view.dev, reid, (int)R, RS.plan, c->dev_err); }
     TRY(dev_experts(&view, q8 ? nullptr : (const float *)rrows, (int)R, RS, rw, q8));
     LayerDev cp = view.dev;
     cp.desc.weight_fold = PM_FOLD_BEFORE_DOWN;  // plain gather back to row order
-    launch_combine(SL, cp, RS.eo, RS.plan.pair_pos, rw, nullptr, nullptr, (int)R, orows, false);
-    for (int i = 0; i < PM_PATH_N; i++) { c->path_count[i] += sc->path_count[i]; sc->path_count[i] = 0; }
-    c->launches += sc->launches;
-    sc->launches = 0;
+    launch_combine(L, cp, RS.eo, RS.plan.pair_pos, rw, nullptr, nullptr, (int)R, orows, false);
   }
   // ---- the outputs go home (they arrive in the sender's plan order: S.eo is what combine takes) ----
   {
