@@ -52,9 +52,14 @@ enum {
   PM_TYPE_F16 = 1,
   PM_TYPE_Q8_0 = 8,   /* 32 values / 34 B  */
   PM_TYPE_Q4_K = 12,  /* 256 values / 144 B */
+  PM_TYPE_Q5_K = 13,  /* 256 values / 176 B: Q4_K's header, 32 B of fifth bits, 128 B of nibbles
+                         (src/moe_kernels.rs:74); f32 activations only, as in the reference */
   PM_TYPE_Q6_K = 14,  /* 256 values / 210 B */
   PM_TYPE_IQ4_NL = 20, /* 32 values / 18 B: f16 d + 16 B of 4-bit indices into a fixed
                           non-linear codebook (src/iq_tables.rs:72, src/q4x_cpu.rs:92-101) */
+  PM_TYPE_IQ3_S = 21,  /* 256 values / 110 B: f16 d, 8-bit + 1-bit indices into a 512-entry codebook of
+                          four magnitudes, sign bits, 4-bit sub-scales 1 + 2 s (src/iq_tables.rs:4,
+                          src/q4x_cpu.rs:64-82,118-127) */
   PM_TYPE_IQ4_XS = 23, /* 256 values / 136 B: f16 d, 8 six-bit sub-scales (bias 32), indices into
                           the IQ4_NL codebook (src/q4x_cpu.rs:102-117,462-476) */
   PM_TYPE_BF16 = 30,
@@ -86,7 +91,7 @@ enum {
                          (`Q8x`, src/ds4_cpu.rs:7-36); the hidden vector is
                          re-quantised before down (src/ds4_cpu.rs:306-317)        */
   PM_AQ_Q8_32 = 2     /* int8 per 32 values, f32 scale (`Q8`, src/q4x_cpu.rs:13-51)
-                         against Q8_0 / IQ4_NL / IQ4_XS weights: per block f16(d_w) * x.d * idot
+                         against Q8_0 / IQ4_NL / IQ4_XS / IQ3_S weights: per block f16(d_w) * x.d * idot
                          (src/q4x_cpu.rs:85-101); hidden vector re-quantised the
                          same way before down (src/q4x_cpu.rs:399-440)            */
 };

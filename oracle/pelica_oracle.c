@@ -181,7 +181,9 @@ size_t po_type_block_bytes(int t) {
     case PM_TYPE_IQ4_NL: return 18;
     case PM_TYPE_IQ4_XS: return 136;
     case PM_TYPE_Q4_K: return 144;
+    case PM_TYPE_Q5_K: return 176;
     case PM_TYPE_Q6_K: return 210;
+    case PM_TYPE_IQ3_S: return 110;
     case PM_TYPE_MXFP4: return 17;
   }
   return 0;
@@ -195,7 +197,9 @@ size_t po_type_block_values(int t) {
     case PM_TYPE_IQ4_NL:
     case PM_TYPE_MXFP4: return 32;
     case PM_TYPE_Q4_K:
+    case PM_TYPE_Q5_K:
     case PM_TYPE_IQ4_XS:
+    case PM_TYPE_IQ3_S:
     case PM_TYPE_Q6_K: return 256;
   }
   return 0;
@@ -203,6 +207,11 @@ size_t po_type_block_values(int t) {
 
 /* the IQ4_NL codebook: a constant of the format (src/iq_tables.rs:72) */
 static const int8_t KV_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* the IQ3_S codebook, a constant of the format (src/iq_tables.rs:4), three bits a magnitude */
+static const uint16_t IQ3S_CODES[512] = {
+#include "../include/pelica_iq3s_grid.inc"
+};
 
 static inline float f16le(const uint8_t *b) {
   return po_f16_to_f32((uint16_t)(b[0] | (b[1] << 8)));
@@ -219,6 +228,25 @@ static void q4k_scales(const uint8_t *s, int32_t sc[8], int32_t m[8]) {
       m[j] = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
     }
   }
+}
+
+/* `iq3s_sub` (src/q4x_cpu.rs:64-82): sub-block ib (32 values) of a 110-byte IQ3_S block (d @0,
+ * qs @2, qh @66, signs @74, scales @106) as signed magnitudes; returns the scale 1 + 2 * sc */
+static int iq3s_sub(const uint8_t *blk, int ib, int8_t out[32]) {
+  const uint8_t *qs = blk + 2, *signs = blk + 74;
+  uint8_t qh = blk[66 + ib];
+  int sc = (blk[106 + ib / 2] >> (4 * (ib % 2))) & 15;
+  for (int k = 0; k < 8; k++) {
+    unsigned idx = (unsigned)qs[8 * ib + k] | (((unsigned)(qh >> k) & 1u) << 8);
+    unsigned code = IQ3S_CODES[idx];
+    for (int j = 0; j < 4; j++) {
+      int v = 4 * k + j;
+      int mag = 2 * (int)((code >> (3 * j)) & 7) + 1;
+      int neg = (signs[4 * ib + v / 8] >> (v % 8)) & 1;
+      out[v] = (int8_t)(neg ? -mag : mag);
+    }
+  }
+  return 1 + 2 * sc;
 }
 
 /* `e8` (src/oss_kernels.rs:42-45) */
@@ -287,6 +315,35 @@ int po_dequant(int t, const uint8_t *blocks, size_t n, float *out) {
             out[b * 256 + 32 * ib + 16 + i] = dl * (float)KV_IQ4NL[q >> 4];
           }
         }
+      }
+      return 0;
+    case PM_TYPE_IQ3_S: /* src/q4x_cpu.rs:477-487: d * scale * magnitude, signed */
+      for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = blocks + b * bb;
+        float d = f16le(blk);
+        int8_t q[32];
+        for (int ib = 0; ib < 8; ib++) {
+          int sc = iq3s_sub(blk, ib, q);
+          for (int i = 0; i < 32; i++) out[b * 256 + 32 * ib + i] = d * (float)sc * (float)q[i];
+        }
+      }
+      return 0;
+    case PM_TYPE_Q5_K: /* src/moe_kernels.rs:74: d @0, dmin @2, scales @4, qh @16, qs @48;
+                          dm.x * sm.x * (q | hb << 4) - dm.y * sm.y */
+      for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = blocks + b * bb;
+        float d = f16le(blk), dmin = f16le(blk + 2);
+        int32_t sc[8], m[8];
+        q4k_scales(blk + 4, sc, m);
+        const uint8_t *qh = blk + 16, *qs = blk + 48;
+        for (int c = 0; c < 4; c++)
+          for (int i = 0; i < 32; i++) {
+            uint8_t v = qs[32 * c + i];
+            int lo = (v & 15) | (((qh[i] >> (2 * c)) & 1) << 4);
+            int hi = (v >> 4) | (((qh[i] >> (2 * c + 1)) & 1) << 4);
+            out[b * 256 + 64 * c + i] = d * (float)sc[2 * c] * (float)lo - dmin * (float)m[2 * c];
+            out[b * 256 + 64 * c + 32 + i] = d * (float)sc[2 * c + 1] * (float)hi - dmin * (float)m[2 * c + 1];
+          }
       }
       return 0;
     case PM_TYPE_Q4_K: /* src/moe_kernels.rs:73: dm.x * sm.x * q - dm.y * sm.y */
@@ -490,10 +547,30 @@ float po_row_iq4xs(const uint8_t *w, size_t ncols, const int8_t *q, const float 
   return total;
 }
 
+/* src/q4x_cpu.rs:118-127 */
+float po_row_iq3s(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
+  float total = 0.0f;
+  size_t nb = ncols / 256;
+  for (size_t b = 0; b < nb; b++) {
+    const uint8_t *blk = w + b * 110;
+    float d = f16le(blk);
+    int8_t v[32];
+    for (int ib = 0; ib < 8; ib++) {
+      int sc = iq3s_sub(blk, ib, v);
+      size_t s = 8 * b + (size_t)ib;
+      int32_t acc = 0;
+      for (int i = 0; i < 32; i++) acc += (int32_t)v[i] * (int32_t)q[32 * s + i];
+      total += d * (float)sc * d32[s] * (float)acc;
+    }
+  }
+  return total;
+}
+
 /* a row of a type of the q4x path against 32-block Q8 activations (`row`, src/q4x_cpu.rs:367) */
 static float row_q8_32(int t, const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
   if (t == PM_TYPE_IQ4_NL) return po_row_iq4nl(w, ncols, q, d32);
   if (t == PM_TYPE_IQ4_XS) return po_row_iq4xs(w, ncols, q, d32);
+  if (t == PM_TYPE_IQ3_S) return po_row_iq3s(w, ncols, q, d32);
   return po_row_q8_0(w, ncols, q, d32);
 }
 
@@ -795,7 +872,7 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
     {
       const int ts[3] = {D->type_gate, D->type_up, D->type_down};
       for (int i = 0; i < 3; i++)
-        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL && ts[i] != PM_TYPE_IQ4_XS) {
+        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL && ts[i] != PM_TYPE_IQ4_XS && ts[i] != PM_TYPE_IQ3_S) {
           free(h);
           return PM_ERR_UNSUPPORTED;
         }

@@ -88,6 +88,8 @@ float po_row_q8_0(const uint8_t *w, size_t ncols, const int8_t *q, const float *
 float po_row_iq4nl(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
 /* IQ4_XS row against 32-block activations (src/q4x_cpu.rs:102-117) */
 float po_row_iq4xs(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
+/* IQ3_S row against 32-block activations (src/q4x_cpu.rs:118-127) */
+float po_row_iq3s(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
 /* any decodable type against f32 activations (src/oss_batch.rs:774-789 for
  * MXFP4): per block s = sum_i w_i * x_i in value order, total += s (block order);
  * for MXFP4 the block scale multiplies the block's sum as the shader does. */

@@ -84,7 +84,7 @@ def lib() -> C.CDLL:
             fn = getattr(L, name)
             fn.restype = C.c_float
             fn.argtypes = [u8p, C.c_size_t, i8p, f32p, i32p]
-        for name in ("po_row_q6k", "po_row_q6k_fast", "po_row_q8_0", "po_row_iq4nl", "po_row_iq4xs"):
+        for name in ("po_row_q6k", "po_row_q6k_fast", "po_row_q8_0", "po_row_iq4nl", "po_row_iq4xs", "po_row_iq3s"):
             fn = getattr(L, name)
             fn.restype = C.c_float
             fn.argtypes = [u8p, C.c_size_t, i8p, f32p]
@@ -196,6 +196,11 @@ def row_iq4nl(w, ncols, q, d32) -> float:
 def row_iq4xs(w, ncols, q, d32) -> float:
     w = np.ascontiguousarray(w, np.uint8)
     return lib().po_row_iq4xs(_p(w), ncols, _p(q), _p(d32))
+
+
+def row_iq3s(w, ncols, q, d32) -> float:
+    w = np.ascontiguousarray(w, np.uint8)
+    return lib().po_row_iq3s(_p(w), ncols, _p(q), _p(d32))
 
 
 def row_f32(ggml_type, w, ncols, x) -> float:

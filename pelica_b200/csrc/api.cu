@@ -52,7 +52,9 @@ extern "C" size_t pm_type_block_bytes(int32_t t) {
     case PM_TYPE_IQ4_NL: return 18;
     case PM_TYPE_IQ4_XS: return 136;
     case PM_TYPE_Q4_K: return 144;
+    case PM_TYPE_Q5_K: return 176;
     case PM_TYPE_Q6_K: return 210;
+    case PM_TYPE_IQ3_S: return 110;
     case PM_TYPE_MXFP4: return 17;
   }
   return 0;
@@ -63,7 +65,9 @@ extern "C" size_t pm_type_block_values(int32_t t) {
     case PM_TYPE_IQ4_NL:
     case PM_TYPE_MXFP4: return 32;
     case PM_TYPE_Q4_K:
+    case PM_TYPE_Q5_K:
     case PM_TYPE_IQ4_XS:
+    case PM_TYPE_IQ3_S:
     case PM_TYPE_Q6_K: return 256;
   }
   return 0;
@@ -370,7 +374,7 @@ struct pm_layer {
 
 static bool type_ok(int t) {
   return t == PM_TYPE_Q4_K || t == PM_TYPE_Q6_K || t == PM_TYPE_MXFP4 || t == PM_TYPE_Q8_0 || t == PM_TYPE_IQ4_NL ||
-         t == PM_TYPE_IQ4_XS;
+         t == PM_TYPE_IQ4_XS || t == PM_TYPE_IQ3_S || t == PM_TYPE_Q5_K;
 }
 
 static int32_t wmat_alloc(pm_layer *ly, WMat &W, int type, int n_exp, int rows, int cols) {
@@ -422,8 +426,8 @@ static int32_t validate_desc(const pm_layer_desc *D) {
       return fail(PM_ERR_INVALID, "32-block Q8 activations need d and ff multiples of 32 (src/q4x_cpu.rs:24)");
     const int t32[3] = {D->type_gate, D->type_up, D->type_down};
     for (int t : t32)
-      if (t != PM_TYPE_Q8_0 && t != PM_TYPE_IQ4_NL && t != PM_TYPE_IQ4_XS)
-        return fail(PM_ERR_UNSUPPORTED, "32-block Q8 activations pair with Q8_0 / IQ4_NL / IQ4_XS weights only");
+      if (t != PM_TYPE_Q8_0 && t != PM_TYPE_IQ4_NL && t != PM_TYPE_IQ4_XS && t != PM_TYPE_IQ3_S)
+        return fail(PM_ERR_UNSUPPORTED, "32-block Q8 activations pair with Q8_0 / IQ4_NL / IQ4_XS / IQ3_S weights only");
   } else if (D->act_quant != PM_AQ_F32) {
     return fail(PM_ERR_UNSUPPORTED, "act_quant %d", D->act_quant);
   }
@@ -669,7 +673,7 @@ static int32_t synth_mat(pm_layer *ly, WMat &W, int n_exp, uint64_t seed, float 
   pm_ctx *c = ly->ctx;
   size_t per = raw_bytes(W.type, (size_t)W.rows, (size_t)W.cols);
   size_t nb_per = (size_t)W.rows * (W.cols / pm_type_block_values(W.type));
-  if (W.type == PM_TYPE_Q8_0 || W.type == PM_TYPE_IQ4_NL || W.type == PM_TYPE_IQ4_XS) return fail(PM_ERR_UNSUPPORTED, "synthetic weights of type %d", W.type);
+  if (W.type != PM_TYPE_Q4_K && W.type != PM_TYPE_Q6_K && W.type != PM_TYPE_MXFP4) return fail(PM_ERR_UNSUPPORTED, "synthetic weights of type %d", W.type);
   // groups of experts so the raw staging stays below ~1 GB
   int group = (int)((((size_t)1 << 30) / per) ? (((size_t)1 << 30) / per) : 1);
   if (group > n_exp) group = n_exp;

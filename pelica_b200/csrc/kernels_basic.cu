@@ -66,6 +66,14 @@ void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t nb, uin
     case PM_TYPE_Q4_K:
       cudaMemcpyAsync(p0, raw, nb * 144, cudaMemcpyDeviceToDevice, L.stream);
       break;
+    case PM_TYPE_Q5_K:
+      cudaMemcpyAsync(p0, raw, nb * 176, cudaMemcpyDeviceToDevice, L.stream);
+      break;
+    case PM_TYPE_IQ3_S: {  // the f16 d first in the raw block, the four byte fields after
+      size_t n = nb * 110;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 110, 2, p1, p0, 0);
+      break;
+    }
     case PM_TYPE_Q6_K: {
       size_t n = nb * 105;
       KLAUNCH(L, k_repack_q6k, (unsigned)((n + 255) / 256), 256, 0, raw, nb, p0, p1, p2, p3);
@@ -100,6 +108,15 @@ void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uin
     case PM_TYPE_Q4_K:
       cudaMemcpyAsync(raw, p0, nb * 144, cudaMemcpyDeviceToDevice, L.stream);
       break;
+    case PM_TYPE_Q5_K:
+      cudaMemcpyAsync(raw, p0, nb * 176, cudaMemcpyDeviceToDevice, L.stream);
+      break;
+    case PM_TYPE_IQ3_S: {
+      size_t n = nb * 110;
+      KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 110, 2,
+              const_cast<uint8_t *>(p1), const_cast<uint8_t *>(p0), 1);
+      break;
+    }
     case PM_TYPE_Q6_K: {
       size_t n = nb * 105;
       KLAUNCH(L, k_unpack_q6k, (unsigned)((n + 255) / 256), 256, 0, raw, nb, p0, p1, p2, p3);
@@ -132,6 +149,36 @@ void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uin
   }
 }
 
+// the IQ3_S codebook, a constant of the format (src/iq_tables.rs:4): 512 entries of four odd
+// magnitudes, three bits each
+__device__ const uint16_t g_iq3s_codes[512] = {
+#include "../../include/pelica_iq3s_grid.inc"
+};
+// entry idx as four bytes (magnitude j in byte j), as the reference's table holds them
+__device__ __forceinline__ uint32_t pm_iq3s_grid(uint32_t idx) {
+  const uint32_t c = __ldg(&g_iq3s_codes[idx]);
+  const uint32_t h = (c & 7u) | ((c & 0x38u) << 5) | ((c & 0x1c0u) << 10) | ((c & 0xe00u) << 15);
+  return 2u * h + 0x01010101u;
+}
+// sub-block ib of an IQ3_S block (plane 0: qs @0, qh @64, signs @72, scales @104 of 108 bytes):
+// its 32 signed magnitudes as eight words of four int8, and the scale 1 + 2 * sc
+// (`iq3s_sub`, src/q4x_cpu.rs:64-82)
+__device__ __forceinline__ int pm_iq3s_sub(const uint8_t *__restrict__ blk, int ib, uint32_t out[8]) {
+  const uint32_t qh = blk[64 + ib];
+  const uint32_t sg = *(const uint32_t *)(blk + 72 + 4 * ib);  // bit v = sign of value v
+  const uint32_t q0 = *(const uint32_t *)(blk + 8 * ib), q1 = *(const uint32_t *)(blk + 8 * ib + 4);
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const uint32_t qs = ((k < 4 ? q0 : q1) >> (8 * (k & 3))) & 0xffu;
+    const uint32_t mag = pm_iq3s_grid(qs | (((qh >> k) & 1u) << 8));
+    // negate the bytes whose sign bit is set: (m ^ mask) - mask per byte with mask 0xff
+    const uint32_t nb = (sg >> (4 * k)) & 0xfu;
+    const uint32_t mask = ((nb & 1u) | ((nb & 2u) << 7) | ((nb & 4u) << 14) | ((nb & 8u) << 21)) * 0xffu;
+    out[k] = __vsub4(mag ^ mask, mask);
+  }
+  return 1 + 2 * (int)((blk[104 + ib / 2] >> (4 * (ib % 2))) & 15);
+}
+
 // value v of block b, from the device planes (`deq4`, src/moe_kernels.rs:63-84)
 template <int TYPE>
 __device__ __forceinline__ float deq_value(const uint8_t *p0, const uint8_t *p1, const uint8_t *p2,
@@ -147,6 +194,26 @@ __device__ __forceinline__ float deq_value(const uint8_t *p0, const uint8_t *p1,
     int q = (v % 64) >= 32 ? (byte >> 4) : (byte & 15);
     float d = pm_f16(h0), dmin = pm_f16(h0 >> 16);
     return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
+  } else if (TYPE == PM_TYPE_Q5_K) {  // (d*sc)*(q | hb << 4) - dmin*m (src/moe_kernels.rs:74)
+    const uint8_t *blk = p0 + b * 176;
+    const uint32_t *hw = (const uint32_t *)blk;
+    uint32_t h0 = hw[0];
+    int sc, m;
+    pm_q4k_scmin(hw[1], hw[2], hw[3], v / 32, sc, m);
+    int c = v / 64, i = v % 32, hi = (v % 64) >= 32;
+    uint8_t byte = blk[48 + 32 * c + i];
+    int q = (hi ? (byte >> 4) : (byte & 15)) | (((blk[16 + i] >> (2 * c + hi)) & 1) << 4);
+    float d = pm_f16(h0), dmin = pm_f16(h0 >> 16);
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
+  } else if (TYPE == PM_TYPE_IQ3_S) {  // (d * scale) * signed magnitude (src/q4x_cpu.rs:477-487)
+    const uint8_t *blk = p0 + b * 108;
+    const int ib = v >> 5, i = v & 31, k = i >> 2, j = i & 3;
+    const uint32_t idx = (uint32_t)blk[8 * ib + k] | ((((uint32_t)blk[64 + ib] >> k) & 1u) << 8);
+    const int mag = (int)((pm_iq3s_grid(idx) >> (8 * j)) & 0xffu);
+    const int neg = (blk[72 + 4 * ib + i / 8] >> (i % 8)) & 1;
+    const int sc = 1 + 2 * (int)((blk[104 + ib / 2] >> (4 * (ib % 2))) & 15);
+    const float d = pm_f16(*(const uint16_t *)(p1 + b * 2));
+    return __fmul_rn(__fmul_rn(d, (float)sc), (float)(neg ? -mag : mag));
   } else if (TYPE == PM_TYPE_Q6_K) {  // (d*sc)*(q-32) (src/moe_kernels.rs:75)
     int n = v / 128, r = v % 128, qt = r / 32, l = r % 32;
     uint8_t qlb = p0[b * 128 + 64 * n + l + 32 * (qt & 1)];
@@ -197,6 +264,8 @@ void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, cons
     case PM_TYPE_Q8_0: KLAUNCH(L, (k_dequant<PM_TYPE_Q8_0, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_IQ4_NL: KLAUNCH(L, (k_dequant<PM_TYPE_IQ4_NL, 32>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_IQ4_XS: KLAUNCH(L, (k_dequant<PM_TYPE_IQ4_XS, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_Q5_K: KLAUNCH(L, (k_dequant<PM_TYPE_Q5_K, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_IQ3_S: KLAUNCH(L, (k_dequant<PM_TYPE_IQ3_S, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
   }
 }
 
@@ -629,9 +698,31 @@ __device__ __forceinline__ float row_q8_0_q8(const WMat &W, int el, int r, const
   const int nb = W.cols / 32;  // 32-value units: a block of Q8_0 / IQ4_NL, a sub-block of IQ4_XS
   const bool xs = W.type == PM_TYPE_IQ4_XS;
   const bool nl = W.type == PM_TYPE_IQ4_NL || xs;
+  float total = 0.0f;
+  if (W.type == PM_TYPE_IQ3_S) {  // src/q4x_cpu.rs:118-127: per sub-block ((d * scale) * x.d) * idot
+    const uint8_t *blks = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * (nb / 8) * 108;
+    const uint8_t *ds = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * (nb / 8) * 2;
+    for (int b0 = 0; b0 < nb; b0 += 32) {
+      const int b = b0 + lane;
+      float term = 0.0f;
+      if (b < nb) {
+        uint32_t w[8];
+        const int sc = pm_iq3s_sub(blks + (size_t)(b >> 3) * 108, b & 7, w);
+        const int4 *xp = (const int4 *)(xq + (size_t)b * 32);
+        const int4 x0 = xp[0], x1 = xp[1];
+        int s = 0;
+        s = __dp4a((int)w[0], x0.x, s); s = __dp4a((int)w[1], x0.y, s); s = __dp4a((int)w[2], x0.z, s); s = __dp4a((int)w[3], x0.w, s);
+        s = __dp4a((int)w[4], x1.x, s); s = __dp4a((int)w[5], x1.y, s); s = __dp4a((int)w[6], x1.z, s); s = __dp4a((int)w[7], x1.w, s);
+        const float d = pm_f16(__ldg((const uint16_t *)(ds + (size_t)(b >> 3) * 2)));
+        term = __fmul_rn(__fmul_rn(__fmul_rn(d, (float)sc), xd[b]), (float)s);
+      }
+      const int n = min(32, nb - b0);
+      for (int j = 0; j < n; j++) total = __fadd_rn(total, __shfl_sync(PM_FULL, term, j));
+    }
+    return total;
+  }
   const uint8_t *vals = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * nb * (nl ? 16 : 32);
   const uint8_t *scl = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * (xs ? (nb / 8) * 8 : nb * 2);
-  float total = 0.0f;
   for (int b0 = 0; b0 < nb; b0 += 32) {
     const int b = b0 + lane;
     float term = 0.0f;
@@ -730,6 +821,8 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
       else if (W.type == PM_TYPE_Q6_K) wv = deq_value<PM_TYPE_Q6_K>(p0, p1, p2, p3, b, iv);
       else if (W.type == PM_TYPE_IQ4_NL) wv = deq_value<PM_TYPE_IQ4_NL>(p0, p1, p2, p3, b, iv);
       else if (W.type == PM_TYPE_IQ4_XS) wv = deq_value<PM_TYPE_IQ4_XS>(p0, p1, p2, p3, b, iv);
+      else if (W.type == PM_TYPE_Q5_K) wv = deq_value<PM_TYPE_Q5_K>(p0, p1, p2, p3, b, iv);
+      else if (W.type == PM_TYPE_IQ3_S) wv = deq_value<PM_TYPE_IQ3_S>(p0, p1, p2, p3, b, iv);
       else wv = deq_value<PM_TYPE_Q8_0>(p0, p1, p2, p3, b, iv);
       acc = __fmaf_rn(wv, x[v], acc);
     }

@@ -14,6 +14,8 @@
 //  IQ4_NL: plane 0 = codebook indices (16 B/block), 1 = f16 scales (2 B/block)
 //  IQ4_XS: plane 0 = codebook indices (128 B/block), 1 = the 8-byte header (f16 d, u16 high
 //          scale bits, 4 bytes of low scale nibbles)
+//  Q5_K : plane 0 = the GGUF blocks unchanged (176 B)
+//  IQ3_S: plane 0 = qs, qh, signs, scales as stored (108 B/block), 1 = f16 d (2 B/block)
 struct WMat {
   int type;
   int rows, cols;
@@ -83,6 +85,12 @@ static inline size_t wmat_plane_bytes(int type, int rows, int cols, int p) {
     case PM_TYPE_IQ4_XS:
       nb = (size_t)rows * (cols / 256);
       return p == 0 ? nb * 128 : (p == 1 ? nb * 8 : 0);
+    case PM_TYPE_Q5_K:
+      nb = (size_t)rows * (cols / 256);
+      return p == 0 ? nb * 176 : 0;
+    case PM_TYPE_IQ3_S:
+      nb = (size_t)rows * (cols / 256);
+      return p == 0 ? nb * 108 : (p == 1 ? nb * 2 : 0);
   }
   return 0;
 }

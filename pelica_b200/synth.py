@@ -1,5 +1,5 @@
 """Synthetic MoE layers: the named config shapes, seeded weights and the GGUF
-block encoders (Q4_K, Q6_K, MXFP4, Q8_0) that quantise them.
+block encoders (Q4_K, Q5_K, Q6_K, MXFP4, Q8_0, IQ4_NL, IQ4_XS, IQ3_S) that quantise them.
 
 Pelica has no quantiser for these formats (it only reads them from GGUF files,
 src/gguf.rs:85-121), so the encoders here are this repository's own. Any valid
@@ -14,8 +14,9 @@ import dataclasses
 import numpy as np
 
 # ggml type ids (src/gguf.rs:85-121)
-F32, F16, Q8_0, Q4_K, Q6_K, IQ4_NL, IQ4_XS, BF16, MXFP4 = 0, 1, 8, 12, 14, 20, 23, 30, 39
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ4_NL: (32, 18), IQ4_XS: (256, 136), MXFP4: (32, 17)}
+F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ3_S, IQ4_XS, BF16, MXFP4 = 0, 1, 8, 12, 13, 14, 20, 21, 23, 30, 39
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18), IQ3_S: (256, 110),
+         IQ4_XS: (256, 136), MXFP4: (32, 17)}
 # the IQ4_NL codebook, a constant of the format (src/iq_tables.rs:72)
 KV_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int8)
 
@@ -198,8 +199,102 @@ def encode_iq4_xs(x: np.ndarray) -> np.ndarray:
     return out.reshape(*lead, -1)
 
 
+def encode_q5_k(x: np.ndarray) -> np.ndarray:
+    """f32 [..., n] (n % 256 == 0) -> uint8 [..., n/256*176]: Q4_K's header (f16 d, f16 dmin, 12 bytes
+    of six-bit scales and mins), 32 bytes of fifth bits (byte l, bit 2c + hi = value 64c + 32hi + l),
+    128 bytes of low nibbles as in Q4_K (src/moe_kernels.rs:74)."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 8, 32)
+    nb = xb.shape[0]
+    mn = np.minimum(xb.min(-1), 0.0)
+    mx = xb.max(-1)
+    scale = np.maximum(mx - mn, 0.0) / 31.0
+    mins = -mn
+    d = (scale.max(-1) / 63.0).astype(np.float16)
+    dmin = (mins.max(-1) / 63.0).astype(np.float16)
+    df, dmf = d.astype(np.float32), dmin.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.clip(np.where(df[:, None] > 0, _round_half_away(scale / df[:, None]), 0.0), 0, 63)
+        m = np.clip(np.where(dmf[:, None] > 0, _round_half_away(mins / dmf[:, None]), 0.0), 0, 63)
+        step = df[:, None] * sc
+        q = np.where(step[..., None] > 0,
+                     _round_half_away((xb + (dmf[:, None] * m)[..., None]) / step[..., None]), 0.0)
+    q = np.clip(q, 0, 31).astype(np.uint8)
+    sc = sc.astype(np.uint8)
+    m = m.astype(np.uint8)
+    out = np.zeros((nb, 176), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(nb, 2)
+    s = out[:, 4:16]
+    s[:, 0:4] = sc[:, 0:4] | ((sc[:, 4:8] >> 4) << 6)
+    s[:, 4:8] = m[:, 0:4] | ((m[:, 4:8] >> 4) << 6)
+    s[:, 8:12] = (sc[:, 4:8] & 15) | ((m[:, 4:8] & 15) << 4)
+    qq = q.reshape(nb, 4, 2, 32)  # [c][hi][l]
+    for c in range(4):
+        for hi in range(2):
+            out[:, 16:48] |= ((qq[:, c, hi, :] >> 4) & 1) << (2 * c + hi)
+    out[:, 48:176] = ((qq[:, :, 0, :] & 15) | ((qq[:, :, 1, :] & 15) << 4)).reshape(nb, 128)
+    return out.reshape(*lead, -1)
+
+
+_IQ3S_GRID = None
+
+
+def iq3s_grid() -> np.ndarray:
+    """The IQ3_S codebook of the format as [512, 4] magnitudes (src/iq_tables.rs:4), from the packed
+    constant table the library and its checker also include."""
+    global _IQ3S_GRID
+    if _IQ3S_GRID is None:
+        import os
+        import re
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "include", "pelica_iq3s_grid.inc")
+        text = open(path).read()
+        codes = np.array([int(w, 16) for w in re.findall(r"0x[0-9a-f]{3}\b", text[text.index("*/"):])], np.int32)
+        assert codes.size == 512
+        _IQ3S_GRID = np.stack([2 * ((codes >> (3 * j)) & 7) + 1 for j in range(4)], -1).astype(np.int32)
+    return _IQ3S_GRID
+
+
+def encode_iq3_s(x: np.ndarray) -> np.ndarray:
+    """256 values -> 110 bytes: f16 d, 64 index bytes (8 per sub-block of 32: one per group of four
+    values), 8 bytes of ninth index bits (byte ib, bit k), 32 bytes of sign bits (bit v % 8 of byte
+    v / 8), 4 bytes of sub-block scale nibbles; value = d * (1 + 2 sc) * +-codebook[index][j]
+    (src/q4x_cpu.rs:64-82). Each group of four takes the nearest codebook entry."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 8, 32)
+    nb = xb.shape[0]
+    grid = iq3s_grid().astype(np.float32)            # [512, 4]
+    amax = np.abs(xb).max(-1)                        # [nb, 8]
+    d = (amax.max(-1) / 15.0 / 31.0).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(df[:, None] > 0, np.rint((amax / 15.0 / df[:, None] - 1.0) / 2.0), 0.0)
+    sc = np.clip(sc, 0, 15).astype(np.int32)
+    dl = df[:, None] * (1 + 2 * sc).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        t = np.where(dl[:, :, None] > 0, np.abs(xb) / dl[:, :, None], 0.0).reshape(-1, 4)  # groups of four
+    idx = np.empty(t.shape[0], np.int32)
+    for i in range(0, t.shape[0], 4096):
+        c = t[i:i + 4096]
+        idx[i:i + 4096] = ((c[:, None, :] - grid[None]) ** 2).sum(-1).argmin(-1)
+    idx = idx.reshape(nb, 8, 8)
+    neg = (xb < 0).reshape(nb, 32, 8)                # [byte][bit]
+    out = np.zeros((nb, 110), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:66] = (idx & 0xFF).astype(np.uint8).reshape(nb, 64)
+    for k in range(8):
+        out[:, 66:74] |= (((idx[:, :, k] >> 8) & 1) << k).astype(np.uint8)
+    for bit in range(8):
+        out[:, 74:106] |= (neg[:, :, bit].astype(np.uint8) << bit)
+    for ib in range(8):
+        out[:, 106 + ib // 2] |= ((sc[:, ib] & 15) << (4 * (ib % 2))).astype(np.uint8)
+    return out.reshape(*lead, -1)
+
+
 ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0, IQ4_NL: encode_iq4_nl,
-            IQ4_XS: encode_iq4_xs}
+            IQ4_XS: encode_iq4_xs, Q5_K: encode_q5_k, IQ3_S: encode_iq3_s}
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:
@@ -282,8 +377,13 @@ C6_Q8_0 = Config("q4x-q8_0", d=2560, ff=640, n_exp=32, top_k=8, gating=GATE_SOFT
 # the same path with the 4-bit non-linear type of the reference's Qwen3.8 down tensors
 C7_IQ4NL = C6_Q8_0.scaled(name="q4x-iq4_nl", type_gate=IQ4_NL, type_up=IQ4_NL, type_down=IQ4_NL)
 C8_IQ4XS = C6_Q8_0.scaled(name="q4x-iq4_xs", type_gate=IQ4_XS, type_up=IQ4_XS, type_down=IQ4_NL)
+# ... with the 3-bit codebook type of the reference's Qwen3.8 gate / up tensors (src/q4x_cpu.rs:118-127)
+C9_IQ3S = C6_Q8_0.scaled(name="q4x-iq3_s", type_gate=IQ3_S, type_up=IQ3_S, type_down=IQ4_NL)
+# Q5_K has a decoder only in the reference (src/moe_kernels.rs:74): f32 activations
+C10_Q5K = C2_QWEN3.scaled(name="qwen3-q5_k-f32", type_gate=Q5_K, type_up=Q5_K, type_down=Q5_K, act_quant=AQ_F32,
+                          weight_fold=FOLD_IN_COMBINE)
 CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0,
-           "c7": C7_IQ4NL, "c8": C8_IQ4XS}
+           "c7": C7_IQ4NL, "c8": C8_IQ4XS, "c9": C9_IQ3S, "c10": C10_Q5K}
 
 
 def make_weights(cfg: Config, seed: int, experts=None) -> dict:

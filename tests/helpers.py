@@ -61,6 +61,8 @@ SMALL = {
     "c6": synth.C6_Q8_0.scaled(d=320, ff=160, n_exp=16),
     "c7": synth.C7_IQ4NL.scaled(d=320, ff=160, n_exp=16, type_down=synth.Q8_0),  # mixed 32-block types
     "c8": synth.C8_IQ4XS.scaled(d=512, ff=160, n_exp=16),
+    "c9": synth.C9_IQ3S.scaled(d=512, ff=160, n_exp=16),
+    "c10": synth.C10_Q5K.scaled(d=512, ff=256, n_exp=16),
 }
 
 

@@ -10,15 +10,15 @@ from pelica_b200 import gguf, synth
 from tests.helpers import SMALL, bits_equal
 
 
-def _file(tmp_path, name, n_layers=2):
+def _file(tmp_path, name, n_layers=2, **kw):
     cfg = SMALL[name]
     layers = [synth.make_weights(cfg, 50 + i) for i in range(n_layers)]
     path = os.path.join(tmp_path, f"{name}.gguf")
-    gguf.write_moe_layers(path, cfg, layers)
+    gguf.write_moe_layers(path, cfg, layers, **kw)
     return cfg, layers, path
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c4", "c6"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c4", "c6", "c9", "c10"])
 def test_round_trip_and_config(tmp_path, name):
     cfg, layers, path = _file(str(tmp_path), name)
     with gguf.GGUFFile(path) as g:
@@ -37,6 +37,48 @@ def test_round_trip_and_config(tmp_path, name):
                 assert bits_equal(w["select_bias"], want["select_bias"])
             if cfg.shared:
                 assert np.array_equal(w["shared_down"], want["shared_down"])
+
+
+@pytest.mark.parametrize("name,between", [("c2", False), ("c2", True), ("c4", True), ("c9", True)])
+def test_repacked_layout(tmp_path, name, between):
+    """Each expert's three pieces side by side (`*_expm`, src/repack.rs:1-24): the same weights come
+    back, other tensors that sat between the expert tensors are found at their new offsets, and undoing
+    restores the file byte for byte."""
+    cfg, layers, path = _file(str(tmp_path), name, router_between=between)
+    before = open(path, "rb").read()
+    assert gguf.repack(path) == 2 and gguf.repack(path) == 0
+    after = open(path, "rb").read()
+    assert len(after) == len(before) and after != before
+    with gguf.GGUFFile(path) as g:
+        assert gguf.layer_is_repacked(g, 0) and "blk.1.ffn_up_exps.weight" not in g.tensors
+        assert gguf.moe_config(g, 1).type_down == cfg.type_down
+        # an expert is one contiguous run of the file: gate, up, down
+        t = [g.tensor(f"blk.1.{p}_expm.weight") for p in gguf.PIECES]
+        lens = [i.nbytes // cfg.n_exp for i in t]
+        base = min(i.offset for i in t)
+        e = 3
+        run = np.frombuffer(after, np.uint8, sum(lens), base + e * sum(lens))
+        want = np.concatenate([np.asarray(layers[1][k][e]).ravel() for k in ("gate", "up", "down")])
+        assert np.array_equal(run, want)
+        for i, want in enumerate(layers):
+            w = gguf.layer_weights(g, i, cfg)
+            for k in ("router", "gate", "up", "down"):
+                assert np.array_equal(np.asarray(w[k]).reshape(-1), np.asarray(want[k]).reshape(-1)), k
+            if cfg.shared:
+                assert np.array_equal(w["shared_up"], want["shared_up"])
+    assert gguf.repack(path, undo=True) == 2
+    assert open(path, "rb").read() == before
+
+
+def test_half_repacked_layer_is_refused(tmp_path):
+    cfg, _, path = _file(str(tmp_path), "c1", 1)
+    data = bytearray(open(path, "rb").read())
+    at = data.index(b"blk.0.ffn_up_exps.weight")
+    data[at:at + 24] = b"blk.0.ffn_up_expm.weight"
+    open(path, "wb").write(data)
+    with gguf.GGUFFile(path) as g:
+        with pytest.raises(gguf.GGUFError):
+            gguf.layer_weights(g, 0, cfg)
 
 
 def test_rejects_bad_files(tmp_path):
@@ -64,11 +106,13 @@ def test_oracle_layer_from_file(tmp_path, oracle):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["c2", "c4"])
-def test_layer_loaded_from_file(tmp_path, ctx, name):
+@pytest.mark.parametrize("name,repacked", [("c2", False), ("c4", False), ("c2", True), ("c9", True)])
+def test_layer_loaded_from_file(tmp_path, ctx, name, repacked):
     import pelica_b200 as pb
 
-    cfg, layers, path = _file(str(tmp_path), name)
+    cfg, layers, path = _file(str(tmp_path), name, router_between=repacked)
+    if repacked:
+        assert gguf.repack(path) == 2
     x = synth.make_activations(9, cfg.d, 78)
     with gguf.GGUFFile(path) as g:
         over = {k: getattr(cfg, k) for k in ("gating", "n_group", "topk_group", "w_scale", "select_bias_sigma")}

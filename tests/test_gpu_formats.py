@@ -9,7 +9,8 @@ from tests.helpers import bits_equal, lcg, ref_acts, ref_q4k_blocks
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS])
+@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.MXFP4, synth.Q8_0, synth.IQ4_NL,
+                                synth.IQ4_XS, synth.IQ3_S])
 def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
     """Every bit pattern path: random block bytes, only the f16 scales kept finite."""
     v, b = synth.BLOCK[ty]
@@ -17,11 +18,11 @@ def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
     nb = 257
     raw = rng.integers(0, 256, nb * b, dtype=np.uint8).reshape(nb, b)
     half = rng.normal(0, 0.05, (nb, 2)).astype(np.float16).view(np.uint8).reshape(nb, 4)
-    if ty == synth.Q4_K:
+    if ty in (synth.Q4_K, synth.Q5_K):
         raw[:, 0:4] = half
     elif ty == synth.Q6_K:
         raw[:, 208:210] = half[:, :2]
-    elif ty in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS):
+    elif ty in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_S):
         raw[:, 0:2] = half[:, :2]
     else:
         raw[:3, 0] = [0, 1, 2]  # the denormal branch of e8 (src/oss_kernels.rs:42-45)
@@ -31,7 +32,8 @@ def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
     assert bits_equal(got, want)
 
 
-@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q6_K, synth.MXFP4, synth.IQ4_NL, synth.IQ4_XS])
+@pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.MXFP4, synth.IQ4_NL, synth.IQ4_XS,
+                                synth.IQ3_S])
 def test_dequant_encoded_weights(ctx, oracle, ty):
     rng = np.random.default_rng(1)
     x = rng.normal(0, 0.02, 4096).astype(np.float32)

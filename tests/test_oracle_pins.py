@@ -82,13 +82,14 @@ def test_rows_match_dequant(oracle):
     # weights . dequantised activations within 1e-3*max(|want|,1)
     rng = np.random.default_rng(5)
     for ty, n in ((synth.Q4_K, 1024), (synth.Q6_K, 768), (synth.Q8_0, 512), (synth.IQ4_NL, 2560),
-                  (synth.IQ4_XS, 2560)):
+                  (synth.IQ4_XS, 2560), (synth.IQ3_S, 2560)):
         w = synth.ENCODERS[ty](rng.normal(0, 0.02, n).astype(np.float32))
         x = rng.normal(0, 1, n).astype(np.float32)
         wd = oracle.dequant(ty, w, n).astype(np.float64)
-        if ty in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS):
+        if ty in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_S):
             q, d = oracle.q8_32(x)
-            got = {synth.Q8_0: oracle.row_q8_0, synth.IQ4_NL: oracle.row_iq4nl, synth.IQ4_XS: oracle.row_iq4xs}[ty](w, n, q, d)
+            got = {synth.Q8_0: oracle.row_q8_0, synth.IQ4_NL: oracle.row_iq4nl, synth.IQ4_XS: oracle.row_iq4xs,
+                   synth.IQ3_S: oracle.row_iq3s}[ty](w, n, q, d)
             xd = q.astype(np.float64) * np.repeat(d, 32)
         else:
             q, d, bs = oracle.q8x(x)
