@@ -63,7 +63,13 @@ enum {
   PM_TYPE_IQ4_XS = 23, /* 256 values / 136 B: f16 d, 8 six-bit sub-scales (bias 32), indices into
                           the IQ4_NL codebook (src/q4x_cpu.rs:102-117,462-476) */
   PM_TYPE_BF16 = 30,
-  PM_TYPE_MXFP4 = 39  /* 32 values / 17 B  */
+  PM_TYPE_MXFP4 = 39, /* 32 values / 17 B  */
+  /* not a ggml id: the reference's own int4 container (src/quant.rs:9-11, src/gpu.rs:70-117). A
+     [rows][cols] matrix is rows * cols / 2 bytes of nibbles (value c in byte c / 2, low nibble
+     first, stored as level + 8) followed by rows * cols / 64 f32 scales, one per group of 64
+     columns; value = (nibble - 8) * scale. f32 activations. (The container's table-indexed
+     scales, `Q4T`, hold the same values: expand them to f32 before the upload.) */
+  PM_TYPE_GLM_Q4 = 1064
 };
 
 /* ---- router gating (src/moe_kernels.rs:1019-1081, src/oss_kernels.rs:15-35,

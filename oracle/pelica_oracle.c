@@ -185,6 +185,7 @@ size_t po_type_block_bytes(int t) {
     case PM_TYPE_Q6_K: return 210;
     case PM_TYPE_IQ3_S: return 110;
     case PM_TYPE_MXFP4: return 17;
+    case PM_TYPE_GLM_Q4: return 36;
   }
   return 0;
 }
@@ -196,6 +197,7 @@ size_t po_type_block_values(int t) {
     case PM_TYPE_Q8_0:
     case PM_TYPE_IQ4_NL:
     case PM_TYPE_MXFP4: return 32;
+    case PM_TYPE_GLM_Q4: return 64;
     case PM_TYPE_Q4_K:
     case PM_TYPE_Q5_K:
     case PM_TYPE_IQ4_XS:
@@ -375,6 +377,20 @@ int po_dequant(int t, const uint8_t *blocks, size_t n, float *out) {
         }
       }
       return 0;
+    case PM_TYPE_GLM_Q4: { /* src/quant.rs:9-11: nibbles (level + 8, low nibble first), then the f32
+                              group scales; value = (nibble - 8) * scale (src/gpu.rs:96-99) */
+      const uint8_t *sc = blocks + nb * 32;
+      for (size_t g = 0; g < nb; g++) {
+        float scale;
+        memcpy(&scale, sc + 4 * g, 4);
+        for (int j = 0; j < 32; j++) {
+          uint8_t v = blocks[g * 32 + j];
+          out[g * 64 + 2 * j] = (float)((int)(v & 15) - 8) * scale;
+          out[g * 64 + 2 * j + 1] = (float)((int)(v >> 4) - 8) * scale;
+        }
+      }
+      return 0;
+    }
     case PM_TYPE_MXFP4: /* src/moe_kernels.rs:80 */
       for (size_t b = 0; b < nb; b++) {
         const uint8_t *blk = blocks + b * bb;
@@ -574,8 +590,35 @@ static float row_q8_32(int t, const uint8_t *w, size_t ncols, const int8_t *q, c
   return po_row_q8_0(w, ncols, q, d32);
 }
 
+/* `dot_q4_scalar` (src/quant.rs:464-476): per group of 64 the sum of level * x, then times the scale */
+float po_row_glm_q4(const uint8_t *q, const uint8_t *scales, size_t ncols, const float *x) {
+  float total = 0.0f;
+  for (size_t g = 0; g < ncols / 64; g++) {
+    float scale, acc = 0.0f;
+    memcpy(&scale, scales + 4 * g, 4);
+    for (int j = 0; j < 32; j++) {
+      uint8_t b = q[g * 32 + j];
+      size_t c = g * 64 + 2 * (size_t)j;
+      acc += (float)((int)(b & 15) - 8) * x[c] + (float)((int)(b >> 4) - 8) * x[c + 1];
+    }
+    total += acc * scale;
+  }
+  return total;
+}
+
+static size_t row_bytes(int type, size_t ncols);
+
+/* row r of a [rows][ncols] matrix of type t, as the layer holds it: GGUF types are rows of whole
+ * blocks; the int4 container keeps all the nibble rows first and the scale rows after them */
+static float mat_row_f32(int t, const uint8_t *m, size_t rows, size_t ncols, size_t r, const float *x) {
+  if (t == PM_TYPE_GLM_Q4)
+    return po_row_glm_q4(m + r * (ncols / 2), m + rows * (ncols / 2) + r * (ncols / 64) * 4, ncols, x);
+  return po_row_f32(t, m + r * row_bytes(t, ncols), ncols, x);
+}
+
 float po_row_f32(int t, const uint8_t *w, size_t ncols, const float *x) {
   float total = 0.0f;
+  if (t == PM_TYPE_GLM_Q4) return po_row_glm_q4(w, w + ncols / 2, ncols, x); /* a one-row matrix */
   if (t == PM_TYPE_MXFP4) { /* src/oss_batch.rs:774-789: scale * (dots of the block) */
     size_t nb = ncols / 32;
     for (size_t b = 0; b < nb; b++) {
@@ -899,14 +942,14 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
   } else if (D->act_quant == PM_AQ_F32) {
     for (int t = 0; t < nt; t++) {
       for (int j = 0; j < ff; j++) {
-        float g = po_row_f32(D->type_gate, W->gate + (size_t)j * bg, (size_t)d, xs[t]);
-        float u = po_row_f32(D->type_up, W->up + (size_t)j * bu, (size_t)d, xs[t]);
+        float g = mat_row_f32(D->type_gate, W->gate, (size_t)ff, (size_t)d, (size_t)j, xs[t]);
+        float u = mat_row_f32(D->type_up, W->up, (size_t)ff, (size_t)d, (size_t)j, xs[t]);
         if (W->bias_gate) g = g + W->bias_gate[j];
         if (W->bias_up) u = u + W->bias_up[j];
         h[j] = act_fn(D, g, u, wts ? wts[t] : 1.0f, fold);
       }
       for (int r = 0; r < d; r++) {
-        float o = po_row_f32(D->type_down, W->down + (size_t)r * bd, (size_t)ff, h);
+        float o = mat_row_f32(D->type_down, W->down, (size_t)d, (size_t)ff, (size_t)r, h);
         if (W->bias_down) o = o + W->bias_down[r]; /* src/oss_batch.rs:89 */
         out[(size_t)t * d + r] = o;
       }

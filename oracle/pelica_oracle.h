@@ -88,6 +88,9 @@ float po_row_q8_0(const uint8_t *w, size_t ncols, const int8_t *q, const float *
 float po_row_iq4nl(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
 /* IQ4_XS row against 32-block activations (src/q4x_cpu.rs:102-117) */
 float po_row_iq4xs(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
+/* a row of the int4 container (groups of 64, f32 scales) against f32 activations
+ * (`dot_q4_scalar`, src/quant.rs:464-476) */
+float po_row_glm_q4(const uint8_t *q, const uint8_t *scales, size_t ncols, const float *x);
 /* IQ3_S row against 32-block activations (src/q4x_cpu.rs:118-127) */
 float po_row_iq3s(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
 /* any decodable type against f32 activations (src/oss_batch.rs:774-789 for

@@ -56,6 +56,7 @@ extern "C" size_t pm_type_block_bytes(int32_t t) {
     case PM_TYPE_Q6_K: return 210;
     case PM_TYPE_IQ3_S: return 110;
     case PM_TYPE_MXFP4: return 17;
+    case PM_TYPE_GLM_Q4: return 36;  // 32 bytes of nibbles + the group's f32 scale (kept in a region of their own)
   }
   return 0;
 }
@@ -64,6 +65,7 @@ extern "C" size_t pm_type_block_values(int32_t t) {
     case PM_TYPE_Q8_0:
     case PM_TYPE_IQ4_NL:
     case PM_TYPE_MXFP4: return 32;
+    case PM_TYPE_GLM_Q4: return 64;
     case PM_TYPE_Q4_K:
     case PM_TYPE_Q5_K:
     case PM_TYPE_IQ4_XS:
@@ -374,7 +376,7 @@ struct pm_layer {
 
 static bool type_ok(int t) {
   return t == PM_TYPE_Q4_K || t == PM_TYPE_Q6_K || t == PM_TYPE_MXFP4 || t == PM_TYPE_Q8_0 || t == PM_TYPE_IQ4_NL ||
-         t == PM_TYPE_IQ4_XS || t == PM_TYPE_IQ3_S || t == PM_TYPE_Q5_K;
+         t == PM_TYPE_IQ4_XS || t == PM_TYPE_IQ3_S || t == PM_TYPE_Q5_K || t == PM_TYPE_GLM_Q4;
 }
 
 static int32_t wmat_alloc(pm_layer *ly, WMat &W, int type, int n_exp, int rows, int cols) {

@@ -69,6 +69,10 @@ void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t nb, uin
     case PM_TYPE_Q5_K:
       cudaMemcpyAsync(p0, raw, nb * 176, cudaMemcpyDeviceToDevice, L.stream);
       break;
+    case PM_TYPE_GLM_Q4:  // the nibble region, then the scale region
+      cudaMemcpyAsync(p0, raw, nb * 32, cudaMemcpyDeviceToDevice, L.stream);
+      cudaMemcpyAsync(p1, raw + nb * 32, nb * 4, cudaMemcpyDeviceToDevice, L.stream);
+      break;
     case PM_TYPE_IQ3_S: {  // the f16 d first in the raw block, the four byte fields after
       size_t n = nb * 110;
       KLAUNCH(L, k_repack_split, (unsigned)((n + 255) / 256), 256, 0, raw, nb, 110, 2, p1, p0, 0);
@@ -110,6 +114,10 @@ void launch_unpack(const Launch &L, int type, uint8_t *raw, size_t nb, const uin
       break;
     case PM_TYPE_Q5_K:
       cudaMemcpyAsync(raw, p0, nb * 176, cudaMemcpyDeviceToDevice, L.stream);
+      break;
+    case PM_TYPE_GLM_Q4:
+      cudaMemcpyAsync(raw, p0, nb * 32, cudaMemcpyDeviceToDevice, L.stream);
+      cudaMemcpyAsync(raw + nb * 32, p1, nb * 4, cudaMemcpyDeviceToDevice, L.stream);
       break;
     case PM_TYPE_IQ3_S: {
       size_t n = nb * 110;
@@ -214,6 +222,10 @@ __device__ __forceinline__ float deq_value(const uint8_t *p0, const uint8_t *p1,
     const int sc = 1 + 2 * (int)((blk[104 + ib / 2] >> (4 * (ib % 2))) & 15);
     const float d = pm_f16(*(const uint16_t *)(p1 + b * 2));
     return __fmul_rn(__fmul_rn(d, (float)sc), (float)(neg ? -mag : mag));
+  } else if (TYPE == PM_TYPE_GLM_Q4) {  // (nibble - 8) * scale of the group (src/gpu.rs:96-99)
+    const uint8_t byte = p0[b * 32 + (v >> 1)];
+    const int q = (v & 1) ? (byte >> 4) : (byte & 15);
+    return __fmul_rn((float)(q - 8), *(const float *)(p1 + b * 4));
   } else if (TYPE == PM_TYPE_Q6_K) {  // (d*sc)*(q-32) (src/moe_kernels.rs:75)
     int n = v / 128, r = v % 128, qt = r / 32, l = r % 32;
     uint8_t qlb = p0[b * 128 + 64 * n + l + 32 * (qt & 1)];
@@ -266,6 +278,7 @@ void launch_dequant(const Launch &L, int type, size_t n, const uint8_t *p0, cons
     case PM_TYPE_IQ4_XS: KLAUNCH(L, (k_dequant<PM_TYPE_IQ4_XS, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_Q5_K: KLAUNCH(L, (k_dequant<PM_TYPE_Q5_K, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
     case PM_TYPE_IQ3_S: KLAUNCH(L, (k_dequant<PM_TYPE_IQ3_S, 256>), g, 256, 0, n, p0, p1, p2, p3, out); break;
+    case PM_TYPE_GLM_Q4: KLAUNCH(L, (k_dequant<PM_TYPE_GLM_Q4, 64>), g, 256, 0, n, p0, p1, p2, p3, out); break;
   }
 }
 
@@ -805,6 +818,32 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
       }
       t = __fmul_rn(t, 32768.0f);
       acc = __fmaf_rn(s, t, acc);
+    }
+  } else if (W.type == PM_TYPE_GLM_Q4) {
+    // `dot_q4_scalar` (src/quant.rs:464-476): per group of 64 the sum of level * x, then times the
+    // group's scale; a lane takes whole groups (two 16-byte loads of nibbles, 64 activations)
+    const int ng = W.cols / 64;
+    const uint8_t *nib = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * ng * 32;
+    const float *scl = (const float *)(W.plane[1] + (size_t)el * W.stride[1]) + (size_t)r * ng;
+    for (int g = lane; g < ng; g += 32) {
+      const uint4 q0 = __ldg((const uint4 *)(nib + (size_t)g * 32)), q1 = __ldg((const uint4 *)(nib + (size_t)g * 32 + 16));
+      const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      const float4 *xp = (const float4 *)(x + g * 64);
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 8; w++) {  // a word = 8 consecutive values, low nibble first
+        const float4 x0 = xp[2 * w], x1 = xp[2 * w + 1];
+        const uint32_t q = qw[w];
+        t = __fmaf_rn((float)((int)(q & 15) - 8), x0.x, t);
+        t = __fmaf_rn((float)((int)((q >> 4) & 15) - 8), x0.y, t);
+        t = __fmaf_rn((float)((int)((q >> 8) & 15) - 8), x0.z, t);
+        t = __fmaf_rn((float)((int)((q >> 12) & 15) - 8), x0.w, t);
+        t = __fmaf_rn((float)((int)((q >> 16) & 15) - 8), x1.x, t);
+        t = __fmaf_rn((float)((int)((q >> 20) & 15) - 8), x1.y, t);
+        t = __fmaf_rn((float)((int)((q >> 24) & 15) - 8), x1.z, t);
+        t = __fmaf_rn((float)((int)(q >> 28) - 8), x1.w, t);
+      }
+      acc = __fmaf_rn(t, __ldg(scl + g), acc);
     }
   } else {
     const uint8_t *p0 = W.plane[0] + (size_t)el * W.stride[0];

@@ -16,6 +16,7 @@
 //          scale bits, 4 bytes of low scale nibbles)
 //  Q5_K : plane 0 = the GGUF blocks unchanged (176 B)
 //  IQ3_S: plane 0 = qs, qh, signs, scales as stored (108 B/block), 1 = f16 d (2 B/block)
+//  GLM_Q4: plane 0 = nibbles (32 B per group of 64), 1 = f32 group scales: the container's two regions
 struct WMat {
   int type;
   int rows, cols;
@@ -91,6 +92,9 @@ static inline size_t wmat_plane_bytes(int type, int rows, int cols, int p) {
     case PM_TYPE_IQ3_S:
       nb = (size_t)rows * (cols / 256);
       return p == 0 ? nb * 108 : (p == 1 ? nb * 2 : 0);
+    case PM_TYPE_GLM_Q4:
+      nb = (size_t)rows * (cols / 64);
+      return p == 0 ? nb * 32 : (p == 1 ? nb * 4 : 0);
   }
   return 0;
 }

@@ -132,12 +132,12 @@ __device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *er
 
 int tc_max_tiles(int n_pairs, int max_groups);
 
-// Compile with -DPM_TC_TRACE to stamp the phases of CTA (0, 0) with the SM clock:
-// [thread 0 | thread 511][block][stamp]; read back with pm_debug_tc_trace.
+// Compile with -DPM_TC_TRACE=1 (gate/up launches) or =2 (down launches) to stamp the phases of
+// CTA (0, 0) with the SM clock: [thread 0 | thread 511][block][stamp]; read back with pm_debug_tc_trace.
 #ifdef PM_TC_TRACE
 __device__ unsigned long long g_tc_trace[2 * 32 * 8];
 #define TC_STAMP(b, i)                                                                         \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 511) && (b) < 32)              \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 511) && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
     g_tc_trace[((tid ? 1 : 0) * 32 + (b)) * 8 + (i)] = clock64();
 extern "C" __attribute__((visibility("default"))) int pm_debug_tc_trace(unsigned long long *out) {
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));

@@ -15,8 +15,9 @@ import numpy as np
 
 # ggml type ids (src/gguf.rs:85-121)
 F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ3_S, IQ4_XS, BF16, MXFP4 = 0, 1, 8, 12, 13, 14, 20, 21, 23, 30, 39
+GLM_Q4 = 1064  # not a ggml id: the reference's int4 container, groups of 64 with f32 scales (src/quant.rs:9-11)
 BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18), IQ3_S: (256, 110),
-         IQ4_XS: (256, 136), MXFP4: (32, 17)}
+         IQ4_XS: (256, 136), MXFP4: (32, 17), GLM_Q4: (64, 36)}
 # the IQ4_NL codebook, a constant of the format (src/iq_tables.rs:72)
 KV_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int8)
 
@@ -293,8 +294,35 @@ def encode_iq3_s(x: np.ndarray) -> np.ndarray:
     return out.reshape(*lead, -1)
 
 
+def encode_glm_q4(x: np.ndarray) -> np.ndarray:
+    """`quantize_q4` (src/quant.rs:179-201): groups of 64, step = max(amax / 7, 1e-8), levels
+    round(v / step) (ties to even) clamped to [-8, 7] and stored + 8, value c in byte c / 2 (low
+    nibble first). f32 [..., n] -> uint8 [..., n/2 + n/64*4]: each row's nibbles, then its scales
+    (`encode_matrix` puts a whole matrix into the container's two regions)."""
+    x = np.asarray(x, np.float32)
+    lead = x.shape[:-1]
+    xb = x.reshape(-1, 64)
+    step = np.maximum(np.abs(xb).max(-1) / np.float32(7.0), np.float32(1e-8)).astype(np.float32)
+    lv = np.clip(np.rint(xb / step[:, None]), -8, 7).astype(np.int32) + 8
+    q = (lv[:, 0::2] | (lv[:, 1::2] << 4)).astype(np.uint8)                 # [groups, 32]
+    n = x.shape[-1]
+    rows = q.reshape(-1, n // 2)
+    sc = step.view(np.uint8).reshape(-1, n // 64 * 4)
+    return np.concatenate([rows, sc], -1).reshape(*lead, -1)
+
+
+def encode_matrix(ty: int, m: np.ndarray) -> np.ndarray:
+    """A [rows][cols] f32 matrix as the bytes `pm_layer_set_expert` takes for type `ty`: rows of
+    whole blocks, except the int4 container, whose nibble rows all come before its scale rows."""
+    enc = ENCODERS[ty](m)
+    if ty == GLM_Q4:
+        nq = m.shape[-1] // 2
+        return np.concatenate([enc[:, :nq].ravel(), enc[:, nq:].ravel()])
+    return enc.ravel()
+
+
 ENCODERS = {Q4_K: encode_q4_k, Q6_K: encode_q6_k, MXFP4: encode_mxfp4, Q8_0: encode_q8_0, IQ4_NL: encode_iq4_nl,
-            IQ4_XS: encode_iq4_xs, Q5_K: encode_q5_k, IQ3_S: encode_iq3_s}
+            IQ4_XS: encode_iq4_xs, Q5_K: encode_q5_k, IQ3_S: encode_iq3_s, GLM_Q4: encode_glm_q4}
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:
@@ -382,8 +410,14 @@ C9_IQ3S = C6_Q8_0.scaled(name="q4x-iq3_s", type_gate=IQ3_S, type_up=IQ3_S, type_
 # Q5_K has a decoder only in the reference (src/moe_kernels.rs:74): f32 activations
 C10_Q5K = C2_QWEN3.scaled(name="qwen3-q5_k-f32", type_gate=Q5_K, type_up=Q5_K, type_down=Q5_K, act_quant=AQ_F32,
                           weight_fold=FOLD_IN_COMBINE)
+# the reference's GLM tier (src/forward.rs:95-113,488-504): int4 container, f32 activations, sigmoid scores
+# ranked with a bias, clamped SwiGLU, a shared expert, weights applied to the expert outputs
+C11_GLM = Config("glm-int4-gs64", d=2048, ff=1536, n_exp=64, top_k=8, gating=GATE_SIGMOID, norm_w=1, w_scale=2.5,
+                 act=ACT_SILU_CLAMP, act_limit=10.0, type_gate=GLM_Q4, type_up=GLM_Q4, type_down=GLM_Q4,
+                 act_quant=AQ_F32, weight_fold=FOLD_IN_COMBINE, shared=SHARED_PLAIN, shared_ff=1536,
+                 select_bias_sigma=0.01)
 CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0,
-           "c7": C7_IQ4NL, "c8": C8_IQ4XS, "c9": C9_IQ3S, "c10": C10_Q5K}
+           "c7": C7_IQ4NL, "c8": C8_IQ4XS, "c9": C9_IQ3S, "c10": C10_Q5K, "c11": C11_GLM}
 
 
 def make_weights(cfg: Config, seed: int, experts=None) -> dict:
@@ -407,9 +441,9 @@ def make_weights(cfg: Config, seed: int, experts=None) -> dict:
         dn = rng.normal(0, cfg.sigma, (d, ff)).astype(np.float32)
         if experts is not None and e not in experts:
             continue
-        gate[e] = ENCODERS[cfg.type_gate](g).ravel()
-        up[e] = ENCODERS[cfg.type_up](u).ravel()
-        down[e] = ENCODERS[cfg.type_down](dn).ravel()
+        gate[e] = encode_matrix(cfg.type_gate, g)
+        up[e] = encode_matrix(cfg.type_up, u)
+        down[e] = encode_matrix(cfg.type_down, dn)
     w.update(gate=gate, up=up, down=down)
     if cfg.has_expert_bias:
         w["bias_gate"] = bf16_round(rng.normal(0, cfg.sigma, (E, ff)).astype(np.float32))
@@ -417,9 +451,9 @@ def make_weights(cfg: Config, seed: int, experts=None) -> dict:
         w["bias_down"] = bf16_round(rng.normal(0, cfg.sigma, (E, d)).astype(np.float32))
     if cfg.shared:
         sf = cfg.shared_ff
-        w["shared_gate"] = ENCODERS[cfg.type_gate](rng.normal(0, cfg.sigma, (sf, d)).astype(np.float32)).ravel()
-        w["shared_up"] = ENCODERS[cfg.type_up](rng.normal(0, cfg.sigma, (sf, d)).astype(np.float32)).ravel()
-        w["shared_down"] = ENCODERS[cfg.type_down](rng.normal(0, cfg.sigma, (d, sf)).astype(np.float32)).ravel()
+        w["shared_gate"] = encode_matrix(cfg.type_gate, rng.normal(0, cfg.sigma, (sf, d)).astype(np.float32))
+        w["shared_up"] = encode_matrix(cfg.type_up, rng.normal(0, cfg.sigma, (sf, d)).astype(np.float32))
+        w["shared_down"] = encode_matrix(cfg.type_down, rng.normal(0, cfg.sigma, (d, sf)).astype(np.float32))
         if cfg.shared == SHARED_SIGMOID_GATED:
             w["shared_gate_inp"] = rng.normal(0, cfg.sigma, d).astype(np.float32)
     return w

@@ -63,6 +63,7 @@ SMALL = {
     "c8": synth.C8_IQ4XS.scaled(d=512, ff=160, n_exp=16),
     "c9": synth.C9_IQ3S.scaled(d=512, ff=160, n_exp=16),
     "c10": synth.C10_Q5K.scaled(d=512, ff=256, n_exp=16),
+    "c11": synth.C11_GLM.scaled(d=512, ff=192, n_exp=16, shared_ff=192),
 }
 
 

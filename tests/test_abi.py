@@ -65,11 +65,11 @@ def test_encoders_round_trip(oracle):
     rng = np.random.default_rng(0)
     x = rng.normal(0, 0.02, (3, 1024)).astype(np.float32)
     bound = {synth.Q4_K: 0.08, synth.Q6_K: 0.03, synth.MXFP4: 0.3, synth.Q8_0: 0.01, synth.IQ4_NL: 0.12, synth.IQ4_XS: 0.14,
-             synth.Q5_K: 0.04, synth.IQ3_S: 0.35}
+             synth.Q5_K: 0.04, synth.IQ3_S: 0.35, synth.GLM_Q4: 0.08}
     for ty, enc in synth.ENCODERS.items():
         b = enc(x)
         assert b.shape == (3, synth.row_bytes(ty, 1024))
-        y = oracle.dequant(ty, b.ravel(), x.size).reshape(x.shape)
+        y = oracle.dequant(ty, synth.encode_matrix(ty, x), x.size).reshape(x.shape)
         assert np.abs(y - x).max() <= bound[ty] * np.abs(x).max()
     z = np.zeros(256, np.float32)
     for ty, enc in synth.ENCODERS.items():

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.MXFP4, synth.Q8_0, synth.IQ4_NL,
-                                synth.IQ4_XS, synth.IQ3_S])
+                                synth.IQ4_XS, synth.IQ3_S, synth.GLM_Q4])
 def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
     """Every bit pattern path: random block bytes, only the f16 scales kept finite."""
     v, b = synth.BLOCK[ty]
@@ -24,6 +24,8 @@ def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
         raw[:, 208:210] = half[:, :2]
     elif ty in (synth.Q8_0, synth.IQ4_NL, synth.IQ4_XS, synth.IQ3_S):
         raw[:, 0:2] = half[:, :2]
+    elif ty == synth.GLM_Q4:  # the nibble region, then finite f32 group scales
+        raw.reshape(-1)[nb * 32:] = rng.normal(0, 0.05, nb).astype(np.float32).view(np.uint8)
     else:
         raw[:3, 0] = [0, 1, 2]  # the denormal branch of e8 (src/oss_kernels.rs:42-45)
         raw[3, 0] = 254
@@ -33,7 +35,7 @@ def test_dequant_random_bytes_bit_exact(ctx, oracle, ty):
 
 
 @pytest.mark.parametrize("ty", [synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.MXFP4, synth.IQ4_NL, synth.IQ4_XS,
-                                synth.IQ3_S])
+                                synth.IQ3_S, synth.GLM_Q4])
 def test_dequant_encoded_weights(ctx, oracle, ty):
     rng = np.random.default_rng(1)
     x = rng.normal(0, 0.02, 4096).astype(np.float32)

@@ -232,3 +232,35 @@ def test_golden_layer_outputs(oracle, name):
     assert np.array_equal(ids, g["ids"])
     assert bits_equal(w, g["w"])
     assert bits_equal(L.forward(x), g["y"])
+
+
+def _rand_vec64(n, seed):
+    """`rand_vec` of the reference's quant tests (src/quant.rs:481-490): a 64-bit LCG, values in
+    [-0.5, 0.5)."""
+    s, out = seed, np.empty(n, np.float32)
+    for i in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        out[i] = np.float32(np.float32(s >> 33) / np.float32(1 << 31)) - np.float32(0.5)
+    return out
+
+
+def test_int4_container_rows(oracle):
+    """`q4_kernel_matches_scalar` (src/quant.rs:492-507) on the restated quantiser and row: the row
+    over the container's bytes equals the dequantised weights times x, and stays within the
+    reference's bound of the unquantised product."""
+    rows, cols = 5, 256
+    w = _rand_vec64(rows * cols, 1).reshape(rows, cols)
+    x = _rand_vec64(cols, 2)
+    m = synth.encode_matrix(synth.GLM_Q4, w)
+    assert m.size == rows * cols // 2 + rows * (cols // 64) * 4
+    # the quantiser's own contract (src/quant.rs:179-201): step = amax / 7, level + 8 per nibble
+    step = m[rows * cols // 2:].view(np.float32).reshape(rows, cols // 64)
+    assert np.array_equal(step, np.abs(w.reshape(rows, -1, 64)).max(-1) / np.float32(7.0))
+    deq = oracle.dequant(synth.GLM_Q4, m, rows * cols).reshape(rows, cols)
+    assert np.abs(deq - w).max() <= step.max() / 2 * 1.0001
+    for o in range(rows):
+        one_row = np.concatenate([m[o * cols // 2:(o + 1) * cols // 2],
+                                  m[rows * cols // 2 + o * 16:rows * cols // 2 + (o + 1) * 16]])
+        got = oracle.row_f32(synth.GLM_Q4, one_row, cols, x)
+        assert abs(got - float(deq[o].astype(np.float64) @ x.astype(np.float64))) < 1e-4
+        assert abs(got - float(w[o] @ x)) < 0.2
