@@ -767,11 +767,21 @@ struct Scratch {
   float *eo;
   uint16_t *xhl, *hhl;  // MXFP4 tensor-core path: bf16 (hi, lo) split of x [2][T*d] and of h [2][P*ff]
   uint32_t *tiles;  // tile list of the tensor-core kernels
+  uint8_t *rec;     // activation rows regrouped into the int8 tensor-core kernel's records
   // shared expert
   int *one; uint32_t *zero_u, *tcount, *iota;
   float *sh; int8_t *shq; float *shd; int32_t *shbsum; uint16_t *shbm; int32_t *shs;
   float *shared_out, *shared_logit;
 };
+
+// the largest record buffer any tensor-core launch of a T-token call needs (Q8x activations only)
+static size_t scratch_rec_bytes(const pm_layer_desc &D, int T) {
+  if (D.act_quant != PM_AQ_Q8X_256) return 0;
+  const int P = T * D.top_k, E = D.n_exp;
+  size_t r = std::max(tc_rec_bytes(P, E, D.d), tc_rec_bytes(P, E, D.ff));
+  if (D.shared) r = std::max(r, std::max(tc_rec_bytes(T, 1, D.d), tc_rec_bytes(T, 1, D.shared_ff)));
+  return r;
+}
 
 static size_t scratch_bytes(const pm_layer_desc &D, int T) {
   size_t P = (size_t)T * D.top_k, E = (size_t)D.n_exp, d = (size_t)D.d, ff = (size_t)D.ff;
@@ -782,7 +792,8 @@ static size_t scratch_bytes(const pm_layer_desc &D, int T) {
   b += al(P * ff * 4) + al(P * ff) + al(P * (ff / 32 + 1) * 4) + al(P * (ff / 256 + 1) * 4) + al(P * (ff / 32) * 4) * 2;
   b += al(P * d * 4);
   if (D.act_quant == PM_AQ_F32 && D.type_gate == PM_TYPE_MXFP4) b += al(T * d * 4) + al(P * ff * 4);
-  b += al((4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1)) * 4);
+  b += al(tc_tile_words((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1) * 4);
+  b += al(scratch_rec_bytes(D, T));
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     b += al(4) + al(4) * 2 + al((size_t)T * 4);
@@ -823,7 +834,8 @@ static void scratch_carve(pm_ctx *c, const pm_layer_desc &D, int T, Scratch &S) 
     S.xhl = ws_take<uint16_t>(c, 2 * T * d);
     S.hhl = ws_take<uint16_t>(c, 2 * P * ff);
   }
-  S.tiles = ws_take<uint32_t>(c, 4 + 2 * (size_t)tc_max_tiles((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1));
+  S.tiles = ws_take<uint32_t>(c, tc_tile_words((int)(P > (size_t)T ? P : (size_t)T), (int)E + 1));
+  S.rec = ws_take<uint8_t>(c, scratch_rec_bytes(D, T));
   if (D.shared) {
     size_t sf = (size_t)D.shared_ff;
     S.one = ws_take<int>(c, 1);
@@ -898,7 +910,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   {
     PROF(c, PH_GATEUP);
     if (tc && D.type_gate == D.type_up) {
-      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.xq, S.xd, S.xbm, S.xs, w, S.h, c->dev_err, c->wait_ns, c->tc_fault_block));
+      CU(launch_tc_q4k(L, dv, false, false, g, P, S.tiles, S.rec, g.pair_token, S.xq, S.xd, S.xbm, S.xs, w, S.h, c->dev_err, c->wait_ns, c->tc_fault_block));
       c->path_count[PM_PATH_TENSOR]++;
     } else {
       launch_gateup(L, dv, false, g, P, x, S.xq, S.xd, S.xbsum, w, S.h);
@@ -910,7 +922,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   {
     PROF(c, PH_DOWN);
     if (tc) {
-      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.hq, S.hd, S.hbm, S.hs, nullptr, S.eo, c->dev_err, c->wait_ns, c->tc_fault_block));
+      CU(launch_tc_q4k(L, dv, false, true, g, P, S.tiles, S.rec, nullptr, S.hq, S.hd, S.hbm, S.hs, nullptr, S.eo, c->dev_err, c->wait_ns, c->tc_fault_block));
       c->path_count[PM_PATH_TENSOR]++;
     } else {
       launch_down(L, dv, false, g, P, S.h, S.hq, S.hd, S.hbsum, S.eo);
@@ -949,13 +961,13 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   if (q32) launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   if (use_tc && D.type_gate == D.type_up)
-    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err, c->wait_ns, c->tc_fault_block));
+    CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.rec, g.pair_token, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err, c->wait_ns, c->tc_fault_block));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum, S.shbm, S.shs);
   if (q32) launch_quant_q8_32(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd);
   if (use_tc)
-    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err, c->wait_ns, c->tc_fault_block));
+    CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.rec, nullptr, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err, c->wait_ns, c->tc_fault_block));
   else
     launch_down(L, dv, true, g, T, S.sh, S.shq, S.shd, S.shbsum, S.shared_out);
   if (D.shared == PM_SHARED_SIGMOID_GATED) launch_shared_gate_logit(L, dv, x, T, S.shared_logit);

@@ -130,12 +130,16 @@ void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int
                  const float *h, const int8_t *hq, const float *hd, const int32_t *hbsum,
                  float *eo);
 // tensor-core (tcgen05 int8) form of launch_gateup / launch_down for Q4_K x Q8x (prefill_tc.cu)
-// tile_buf: 4 + 2 * tc_max_tiles(n_pairs, g.max_groups) words of scratch for the tile list
+// tile_buf: tc_tile_words(n_pairs, g.max_groups) words of scratch for the tile list; rec_buf:
+// tc_rec_bytes(n_pairs, g.max_groups, cols) bytes for the activation rows regrouped by expert in the
+// products' layout; src_row: row of xq / xd / xbm / xs that holds pair p (null: row p itself)
 int tc_max_tiles(int n_pairs, int max_groups);
+size_t tc_tile_words(int n_pairs, int max_groups);
+size_t tc_rec_bytes(int n_pairs, int max_groups, int cols);
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
-                          int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
-                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err,
-                          unsigned long long wait_ns, int fault_block);
+                          int n_pairs, uint32_t *tile_buf, uint8_t *rec_buf, const uint32_t *src_row,
+                          const int8_t *xq, const float *xd, const uint16_t *xbm, const int32_t *xs,
+                          const float *wts, float *out, int *err, unsigned long long wait_ns, int fault_block);
 // tensor-core (tcgen05 bf16) form for MXFP4 weights and f32 activations given as their bf16
 // (hi, lo) split (prefill_mx.cu); launch_split_bf16 makes the split: hi[n], lo[n] bf16
 void launch_split_bf16(const Launch &L, const float *x, size_t n, void *hi, void *lo);

@@ -3,9 +3,9 @@
 // the integer domain of the reference's CPU path (src/ds4_cpu.rs:59-83).
 //
 // One CTA = (128 weight rows of one active expert) x (up to 128 of its tokens): 16 worker
-// warps and one warp that issues the tensor-core instructions. Per 256-value block b of
-// the rows:
-//   1. the block's bytes arrive by cp.async in row-contiguous pieces; each worker unpacks
+// warps, one warp that issues the tensor-core instructions and one producer warp. Per
+// 256-value block b of the rows:
+//   1. the producer stages the block's bytes in row-contiguous pieces; each worker unpacks
 //      64 values of one row into two u8 operand planes IN REGISTERS and stores them to
 //      tensor memory (tcgen05.st), where the products read operand A from: shared memory
 //      carries only the tokens' activations. Q4_K: A_hi = nibble * (sc >> 3),
@@ -26,7 +26,17 @@
 #include "moe_internal.cuh"
 
 #define TC_NW 512                 /* worker threads */
-#define TC_NT (TC_NW + 32)        /* + the warp that issues the products */
+#define TC_NT (TC_NW + 64)        /* workers, the warp that issues the products, the producer warp */
+// The tokens' operand is read from records laid out for the products (k_tc_rows writes them):
+// record (row group rg of 8 rows, block b) = [16 K chunks][8 rows][16 B] int8 activations,
+// [2 K chunks][8 rows][8 f16] sub-block sums for the Q4_K mins product, [8] f32 x.d, [8] i32
+// block sums (Q6_K), padded to a multiple of 128 bytes so that every 8 x 16 B core matrix sits in
+// one 128-byte line of shared memory - one contiguous bulk copy per row group and block, at
+// ((rg * n_blocks) + b) * TC_REC
+#define TC_REC 2432
+#define TC_REC_BM 2048
+#define TC_REC_XD 2304
+#define TC_REC_XS 2336
 #define TC_M 128
 #define TC_NMAX 128
 #define TC_TMEM_COLS 512
@@ -96,7 +106,7 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t r[16]) {
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-// global -> shared without registers (completion: cp.async.wait_all by the issuing thread)
+// global -> shared without registers, 16 / 4 bytes
 __device__ __forceinline__ void tc_cp16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -106,8 +116,14 @@ __device__ __forceinline__ void tc_cp4(uint32_t dst, const void *src) {
 // named barriers: 1 = operands of a block ready (workers arrive, the issuing warp waits),
 // 2 = among the workers
 __device__ __forceinline__ void tc_workers_sync() { asm volatile("bar.sync 2, %0;" ::"n"(TC_NW) : "memory"); }
-__device__ __forceinline__ void tc_ready_arrive() { asm volatile("bar.arrive 1, %0;" ::"n"(TC_NT) : "memory"); }
-__device__ __forceinline__ void tc_ready_wait() { asm volatile("bar.sync 1, %0;" ::"n"(TC_NT) : "memory"); }
+__device__ __forceinline__ void tc_ready_arrive() { asm volatile("bar.arrive 1, %0;" ::"n"(TC_NW + 32) : "memory"); }
+__device__ __forceinline__ void tc_ready_wait() { asm volatile("bar.sync 1, %0;" ::"n"(TC_NW + 32) : "memory"); }
+__device__ __forceinline__ void tc_mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_s32(bar)) : "memory");
+}
 __device__ __forceinline__ bool tc_bar_test(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -130,20 +146,30 @@ __device__ __noinline__ bool tc_bar_wait(uint64_t *bar, uint32_t parity, int *er
   return false;
 }
 
+// a bounded wait on a phase of an mbarrier (see tc_bar_wait)
+__device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int *err, unsigned long long wait_ns) {
+  return tc_bar_test(bar, parity) || tc_bar_wait(bar, parity, err, wait_ns);
+}
+
 int tc_max_tiles(int n_pairs, int max_groups);
 
 // Compile with -DPM_TC_TRACE=1 (gate/up launches) or =2 (down launches) to stamp the phases of
 // CTA (0, 0) with the SM clock: [thread 0 | thread 511][block][stamp]; read back with pm_debug_tc_trace.
 #ifdef PM_TC_TRACE
-__device__ unsigned long long g_tc_trace[2 * 32 * 8];
+__device__ unsigned long long g_tc_trace[3 * 32 * 8];
 #define TC_STAMP(b, i)                                                                         \
   if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 511) && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
     g_tc_trace[((tid ? 1 : 0) * 32 + (b)) * 8 + (i)] = clock64();
 extern "C" __attribute__((visibility("default"))) int pm_debug_tc_trace(unsigned long long *out) {
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));
 }
+// the issuing warp's lane 0: section 2
+#define TC_STAMP_M(b, i)                                                                       \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid & 31) == 0 && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
+    g_tc_trace[(2 * 32 + (b)) * 8 + (i)] = clock64();
 #else
 #define TC_STAMP(b, i)
+#define TC_STAMP_M(b, i)
 #endif
 
 struct TcArgs {
@@ -151,43 +177,106 @@ struct TcArgs {
   int shared;      // 1: the shared expert's matrices (one group over all tokens)
   int down;        // 0: gate+up with activation -> h; 1: down -> pair outputs
   Groups g;
-  const int8_t *xq;      // gate/up: [T][d] by token; down: [P][ff] by pair
-  const float *xd;       // per row of xq: [cols/256]
-  const uint16_t *xbm;   // per row of xq: [cols/256][16] f16: 64 * (bsum_j >> 6) (8), bsum_j & 63 (8)
-  const int32_t *xs;     // per row of xq: [cols/256] sum of the block's values
+  const uint8_t *rec;    // the tokens' operand as records (see TC_REC), rows grouped and padded as tile_r0 says
   const float *wts;      // routing weights [T*K] (gate/up with fold) or null
   float *out;            // gate/up: h [P][ff]; down: eo [P][d]
   int *err;
-  unsigned long long wait_ns;  // limit of the workers' wait for a block's products
+  unsigned long long wait_ns;  // limit of every wait on an mbarrier
   int fault_block;             // test hook: no products are issued or signalled from this block on (-1 = off)
   const int *n_tiles;          // [1]
   const uint32_t *tile_group;  // [tiles] index into the groups
   const uint32_t *tile_n0;     // [tiles] first token of the tile inside its group
+  const uint32_t *tile_r0;     // [tiles] row of that token among the records' rows (a multiple of 16)
 };
 
 // The (group, token tile) list of a grouping: group a contributes ceil(count/128)
-// tiles. One CTA; groups <= 512 (experts of a layer, or the one shared-expert group
-// whose count may be the whole batch).
+// tiles. The records' rows keep a group's pairs together and start every group on a
+// multiple of 16 rows (group_r0), so that a tile's rows are whole row groups. One CTA;
+// groups <= 512 (experts of a layer, or the one shared-expert group whose count may be the
+// whole batch). tile_r0 / group_r0 may be null (callers that only want the tile list).
 __global__ void __launch_bounds__(512) k_tc_tiles(Groups g, int *n_tiles, uint32_t *tile_group,
-                                                  uint32_t *tile_n0, int max_tiles) {
-  __shared__ uint32_t s[512];
+                                                  uint32_t *tile_n0, uint32_t *tile_r0, uint32_t *group_r0,
+                                                  int max_tiles) {
+  __shared__ uint32_t s[512], sr[512];
   const int a = threadIdx.x;
   const int ng = min(*g.n_groups, 512);
-  uint32_t tc = a < ng ? (g.count[a] + TC_NMAX - 1) / TC_NMAX : 0;
+  const uint32_t cnt = a < ng ? g.count[a] : 0;
+  uint32_t tc = (cnt + TC_NMAX - 1) / TC_NMAX;
+  const uint32_t rp = (cnt + 15u) & ~15u;
   s[a] = tc;
+  sr[a] = rp;
   __syncthreads();
   for (int off = 1; off < 512; off <<= 1) {
-    uint32_t v = a >= off ? s[a - off] : 0;
+    uint32_t v = a >= off ? s[a - off] : 0, w = a >= off ? sr[a - off] : 0;
     __syncthreads();
     s[a] += v;
+    sr[a] += w;
     __syncthreads();
   }
-  uint32_t first = s[a] - tc;
+  uint32_t first = s[a] - tc, r0 = sr[a] - rp;
+  if (group_r0 && a < ng) group_r0[a] = r0;
   for (uint32_t i = 0; i < tc && (int)(first + i) < max_tiles; i++) {
     tile_group[first + i] = (uint32_t)a;
     tile_n0[first + i] = i * TC_NMAX;
+    if (tile_r0) tile_r0[first + i] = r0 + i * TC_NMAX;
   }
   if (a == 511) *n_tiles = min((int)s[511], max_tiles);
+}
+
+// Quantised activation rows -> the records the products read (TC_REC): one warp per (row
+// group of 8 rows, block). Row i of group a is record row group_r0[a] + i and comes from
+// row src_row[offset[a] + i] of the quantiser's outputs (null: row offset[a] + i itself);
+// rows past a group's count are zeros.
+__global__ void __launch_bounds__(256) k_tc_rows(Groups g, const uint32_t *__restrict__ group_r0,
+                                                 const uint32_t *__restrict__ src_row, int cols,
+                                                 const int8_t *__restrict__ xq, const float *__restrict__ xd,
+                                                 const uint16_t *__restrict__ xbm, const int32_t *__restrict__ xs,
+                                                 uint8_t *__restrict__ rec) {
+  const int a = blockIdx.y;
+  if (a >= *g.n_groups) return;
+  const int nb = cols / 256;
+  const uint32_t off = g.offset[a], cnt = g.count[a], r0 = group_r0[a];
+  const int lane = threadIdx.x & 31;
+  const int units = (int)((cnt + 15u) / 16u) * 2 * nb;  // (row group, block) pairs of this group
+  for (int u = blockIdx.x * 8 + (threadIdx.x >> 5); u < units; u += gridDim.x * 8) {
+    const int rgl = u / nb, b = u - rgl * nb;
+    uint8_t *R = rec + ((size_t)(r0 / 8 + rgl) * nb + b) * TC_REC;
+    {  // int8 values: lane = (row of the group, quarter of the block's 16 chunks)
+      const int r8 = lane >> 2, q = lane & 3;
+      const uint32_t i = (uint32_t)rgl * 8 + r8;
+      uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      if (i < cnt) {
+        const size_t row = src_row ? src_row[off + i] : off + i;
+        const uint4 *src = (const uint4 *)(xq + row * cols + (size_t)b * 256 + 64 * q);
+#pragma unroll
+        for (int c = 0; c < 4; c++) v[c] = __ldg(src + c);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; c++) *(uint4 *)(R + ((4 * q + c) * 8 + r8) * 16) = v[c];
+    }
+    if (lane < 16) {  // the f16 form of the sub-block sums: lane = (row, K chunk of the mins product)
+      const int r8 = lane >> 1, k = lane & 1;
+      const uint32_t i = (uint32_t)rgl * 8 + r8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (i < cnt && xbm) {
+        const size_t row = src_row ? src_row[off + i] : off + i;
+        v = __ldg((const uint4 *)(xbm + (row * nb + b) * 16 + 8 * k));
+      }
+      *(uint4 *)(R + TC_REC_BM + (k * 8 + r8) * 16) = v;
+    } else if (lane < 24) {
+      const int r8 = lane - 16;
+      const uint32_t i = (uint32_t)rgl * 8 + r8;
+      float v = 0.0f;
+      if (i < cnt) v = xd[(src_row ? (size_t)src_row[off + i] : (size_t)(off + i)) * nb + b];
+      *(float *)(R + TC_REC_XD + r8 * 4) = v;
+    } else {
+      const int r8 = lane - 24;
+      const uint32_t i = (uint32_t)rgl * 8 + r8;
+      int32_t v = 0;
+      if (i < cnt && xs) v = xs[(src_row ? (size_t)src_row[off + i] : (size_t)(off + i)) * nb + b];
+      *(int32_t *)(R + TC_REC_XS + r8 * 4) = v;
+    }
+  }
 }
 
 // WT: the weight type of the product's matrices.
@@ -198,21 +287,22 @@ __global__ void __launch_bounds__(512) k_tc_tiles(Groups g, int *n_tiles, uint32
 //  PM_TYPE_Q6_K: the product v = sc * (q - 32) in [-4064, 4096] is split after the
 //    multiplication: v + 4128 = 64 * th + tl with th in [1, 128], tl in [0, 63] - two u8
 //    planes, and isum = 64 * (th . xq) + (tl . xq) - 4128 * sum(xq) exactly.
-// Memory: the weight bytes of a block arrive by cp.async in row-contiguous pieces (a warp
-// reads whole 144-byte / 128-byte runs) into one of TC_RAW_STAGES raw areas, issued that
-// many blocks ahead (HBM answers in about 2000 cycles under load; one block lasts less);
-// the tokens' int8 activations go to one of three areas, two blocks ahead. The first half
-// of the workers issues the weight copies, the second half the activation copies, so
-// that each thread's cp.async groups complete in the order they are needed.
+// Memory: one producer warp feeds two rings, each with a full and an empty mbarrier per stage.
+// The weight bytes of a block go to one of TC_RAW_STAGES raw areas as stored, by 16-byte
+// cp.async pieces (consecutive lanes on consecutive pieces of a row; the completion of a
+// lane's pieces arrives on the stage's barrier), freed once every worker warp has unpacked
+// it. The tokens' operand of a block - up to 16 records written by k_tc_rows in the
+// products' own layout - comes by one bulk copy a record into one of three areas, freed once
+// its products have completed (tcgen05.commit) and every worker warp has read the block's
+// x.d for the fold. (The workers used to issue the copies themselves, the activations as
+// 16-byte cp.async pieces: those retire at about one warp instruction per 24 cycles on this
+// part, and waiting for them was the longest phase of a block.)
 template <int WT>
 __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   constexpr bool Q6 = WT == PM_TYPE_Q6_K;
   constexpr int NS = Q6 ? TC_RAW_STAGES_Q6 : TC_RAW_STAGES_Q4;
   constexpr int RAWB = Q6 ? TC_RAW_Q6 : TC_RAW_Q4;
-  // the tokens' block: [16 chunks][npad tokens + 1][16 B] (+ Q4_K: [2 chunks][npad + 1][8 f16]); the
-  // odd pitch lets a quarter-warp write the 8 chunks of one token without bank conflicts
-  constexpr int BMOFF = 16 * (TC_NMAX + 1) * 16;
-  constexpr int BSTAGE = BMOFF + (Q6 ? 0 : 2 * (TC_NMAX + 1) * 16);
+  constexpr int BSTAGE = (TC_NMAX / 8) * TC_REC;  // the tokens' block: a record per 8 tokens
   extern __shared__ __align__(128) uint8_t smem[];
   // blockIdx.y walks the list of (group, token tile) pairs made by k_tc_tiles
   if ((int)blockIdx.y >= *A.n_tiles) return;
@@ -243,13 +333,12 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   uint8_t *sRaw = smem;                                        // [NS] blocks of the 128 rows as stored
   float *sS = (float *)smem;                                   // (after the last block) gate/up exchange [128][129]
   uint8_t *sB = smem + (NS * RAWB > TC_M * (TC_NMAX + 1) * 4 ? NS * RAWB : TC_M * (TC_NMAX + 1) * 4);
-                                                               // [3] x ([16 chunks][npad tokens][16 B] + Q4_K:
-                                                               //        [2 chunks][npad tokens][8 f16])
+                                                               // [3] x [npad / 8 records]
   uint8_t *sAm = sB + 3 * BSTAGE;                              // Q4_K: [2][2 chunks][128 rows][8 f16]
-  float *sXd = (float *)(sAm + 2 * 2 * TC_M * 16);             // [4][128] x.d of a block per token
-  int32_t *sXs = (int32_t *)(sXd + 4 * TC_NMAX);               // Q6_K: [4][128] sum of the block's xq
-  uint64_t *bar = (uint64_t *)(sXs + 4 * TC_NMAX);
-  uint32_t *tmem_slot = (uint32_t *)(bar + 1);
+  uint64_t *bar = (uint64_t *)(sAm + 2 * 2 * TC_M * 16);       // the products of a block have completed
+  uint64_t *full_raw = bar + 1, *empty_raw = full_raw + 4;     // rings of the raw areas ...
+  uint64_t *full_b = empty_raw + 4, *empty_b = full_b + 3;     // ... and of the tokens' areas
+  uint32_t *tmem_slot = (uint32_t *)(empty_b + 3);
 
   if (warp == TC_NW / 32) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -259,7 +348,15 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_s32(bar)), "r"(1));
+    tc_mbar_init(bar, 1);
+    for (int i = 0; i < 4; i++) {
+      tc_mbar_init(full_raw + i, 32);  // every producer lane's copies
+      tc_mbar_init(empty_raw + i, TC_NW / 32);
+    }
+    for (int i = 0; i < 3; i++) {
+      tc_mbar_init(full_b + i, 1);  // the producer's expect_tx; the bulk copies complete the bytes
+      tc_mbar_init(empty_b + i, 1 + TC_NW / 32);  // the products' commit and every worker warp after its fold
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -268,182 +365,141 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   const uint32_t tmem = *tmem_slot;
   const uint32_t sB_a = tc_s32(sB), sAm_a = tc_s32(sAm);
 
+  // Global row of tile row i (gate rows, then up rows, in a gate/up tile), or -1 past the
+  // matrix; `second`: the row belongs to the up matrix
+  auto grow = [&](int i, bool &second) -> int {
+    second = !A.down && i >= 64;
+    int r = r0 + (second ? i - 64 : i);
+    return r < rows ? r : -1;
+  };
+
   if (warp == TC_NW / 32) {
     // ================= the issuing warp =================
     // instruction descriptors: D s32, A u8, B s8, K-major; and the f16 one (D f32)
     const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     for (int b = 0; b < nb; b++) {
-      const uint32_t bs = sB_a + (uint32_t)(b % 3) * BSTAGE;
-      const uint64_t dB0 = tc_desc(bs, (uint32_t)(npad + 1) * 16u, 128u);
-      tc_ready_wait();  // operand A in TMEM, the tokens' block in shared memory, accumulators read
+      const int sb = b % 3;
+      const uint32_t bs = sB_a + (uint32_t)sb * BSTAGE;
+      const uint64_t dB0 = tc_desc(bs, 128u, (uint32_t)TC_REC);  // K chunks 128 B apart, 8-token groups a record apart
+      TC_STAMP_M(b, 0)
+      tc_wait(full_b + sb, (uint32_t)((b / 3) & 1), A.err, A.wait_ns);  // the tokens' block is in shared memory
+      TC_STAMP_M(b, 1)
+      tc_ready_wait();  // operand A in TMEM, the accumulators read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      TC_STAMP_M(b, 2)
       if ((tid & 31) == 0 && !(A.fault_block >= 0 && b >= A.fault_block)) {
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
-          const uint64_t db = dB0 + (uint64_t)(ks * 2 * (npad + 1));
+          const uint64_t db = dB0 + (uint64_t)(ks * 16);  // two K chunks a step
           tc_mma_i8_ta(tmem + TC_ACC_HI, tmem + TC_A_HI + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
           tc_mma_i8_ta(tmem + TC_ACC_LO, tmem + TC_A_LO + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
         }
         if (!Q6)
           tc_mma_f16(tmem + TC_ACC_M, tc_desc(sAm_a + (uint32_t)(b & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
-                     tc_desc(bs + BMOFF, (uint32_t)(npad + 1) * 16u, 128u), idesc_h, 0u);
+                     tc_desc(bs + TC_REC_BM, 128u, (uint32_t)TC_REC), idesc_h, 0u);
         tc_commit(bar);
+        tc_commit(empty_b + sb);
       }
+      TC_STAMP_M(b, 3)
       __syncwarp();
     }
-  } else {
-    // ================= the workers =================
-    const bool raw_role = tid < TC_NW / 2;  // copies: weights (first half) / activations (second half)
-    const int ct = tid & (TC_NW / 2 - 1);   // index within the role
-
-    // (1) activations: a quarter-warp copies 128 contiguous bytes of one token's row (the 8
-    // chunks of half a block: one line of global memory) per instruction; warp w of the role
-    // takes tokens 16 w .. 16 w + 15, four at a time
-    const int bc = ct & 7, bsub = (ct >> 3) & 3, bw = ct >> 5;
-    int brow[4] = {-1, -1, -1, -1};
-    if (!raw_role) {
+  } else if (warp > TC_NW / 32) {
+    // ================= the producer =================
+    const int lane = tid & 31;
+    const uint8_t *wb0[4], *wb1[4];  // the expert's planes of the tile's matrices
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int t = 16 * bw + 4 * i + bsub;
-        if (t < nvalid) brow[i] = A.down ? (int)(off + n0 + t) : (int)A.g.pair_token[off + n0 + t];
-      }
+    for (int pl = 0; pl < 4; pl++) {
+      wb0[pl] = W0.plane[pl] ? W0.plane[pl] + (size_t)el * W0.stride[pl] : nullptr;
+      wb1[pl] = (!A.down && W1.plane[pl]) ? W1.plane[pl] + (size_t)el * W1.stride[pl] : nullptr;
     }
-    const uint32_t sXd_a = tc_s32(sXd), sXs_a = tc_s32(sXs);
-    const uint32_t bpitch = (uint32_t)(npad + 1) * 16u;
-    auto issue_b = [&](int bb) {  // the tokens' block bb -> its area, asynchronously (one group)
-      if (bb < nb) {
-        const uint32_t bs = sB_a + (uint32_t)(bb % 3) * BSTAGE;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          if (brow[i] < 0) continue;
-          const int t = 16 * bw + 4 * i + bsub;
-          const int8_t *src = A.xq + (size_t)brow[i] * cols + (size_t)bb * 256 + 16 * bc;
-          const uint32_t dst = bs + (uint32_t)bc * bpitch + (uint32_t)t * 16u;
-          tc_cp16(dst, src);
-          tc_cp16(dst + 8u * bpitch, src + 128);
-          if (bc == 0) tc_cp4(sXd_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xd + (size_t)brow[i] * nb + bb);
-          if (!Q6 && (bc == 1 || bc == 2))
-            tc_cp16(bs + BMOFF + (uint32_t)(bc - 1) * bpitch + (uint32_t)t * 16u,
-                    A.xbm + ((size_t)brow[i] * nb + bb) * 16 + 8 * (bc - 1));
-          if (Q6 && bc == 1) tc_cp4(sXs_a + (uint32_t)((bb & 3) * TC_NMAX + t) * 4u, A.xs + (size_t)brow[i] * nb + bb);
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    if (!raw_role) {  // padding tokens: zero operands, once, every area
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int t = 16 * bw + 4 * i + bsub;
-        if (t >= nvalid && t < npad) {
-#pragma unroll
-          for (int st = 0; st < 3; st++) {
-            uint8_t *bs = sB + st * BSTAGE;
-            *(uint4 *)(bs + (size_t)bc * bpitch + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
-            *(uint4 *)(bs + (size_t)(bc + 8) * bpitch + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
-            if (!Q6 && (bc == 1 || bc == 2))
-              *(uint4 *)(bs + BMOFF + (size_t)(bc - 1) * bpitch + (size_t)t * 16) = make_uint4(0, 0, 0, 0);
-          }
-          if (bc == 0)
-            for (int k = 0; k < 4; k++) sXd[k * TC_NMAX + t] = 0.0f;
-          if (Q6 && bc == 1)
-            for (int k = 0; k < 4; k++) sXs[k * TC_NMAX + t] = 0;
-        }
-      }
-    }
-
-    // (2) weights. Global row of tile row i (gate rows, then up rows, in a gate/up tile), or
-    // -1 past the matrix; `second`: the row belongs to the up matrix
-    auto grow = [&](int i, bool &second) -> int {
-      second = !A.down && i >= 64;
-      int r = r0 + (second ? i - 64 : i);
-      return r < rows ? r : -1;
-    };
     const uint32_t sRaw_a = tc_s32(sRaw);
-    // The pieces (16 bytes each) this thread copies per block, consecutive lanes on consecutive
-    // pieces of a row: byte offset of the piece in block 0 of its row within the expert's matrix
-    // (bit 31: the up matrix; ~0: a row past the matrix). Q4_K: 9 pieces a row, [row][144 B] (row-
-    // per-lane 16-byte reads of that pitch are conflict-free). Q6_K: ql 8 pieces a row, [row][128 B],
-    // piece c at c ^ (row & 7); qh 4 pieces a row, [row][64 B], piece c at c ^ ((row >> 1) & 3) (both
-    // conflict-free for the row-per-lane reads below); sc [row][16 B]; d: the aligned word holding
-    // the row's f16.
-    constexpr int NPC = Q6 ? 7 : 5;
-    uint32_t roff[NPC];
+    const uint8_t *rec0 = A.rec + (size_t)(A.tile_r0[blockIdx.y] / 8) * nb * TC_REC;  // the tile's first record
+    const int nrec = npad >> 3;
+    // Q4_K: 9 pieces a row, [row][144 B]; piece p = lane + 32 j of the tile. Pieces 0..575 are
+    // tile rows 0..63 and pieces 576.. the same (row, piece) pattern 64 rows on: of the other matrix
+    // (gate/up tiles) or of the same one (down tiles). So 18 byte offsets (of the piece in block 0
+    // of its row) and two validity masks stay in registers, and a block costs one address and one
+    // copy instruction a piece.
+    uint32_t roff[Q6 ? 1 : 18];
+    uint32_t okA = 0, okB = 0;
+    const uint8_t *pA = wb0[0], *pB = A.down ? wb0[0] + (size_t)64 * nb * 144 : wb1[0];
+    if (!Q6) {
 #pragma unroll
-    for (int j = 0; j < NPC; j++) roff[j] = ~0u;
-    if (raw_role) {
-      if (Q6) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          bool sec;
-          const int r = grow((ct >> 3) + 32 * j, sec);
-          if (r >= 0) roff[j] = ((uint32_t)r * (uint32_t)nb * 128u + 16u * (ct & 7)) | (sec ? 0x80000000u : 0u);
-        }
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-          bool sec;
-          const int r = grow((ct >> 2) + 64 * j, sec);
-          if (r >= 0) roff[4 + j] = ((uint32_t)r * (uint32_t)nb * 64u + 16u * (ct & 3)) | (sec ? 0x80000000u : 0u);
-        }
-        {
-          bool sec;
-          const int r = grow(ct & 127, sec);
-          if (r >= 0) roff[6] = ((uint32_t)r * (uint32_t)nb * (ct < 128 ? 16u : 2u)) | (sec ? 0x80000000u : 0u);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 5; j++) {
-          const int p = ct + (TC_NW / 2) * j;
-          if (p < TC_M * 9) {
-            const int i = p / 9, c = p - 9 * i;
-            bool sec;
-            const int r = grow(i, sec);
-            if (r >= 0) roff[j] = ((uint32_t)r * (uint32_t)nb * 144u + 16u * c) | (sec ? 0x80000000u : 0u);
-          }
-        }
+      for (int j = 0; j < 18; j++) {
+        const int p = lane + 32 * j, i = p / 9, c = p - 9 * i;
+        roff[j] = (uint32_t)(r0 + i) * (uint32_t)nb * 144u + 16u * c;
+        if (r0 + i < rows) okA |= 1u << j;
+        if (r0 + i + (A.down ? 64 : 0) < rows) okB |= 1u << j;
       }
     }
-    auto wbase = [&](int plane, uint32_t o) -> const uint8_t * {  // the piece's matrix, plane `plane`
-      const WMat &W = (o & 0x80000000u) ? W1 : W0;
-      return W.plane[plane] + (size_t)el * W.stride[plane] + (o & 0x7fffffffu);
-    };
-    // the block bb of the tile's rows -> raw area bb % NS (one group)
-    auto issue_raw = [&](int bb) {
-      if (bb < nb) {
-        const uint32_t ra = sRaw_a + (uint32_t)(bb % NS) * RAWB;
-        if (Q6) {
+    // Q6_K: ql 8 pieces a row, [row][128 B], piece c at c ^ (row & 7); qh 4 pieces a row,
+    // [row][64 B], piece c at c ^ ((row >> 1) & 3) (both conflict-free for the row-per-lane reads
+    // of the unpack); sc [row][16 B]; d: the aligned word holding the row's f16. A lane keeps its
+    // piece column and walks rows: tile row i = i0 + step * j.
+    for (int bb = 0; bb < nb; bb++) {
+      // ---- the weights of block bb -> raw area bb % NS ----
+      {
+        const int st = bb % NS;
+        const uint32_t ra = sRaw_a + (uint32_t)st * RAWB;
+        if (bb >= NS) tc_wait(empty_raw + st, (uint32_t)((bb / NS - 1) & 1), A.err, A.wait_ns);
+        if (!Q6) {
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const int i = (ct >> 3) + 32 * j, c = ct & 7;
-            if (roff[j] != ~0u) tc_cp16(ra + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)), wbase(0, roff[j]) + (size_t)bb * 128);
-          }
-#pragma unroll
-          for (int j = 0; j < 2; j++) {
-            const int i = (ct >> 2) + 64 * j, c = ct & 3;
-            if (roff[4 + j] != ~0u)
-              tc_cp16(ra + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)), wbase(1, roff[4 + j]) + (size_t)bb * 64);
-          }
-          if (roff[6] != ~0u) {
-            const int i = ct & 127;
-            if (ct < 128) tc_cp16(ra + 24576u + (uint32_t)i * 16u, wbase(2, roff[6]) + (size_t)bb * 16);
-            else tc_cp4(ra + 26624u + (uint32_t)i * 4u, (const uint8_t *)((uintptr_t)(wbase(3, roff[6]) + (size_t)bb * 2) & ~(uintptr_t)3));
+          for (int j = 0; j < 18; j++) {
+            if (okA & (1u << j)) tc_cp16(ra + (uint32_t)(lane + 32 * j) * 16u, pA + roff[j] + (size_t)bb * 144);
+            if (okB & (1u << j)) tc_cp16(ra + (uint32_t)(lane + 32 * (j + 18)) * 16u, pB + roff[j] + (size_t)bb * 144);
           }
         } else {
-#pragma unroll
-          for (int j = 0; j < 5; j++)
-            if (roff[j] != ~0u) tc_cp16(ra + (uint32_t)(ct + (TC_NW / 2) * j) * 16u, wbase(0, roff[j]) + (size_t)bb * 144);
+          const int halves = A.down ? 1 : 2, hrows = A.down ? TC_M : TC_M / 2;
+          for (int hf = 0; hf < halves; hf++) {
+            const uint8_t *const *wb = hf ? wb1 : wb0;
+            const int lim = min(hrows, rows - r0);  // rows of this half inside the matrix
+            {
+              const int c = lane & 7;
+              const uint8_t *src = wb[0] + ((size_t)(r0 + (lane >> 3)) * nb + bb) * 128 + 16 * c;
+              for (int il = lane >> 3; il < lim; il += 4, src += (size_t)4 * nb * 128) {
+                const int i = hf * hrows + il;
+                tc_cp16(ra + (uint32_t)(i * 128 + ((c ^ (i & 7)) << 4)), src);
+              }
+            }
+            {
+              const int c = lane & 3;
+              const uint8_t *src = wb[1] + ((size_t)(r0 + (lane >> 2)) * nb + bb) * 64 + 16 * c;
+              for (int il = lane >> 2; il < lim; il += 8, src += (size_t)8 * nb * 64) {
+                const int i = hf * hrows + il;
+                tc_cp16(ra + 16384u + (uint32_t)(i * 64 + ((c ^ ((i >> 1) & 3)) << 4)), src);
+              }
+            }
+            for (int il = lane; il < lim; il += 32) {
+              const int i = hf * hrows + il;
+              tc_cp16(ra + 24576u + (uint32_t)i * 16u, wb[2] + ((size_t)(r0 + il) * nb + bb) * 16);
+              tc_cp4(ra + 26624u + (uint32_t)i * 4u,
+                     (const uint8_t *)((uintptr_t)(wb[3] + ((size_t)(r0 + il) * nb + bb) * 2) & ~(uintptr_t)3));
+            }
+          }
         }
+        // this lane's pieces, once they have landed, count as its arrival on the stage's barrier
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(tc_s32(full_raw + st)) : "memory");
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    if (raw_role) {
-#pragma unroll
-      for (int i = 0; i < NS; i++) issue_raw(i);
-    } else {
-      issue_b(0);
-      issue_b(1);
+      // ---- the tokens' records of block bb -> their area ----
+      {
+        const int sb = bb % 3;
+        if (bb >= 3) tc_wait(empty_b + sb, (uint32_t)((bb / 3 - 1) & 1), A.err, A.wait_ns);
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_s32(full_b + sb)),
+                       "r"((uint32_t)(nrec * TC_REC))
+                       : "memory");
+        __syncwarp();
+        if (lane < nrec)
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           sB_a + (uint32_t)(sb * BSTAGE + lane * TC_REC)),
+                       "l"(rec0 + ((size_t)lane * nb + bb) * TC_REC), "r"((uint32_t)TC_REC), "r"(tc_s32(full_b + sb))
+                       : "memory");
+      }
     }
-
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else {
+    // ================= the workers =================
     // unpack: thread = (row m of the tile, quarter `part` of the block: K values
     // 64 part .. 64 part + 63 = TMEM columns 16 part .. 16 part + 15 of each plane). The same
     // thread folds row m's accumulators (TMEM lane m), a quarter of the token columns, so
@@ -529,6 +585,14 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         }
       }
     };
+    // wait for raw block bb, unpack it, and free its area once the whole warp has read it
+    auto take = [&](int bb) {
+      const int st = bb % NS;
+      tc_wait(full_raw + st, (uint32_t)((bb / NS) & 1), A.err, A.wait_ns);
+      unpack(bb);
+      __syncwarp();
+      if ((tid & 31) == 0) tc_mbar_arrive(empty_raw + st);
+    };
 
     // (3) fold: TMEM lane m, a quarter of the tile's token columns (npad / 4: a multiple of 4)
     const uint32_t tlane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
@@ -537,12 +601,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
 #pragma unroll
     for (int i = 0; i < 32; i++) total[i] = 0.0f;
 
-    if (raw_role) asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
-    tc_workers_sync();
-    unpack(0);
-    tc_workers_sync();
-    if (raw_role) issue_raw(NS);
-
+    take(0);
     for (int b = 0; b < nb; b++) {
       TC_STAMP(b, 0)
       const float rd = nrd, rdmin = nrdmin;
@@ -551,29 +610,24 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       tc_st16(tlane + TC_A_HI + 16u * part, ah);
       tc_st16(tlane + TC_A_LO + 16u * part, al);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (!raw_role) asm volatile("cp.async.wait_group 1;" ::: "memory");  // the tokens' block b has landed
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the mins written by unpack(b)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       tc_ready_arrive();
-      if (!raw_role) issue_b(b + 2);  // its area was read by the products of block b - 1: free
       TC_STAMP(b, 1)
       // ---- 2. while the products run: the next block -> registers ----
-      if (b + 1 < nb) {
-        if (raw_role) asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
-        tc_workers_sync();  // every copy of the raw block b + 1 has landed
-        unpack(b + 1);
-        tc_workers_sync();  // its raw area is free again
-        if (raw_role) issue_raw(b + 1 + NS);
-      }
+      if (b + 1 < nb) take(b + 1);
       TC_STAMP(b, 2)
       // ---- 3. the block's float term, in block order ----
-      if (!tc_bar_test(bar, (uint32_t)(b & 1))) tc_bar_wait(bar, (uint32_t)(b & 1), A.err, A.wait_ns);
+      tc_wait(bar, (uint32_t)(b & 1), A.err, A.wait_ns);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int sb = b % 3;
+      tc_wait(full_b + sb, (uint32_t)((b / 3) & 1), A.err, A.wait_ns);  // (long complete) the block's x.d is visible
       TC_STAMP(b, 3)
       TC_STAMP(b, 4)
       {
-        const float *xdv = sXd + (b & 3) * TC_NMAX + ecol0;
-        const int32_t *xsv = sXs + (b & 3) * TC_NMAX + ecol0;
+        const uint8_t *bst = sB + (size_t)sb * BSTAGE;  // column n: record n / 8, slot n % 8
+        // (four columns a wait: eight a wait, and requesting a step ahead, both measured slower -
+        // the extra live registers cost more than the read latency they hide)
 #pragma unroll
         for (int c4 = 0; c4 < 32; c4 += 4) {
           if (c4 < ew) {
@@ -582,11 +636,13 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
             tc_ld4(tlane + TC_ACC_LO + (uint32_t)(ecol0 + c4), v1);
             if (!Q6) tc_ld4(tlane + TC_ACC_M + (uint32_t)(ecol0 + c4), v2);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            const float4 x4 = *(const float4 *)(xdv + c4);
+            const int n = ecol0 + c4;
+            const uint8_t *rcd = bst + (size_t)(n >> 3) * TC_REC + (n & 7) * 4;
+            const float4 x4 = *(const float4 *)(rcd + TC_REC_XD);
             const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
             int ss[4] = {0, 0, 0, 0};
             if (Q6) {
-              const int4 s4 = *(const int4 *)(xsv + c4);
+              const int4 s4 = *(const int4 *)(rcd + TC_REC_XS);
               ss[0] = s4.x; ss[1] = s4.y; ss[2] = s4.z; ss[3] = s4.w;
             }
             // (scalar on purpose: a packed mul.rn.f32x2 followed by add.rn.f32x2 comes out
@@ -607,9 +663,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if ((tid & 31) == 0) tc_mbar_arrive(empty_b + sb);  // this warp has read the block's x.d
       TC_STAMP(b, 5)
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
     tc_workers_sync();  // the raw areas are dead: their memory carries the gate/up exchange
 
     const bool dead = *(volatile int *)A.err != 0;
@@ -657,7 +714,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
 }
 
 void launch_tc_tiles(const Launch &L, Groups g, int *n_tiles, uint32_t *tile_group, uint32_t *tile_n0, int max_tiles) {
-  k_tc_tiles<<<1, 512, 0, L.stream>>>(g, n_tiles, tile_group, tile_n0, max_tiles);
+  k_tc_tiles<<<1, 512, 0, L.stream>>>(g, n_tiles, tile_group, tile_n0, nullptr, nullptr, max_tiles);
   if (L.count) ++*L.count;
 }
 
@@ -665,28 +722,48 @@ int tc_max_tiles(int n_pairs, int max_groups) {
   int groups = max_groups < n_pairs ? max_groups : n_pairs;
   return n_pairs / TC_NMAX + groups;
 }
+size_t tc_tile_words(int n_pairs, int max_groups) {
+  return 4 + 3 * (size_t)tc_max_tiles(n_pairs, max_groups) + 512;
+}
+// bytes of the records of n_pairs rows of `cols` values in at most max_groups groups (every group
+// starts on a multiple of 16 rows)
+size_t tc_rec_bytes(int n_pairs, int max_groups, int cols) {
+  size_t groups = (size_t)(max_groups < n_pairs ? max_groups : n_pairs);
+  size_t rows = (size_t)n_pairs + 15 * groups + 16;
+  return (rows / 8 + 1) * (size_t)(cols / 256) * TC_REC;
+}
 static size_t tc_smem(bool q6) {
   size_t raw = q6 ? (size_t)TC_RAW_STAGES_Q6 * TC_RAW_Q6 : (size_t)TC_RAW_STAGES_Q4 * TC_RAW_Q4;
   size_t ex = (size_t)TC_M * (TC_NMAX + 1) * 4;  // the gate/up exchange shares the raw areas' memory
-  size_t bstage = (size_t)16 * (TC_NMAX + 1) * 16 + (q6 ? 0 : 2 * (TC_NMAX + 1) * 16);
-  return (raw > ex ? raw : ex) + 3 * bstage + 2 * 2 * TC_M * 16 + 4 * TC_NMAX * 4 + 4 * TC_NMAX * 4 + 16;
+  return (raw > ex ? raw : ex) + 3 * (size_t)(TC_NMAX / 8) * TC_REC + 2 * 2 * TC_M * 16 + 15 * 8 + 16;
 }
 
 // Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x
-// activations (xbm: the f16 form of the sub-block sums the quantiser writes).
+// activations (xbm: the f16 form of the sub-block sums the quantiser writes): the tile list,
+// the activation rows regrouped into records (rec_buf: tc_rec_bytes), the products.
+// src_row: row of xq / xd / xbm / xs that holds pair p (null: row p itself).
 cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool down, Groups g,
-                          int n_pairs, uint32_t *tile_buf, const int8_t *xq, const float *xd,
-                          const uint16_t *xbm, const int32_t *xs, const float *wts, float *out, int *err,
-                          unsigned long long wait_ns, int fault_block) {
+                          int n_pairs, uint32_t *tile_buf, uint8_t *rec_buf, const uint32_t *src_row,
+                          const int8_t *xq, const float *xd, const uint16_t *xbm, const int32_t *xs,
+                          const float *wts, float *out, int *err, unsigned long long wait_ns, int fault_block) {
   if (n_pairs == 0) return cudaSuccess;
   // tile list: at most one partial tile per group plus the full ones
   const int max_tiles = tc_max_tiles(n_pairs, g.max_groups);
   int *n_tiles = (int *)tile_buf;
-  uint32_t *tile_group = tile_buf + 4, *tile_n0 = tile_buf + 4 + max_tiles;
-  k_tc_tiles<<<1, 512, 0, L.stream>>>(g, n_tiles, tile_group, tile_n0, max_tiles);
+  uint32_t *tile_group = tile_buf + 4, *tile_n0 = tile_group + max_tiles, *tile_r0 = tile_n0 + max_tiles;
+  uint32_t *group_r0 = tile_r0 + max_tiles;
+  k_tc_tiles<<<1, 512, 0, L.stream>>>(g, n_tiles, tile_group, tile_n0, tile_r0, group_r0, max_tiles);
   if (L.count) ++*L.count;
   const WMat &W = down ? (shared ? ly.sdown : ly.down) : (shared ? ly.sgate : ly.gate);
   const bool q6 = W.type == PM_TYPE_Q6_K;
+  {
+    const int groups = g.max_groups < n_pairs ? g.max_groups : n_pairs;
+    const long units = ((long)n_pairs / 8 + 2 * groups) * (W.cols / 256);  // (row group, block) records in all
+    long gx = units / groups / 32;  // a warp writes a few records
+    gx = gx < 1 ? 1 : (gx > 128 ? 128 : gx);
+    k_tc_rows<<<dim3((unsigned)gx, (unsigned)groups), 256, 0, L.stream>>>(g, group_r0, src_row, W.cols, xq, xd, xbm, xs, rec_buf);
+    if (L.count) ++*L.count;
+  }
   const size_t smem = tc_smem(q6);
   const void *kern = q6 ? (const void *)k_tc<PM_TYPE_Q6_K> : (const void *)k_tc<PM_TYPE_Q4_K>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -696,10 +773,7 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.shared = shared;
   A.down = down;
   A.g = g;
-  A.xq = xq;
-  A.xd = xd;
-  A.xbm = xbm;
-  A.xs = xs;
+  A.rec = rec_buf;
   A.wts = wts;
   A.out = out;
   A.err = err;
@@ -708,6 +782,7 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.n_tiles = n_tiles;
   A.tile_group = tile_group;
   A.tile_n0 = tile_n0;
+  A.tile_r0 = tile_r0;
   int row_tiles = down ? (W.rows + TC_M - 1) / TC_M : (W.rows + 63) / 64;
   dim3 grid(row_tiles, max_tiles);
   if (q6) k_tc<PM_TYPE_Q6_K><<<grid, TC_NT, smem, L.stream>>>(A);
