@@ -645,8 +645,9 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
               const int4 s4 = *(const int4 *)(rcd + TC_REC_XS);
               ss[0] = s4.x; ss[1] = s4.y; ss[2] = s4.z; ss[3] = s4.w;
             }
-            // (scalar on purpose: a packed mul.rn.f32x2 followed by add.rn.f32x2 comes out
-            // contracted into one fused operation, which is not the reference's rounding)
+            // (scalar on purpose: packed f32x2 forms - mul.rn.f32x2 then add.rn.f32x2, and the same
+            // written as fma.rn.f32x2 with a -0 addend / a unit factor - came out with other bits
+            // than the reference's separately rounded steps, and ran no faster)
 #pragma unroll
             for (int u = 0; u < 4; u++) {
               float term;
