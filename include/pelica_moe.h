@@ -303,6 +303,42 @@ PM_API int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *layer, const float *x, int
  * (to and from other ranks; rows that stay on the rank are not counted) */
 PM_API int32_t pm_ep_last_stats(pm_ep *ep, uint64_t *out);
 
+/* ---- usage-driven placement of experts over the ranks ------------------
+ * replaces: `Adapt` / `adapt` / `swap_round` (src/moe.rs:246-278,1965-2069): a decayed use score per
+ * (layer, expert) from the plan's counters; the experts used more than the least used resident ones
+ * change places with them, biggest gains first, up to a byte budget a round, with a margin against
+ * going back and forth; a slot table says where each expert sits. The reference's places are VRAM and
+ * host memory; here they are the ranks of an expert-parallel group: slot s is held by rank
+ * s / (n_exp / world), and a round evens out the scores the ranks serve. */
+typedef struct pm_placement pm_placement;
+/* host-side planner (no GPU work) */
+PM_API int32_t pm_placement_create(int32_t n_layers, int32_t n_exp, int32_t world, pm_placement **out);
+PM_API int32_t pm_placement_destroy(pm_placement *p);
+/* usage[n_exp]: the layer's cumulative counters (pm_layer_usage); score = score * 0.944 + the increase
+ * since the last observation (src/moe.rs:273,1977-1980) */
+PM_API int32_t pm_placement_observe(pm_placement *p, int32_t layer, const uint32_t *usage);
+/* One round: swaps[3 * i] = (layer, hot expert, cold expert), at most max_swaps and at most
+ * budget_bytes moved (2 * expert_bytes a swap); a swap must clear the reference's margin
+ * (hot >= cold * 1.25 + 1.5, src/moe.rs:2013) and lower the load of the heavier rank. The planner's
+ * table is updated as if the swaps were done: carry them out in the order returned. */
+PM_API int32_t pm_placement_plan(pm_placement *p, uint64_t expert_bytes, uint64_t budget_bytes, int32_t *swaps,
+                                 int32_t max_swaps, int32_t *n_swaps);
+PM_API int32_t pm_placement_slots(const pm_placement *p, int32_t layer, int32_t *slot_of_expert);
+/* score[n_exp] and / or rank_load[world] (sum of the scores of the experts a rank holds); either may be null */
+PM_API int32_t pm_placement_scores(const pm_placement *p, int32_t layer, float *score, float *rank_load);
+/* The layer's slot table on an expert-parallel group (`loc`, src/moe.rs:262-263,2065): after routing,
+ * expert ids are mapped through it, and everything downstream - plan, destination rank, the serving
+ * rank's planes - names slots. The weights must already sit in the slots the table says
+ * (pm_layer_set_expert takes the slot index then). Null: expert e in slot e again. The usage counters
+ * keep counting by expert id. */
+PM_API int32_t pm_ep_set_slots(pm_ep *ep, pm_layer *layer, const int32_t *slot_of_expert);
+PM_API int32_t pm_ep_get_slots(pm_ep *ep, pm_layer *layer, int32_t *slot_of_expert);
+/* Collective: experts a and b change places - the ranks that hold them exchange the experts' bytes
+ * (grouped ncclSend / ncclRecv through a staging area; device copies when one rank holds both) and
+ * every rank rewrites its table. Every rank calls it with the same arguments in the same order, between
+ * forward calls. */
+PM_API int32_t pm_ep_swap_experts(pm_ep *ep, pm_layer *layer, int32_t expert_a, int32_t expert_b);
+
 /* ---- format checks (bit-exact against the reference arithmetic) -------- */
 /* replaces: `deq4` src/moe_kernels.rs:63-84, `deq_row` src/q4x_cpu.rs:443-496 */
 PM_API int32_t pm_dequant(pm_ctx *ctx, int32_t ggml_type, const uint8_t *blocks,

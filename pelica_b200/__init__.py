@@ -93,6 +93,15 @@ ABI = {
     "pm_ep_set_timeout_ms": (C.c_int32, [_VP, C.c_int64]),
     "pm_moe_forward_ep": (C.c_int32, [_VP, _VP, _VP, C.c_int32, _VP, C.c_uint32]),
     "pm_ep_last_stats": (C.c_int32, [_VP, _VP]),
+    "pm_placement_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(_VP)]),
+    "pm_placement_destroy": (C.c_int32, [_VP]),
+    "pm_placement_observe": (C.c_int32, [_VP, C.c_int32, _VP]),
+    "pm_placement_plan": (C.c_int32, [_VP, C.c_uint64, C.c_uint64, _VP, C.c_int32, C.POINTER(C.c_int32)]),
+    "pm_placement_slots": (C.c_int32, [_VP, C.c_int32, _VP]),
+    "pm_placement_scores": (C.c_int32, [_VP, C.c_int32, _VP, _VP]),
+    "pm_ep_set_slots": (C.c_int32, [_VP, _VP, _VP]),
+    "pm_ep_get_slots": (C.c_int32, [_VP, _VP, _VP]),
+    "pm_ep_swap_experts": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32]),
     "pm_dequant": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP]),
     "pm_quant_act": (C.c_int32, [_VP, C.c_int32, _VP, C.c_size_t, _VP, _VP, _VP]),
     "pm_rmsnorm": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_float, _VP]),
@@ -596,7 +605,65 @@ class ExpertParallel:
         dy.free()
         return out
 
+    def set_slots(self, layer: MoeLayer, slot_of_expert=None):
+        """The layer's placement table (None: expert e in slot e). The weights must already sit in
+        the slots it names."""
+        if slot_of_expert is None:
+            _check(self.lib.pm_ep_set_slots(self.h, layer.h, None))
+        else:
+            t = np.ascontiguousarray(slot_of_expert, np.int32)
+            assert t.size == layer.desc.n_exp
+            _check(self.lib.pm_ep_set_slots(self.h, layer.h, t.ctypes.data))
+
+    def get_slots(self, layer: MoeLayer) -> np.ndarray:
+        t = np.zeros(layer.desc.n_exp, np.int32)
+        _check(self.lib.pm_ep_get_slots(self.h, layer.h, t.ctypes.data))
+        return t
+
+    def swap_experts(self, layer: MoeLayer, a: int, b: int):
+        """Collective: experts a and b change places (every rank calls it, same arguments, same order)."""
+        _check(self.lib.pm_ep_swap_experts(self.h, layer.h, a, b))
+
     def last_stats(self) -> dict:
         out = np.zeros(4, np.uint64)
         _check(self.lib.pm_ep_last_stats(self.h, out.ctypes.data))
         return dict(rows_sent=int(out[0]), rows_received=int(out[1]), bytes_sent=int(out[2]), bytes_received=int(out[3]))
+
+
+class Placement:
+    """The host-side planner of usage-driven expert placement (pm_placement_*): decayed use scores
+    per (layer, expert) and rounds of swaps that even out what the ranks serve."""
+
+    def __init__(self, n_layers: int, n_exp: int, world: int):
+        self.lib = load_library()
+        self.n_layers, self.n_exp, self.world = n_layers, n_exp, world
+        h = _VP()
+        _check(self.lib.pm_placement_create(n_layers, n_exp, world, C.byref(h)))
+        self.h = h.value
+
+    def close(self):
+        if self.h:
+            self.lib.pm_placement_destroy(self.h)
+            self.h = None
+
+    def observe(self, layer: int, usage):
+        u = np.ascontiguousarray(usage, np.uint32)
+        assert u.size == self.n_exp
+        _check(self.lib.pm_placement_observe(self.h, layer, u.ctypes.data))
+
+    def plan(self, expert_bytes: int, budget_bytes: int, max_swaps: int = 256) -> list:
+        """One round: [(layer, hot expert, cold expert), ...] in the order to carry them out."""
+        out = np.zeros(3 * max(max_swaps, 1), np.int32)
+        n = C.c_int32(0)
+        _check(self.lib.pm_placement_plan(self.h, expert_bytes, budget_bytes, out.ctypes.data, max_swaps, C.byref(n)))
+        return [tuple(int(v) for v in out[3 * i:3 * i + 3]) for i in range(n.value)]
+
+    def slots(self, layer: int) -> np.ndarray:
+        t = np.zeros(self.n_exp, np.int32)
+        _check(self.lib.pm_placement_slots(self.h, layer, t.ctypes.data))
+        return t
+
+    def scores(self, layer: int):
+        s, r = np.zeros(self.n_exp, np.float32), np.zeros(self.world, np.float32)
+        _check(self.lib.pm_placement_scores(self.h, layer, s.ctypes.data, r.ctypes.data))
+        return s, r

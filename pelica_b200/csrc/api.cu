@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <map>
 #include <vector>
 
 #include "decode_mega.cuh"
@@ -1825,6 +1826,12 @@ struct pm_ep {
   cudaEvent_t ev = nullptr;
   int64_t timeout_ms = 60000;  // host watchdog on the counts (a peer that never enters the call)
   uint64_t stats[4] = {0, 0, 0, 0};  // last call: rows sent, rows received, bytes sent, bytes received
+  // placement tables: slot of every expert of a layer (absent: expert e sits in slot e)
+  struct Slots {
+    std::vector<int32_t> host;
+    int32_t *dev = nullptr;
+  };
+  std::map<pm_layer *, Slots> slots;
 };
 
 extern "C" int32_t pm_ep_unique_id(uint8_t *out) {
@@ -1846,6 +1853,8 @@ extern "C" int32_t pm_ep_destroy(pm_ep *ep) {
     else g_nccl.CommDestroy(ep->comm);
   }
   cudaGetLastError();
+  for (auto &kv : ep->slots)
+    if (kv.second.dev) cudaFree(kv.second.dev);
   if (ep->ws2) cudaFree(ep->ws2);
   if (ep->d_cnt) cudaFree(ep->d_cnt);
   if (ep->h_cnt) cudaFreeHost(ep->h_cnt);
@@ -1888,6 +1897,126 @@ extern "C" int32_t pm_ep_set_timeout_ms(pm_ep *ep, int64_t ms) {
   ep->timeout_ms = ms;
   return PM_OK;
 }
+static int32_t ep_comm_ok(pm_ep *ep);
+
+// ---- usage-driven placement (the reference moves experts between VRAM and host memory by a decayed
+// use score and rewrites its slot table, src/moe.rs:246-278,1965-2069; here the places are the ranks)
+extern "C" int32_t pm_ep_set_slots(pm_ep *ep, pm_layer *ly, const int32_t *slot_of_expert) {
+  if (!ep || !ly) return fail(PM_ERR_INVALID, "pm_ep_set_slots: null argument");
+  pm_ctx *c = ep->ctx;
+  if (ly->ctx != c) return fail(PM_ERR_INVALID, "pm_ep_set_slots: the layer belongs to another context");
+  CU(cudaSetDevice(c->device));
+  const int E = ly->dev.desc.n_exp;
+  auto it = ep->slots.find(ly);
+  if (!slot_of_expert) {  // back to expert e in slot e
+    if (it != ep->slots.end()) {
+      CU(cudaStreamSynchronize(c->stream));
+      if (it->second.dev) cudaFree(it->second.dev);
+      ep->slots.erase(it);
+    }
+    return PM_OK;
+  }
+  std::vector<char> seen((size_t)E, 0);
+  for (int e = 0; e < E; e++) {
+    const int32_t sl = slot_of_expert[e];
+    if (sl < 0 || sl >= E || seen[(size_t)sl]) return fail(PM_ERR_INVALID, "pm_ep_set_slots: not a permutation of the %d slots", E);
+    seen[(size_t)sl] = 1;
+  }
+  pm_ep::Slots &S = ep->slots[ly];
+  if (!S.dev) CU(cudaMalloc(&S.dev, (size_t)E * 4));
+  S.host.assign(slot_of_expert, slot_of_expert + E);
+  CU(cudaStreamSynchronize(c->stream));  // earlier calls read the old table
+  CU(cudaMemcpyAsync(S.dev, S.host.data(), (size_t)E * 4, cudaMemcpyHostToDevice, c->stream));
+  CU(cudaStreamSynchronize(c->stream));
+  return PM_OK;
+}
+
+extern "C" int32_t pm_ep_get_slots(pm_ep *ep, pm_layer *ly, int32_t *slot_of_expert) {
+  if (!ep || !ly || !slot_of_expert) return fail(PM_ERR_INVALID, "pm_ep_get_slots: null argument");
+  const int E = ly->dev.desc.n_exp;
+  auto it = ep->slots.find(ly);
+  for (int e = 0; e < E; e++) slot_of_expert[e] = it == ep->slots.end() ? e : it->second.host[(size_t)e];
+  return PM_OK;
+}
+
+// the device regions of one slot of a sharded layer: every plane of the three matrices, and the biases
+static void slot_regions(pm_layer *ly, int el, std::vector<std::pair<uint8_t *, size_t>> &out) {
+  LayerDev &dv = ly->dev;
+  WMat *ms[3] = {&dv.gate, &dv.up, &dv.down};
+  for (WMat *m : ms)
+    for (int p = 0; p < 4; p++)
+      if (m->plane[p] && m->stride[p]) out.push_back({m->plane[p] + (size_t)el * m->stride[p], m->stride[p]});
+  const int ff = dv.desc.ff, d = dv.desc.d;
+  if (ly->bias_gate) out.push_back({(uint8_t *)(ly->bias_gate + (size_t)el * ff), (size_t)ff * 4});
+  if (ly->bias_up) out.push_back({(uint8_t *)(ly->bias_up + (size_t)el * ff), (size_t)ff * 4});
+  if (ly->bias_down) out.push_back({(uint8_t *)(ly->bias_down + (size_t)el * d), (size_t)d * 4});
+}
+
+// Collective: experts a and b of the layer change places. The ranks that hold them exchange the
+// experts' bytes (every plane of gate, up and down, and the biases) through a staging area, every rank
+// rewrites its table. All ranks call it with the same arguments in the same order.
+extern "C" int32_t pm_ep_swap_experts(pm_ep *ep, pm_layer *ly, int32_t expert_a, int32_t expert_b) {
+  if (!ep || !ly) return fail(PM_ERR_INVALID, "pm_ep_swap_experts: null argument");
+  pm_ctx *c = ep->ctx;
+  if (ly->ctx != c) return fail(PM_ERR_INVALID, "pm_ep_swap_experts: the layer belongs to another context");
+  const LayerDev &dv = ly->dev;
+  const int E = dv.desc.n_exp, W = ep->world, rank = ep->rank;
+  if (E % W) return fail(PM_ERR_INVALID, "%d experts do not split over %d ranks", E, W);
+  const int per = E / W;
+  if (dv.first_local != rank * per || dv.n_local != per)
+    return fail(PM_ERR_INVALID, "pm_ep_swap_experts: the layer does not hold this rank's slots");
+  if (expert_a < 0 || expert_a >= E || expert_b < 0 || expert_b >= E) return fail(PM_ERR_INVALID, "pm_ep_swap_experts: expert id");
+  if (expert_a == expert_b) return PM_OK;
+  CU(cudaSetDevice(c->device));
+  pm_ep::Slots &S = ep->slots[ly];
+  if (S.host.empty()) {
+    S.host.resize((size_t)E);
+    for (int e = 0; e < E; e++) S.host[(size_t)e] = e;
+  }
+  if (!S.dev) CU(cudaMalloc(&S.dev, (size_t)E * 4));
+  const int sa = S.host[(size_t)expert_a], sb = S.host[(size_t)expert_b];
+  const int ra = sa / per, rb = sb / per;
+  std::vector<std::pair<uint8_t *, size_t>> mine, other;
+  size_t bytes = 0;
+  if (ra == rank) slot_regions(ly, sa - rank * per, mine);
+  if (rb == rank) slot_regions(ly, sb - rank * per, ra == rank ? other : mine);
+  for (auto &r : mine) bytes += al(r.second);
+  if (ra == rank || rb == rank) {
+    TRY(stage_reserve(c, bytes));
+    uint8_t *tmp = c->stage;
+    if (ra == rank && rb == rank) {  // both here: through the staging area
+      size_t o = 0;
+      for (size_t i = 0; i < mine.size(); i++) {
+        CU(cudaMemcpyAsync(tmp + o, mine[i].first, mine[i].second, cudaMemcpyDeviceToDevice, c->stream));
+        CU(cudaMemcpyAsync(mine[i].first, other[i].first, mine[i].second, cudaMemcpyDeviceToDevice, c->stream));
+        CU(cudaMemcpyAsync(other[i].first, tmp + o, mine[i].second, cudaMemcpyDeviceToDevice, c->stream));
+        o += al(mine[i].second);
+      }
+    } else {  // send this rank's expert, receive the peer's into the staging area, then put it in the slot
+      const int peer = ra == rank ? rb : ra;
+      TRY(ep_comm_ok(ep));
+      NC(g_nccl.GroupStart());
+      size_t o = 0;
+      for (auto &r : mine) {
+        NC(g_nccl.Send(r.first, r.second, PM_NCCL_UINT8, peer, ep->comm, c->stream));
+        NC(g_nccl.Recv(tmp + o, r.second, PM_NCCL_UINT8, peer, ep->comm, c->stream));
+        o += al(r.second);
+      }
+      NC(g_nccl.GroupEnd());
+      o = 0;
+      for (auto &r : mine) {
+        CU(cudaMemcpyAsync(r.first, tmp + o, r.second, cudaMemcpyDeviceToDevice, c->stream));
+        o += al(r.second);
+      }
+    }
+  }
+  std::swap(S.host[(size_t)expert_a], S.host[(size_t)expert_b]);
+  CU(cudaMemcpyAsync(S.dev, S.host.data(), (size_t)E * 4, cudaMemcpyHostToDevice, c->stream));
+  CU(cudaStreamSynchronize(c->stream));
+  ly->gen++;
+  return ep_comm_ok(ep);
+}
+
 extern "C" int32_t pm_ep_last_stats(pm_ep *ep, uint64_t *out) {
   if (!ep || !out) return fail(PM_ERR_INVALID, "pm_ep_last_stats");
   for (int i = 0; i < 4; i++) out[i] = ep->stats[i];
@@ -1944,7 +2073,18 @@ extern "C" int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *ly, const float *x, in
     { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
     { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
   }
-  { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan, c->dev_err); }
+  {
+    // with a placement table everything from here on names slots: the plan groups by slot, a pair goes
+    // to the rank of its slot, the serving rank indexes its planes by slot
+    auto st = ep->slots.find(ly);
+    LayerDev dvp = dv;
+    if (st != ep->slots.end()) {
+      launch_ep_slots(L, S.ids, (int)P, E, st->second.dev, dv.usage);
+      dvp.usage = nullptr;  // counted by expert above
+    }
+    PROF(c, PH_PLAN);
+    launch_plan(L, dvp, S.ids, T, S.plan, c->dev_err);
+  }
   launch_ep_rank_counts(L, S.plan.cnt, E, W, ep->d_cnt);
   NC(g_nccl.AllGather(ep->d_cnt, ep->d_cnt + W, (size_t)W, PM_NCCL_INT32, ep->comm, c->stream));
   CU(cudaMemcpyAsync(ep->h_cnt, ep->d_cnt + W, (size_t)W * W * 4, cudaMemcpyDeviceToHost, c->stream));

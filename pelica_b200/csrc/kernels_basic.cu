@@ -869,6 +869,130 @@ __device__ __forceinline__ float row_f32(const WMat &W, int el, int r, const flo
   return pm_warp_sum_16_1(acc);
 }
 
+// NR MXFP4 rows against one f32 activation vector, the activations read once for all of them (a
+// single row reads 8 times as many activation bytes as weight bytes, and the L1 path was what
+// bound it). Per row the same operations in the same order as row_f32.
+template <int NR>
+__device__ __forceinline__ void rows_mx_f32(const uint8_t *const (&nib)[NR], const uint8_t *const (&scl)[NR], int nb,
+                                            const float *__restrict__ x, int lane, float (&out)[NR]) {
+  float acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; i++) acc[i] = 0.0f;
+  for (int b = lane; b < nb; b += 32) {
+    const float4 *xp = (const float4 *)(x + b * 32);
+    float4 xv[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) xv[w] = xp[w];
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+      const uint4 qv = __ldg((const uint4 *)(nib[i] + (size_t)b * 16));
+      const float s = pm_e8(__ldg(scl[i] + b));
+      const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 4; w++) {
+        const float4 x0 = xv[w], x1 = xv[4 + w];
+        const uint32_t q = qw[w];
+        const uint32_t ha = ((q << 9) & 0x0e000e00u) | ((q << 12) & 0x80008000u);
+        const uint32_t hb = ((q << 1) & 0x0e000e00u) | ((q << 4) & 0x80008000u);
+        const uint32_t hc = ((q << 5) & 0x0e000e00u) | ((q << 8) & 0x80008000u);
+        const uint32_t hd = ((q >> 3) & 0x0e000e00u) | (q & 0x80008000u);
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&ha));
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&hb));
+        const float2 fc = __half22float2(*reinterpret_cast<const __half2 *>(&hc));
+        const float2 fd = __half22float2(*reinterpret_cast<const __half2 *>(&hd));
+        t = __fmaf_rn(fa.x, x0.x, t);
+        t = __fmaf_rn(fb.x, x0.y, t);
+        t = __fmaf_rn(fa.y, x0.z, t);
+        t = __fmaf_rn(fb.y, x0.w, t);
+        t = __fmaf_rn(fc.x, x1.x, t);
+        t = __fmaf_rn(fd.x, x1.y, t);
+        t = __fmaf_rn(fc.y, x1.z, t);
+        t = __fmaf_rn(fd.y, x1.w, t);
+      }
+      t = __fmul_rn(t, 32768.0f);
+      acc[i] = __fmaf_rn(s, t, acc[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NR; i++) out[i] = pm_warp_sum_16_1(acc[i]);
+}
+
+// gate/up for MXFP4 experts and f32 activations: a warp takes the gate and the up row of two
+// consecutive h values (four rows an activation read); grid (ceil(ff / 16), groups)
+__global__ void __launch_bounds__(256) k_gateup_mx(LayerDev ly, Groups g, const float *__restrict__ x,
+                                                   const float *__restrict__ wts, float *h) {
+  int a = blockIdx.y;
+  if (a >= *g.n_groups) return;
+  const WMat &G = ly.gate, &U = ly.up;
+  const int ff = G.rows, d = G.cols, nb = d / 32;
+  const int lane = threadIdx.x & 31;
+  const int r = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
+  if (r >= ff) return;
+  const int r1 = min(r + 1, ff - 1);  // an odd ff: the last warp computes its row twice
+  const int el = (int)g.expert[a] - ly.first_local;
+  if (el < 0 || el >= ly.n_local) return;  // not held here
+  const uint32_t off = g.offset[a], cnt = g.count[a];
+  const pm_layer_desc &D = ly.desc;
+  const bool fold = D.weight_fold == PM_FOLD_BEFORE_DOWN;
+  const bool bias = ly.bias_gate != nullptr;
+  const uint8_t *gn = G.plane[0] + (size_t)el * G.stride[0], *gs = G.plane[1] + (size_t)el * G.stride[1];
+  const uint8_t *un = U.plane[0] + (size_t)el * U.stride[0], *us = U.plane[1] + (size_t)el * U.stride[1];
+  const uint8_t *const nib[4] = {gn + (size_t)r * nb * 16, un + (size_t)r * nb * 16, gn + (size_t)r1 * nb * 16,
+                                 un + (size_t)r1 * nb * 16};
+  const uint8_t *const scl[4] = {gs + (size_t)r * nb, us + (size_t)r * nb, gs + (size_t)r1 * nb, us + (size_t)r1 * nb};
+  for (uint32_t i = 0; i < cnt; i++) {
+    const uint32_t p = off + i;
+    float v[4];
+    rows_mx_f32<4>(nib, scl, nb, x + (size_t)g.pair_token[p] * d, lane, v);
+    if (lane < 2 && r + lane < ff) {
+      const int rr = r + lane;
+      float gv = lane ? v[2] : v[0], uv = lane ? v[3] : v[1];
+      if (bias) {
+        gv = __fadd_rn(gv, ly.bias_gate[(size_t)el * ff + rr]);
+        uv = __fadd_rn(uv, ly.bias_up[(size_t)el * ff + rr]);
+      }
+      const float w = (fold && wts) ? wts[g.pair_src[p]] : 1.0f;
+      h[(size_t)p * ff + rr] = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, w, fold && wts);
+    }
+  }
+}
+
+// down for MXFP4 experts and f32 hidden vectors: a warp takes four consecutive output rows;
+// grid (ceil(d / 32), groups)
+__global__ void __launch_bounds__(256) k_down_mx(LayerDev ly, Groups g, const float *__restrict__ h, float *eo) {
+  int a = blockIdx.y;
+  if (a >= *g.n_groups) return;
+  const WMat &Dn = ly.down;
+  const int d = Dn.rows, ff = Dn.cols, nb = ff / 32;
+  const int lane = threadIdx.x & 31;
+  const int r = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 4;
+  if (r >= d) return;
+  const int el = (int)g.expert[a] - ly.first_local;
+  const uint32_t off = g.offset[a], cnt = g.count[a];
+  if (el < 0 || el >= ly.n_local) {  // not held here: zeros
+    if (lane < 4 && r + lane < d)
+      for (uint32_t i = 0; i < cnt; i++) eo[(size_t)(off + i) * d + r + lane] = 0.0f;
+    return;
+  }
+  const uint8_t *dn = Dn.plane[0] + (size_t)el * Dn.stride[0], *ds = Dn.plane[1] + (size_t)el * Dn.stride[1];
+  const int rr[4] = {r, min(r + 1, d - 1), min(r + 2, d - 1), min(r + 3, d - 1)};
+  const uint8_t *const nib[4] = {dn + (size_t)rr[0] * nb * 16, dn + (size_t)rr[1] * nb * 16, dn + (size_t)rr[2] * nb * 16,
+                                 dn + (size_t)rr[3] * nb * 16};
+  const uint8_t *const scl[4] = {ds + (size_t)rr[0] * nb, ds + (size_t)rr[1] * nb, ds + (size_t)rr[2] * nb,
+                                 ds + (size_t)rr[3] * nb};
+  for (uint32_t i = 0; i < cnt; i++) {
+    const uint32_t p = off + i;
+    float v[4];
+    rows_mx_f32<4>(nib, scl, nb, h + (size_t)p * ff, lane, v);
+    if (lane < 4 && r + lane < d) {
+      float o = lane == 0 ? v[0] : (lane == 1 ? v[1] : (lane == 2 ? v[2] : v[3]));
+      if (ly.bias_down) o = __fadd_rn(o, ly.bias_down[(size_t)el * d + r + lane]);  // src/oss_batch.rs:89
+      eo[(size_t)p * d + r + lane] = o;
+    }
+  }
+}
+
 // ===========================================================================
 // grouped gate/up + activation, grouped down
 // ===========================================================================
@@ -975,6 +1099,11 @@ void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, i
                    const float *w, float *h) {
   if (n_pairs == 0) return;
   int ff = shared ? ly.sgate.rows : ly.gate.rows;
+  if (!shared && ly.desc.act_quant == PM_AQ_F32 && ly.gate.type == PM_TYPE_MXFP4 && ly.up.type == PM_TYPE_MXFP4) {
+    dim3 grid((ff + 15) / 16, min(g.max_groups, n_pairs));
+    KLAUNCH(L, k_gateup_mx, grid, 256, 0, ly, g, x, w, h);
+    return;
+  }
   dim3 grid((ff + 7) / 8, min(g.max_groups, n_pairs));
   KLAUNCH(L, k_gateup, grid, 256, 0, ly, (int)shared, g, x, xq, xd, xbsum, w, h);
 }
@@ -983,6 +1112,11 @@ void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int
                  float *eo) {
   if (n_pairs == 0) return;
   int d = ly.desc.d;
+  if (!shared && ly.desc.act_quant == PM_AQ_F32 && ly.down.type == PM_TYPE_MXFP4) {
+    dim3 grid((d + 31) / 32, min(g.max_groups, n_pairs));
+    KLAUNCH(L, k_down_mx, grid, 256, 0, ly, g, h, eo);
+    return;
+  }
   dim3 grid((d + 7) / 8, min(g.max_groups, n_pairs));
   KLAUNCH(L, k_down, grid, 256, 0, ly, (int)shared, g, h, hq, hd, hbsum, eo);
 }
@@ -1107,6 +1241,21 @@ void launch_ep_unmeta(const Launch &L, int R, const uint32_t *meta, int first, i
                       int *err) {
   if (R == 0) return;
   KLAUNCH(L, k_ep_unmeta, (R + 255) / 256, 256, 0, R, meta, first, n_local, eids, w, err);
+}
+
+// expert ids -> the slots that hold them (a placement table), counting the use of every expert
+// on the way (the plan that follows sees slots, so it cannot)
+__global__ void k_ep_slots(uint32_t *ids, int P, int E, const int32_t *__restrict__ table, uint32_t *usage) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  const uint32_t e = ids[i];
+  if (e >= (uint32_t)E) return;  // the plan refuses it
+  if (usage) atomicAdd(&usage[e], 1u);
+  ids[i] = (uint32_t)table[e];
+}
+void launch_ep_slots(const Launch &L, uint32_t *ids, int P, int E, const int32_t *table, uint32_t *usage) {
+  if (P == 0) return;
+  KLAUNCH(L, k_ep_slots, (P + 255) / 256, 256, 0, ids, P, E, table, usage);
 }
 
 // the two derived forms of the 8 group sums of a Q8x block that the tensor-core kernels read

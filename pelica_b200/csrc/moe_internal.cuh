@@ -148,6 +148,7 @@ cudaError_t launch_tc_mx(const Launch &L, const LayerDev &ly, bool down, Groups 
                          unsigned long long wait_ns);
 // expert parallelism (kernels_basic.cu): per-rank pair counts, the wire records of a dispatch,
 // the received (expert, weight) records, the derived forms of received Q8x group sums
+void launch_ep_slots(const Launch &L, uint32_t *ids, int P, int E, const int32_t *table, uint32_t *usage);
 void launch_ep_rank_counts(const Launch &L, const uint32_t *cnt, int E, int W, int32_t *out);
 void launch_ep_pack(const Launch &L, int P, int row_bytes, int nd, int nbs, const void *rows, const float *xd,
                     const int32_t *xbs, const uint32_t *pair_token, const uint32_t *pair_src, const uint32_t *ids,

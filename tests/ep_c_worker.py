@@ -42,6 +42,22 @@ def main():
         y = ep.forward(layer, x_all[lo:hi])
     np.save(os.path.join(out_dir, f"y{rank}.npy"), y)
     np.save(os.path.join(out_dir, f"stats{rank}.npy"), np.array(list(ep.last_stats().values()), np.uint64))
+    # a round of usage-driven placement: every rank plans from the same counters (the use of all the
+    # ranks' tokens; the router is replicated), carries out the same swaps, and the outputs do not change
+    ids, _ = layer.route(x_all)
+    usage = np.bincount(ids.ravel(), minlength=cfg.n_exp).astype(np.uint32)
+    pl = pb.Placement(1, cfg.n_exp, world)
+    pl.observe(0, usage)
+    swaps = pl.plan(cfg.expert_bytes(), 1 << 30)
+    for _, a, b in swaps:
+        ep.swap_experts(layer, a, b)
+    assert np.array_equal(ep.get_slots(layer), pl.slots(0))
+    ep.swap_experts(layer, 0, cfg.n_exp - 1)  # and one swap the planner did not ask for, across the ranks
+    y2 = ep.forward(layer, x_all[lo:hi])
+    np.save(os.path.join(out_dir, f"y2_{rank}.npy"), y2)
+    np.save(os.path.join(out_dir, f"swaps{rank}.npy"), np.array(swaps, np.int32).reshape(-1, 3))
+    np.save(os.path.join(out_dir, f"slots{rank}.npy"), ep.get_slots(layer))
+    pl.close()
     ep.close()
     layer.close()
     ctx.close()

@@ -146,4 +146,52 @@ def test_c_abi_two_gpus_match_the_unsharded_layer(ctx, tmp_path, name):
     st = [np.load(tmp_path / f"stats{r}.npy") for r in range(2)]
     assert int(st[0][0]) == int(st[1][1]) and int(st[1][0]) == int(st[0][1])  # rows sent by one = received by the other
     assert int(st[0][0]) > 0
+    # after the placement round (planned swaps plus one forced swap across the ranks): the same bits
+    got2 = np.concatenate([np.load(tmp_path / f"y2_{r}.npy") for r in range(2)])
+    assert bits_equal(got2, want)
+    slots = [np.load(tmp_path / f"slots{r}.npy") for r in range(2)]
+    assert np.array_equal(slots[0], slots[1]) and sorted(slots[0]) == list(range(cfg.n_exp))
+    assert not np.array_equal(slots[0], np.arange(cfg.n_exp))
+    assert np.array_equal(np.load(tmp_path / "swaps0.npy"), np.load(tmp_path / "swaps1.npy"))
     layer.close()
+
+
+
+@pytest.mark.parametrize("name", ["c2", "c3", "c4"])
+def test_slot_table_and_swaps_on_one_rank(ctx, name):
+    """Placement tables (`loc`, src/moe.rs:262-263): weights loaded slot by slot under a random
+    permutation, then experts swapped in place - the outputs and the per-expert use counters are those
+    of the layer that keeps expert e in slot e."""
+    cfg = SMALL[name]
+    W = synth.make_weights(cfg, 93)
+    E = cfg.n_exp
+    ref = pb.MoeLayer(ctx, cfg).load(W)
+    x = synth.make_activations(70, cfg.d, 9)
+    want = ref.forward(x)
+    want_usage = ref.usage()
+    perm = np.random.default_rng(4).permutation(E).astype(np.int32)  # slot of expert e
+    Wp = dict(W)
+    for k in ("gate", "up", "down", "bias_gate", "bias_up", "bias_down"):
+        if k in W:
+            a = np.empty_like(np.asarray(W[k]))
+            a[perm] = np.asarray(W[k])
+            Wp[k] = a
+    layer = pb.MoeLayer(ctx, cfg).load(Wp)
+    ep = pb.ExpertParallel(ctx, pb.ep_unique_id(), 0, 1)
+    ep.set_slots(layer, perm)
+    check = bits_equal if cfg.act_quant == synth.AQ_Q8X_256 else tol_ok
+    assert check(ep.forward(layer, x), want)
+    assert np.array_equal(layer.usage(), want_usage)
+    ep.swap_experts(layer, 1, 5)
+    ep.swap_experts(layer, 5, 2)
+    slots = ep.get_slots(layer)
+    assert sorted(slots) == list(range(E)) and slots[5] == perm[2] and slots[2] == perm[1] and slots[1] == perm[5]
+    assert check(ep.forward(layer, x), want)
+    with pytest.raises(pb.PelicaError) as e:
+        ep.set_slots(layer, np.zeros(E, np.int32))  # not a permutation
+    assert e.value.code == -1
+    ep.set_slots(layer, None)  # expert e in slot e again: the weights are not there, the outputs differ
+    assert not bits_equal(ep.forward(layer, x), want)
+    ep.close()
+    layer.close()
+    ref.close()
