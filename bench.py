@@ -390,7 +390,7 @@ def algorithmic_bytes_per_step(cfg, n_layers, T, distinct_experts_per_layer):
 
 # dram__bytes_read + dram__bytes_write of k_decode_mega in an ncu capture of a 4-layer launch
 # (profiles/k_decode_mega_c2_decode.md), per layer
-NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102217472 + 3546112) // 4
+NCU_DRAM_BYTES_PER_LAYER_C2_DECODE = (102226688 + 4401152) // 4
 
 
 def run_sweep(args, cfg, desc):
