@@ -116,6 +116,7 @@ enum { PM_SHARED_NONE = 0, PM_SHARED_PLAIN = 1, PM_SHARED_SIGMOID_GATED = 2 };
 #define PM_MAX_EXPERTS 512
 #define PM_MAX_TOPK 16
 #define PM_MAX_TOKENS 16384
+#define PM_MAX_D 49152       /* model width: a token's f32 row must fit one SM's shared memory */
 
 /* One MoE FFN layer. Plain data; copy freely. */
 typedef struct pm_layer_desc {

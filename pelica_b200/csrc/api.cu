@@ -87,6 +87,7 @@ struct pm_ctx {
   cudaStream_t stream = nullptr;
   bool own_stream = true;
   int *dev_err = nullptr;   // error word of kernels with bounded waits
+  unsigned int *route_ticket = nullptr;  // [1] zero between launches: the few-token routing kernel's last-CTA ticket
   int tc_min_tokens = 32;   // tensor-core expert products from this many tokens (the reference's TC_MIN, src/moe.rs:35); 0 = never
   int64_t launches = 0;
   int64_t path_count[PM_PATH_N] = {0, 0, 0, 0};  // launches per expert-product path (pelica_moe_diag.h)
@@ -193,6 +194,8 @@ extern "C" int32_t pm_ctx_create(int32_t device, pm_ctx **out) {
   CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   CU(cudaMalloc(&c->dev_err, 4));
   CU(cudaMemset(c->dev_err, 0, 4));
+  CU(cudaMalloc(&c->route_ticket, 4));
+  CU(cudaMemset(c->route_ticket, 0, 4));
   CU(cudaEventCreate(&c->ev0));
   CU(cudaEventCreate(&c->ev1));
   *out = c;
@@ -217,6 +220,8 @@ extern "C" int32_t pm_ctx_create_on_stream(int32_t device, void *stream, pm_ctx 
   c->own_stream = false;
   CU(cudaMalloc(&c->dev_err, 4));
   CU(cudaMemset(c->dev_err, 0, 4));
+  CU(cudaMalloc(&c->route_ticket, 4));
+  CU(cudaMemset(c->route_ticket, 0, 4));
   CU(cudaEventCreate(&c->ev0));
   CU(cudaEventCreate(&c->ev1));
   *out = c;
@@ -231,6 +236,7 @@ extern "C" int32_t pm_ctx_destroy(pm_ctx *c) {
   if (c->stage) cudaFree(c->stage);
   if (c->flush) cudaFree(c->flush);
   if (c->dev_err) cudaFree(c->dev_err);
+  if (c->route_ticket) cudaFree(c->route_ticket);
   for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
@@ -399,6 +405,7 @@ static int32_t wmat_alloc(pm_layer *ly, WMat &W, int type, int n_exp, int rows, 
 static int32_t validate_desc(const pm_layer_desc *D) {
   if (D->d < 32 || D->ff < 32 || D->d % 32 || D->ff % 32)
     return fail(PM_ERR_INVALID, "d and ff must be multiples of 32 (d=%d ff=%d)", D->d, D->ff);
+  if (D->d > PM_MAX_D) return fail(PM_ERR_LIMIT, "d %d above %d", D->d, PM_MAX_D);
   if (D->n_exp < 1 || D->n_exp > PM_MAX_EXPERTS)
     return fail(PM_ERR_LIMIT, "n_exp %d outside 1..%d", D->n_exp, PM_MAX_EXPERTS);
   if (D->top_k < 1 || D->top_k > PM_MAX_TOPK || D->top_k > D->n_exp)
@@ -983,9 +990,14 @@ static int32_t dev_forward(pm_layer *ly, const float *x, int T, float *y, bool a
   pm_ctx *c = ly->ctx;
   const LayerDev &dv = ly->dev;
   Launch L = c->launch();
-  { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
-  { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
-  { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan, c->dev_err); }
+  if (T < PM_SMALL_ROUTE_TOKENS) {  // a few tokens: logits, top-k and plan in one launch
+    PROF(c, PH_ROUTER);
+    launch_route_plan_small(L, dv, x, T, S.logits, S.ids, S.w, S.plan, c->route_ticket);
+  } else {
+    { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
+    { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
+    { PROF(c, PH_PLAN); launch_plan(L, dv, S.ids, T, S.plan, c->dev_err); }
+  }
   TRY(dev_experts(ly, x, T, S, S.w));
   TRY(dev_shared(ly, x, T, S));
   {

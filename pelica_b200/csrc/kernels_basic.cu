@@ -448,6 +448,9 @@ void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, f
     return;
   }
   dim3 grid((E + 7) / 8, T);
+  // (x is staged in d * 4 bytes of dynamic shared memory: beyond 48 KB that needs the opt-in; the
+  // layer descriptor is refused above PM_MAX_D, which fits)
+  if ((size_t)d * 4 > 48 * 1024) cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, d * 4);
   KLAUNCH(L, k_router, grid, 256, (size_t)d * 4, ly.router, ly.logit_bias, x, E, d, logits);
 }
 
@@ -591,6 +594,119 @@ void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T
   if (P > 0) KLAUNCH(L, k_plan_count, (P + 255) / 256, 256, 0, ids, P, E, pl.cnt, pl.pair_pos, err);
   KLAUNCH(L, k_plan_scan, 1, 512, 0, pl, E, ly.usage);
   if (P > 0) KLAUNCH(L, k_plan_place, E, 256, 0, ids, P, K, pl);
+}
+
+// Router logits, top-k and the dispatch plan of a few tokens (T < 8) in ONE launch: the grid of
+// k_router computes the logits; the CTA that finishes last (a ticket counter; nobody waits for
+// anybody) routes every token, one warp each, and builds the plan in shared memory. Six launches of a
+// decode step become one; the values are those of k_router, k_route and k_plan_*.
+#define RS_TOK 8   /* tokens (= warps of the last CTA) */
+__global__ void __launch_bounds__(256) k_route_plan_small(pm_layer_desc D, const float *__restrict__ wr,
+                                                          const float *__restrict__ bias,
+                                                          const float *__restrict__ sel_bias,
+                                                          const float *__restrict__ x, int T, float *logits,
+                                                          uint32_t *ids, float *wout, PlanDev pl, uint32_t *usage,
+                                                          unsigned int *ticket) {
+  extern __shared__ float xs[];  // d floats (the token's row), reused by the last CTA
+  const int E = D.n_exp, d = D.d, K = D.top_k;
+  const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < d; i += 256) xs[i] = x[(size_t)t * d + i];
+  __syncthreads();
+  {
+    const int e = blockIdx.x * 8 + warp;
+    if (e < E) {
+      const float *w = wr + (size_t)e * d;
+      float acc = 0.0f;
+      for (int c = lane; c < d; c += 32) acc = __fmaf_rn(w[c], xs[c], acc);
+      float s = pm_warp_sum_dot(acc);
+      if (lane == 0) {
+        if (bias) s = __fadd_rn(s, bias[e]);
+        logits[(size_t)t * E + e] = s;
+      }
+    }
+  }
+  __shared__ unsigned int s_last;
+  __threadfence();  // this CTA's logits before its ticket
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1 ? 1u : 0u;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid == 0) *ticket = 0;  // ready for the next launch (graph replays included)
+
+  // ---- the last CTA: top-k per token (warp = token) ----
+  __shared__ float sm_lg[RS_TOK][PM_MAX_EXPERTS];
+  __shared__ float sm_sv[RS_TOK][PM_MAX_EXPERTS];
+  __shared__ float sm_gs[RS_TOK][PM_MAX_EXPERTS / 2];
+  __shared__ unsigned char sm_keep[RS_TOK][PM_MAX_EXPERTS / 2];
+  __shared__ uint32_t s_ids[RS_TOK * PM_MAX_TOPK];
+  __shared__ uint32_t s_cnt[PM_MAX_EXPERTS], s_base[PM_MAX_EXPERTS], s_act[PM_MAX_EXPERTS];
+  if (warp < T) {
+    for (int e = lane; e < E; e += 32) sm_lg[warp][e] = __ldcg(logits + (size_t)warp * E + e);
+    __syncwarp();
+    pm_route_warp(D, sm_lg[warp], sel_bias, lane, sm_sv[warp], sm_gs[warp], sm_keep[warp], ids + (size_t)warp * K,
+                  wout + (size_t)warp * K);
+    __syncwarp();
+  }
+  for (int e = tid; e < PM_MAX_EXPERTS; e += 256) s_cnt[e] = 0;
+  __syncthreads();
+  // ---- the plan of the P = T * K pairs (src/moe_kernels.rs:1083-1129 layout) ----
+  const int P = T * K;
+  if (tid < P) {
+    s_ids[tid] = ids[tid];  // written by this CTA's warps above
+    atomicAdd(&s_cnt[s_ids[tid]], 1u);
+  }
+  __syncthreads();
+  if (tid == 0) {  // E <= 512 counts: one thread's pass is shorter than a scan's barriers
+    uint32_t o = 0, na = 0;
+    for (int e = 0; e < E; e++) {
+      const uint32_t c = s_cnt[e];
+      s_base[e] = o;
+      pl.base[e] = o;
+      pl.cnt[e] = c;
+      if (c) {
+        pl.active[na] = (uint32_t)e;
+        pl.offset[na] = o;
+        pl.count[na] = c;
+        if (usage) usage[e] += c;
+        na++;
+      }
+      o += c;
+    }
+    s_act[0] = na;
+    *pl.n_active = (int)na;
+  }
+  __syncthreads();
+  for (int e = (int)s_act[0] + tid; e < E; e += 256) {
+    pl.active[e] = 0;
+    pl.offset[e] = 0;
+    pl.count[e] = 0;
+  }
+  if (tid < P) {  // stable: a pair goes behind the earlier pairs of its expert
+    const uint32_t e = s_ids[tid];
+    uint32_t before = 0;
+    for (int j = 0; j < tid; j++) before += s_ids[j] == e;
+    const uint32_t p = s_base[e] + before;
+    pl.pair_pos[tid] = p;
+    pl.pair_token[p] = (uint32_t)(tid / K);
+    pl.pair_src[p] = (uint32_t)tid;
+  }
+}
+
+// T < 8 tokens; ticket: a zeroed word of the context
+void launch_route_plan_small(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits, uint32_t *ids,
+                             float *w, PlanDev pl, unsigned int *ticket) {
+  const int E = ly.desc.n_exp, d = ly.desc.d;
+  dim3 grid((E + 7) / 8, T);
+  // (its static arrays take most of the 48 KB a kernel gets without asking; the attribute is raised on
+  // a layer's first call, which is never inside a stream capture)
+  static int smem_set = 0;
+  if (d * 4 > smem_set) {
+    cudaFuncSetAttribute(k_route_plan_small, cudaFuncAttributeMaxDynamicSharedMemorySize, d * 4);
+    smem_set = d * 4;
+  }
+  KLAUNCH(L, k_route_plan_small, grid, 256, (size_t)d * 4, ly.desc, ly.router, ly.logit_bias, ly.select_bias, x, T, logits,
+          ids, w, pl, ly.usage, ticket);
 }
 
 __global__ void k_iota(uint32_t *p, uint32_t n) {

@@ -122,6 +122,11 @@ void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int 
                   float *w);
 // err: the context's error word (an expert id outside the layer is reported there, never used)
 void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev plan, int *err);
+// router + top-k + plan of T < PM_SMALL_ROUTE_TOKENS tokens in one launch (ticket: a zeroed word the
+// kernel leaves zeroed)
+#define PM_SMALL_ROUTE_TOKENS 8
+void launch_route_plan_small(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits, uint32_t *ids,
+                             float *w, PlanDev pl, unsigned int *ticket);
 void launch_iota(const Launch &L, uint32_t *p, uint32_t n);
 void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
                    const float *x, const int8_t *xq, const float *xd, const int32_t *xbsum,

@@ -37,6 +37,8 @@ ROUTE_CASES = {
                                           shared=0),
     "q4x-16-of-512": synth.C2_QWEN3.scaled(gating=synth.GATE_SOFTMAX_SELECTED, n_exp=512, top_k=16, d=1024),
     "ragged-experts": synth.C2_QWEN3.scaled(n_exp=77, top_k=5, d=256),
+    # a token's row beyond the 48 KB a kernel gets without asking: the few-token router stages it whole
+    "wide-16384": synth.C2_QWEN3.scaled(n_exp=24, top_k=4, d=16384, ff=256),
 }
 
 
@@ -142,3 +144,9 @@ def test_bf16_router_weights(ctx, oracle):
         ids_g, w_g = gl.route(x)
         assert np.array_equal(ids_g, ids_o) and bits_equal(w_g, w_o)
     gl.close()
+
+
+def test_width_limit(ctx):
+    with pytest.raises(pb.PelicaError) as e:
+        pb.MoeLayer(ctx, synth.C2_QWEN3.scaled(n_exp=8, top_k=2, d=65536, ff=256))
+    assert e.value.code == -7
