@@ -194,7 +194,8 @@ def ep_measure(pb, ctx, dist, world, rank, local, cfg, n_layers, T, steps, warmu
     d = cfg.d
     POOL = 4
     rng = np.random.default_rng(SEED + rank)
-    pool = [ctx.alloc(max(Tl, 1) * d * 4).upload(rng.normal(0, 1, (max(Tl, 1), d)).astype(np.float32)) for _ in range(POOL)]
+    host_pool = [rng.normal(0, 1, (max(Tl, 1), d)).astype(np.float32) for _ in range(POOL)]
+    pool = [ctx.alloc(max(Tl, 1) * d * 4).upload(h) for h in host_pool]
     xb = ctx.alloc(max(Tl, 1) * d * 4)
     xn = ctx.alloc(max(Tl, 1) * d * 4)
     lib = ctx.lib
@@ -239,13 +240,16 @@ def ep_measure(pb, ctx, dist, world, rank, local, cfg, n_layers, T, steps, warmu
         hit = t.cpu().numpy()
     distinct = int(hit.sum())  # (layer, expert) pairs read in a step
     # end to end: host tokens in, host result out, every step
-    hx = ctx.pinned((max(Tl, 1), d))
+    hxs = []  # the tokens of the device-resident run, in pinned memory: the same routing
+    for h in host_pool:
+        p = ctx.pinned((max(Tl, 1), d))
+        p[:] = h
+        hxs.append(p)
     hy = ctx.pinned((max(Tl, 1), d))
-    hx[:] = 0.5
     barrier()
     t0 = time.perf_counter()
     for i in range(steps):
-        step(hx.ctypes.data)
+        step(hxs[(warmup + i) % POOL].ctypes.data)
         pb._check(lib.pm_copy(ctx.h, hy.ctypes.data, xb.ptr, max(Tl, 1) * d * 4))
     e2e_ms = (time.perf_counter() - t0) / steps * 1e3
     barrier()

@@ -992,7 +992,7 @@ static int32_t dev_forward(pm_layer *ly, const float *x, int T, float *y, bool a
   Launch L = c->launch();
   if (T < PM_SMALL_ROUTE_TOKENS) {  // a few tokens: logits, top-k and plan in one launch
     PROF(c, PH_ROUTER);
-    launch_route_plan_small(L, dv, x, T, S.logits, S.ids, S.w, S.plan, c->route_ticket);
+    launch_route_plan_small(L, dv, x, T, S.logits, S.ids, S.w, S.plan, nullptr, c->route_ticket);
   } else {
     { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
     { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
@@ -2081,11 +2081,16 @@ extern "C" int32_t pm_moe_forward_ep(pm_ep *ep, pm_layer *ly, const float *x, in
   float *sd = ws_take<float>(c, P * (size_t)(nd + 1));
   int32_t *sbs = ws_take<int32_t>(c, P * (size_t)(nbs + 1));
   uint32_t *smeta = ws_take<uint32_t>(c, P * 2);
-  if (T > 0) {
-    { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
-    { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
-  }
-  {
+  if (T > 0 && T < PM_SMALL_ROUTE_TOKENS) {  // a few tokens: logits, top-k, (slots) and plan in one launch
+    auto st = ep->slots.find(ly);
+    PROF(c, PH_ROUTER);
+    launch_route_plan_small(L, dv, x, T, S.logits, S.ids, S.w, S.plan, st != ep->slots.end() ? st->second.dev : nullptr,
+                            c->route_ticket);
+  } else {
+    if (T > 0) {
+      { PROF(c, PH_ROUTER); launch_router(L, dv, x, T, S.logits); }
+      { PROF(c, PH_ROUTE); launch_route(L, dv, S.logits, T, S.ids, S.w); }
+    }
     // with a placement table everything from here on names slots: the plan groups by slot, a pair goes
     // to the rank of its slot, the serving rank indexes its planes by slot
     auto st = ep->slots.find(ly);

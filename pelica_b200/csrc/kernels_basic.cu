@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(256) k_route_plan_small(pm_layer_desc D, const
                                                           const float *__restrict__ sel_bias,
                                                           const float *__restrict__ x, int T, float *logits,
                                                           uint32_t *ids, float *wout, PlanDev pl, uint32_t *usage,
-                                                          unsigned int *ticket) {
+                                                          const int32_t *__restrict__ slot_table, unsigned int *ticket) {
   extern __shared__ float xs[];  // d floats (the token's row), reused by the last CTA
   const int E = D.n_exp, d = D.d, K = D.top_k;
   const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -653,8 +653,14 @@ __global__ void __launch_bounds__(256) k_route_plan_small(pm_layer_desc D, const
   // ---- the plan of the P = T * K pairs (src/moe_kernels.rs:1083-1129 layout) ----
   const int P = T * K;
   if (tid < P) {
-    s_ids[tid] = ids[tid];  // written by this CTA's warps above
-    atomicAdd(&s_cnt[s_ids[tid]], 1u);
+    uint32_t e = ids[tid];  // written by this CTA's warps above
+    if (slot_table) {  // a placement table: everything from here on names slots; use is counted by expert
+      if (usage) atomicAdd(&usage[e], 1u);
+      e = (uint32_t)slot_table[e];
+      ids[tid] = e;
+    }
+    s_ids[tid] = e;
+    atomicAdd(&s_cnt[e], 1u);
   }
   __syncthreads();
   if (tid == 0) {  // E <= 512 counts: one thread's pass is shorter than a scan's barriers
@@ -668,7 +674,7 @@ __global__ void __launch_bounds__(256) k_route_plan_small(pm_layer_desc D, const
         pl.active[na] = (uint32_t)e;
         pl.offset[na] = o;
         pl.count[na] = c;
-        if (usage) usage[e] += c;
+        if (usage && !slot_table) usage[e] += c;
         na++;
       }
       o += c;
@@ -695,7 +701,7 @@ __global__ void __launch_bounds__(256) k_route_plan_small(pm_layer_desc D, const
 
 // T < 8 tokens; ticket: a zeroed word of the context
 void launch_route_plan_small(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits, uint32_t *ids,
-                             float *w, PlanDev pl, unsigned int *ticket) {
+                             float *w, PlanDev pl, const int32_t *slot_table, unsigned int *ticket) {
   const int E = ly.desc.n_exp, d = ly.desc.d;
   dim3 grid((E + 7) / 8, T);
   // (its static arrays take most of the 48 KB a kernel gets without asking; the attribute is raised on
@@ -706,7 +712,7 @@ void launch_route_plan_small(const Launch &L, const LayerDev &ly, const float *x
     smem_set = d * 4;
   }
   KLAUNCH(L, k_route_plan_small, grid, 256, (size_t)d * 4, ly.desc, ly.router, ly.logit_bias, ly.select_bias, x, T, logits,
-          ids, w, pl, ly.usage, ticket);
+          ids, w, pl, ly.usage, slot_table, ticket);
 }
 
 __global__ void k_iota(uint32_t *p, uint32_t n) {

@@ -123,10 +123,10 @@ void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int 
 // err: the context's error word (an expert id outside the layer is reported there, never used)
 void launch_plan(const Launch &L, const LayerDev &ly, const uint32_t *ids, int T, PlanDev plan, int *err);
 // router + top-k + plan of T < PM_SMALL_ROUTE_TOKENS tokens in one launch (ticket: a zeroed word the
-// kernel leaves zeroed)
+// kernel leaves zeroed; slot_table: expert -> slot of an expert-parallel placement, or null)
 #define PM_SMALL_ROUTE_TOKENS 8
 void launch_route_plan_small(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits, uint32_t *ids,
-                             float *w, PlanDev pl, unsigned int *ticket);
+                             float *w, PlanDev pl, const int32_t *slot_table, unsigned int *ticket);
 void launch_iota(const Launch &L, uint32_t *p, uint32_t n);
 void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
                    const float *x, const int8_t *xq, const float *xd, const int32_t *xbsum,

@@ -182,6 +182,9 @@ def test_slot_table_and_swaps_on_one_rank(ctx, name):
     check = bits_equal if cfg.act_quant == synth.AQ_Q8X_256 else tol_ok
     assert check(ep.forward(layer, x), want)
     assert np.array_equal(layer.usage(), want_usage)
+    x3 = synth.make_activations(3, cfg.d, 10)  # a few tokens: the one-launch routing applies the table itself
+    assert check(ep.forward(layer, x3), ref.forward(x3))
+    assert np.array_equal(layer.usage(), ref.usage())
     ep.swap_experts(layer, 1, 5)
     ep.swap_experts(layer, 5, 2)
     slots = ep.get_slots(layer)
