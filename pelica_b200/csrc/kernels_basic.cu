@@ -780,6 +780,79 @@ __device__ __forceinline__ float row_q4k_q8x(const uint8_t *__restrict__ rowp, i
   return total;
 }
 
+// Two Q4_K rows against the same Q8x activations (a gate row and its up row, or two down rows): the
+// loads of both rows leave together and the activations are read once, so a warp keeps twice the
+// weight bytes in flight; per row the same operations in the same order as row_q4k_q8x.
+__device__ __forceinline__ void rows2_q4k_q8x(const uint8_t *__restrict__ rowA, const uint8_t *__restrict__ rowB,
+                                              int nb, const int8_t *__restrict__ xq, const float *__restrict__ xd,
+                                              const int32_t *__restrict__ xbsum, int lane, float &outA, float &outB) {
+  float totA = 0.0f, totB = 0.0f;
+  const int nchunks = nb * 4;
+  const uint32_t M = 0x0f0f0f0fu;
+  for (int c0 = 0; c0 < nchunks; c0 += 32) {
+    const int ci = c0 + lane;
+    const bool valid = ci < nchunks;
+    const int b = ci >> 2, c = ci & 3;
+    int piA = 0, pmA = 0, piB = 0, pmB = 0;
+    float ddA = 0.0f, dmA = 0.0f, ddB = 0.0f, dmB = 0.0f;
+    if (valid) {
+      const uint8_t *ba = rowA + (size_t)b * 144, *bb = rowB + (size_t)b * 144;
+      const uint4 ha = __ldg((const uint4 *)ba), hb = __ldg((const uint4 *)bb);
+      const uint4 *qa = (const uint4 *)(ba + 16 + 32 * c), *qb = (const uint4 *)(bb + 16 + 32 * c);
+      const uint4 a0 = __ldg(qa), a1 = __ldg(qa + 1), b0 = __ldg(qb), b1 = __ldg(qb + 1);
+      const int4 *xp = (const int4 *)(xq + (size_t)b * 256 + 64 * c);
+      const int4 xl0 = xp[0], xl1 = xp[1], xh0 = xp[2], xh1 = xp[3];
+      const int s0 = xbsum[b * 8 + 2 * c], s1 = xbsum[b * 8 + 2 * c + 1];
+      const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const int xl[8] = {xl0.x, xl0.y, xl0.z, xl0.w, xl1.x, xl1.y, xl1.z, xl1.w};
+      const int xh[8] = {xh0.x, xh0.y, xh0.z, xh0.w, xh1.x, xh1.y, xh1.z, xh1.w};
+      int loA = 0, hiA = 0, loB = 0, hiB = 0;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        loA = __dp4a((int)(wa[i] & M), xl[i], loA);
+        hiA = __dp4a((int)((wa[i] >> 4) & M), xh[i], hiA);
+        loB = __dp4a((int)(wb[i] & M), xl[i], loB);
+        hiB = __dp4a((int)((wb[i] >> 4) & M), xh[i], hiB);
+      }
+      int sc0, m0, sc1, m1;
+      pm_q4k_scmin(ha.y, ha.z, ha.w, 2 * c, sc0, m0);
+      pm_q4k_scmin(ha.y, ha.z, ha.w, 2 * c + 1, sc1, m1);
+      piA = sc0 * loA + sc1 * hiA;
+      pmA = m0 * s0 + m1 * s1;
+      pm_q4k_scmin(hb.y, hb.z, hb.w, 2 * c, sc0, m0);
+      pm_q4k_scmin(hb.y, hb.z, hb.w, 2 * c + 1, sc1, m1);
+      piB = sc0 * loB + sc1 * hiB;
+      pmB = m0 * s0 + m1 * s1;
+      ddA = pm_f16(ha.x);
+      dmA = pm_f16(ha.x >> 16);
+      ddB = pm_f16(hb.x);
+      dmB = pm_f16(hb.x >> 16);
+    }
+    piA += __shfl_xor_sync(PM_FULL, piA, 1);
+    pmA += __shfl_xor_sync(PM_FULL, pmA, 1);
+    piB += __shfl_xor_sync(PM_FULL, piB, 1);
+    pmB += __shfl_xor_sync(PM_FULL, pmB, 1);
+    piA += __shfl_xor_sync(PM_FULL, piA, 2);
+    pmA += __shfl_xor_sync(PM_FULL, pmA, 2);
+    piB += __shfl_xor_sync(PM_FULL, piB, 2);
+    pmB += __shfl_xor_sync(PM_FULL, pmB, 2);
+    float tA = 0.0f, tB = 0.0f;
+    if (valid) {
+      const float x = xd[b];
+      tA = __fmul_rn(x, __fsub_rn(__fmul_rn(ddA, (float)piA), __fmul_rn(dmA, (float)pmA)));
+      tB = __fmul_rn(x, __fsub_rn(__fmul_rn(ddB, (float)piB), __fmul_rn(dmB, (float)pmB)));
+    }
+    const int nblk = min(8, nb - (c0 >> 2));
+    for (int j = 0; j < nblk; j++) {
+      totA = __fadd_rn(totA, __shfl_sync(PM_FULL, tA, 4 * j));
+      totB = __fadd_rn(totB, __shfl_sync(PM_FULL, tB, 4 * j));
+    }
+  }
+  outA = totA;
+  outB = totB;
+}
+
 // Q6_K row . Q8x activations (planes of this row given). Per block
 // isum = sum_k sc[k] * sum_16 (q-32)*xq, term = x.d[b]*(d*isum), block order.
 __device__ __forceinline__ float row_q6k_q8x(const uint8_t *__restrict__ ql,
@@ -1119,7 +1192,7 @@ __global__ void __launch_bounds__(256) k_down_mx(LayerDev ly, Groups g, const fl
 // grouped gate/up + activation, grouped down
 // ===========================================================================
 // grid (rows/8, groups); one warp per output row, looping over the group's pairs
-__global__ void __launch_bounds__(256) k_gateup(LayerDev ly, int shared, Groups g,
+__global__ void __launch_bounds__(256, 3) k_gateup(LayerDev ly, int shared, Groups g,
                                                 const float *__restrict__ x,
                                                 const int8_t *__restrict__ xq,
                                                 const float *__restrict__ xd,
@@ -1154,8 +1227,13 @@ __global__ void __launch_bounds__(256) k_gateup(LayerDev ly, int shared, Groups 
       const int8_t *q = xq + (size_t)t * d;
       const float *qd = xd + (size_t)t * nbx;
       const int32_t *qb = xbsum + (size_t)t * nbx * 8;
-      gv = row_q8x(G, el, r, q, qd, qb, lane);
-      uv = row_q8x(U, el, r, q, qd, qb, lane);
+      if (G.type == PM_TYPE_Q4_K && U.type == PM_TYPE_Q4_K) {
+        rows2_q4k_q8x(G.plane[0] + (size_t)el * G.stride[0] + (size_t)r * nbx * 144,
+                      U.plane[0] + (size_t)el * U.stride[0] + (size_t)r * nbx * 144, nbx, q, qd, qb, lane, gv, uv);
+      } else {
+        gv = row_q8x(G, el, r, q, qd, qb, lane);
+        uv = row_q8x(U, el, r, q, qd, qb, lane);
+      }
     } else if (D.act_quant == PM_AQ_Q8_32) {
       const int8_t *q = xq + (size_t)t * d;
       const float *qd = xd + (size_t)t * (d / 32);
@@ -1216,6 +1294,41 @@ __global__ void __launch_bounds__(256) k_down(LayerDev ly, int shared, Groups g,
   }
 }
 
+// down for Q4_K experts and Q8x hidden vectors: a warp takes two consecutive output rows
+// (rows2_q4k_q8x); grid (ceil(d / 16), groups)
+__global__ void __launch_bounds__(256, 3) k_down_q4k2(LayerDev ly, int shared, Groups g, const int8_t *__restrict__ hq,
+                                                      const float *__restrict__ hd, const int32_t *__restrict__ hbsum,
+                                                      float *eo) {
+  int a = blockIdx.y;
+  if (a >= *g.n_groups) return;
+  const WMat &Dn = shared ? ly.sdown : ly.down;
+  const int d = Dn.rows, ff = Dn.cols, nbh = ff / 256;
+  const int lane = threadIdx.x & 31;
+  const int r = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
+  if (r >= d) return;
+  const int r1 = min(r + 1, d - 1);
+  const int el = shared ? 0 : (int)g.expert[a] - ly.first_local;
+  const uint32_t off = g.offset[a], cnt = g.count[a];
+  if (el < 0 || el >= (shared ? 1 : ly.n_local)) {  // not held here: zeros
+    if (lane < 2 && r + lane < d)
+      for (uint32_t i = 0; i < cnt; i++) eo[(size_t)(off + i) * d + r + lane] = 0.0f;
+    return;
+  }
+  const uint8_t *base = Dn.plane[0] + (size_t)el * Dn.stride[0];
+  const uint8_t *rowA = base + (size_t)r * nbh * 144, *rowB = base + (size_t)r1 * nbh * 144;
+  const bool bias = !shared && ly.bias_down;
+  for (uint32_t i = 0; i < cnt; i++) {
+    const size_t p = off + i;
+    float oA, oB;
+    rows2_q4k_q8x(rowA, rowB, nbh, hq + p * ff, hd + p * nbh, hbsum + p * nbh * 8, lane, oA, oB);
+    if (lane < 2 && r + lane < d) {
+      float o = lane ? oB : oA;
+      if (bias) o = __fadd_rn(o, ly.bias_down[(size_t)el * d + r + lane]);  // src/oss_batch.rs:89
+      eo[p * d + r + lane] = o;
+    }
+  }
+}
+
 void launch_gateup(const Launch &L, const LayerDev &ly, bool shared, Groups g, int n_pairs,
                    const float *x, const int8_t *xq, const float *xd, const int32_t *xbsum,
                    const float *w, float *h) {
@@ -1237,6 +1350,11 @@ void launch_down(const Launch &L, const LayerDev &ly, bool shared, Groups g, int
   if (!shared && ly.desc.act_quant == PM_AQ_F32 && ly.down.type == PM_TYPE_MXFP4) {
     dim3 grid((d + 31) / 32, min(g.max_groups, n_pairs));
     KLAUNCH(L, k_down_mx, grid, 256, 0, ly, g, h, eo);
+    return;
+  }
+  if (ly.desc.act_quant == PM_AQ_Q8X_256 && (shared ? ly.sdown : ly.down).type == PM_TYPE_Q4_K) {
+    dim3 grid((d + 15) / 16, min(g.max_groups, n_pairs));
+    KLAUNCH(L, k_down_q4k2, grid, 256, 0, ly, (int)shared, g, hq, hd, hbsum, eo);
     return;
   }
   dim3 grid((d + 7) / 8, min(g.max_groups, n_pairs));
