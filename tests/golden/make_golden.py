@@ -5,7 +5,7 @@ is built and its tests store no expected numbers for this path, so these
 fixtures freeze the oracle's own outputs on seeded inputs: they pin the oracle
 against drift and give the CUDA path fixed vectors to hit.
 
-    python -m tests.golden.make_golden
+    python -m tests.golden.make_golden [names ...]     (default: every fixture)
 """
 import os
 import sys
@@ -25,12 +25,15 @@ SHAPES = {
     "c3": synth.C3_GPTOSS.scaled(d=96, ff=64, n_exp=6, top_k=2),
     "c4": synth.C4_DSV3.scaled(d=256, ff=256, n_exp=16, top_k=4, n_group=4, topk_group=2, shared_ff=256),
     "c6": synth.C6_Q8_0.scaled(d=160, ff=96, n_exp=8, top_k=2),
+    "c9": synth.C9_IQ3S.scaled(d=256, ff=96, n_exp=8, top_k=2),
+    "c10": synth.C10_Q5K.scaled(d=256, ff=256, n_exp=8, top_k=2),
+    "c11": synth.C11_GLM.scaled(d=256, ff=128, n_exp=8, top_k=2, shared_ff=128),
 }
 
 
 def case(name):
     cfg = SHAPES[name]
-    seed = {"c1": 101, "c2": 102, "c3": 103, "c4": 104, "c6": 106}[name]
+    seed = {"c1": 101, "c2": 102, "c3": 103, "c4": 104, "c6": 106, "c9": 109, "c10": 110, "c11": 111}[name]
     W = synth.make_weights(cfg, seed)
     x = synth.make_activations(5, cfg.d, seed + 1000)
     return cfg, W, x
@@ -39,7 +42,7 @@ def case(name):
 def main():
     from oracle import pelica_oracle as po
 
-    for name in SHAPES:
+    for name in (sys.argv[1:] or SHAPES):
         cfg, W, x = case(name)
         L = po.Layer(po.LayerDesc(**cfg.desc_fields()), W)
         ids, w = L.route(x)

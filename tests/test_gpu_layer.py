@@ -141,7 +141,7 @@ def test_usage_counters(ctx, oracle):
     gl.close()
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c9", "c10", "c11"])
 def test_golden_fixtures(ctx, name):
     """The committed vectors (tests/golden), no oracle involved."""
     from tests.golden.make_golden import case

@@ -219,7 +219,7 @@ def test_fast_layer_matches_canonical(oracle):
     assert np.abs(y - yf).max() <= 1e-3 * np.abs(y).max()
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c9", "c10", "c11"])
 def test_golden_layer_outputs(oracle, name):
     """The committed fixtures (tests/golden/make_golden.py) pin the oracle itself."""
     from tests.golden.make_golden import case
@@ -264,3 +264,52 @@ def test_int4_container_rows(oracle):
         got = oracle.row_f32(synth.GLM_Q4, one_row, cols, x)
         assert abs(got - float(deq[o].astype(np.float64) @ x.astype(np.float64))) < 1e-4
         assert abs(got - float(w[o] @ x)) < 0.2
+
+
+def test_q5k_and_iq3s_known_answers(oracle):
+    # Q5_K (src/moe_kernels.rs:74): d = 1.0, dmin = 0.5; sub-block 5 (c = 2, high nibbles): sc 33, m 17;
+    # value 163 = 64*2 + 32 + 3: nibble 0xA of qs byte 32*2 + 3, fifth bit = bit 2*2+1 of qh byte 3
+    blk = np.zeros(176, np.uint8)
+    blk[0:2] = [0x00, 0x3C]
+    blk[2:4] = [0x00, 0x38]
+    s = blk[4:16]
+    s[0], s[4] = 3, 2
+    s[1] = (33 >> 4) << 6
+    s[5] = (17 >> 4) << 6
+    s[9] = (33 & 15) | ((17 & 15) << 4)
+    blk[48 + 64 + 3] = 0xA0
+    blk[16 + 3] = 1 << 5
+    blk[48 + 0] = 0x07              # value 0: nibble 7, no fifth bit (sub-block 0: sc 3, m 2)
+    blk[16 + 1] = 1 << 0            # value 1: fifth bit only -> 16
+    out = oracle.dequant(synth.Q5_K, blk, 256)
+    assert out[163] == 1.0 * 33 * (0xA | 16) - 0.5 * 17
+    assert out[0] == 1.0 * 3 * 7 - 0.5 * 2
+    assert out[1] == 1.0 * 3 * 16 - 0.5 * 2
+    # IQ3_S (src/q4x_cpu.rs:64-82): d = 0.5; sub-block 3: scale nibble 6 -> 1 + 2*6 = 13; its group 2 (values
+    # 8..11 of the sub-block) takes codebook entry 0x100 | 0x2A with the ninth bit from qh; signs byte 4*3 + 1
+    grid = synth.iq3s_grid()
+    blk = np.zeros(110, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(0.5).tobytes(), np.uint8)
+    blk[2 + 8 * 3 + 2] = 0x2A
+    blk[66 + 3] = 1 << 2
+    blk[74 + 4 * 3 + 1] = 0b00000101   # values 8 and 10 of the sub-block negative
+    blk[106 + 1] = 6 << 4              # sub-block 3 = high nibble of scales byte 1
+    out = oracle.dequant(synth.IQ3_S, blk, 256)
+    mags = grid[0x12A]
+    want = [-mags[0], mags[1], -mags[2], mags[3]]
+    assert [float(v) for v in out[96 + 8:96 + 12]] == [0.5 * 13 * m for m in want]
+    # every other value of the block: entry 0 of the codebook, scale 1, positive
+    assert float(out[0]) == 0.5 * 1 * grid[0][0] and float(out[255]) == 0.5 * 1 * grid[0][3]
+    # and the row against 32-block activations follows the same decode (src/q4x_cpu.rs:118-127)
+    rng = np.random.default_rng(9)
+    w = rng.integers(0, 256, 3 * 110, dtype=np.uint8)
+    w[0::110], w[1::110] = 0x00, 0x2C
+    x = rng.normal(0, 1, 768).astype(np.float32)
+    q, d = oracle.q8_32(x)
+    deq = oracle.dequant(synth.IQ3_S, w, 768).astype(np.float64)
+    want_row = float(deq @ (q.astype(np.float64) * np.repeat(d, 32)))
+    assert abs(oracle.row_iq3s(w, 768, q, d) - want_row) <= 1e-3 * max(abs(want_row), 1.0)
+    # the codebook itself: 512 distinct entries of odd magnitudes 1..15, first and last as the format has them
+    assert grid.shape == (512, 4) and len({tuple(g) for g in grid}) == 512
+    assert set(np.unique(grid)) <= set(range(1, 16, 2))
+    assert tuple(grid[0]) == (1, 1, 1, 1) and tuple(grid[1]) == (3, 1, 1, 1)
