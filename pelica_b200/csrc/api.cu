@@ -107,7 +107,8 @@ struct pm_ctx {
   std::vector<cudaEvent_t> prof_ev;
   size_t prof_used = 0;
   std::vector<int> prof_phase;  // phase of event pair i
-  Launch launch() { return Launch{stream, &launches}; }
+  int n_sm = 148;  // SMs of the device
+  Launch launch() { return Launch{stream, &launches, n_sm}; }
 };
 
 enum { PH_ROUTER = 0, PH_ROUTE, PH_PLAN, PH_QUANT_X, PH_GATEUP, PH_QUANT_H, PH_DOWN, PH_SHARED,
@@ -191,6 +192,7 @@ extern "C" int32_t pm_ctx_create(int32_t device, pm_ctx **out) {
   pm_ctx *c = new (std::nothrow) pm_ctx();
   if (!c) return fail(PM_ERR_OOM, "pm_ctx_create: host allocation");
   c->device = device;
+  CU(cudaDeviceGetAttribute(&c->n_sm, cudaDevAttrMultiProcessorCount, device));
   CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   CU(cudaMalloc(&c->dev_err, 4));
   CU(cudaMemset(c->dev_err, 0, 4));
@@ -216,6 +218,7 @@ extern "C" int32_t pm_ctx_create_on_stream(int32_t device, void *stream, pm_ctx 
   pm_ctx *c = new (std::nothrow) pm_ctx();
   if (!c) return fail(PM_ERR_OOM, "host allocation");
   c->device = device;
+  CU(cudaDeviceGetAttribute(&c->n_sm, cudaDevAttrMultiProcessorCount, device));
   c->stream = (cudaStream_t)stream;
   c->own_stream = false;
   CU(cudaMalloc(&c->dev_err, 4));

@@ -392,6 +392,10 @@ __global__ void __launch_bounds__(256) k_router(const float *__restrict__ wr,
 #define RT_TOK 8
 #define RT_EXP 8
 #define RT_CH 512
+// UNROLL: columns whose router loads are in flight together. 4 costs 141 registers (one CTA an SM):
+// worth it only while the grid does not fill the SMs anyway (a 512-token call on 128 experts is 128
+// CTAs, each waiting for an L2 round trip per column otherwise).
+template <int UNROLL>
 __global__ void __launch_bounds__(256) k_router_tile(const float *__restrict__ wr,
                                                      const float *__restrict__ bias,
                                                      const float *__restrict__ x, int T, int E, int d,
@@ -413,6 +417,7 @@ __global__ void __launch_bounds__(256) k_router_tile(const float *__restrict__ w
     }
     __syncthreads();
     if (e0 < E) {
+#pragma unroll UNROLL
       for (int c = lane; c < n; c += 32) {
         float w[RT_EXP], xv[RT_TOK];
 #pragma unroll
@@ -444,7 +449,8 @@ void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, f
   int E = ly.desc.n_exp, d = ly.desc.d;
   if (T >= RT_TOK) {
     dim3 grid((E + 8 * RT_EXP - 1) / (8 * RT_EXP), (T + RT_TOK - 1) / RT_TOK);
-    KLAUNCH(L, k_router_tile, grid, 256, 0, ly.router, ly.logit_bias, x, T, E, d, logits);
+    if ((int)(grid.x * grid.y) <= L.n_sm) KLAUNCH(L, k_router_tile<4>, grid, 256, 0, ly.router, ly.logit_bias, x, T, E, d, logits);
+    else KLAUNCH(L, k_router_tile<1>, grid, 256, 0, ly.router, ly.logit_bias, x, T, E, d, logits);
     return;
   }
   dim3 grid((E + 7) / 8, T);

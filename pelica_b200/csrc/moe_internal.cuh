@@ -103,6 +103,7 @@ static inline size_t wmat_plane_bytes(int type, int rows, int cols, int p) {
 struct Launch {
   cudaStream_t stream;
   int64_t *count;  // kernels launched
+  int n_sm = 148;  // SMs of the device
 };
 
 void launch_repack(const Launch &L, int type, const uint8_t *raw, size_t n_blocks, uint8_t *p0,
