@@ -158,14 +158,14 @@ int tc_max_tiles(int n_pairs, int max_groups);
 #ifdef PM_TC_TRACE
 __device__ unsigned long long g_tc_trace[3 * 32 * 8];
 #define TC_STAMP(b, i)                                                                         \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 511) && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
+  if (blockIdx.x == 0 && tc_trace_item && (tid == 0 || tid == 511) && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
     g_tc_trace[((tid ? 1 : 0) * 32 + (b)) * 8 + (i)] = clock64();
 extern "C" __attribute__((visibility("default"))) int pm_debug_tc_trace(unsigned long long *out) {
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));
 }
 // the issuing warp's lane 0: section 2
 #define TC_STAMP_M(b, i)                                                                       \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && (tid & 31) == 0 && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
+  if (blockIdx.x == 0 && tc_trace_item && (tid & 31) == 0 && (b) < 32 && A.down + 1 == PM_TC_TRACE) \
     g_tc_trace[(2 * 32 + (b)) * 8 + (i)] = clock64();
 #else
 #define TC_STAMP(b, i)
@@ -187,6 +187,7 @@ struct TcArgs {
   const uint32_t *tile_group;  // [tiles] index into the groups
   const uint32_t *tile_n0;     // [tiles] first token of the tile inside its group
   const uint32_t *tile_r0;     // [tiles] row of that token among the records' rows (a multiple of 16)
+  int row_tiles;               // tiles of rows of the matrix (128 rows, or 64 gate + 64 up)
 };
 
 // The (group, token tile) list of a grouping: group a contributes ceil(count/128)
@@ -297,38 +298,56 @@ __global__ void __launch_bounds__(256) k_tc_rows(Groups g, const uint32_t *__res
 // x.d for the fold. (The workers used to issue the copies themselves, the activations as
 // 16-byte cp.async pieces: those retire at about one warp instruction per 24 cycles on this
 // part, and waiting for them was the longest phase of a block.)
-template <int WT>
+template <int WT, bool PERSIST, bool DOWN>
 __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   constexpr bool Q6 = WT == PM_TYPE_Q6_K;
   constexpr int NS = Q6 ? TC_RAW_STAGES_Q6 : TC_RAW_STAGES_Q4;
   constexpr int RAWB = Q6 ? TC_RAW_Q6 : TC_RAW_Q4;
   constexpr int BSTAGE = (TC_NMAX / 8) * TC_REC;  // the tokens' block: a record per 8 tokens
   extern __shared__ __align__(128) uint8_t smem[];
-  // blockIdx.y walks the list of (group, token tile) pairs made by k_tc_tiles
-  if ((int)blockIdx.y >= *A.n_tiles) return;
-  const int a = (int)A.tile_group[blockIdx.y];
   const LayerDev &ly = A.ly;
-  const WMat &W0 = A.down ? (A.shared ? ly.sdown : ly.down) : (A.shared ? ly.sgate : ly.gate);
+  const WMat &W0 = DOWN ? (A.shared ? ly.sdown : ly.down) : (A.shared ? ly.sgate : ly.gate);
   const WMat &W1 = A.shared ? ly.sup : ly.up;  // used by gate/up only
   const int cols = W0.cols, nb = cols / 256, rows = W0.rows;
-  const int e = (int)A.g.expert[a];
-  const int el = A.shared ? 0 : e - ly.first_local;
-  const uint32_t off = A.g.offset[a], cnt = A.g.count[a];
-  const int n0 = (int)A.tile_n0[blockIdx.y];
-  const int nvalid = min((int)cnt - n0, TC_NMAX);
-  const int npad = (nvalid + 15) & ~15;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool local = el >= 0 && el < (A.shared ? 1 : ly.n_local);
-  const int rows_per_cta = A.down ? TC_M : TC_M / 2;  // gate/up: 64 gate + 64 up rows
-  const int r0 = blockIdx.x * rows_per_cta;
-  if (!local) {  // an expert another rank holds: zeros (down) / nothing to do (gate/up)
-    if (A.down)
-      for (int i = tid; i < nvalid * TC_M; i += TC_NT) {
-        int n = i / TC_M, m = i % TC_M;
-        if (r0 + m < rows) A.out[(size_t)(off + n0 + n) * rows + r0 + m] = 0.0f;
-      }
-    return;
-  }
+  const int rows_per_cta = DOWN ? TC_M : TC_M / 2;  // gate/up: 64 gate + 64 up rows
+  // Work items are (token tile, row tile) pairs, row tiles fastest so that the CTAs running together
+  // share a tile's records in L2. One-item form: a CTA per item, grid (row tiles, token tiles).
+  // Persistent form: gridDim.x CTAs, CTA i takes items i, i + gridDim.x, ...; the rings and the
+  // block counter run on across items, and the producer is already fetching the next item's
+  // operands while the workers write an item's outputs.
+  const int n_items = *A.n_tiles * A.row_tiles;
+  int a = 0, el = 0, n0 = 0, nvalid = 0, npad = 16, r0 = 0, tile = 0;
+  uint32_t off = 0, cnt = 0;
+  bool local = false;
+  auto set_item = [&](int w) {
+    if (!PERSIST) {
+      tile = blockIdx.y;
+      r0 = blockIdx.x * rows_per_cta;
+    } else {
+      tile = w / A.row_tiles;
+      r0 = (w - tile * A.row_tiles) * rows_per_cta;
+    }
+    a = (int)A.tile_group[tile];
+    el = A.shared ? 0 : (int)A.g.expert[a] - ly.first_local;
+    off = A.g.offset[a];
+    cnt = A.g.count[a];
+    n0 = (int)A.tile_n0[tile];
+    nvalid = min((int)cnt - n0, TC_NMAX);
+    npad = (nvalid + 15) & ~15;
+    local = el >= 0 && el < (A.shared ? 1 : ly.n_local);  // else: an expert another rank holds
+  };
+  // every role walks the CTA's items with its own copy of w
+  int w = PERSIST ? blockIdx.x : blockIdx.y * A.row_tiles + blockIdx.x;
+  if (w >= n_items) return;
+  set_item(w);
+  auto next_item = [&]() -> bool {
+    if (!PERSIST) return false;
+    w += gridDim.x;
+    if (w >= n_items) return false;
+    set_item(w);
+    return true;
+  };
 
   uint8_t *sRaw = smem;                                        // [NS] blocks of the 128 rows as stored
   float *sS = (float *)smem;                                   // (after the last block) gate/up exchange [128][129]
@@ -338,7 +357,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   uint64_t *bar = (uint64_t *)(sAm + 2 * 2 * TC_M * 16);       // the products of a block have completed
   uint64_t *full_raw = bar + 1, *empty_raw = full_raw + 4;     // rings of the raw areas ...
   uint64_t *full_b = empty_raw + 4, *empty_b = full_b + 3;     // ... and of the tokens' areas
-  uint32_t *tmem_slot = (uint32_t *)(empty_b + 3);
+  uint64_t *epi_done = empty_b + 3;                            // gate/up over the raw areas: the exchange has been read
+  uint32_t *tmem_slot = (uint32_t *)(epi_done + 1);
 
   if (warp == TC_NW / 32) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -357,6 +377,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       tc_mbar_init(full_b + i, 1);  // the producer's expect_tx; the bulk copies complete the bytes
       tc_mbar_init(empty_b + i, 1 + TC_NW / 32);  // the products' commit and every worker warp after its fold
     }
+    tc_mbar_init(epi_done, TC_NW / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -368,7 +389,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   // Global row of tile row i (gate rows, then up rows, in a gate/up tile), or -1 past the
   // matrix; `second`: the row belongs to the up matrix
   auto grow = [&](int i, bool &second) -> int {
-    second = !A.down && i >= 64;
+    second = !DOWN && i >= 64;
     int r = r0 + (second ? i - 64 : i);
     return r < rows ? r : -1;
   };
@@ -376,14 +397,22 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   if (warp == TC_NW / 32) {
     // ================= the issuing warp =================
     // instruction descriptors: D s32, A u8, B s8, K-major; and the f16 one (D f32)
+    int gb = 0;  // blocks this CTA has run so far
+    for (;;) {
+    if (!local) {
+      if (next_item()) continue;
+      break;
+    }
+    const bool tc_trace_item = w == 0;
+    (void)tc_trace_item;
     const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
-    for (int b = 0; b < nb; b++) {
-      const int sb = b % 3;
+    for (int b = 0; b < nb; b++, gb++) {
+      const int sb = gb % 3;
       const uint32_t bs = sB_a + (uint32_t)sb * BSTAGE;
       const uint64_t dB0 = tc_desc(bs, 128u, (uint32_t)TC_REC);  // K chunks 128 B apart, 8-token groups a record apart
       TC_STAMP_M(b, 0)
-      tc_wait(full_b + sb, (uint32_t)((b / 3) & 1), A.err, A.wait_ns);  // the tokens' block is in shared memory
+      tc_wait(full_b + sb, (uint32_t)((gb / 3) & 1), A.err, A.wait_ns);  // the tokens' block is in shared memory
       TC_STAMP_M(b, 1)
       tc_ready_wait();  // operand A in TMEM, the accumulators read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -396,7 +425,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
           tc_mma_i8_ta(tmem + TC_ACC_LO, tmem + TC_A_LO + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
         }
         if (!Q6)
-          tc_mma_f16(tmem + TC_ACC_M, tc_desc(sAm_a + (uint32_t)(b & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
+          tc_mma_f16(tmem + TC_ACC_M, tc_desc(sAm_a + (uint32_t)(gb & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
                      tc_desc(bs + TC_REC_BM, 128u, (uint32_t)TC_REC), idesc_h, 0u);
         tc_commit(bar);
         tc_commit(empty_b + sb);
@@ -404,17 +433,25 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       TC_STAMP_M(b, 3)
       __syncwarp();
     }
+    if (!next_item()) break;
+    }
   } else if (warp > TC_NW / 32) {
     // ================= the producer =================
     const int lane = tid & 31;
+    const uint32_t sRaw_a = tc_s32(sRaw);
+    int gb = 0, k_local = 0;  // blocks and items this CTA has run so far
+    for (;;) {
+    if (!local) {
+      if (next_item()) continue;
+      break;
+    }
     const uint8_t *wb0[4], *wb1[4];  // the expert's planes of the tile's matrices
 #pragma unroll
     for (int pl = 0; pl < 4; pl++) {
       wb0[pl] = W0.plane[pl] ? W0.plane[pl] + (size_t)el * W0.stride[pl] : nullptr;
-      wb1[pl] = (!A.down && W1.plane[pl]) ? W1.plane[pl] + (size_t)el * W1.stride[pl] : nullptr;
+      wb1[pl] = (!DOWN && W1.plane[pl]) ? W1.plane[pl] + (size_t)el * W1.stride[pl] : nullptr;
     }
-    const uint32_t sRaw_a = tc_s32(sRaw);
-    const uint8_t *rec0 = A.rec + (size_t)(A.tile_r0[blockIdx.y] / 8) * nb * TC_REC;  // the tile's first record
+    const uint8_t *rec0 = A.rec + (size_t)(A.tile_r0[tile] / 8) * nb * TC_REC;  // the tile's first record
     const int nrec = npad >> 3;
     // Q4_K: 9 pieces a row, [row][144 B]; piece p = lane + 32 j of the tile. Pieces 0..575 are
     // tile rows 0..63 and pieces 576.. the same (row, piece) pattern 64 rows on: of the other matrix
@@ -423,26 +460,30 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     // copy instruction a piece.
     uint32_t roff[Q6 ? 1 : 18];
     uint32_t okA = 0, okB = 0;
-    const uint8_t *pA = wb0[0], *pB = A.down ? wb0[0] + (size_t)64 * nb * 144 : wb1[0];
+    const uint8_t *pA = wb0[0], *pB = DOWN ? wb0[0] + (size_t)64 * nb * 144 : wb1[0];
     if (!Q6) {
 #pragma unroll
       for (int j = 0; j < 18; j++) {
         const int p = lane + 32 * j, i = p / 9, c = p - 9 * i;
         roff[j] = (uint32_t)(r0 + i) * (uint32_t)nb * 144u + 16u * c;
         if (r0 + i < rows) okA |= 1u << j;
-        if (r0 + i + (A.down ? 64 : 0) < rows) okB |= 1u << j;
+        if (r0 + i + (DOWN ? 64 : 0) < rows) okB |= 1u << j;
       }
     }
     // Q6_K: ql 8 pieces a row, [row][128 B], piece c at c ^ (row & 7); qh 4 pieces a row,
     // [row][64 B], piece c at c ^ ((row >> 1) & 3) (both conflict-free for the row-per-lane reads
     // of the unpack); sc [row][16 B]; d: the aligned word holding the row's f16. A lane keeps its
     // piece column and walks rows: tile row i = i0 + step * j.
-    for (int bb = 0; bb < nb; bb++) {
-      // ---- the weights of block bb -> raw area bb % NS ----
+    // gate/up: the previous item's exchange of gate and up sums lives in the raw areas; its readers
+    // must be done before this item's weights land there
+    if (!DOWN && k_local > 0) tc_wait(epi_done, (uint32_t)((k_local - 1) & 1), A.err, A.wait_ns);
+    k_local++;
+    for (int bb = 0; bb < nb; bb++, gb++) {
+      // ---- the weights of block bb -> the next raw area ----
       {
-        const int st = bb % NS;
+        const int st = gb % NS;
         const uint32_t ra = sRaw_a + (uint32_t)st * RAWB;
-        if (bb >= NS) tc_wait(empty_raw + st, (uint32_t)((bb / NS - 1) & 1), A.err, A.wait_ns);
+        if (gb >= NS) tc_wait(empty_raw + st, (uint32_t)((gb / NS - 1) & 1), A.err, A.wait_ns);
         if (!Q6) {
 #pragma unroll
           for (int j = 0; j < 18; j++) {
@@ -450,7 +491,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
             if (okB & (1u << j)) tc_cp16(ra + (uint32_t)(lane + 32 * (j + 18)) * 16u, pB + roff[j] + (size_t)bb * 144);
           }
         } else {
-          const int halves = A.down ? 1 : 2, hrows = A.down ? TC_M : TC_M / 2;
+          const int halves = DOWN ? 1 : 2, hrows = DOWN ? TC_M : TC_M / 2;
           for (int hf = 0; hf < halves; hf++) {
             const uint8_t *const *wb = hf ? wb1 : wb0;
             const int lim = min(hrows, rows - r0);  // rows of this half inside the matrix
@@ -483,8 +524,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       }
       // ---- the tokens' records of block bb -> their area ----
       {
-        const int sb = bb % 3;
-        if (bb >= 3) tc_wait(empty_b + sb, (uint32_t)((bb / 3 - 1) & 1), A.err, A.wait_ns);
+        const int sb = gb % 3;
+        if (gb >= 3) tc_wait(empty_b + sb, (uint32_t)((gb / 3 - 1) & 1), A.err, A.wait_ns);
         if (lane == 0)
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_s32(full_b + sb)),
                        "r"((uint32_t)(nrec * TC_REC))
@@ -497,7 +538,18 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
                        : "memory");
       }
     }
+    if (!next_item()) break;
+    }
     asm volatile("cp.async.wait_all;" ::: "memory");
+    // the last bulk copies have landed before the CTA gives up its shared memory (the workers waited
+    // for them already unless a wait ran out; in the one-item form, where the check measured 3 %
+    // slower, that is relied on)
+    if (PERSIST)
+    for (int g = gb > 3 ? gb - 3 : 0; g < gb; g++) {
+      const unsigned long long t0 = tc_now();
+      while (!tc_bar_test(full_b + g % 3, (uint32_t)((g / 3) & 1)) && tc_now() - t0 < A.wait_ns) {
+      }
+    }
   } else {
     // ================= the workers =================
     // unpack: thread = (row m of the tile, quarter `part` of the block: K values
@@ -505,6 +557,20 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     // thread folds row m's accumulators (TMEM lane m), a quarter of the token columns, so
     // the row's (d, dmin) stay in registers.
     const int m = tid & 127, part = tid >> 7;
+    const uint32_t tlane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+    int gb0 = 0;  // blocks this CTA ran before the current item
+    for (;;) {
+    if (!local) {  // zeros (down) / nothing to do (gate/up)
+      if (DOWN)
+        for (int i = tid; i < nvalid * TC_M; i += TC_NW) {
+          int n = i / TC_M, mm = i % TC_M;
+          if (r0 + mm < rows) A.out[(size_t)(off + n0 + n) * rows + r0 + mm] = 0.0f;
+        }
+      if (next_item()) continue;
+      break;
+    }
+    const bool tc_trace_item = w == 0;
+    (void)tc_trace_item;
     bool msec;
     const int mrow = grow(m, msec);
     // the f16 d of a Q6_K row sits in the low or high half of the staged word
@@ -519,10 +585,11 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       if (part < 2) *(uint4 *)(sAm + (size_t)(part * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
       else *(uint4 *)(sAm + 2 * TC_M * 16 + (size_t)((part - 2) * TC_M + m) * 16) = make_uint4(0, 0, 0, 0);
     }
-    // block bb of its raw area -> ah/al, nrd/nrdmin (and the mins of the row into sAm[bb & 1])
-    auto unpack = [&](int bb) {
+    // block bb of the item (the CTA's block g) of its raw area -> ah/al, nrd/nrdmin (and the mins of
+    // the row into sAm[g & 1])
+    auto unpack = [&](int bb, int g) {
       if (mrow < 0) return;
-      const uint8_t *raw = sRaw + (size_t)(bb % NS) * RAWB;
+      const uint8_t *raw = sRaw + (size_t)(g % NS) * RAWB;
       if (Q6) {
         const int hf = part >> 1, p2 = part & 1;
         const uint8_t *rq = raw + m * 128, *rh = raw + 16384 + m * 64;
@@ -563,7 +630,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         uint32_t sc03, sc47, m03, m47;
         pm_q4k_scmin_packed(hdr.y, hdr.z, hdr.w, sc03, sc47, m03, m47);
         if (part < 2)  // the eight mins as f16, K chunk `part` of the f16 product (both hold m_0..m_7)
-          *(uint4 *)(sAm + (size_t)(bb & 1) * (2 * TC_M * 16) + (size_t)(part * TC_M + m) * 16) =
+          *(uint4 *)(sAm + (size_t)(g & 1) * (2 * TC_M * 16) + (size_t)(part * TC_M + m) * 16) =
               make_uint4(pm_bytes_to_half2(m03, 0x4140), pm_bytes_to_half2(m03, 0x4342),
                          pm_bytes_to_half2(m47, 0x4140), pm_bytes_to_half2(m47, 0x4342));
         const int c = part;
@@ -587,15 +654,14 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     };
     // wait for raw block bb, unpack it, and free its area once the whole warp has read it
     auto take = [&](int bb) {
-      const int st = bb % NS;
-      tc_wait(full_raw + st, (uint32_t)((bb / NS) & 1), A.err, A.wait_ns);
-      unpack(bb);
+      const int g = gb0 + bb, st = g % NS;
+      tc_wait(full_raw + st, (uint32_t)((g / NS) & 1), A.err, A.wait_ns);
+      unpack(bb, g);
       __syncwarp();
       if ((tid & 31) == 0) tc_mbar_arrive(empty_raw + st);
     };
 
     // (3) fold: TMEM lane m, a quarter of the tile's token columns (npad / 4: a multiple of 4)
-    const uint32_t tlane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
     const int ew = npad >> 2, ecol0 = part * ew;
     float total[32];
 #pragma unroll
@@ -618,10 +684,11 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       if (b + 1 < nb) take(b + 1);
       TC_STAMP(b, 2)
       // ---- 3. the block's float term, in block order ----
-      tc_wait(bar, (uint32_t)(b & 1), A.err, A.wait_ns);
+      const int g = gb0 + b;
+      tc_wait(bar, (uint32_t)(g & 1), A.err, A.wait_ns);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int sb = b % 3;
-      tc_wait(full_b + sb, (uint32_t)((b / 3) & 1), A.err, A.wait_ns);  // (long complete) the block's x.d is visible
+      const int sb = g % 3;
+      tc_wait(full_b + sb, (uint32_t)((g / 3) & 1), A.err, A.wait_ns);  // (long complete) the block's x.d is visible
       TC_STAMP(b, 3)
       TC_STAMP(b, 4)
       {
@@ -668,10 +735,11 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       if ((tid & 31) == 0) tc_mbar_arrive(empty_b + sb);  // this warp has read the block's x.d
       TC_STAMP(b, 5)
     }
-    tc_workers_sync();  // the raw areas are dead: their memory carries the gate/up exchange
+    gb0 += nb;
+    if (!DOWN) tc_workers_sync();  // every worker has unpacked the item's last block: the raw areas carry the gate/up exchange
 
     const bool dead = *(volatile int *)A.err != 0;
-    if (A.down) {
+    if (DOWN) {
       if (!dead) {
         const float bd = (!A.shared && ly.bias_down && r0 + m < rows) ? ly.bias_down[(size_t)el * rows + r0 + m] : 0.0f;
 #pragma unroll
@@ -706,6 +774,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
           float w = fold ? A.wts[A.g.pair_src[p]] : 1.0f;
           A.out[(size_t)p * rows + r0 + j] = pm_act(D.act, D.act_limit, D.act_alpha, gv, uv, w, fold);
         }
+      __syncwarp();
+      if (PERSIST && (tid & 31) == 0) tc_mbar_arrive(epi_done);  // this warp has read the exchange area
+    }
+    if (!next_item()) break;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -736,7 +808,7 @@ size_t tc_rec_bytes(int n_pairs, int max_groups, int cols) {
 static size_t tc_smem(bool q6) {
   size_t raw = q6 ? (size_t)TC_RAW_STAGES_Q6 * TC_RAW_Q6 : (size_t)TC_RAW_STAGES_Q4 * TC_RAW_Q4;
   size_t ex = (size_t)TC_M * (TC_NMAX + 1) * 4;  // the gate/up exchange shares the raw areas' memory
-  return (raw > ex ? raw : ex) + 3 * (size_t)(TC_NMAX / 8) * TC_REC + 2 * 2 * TC_M * 16 + 15 * 8 + 16;
+  return (raw > ex ? raw : ex) + 3 * (size_t)(TC_NMAX / 8) * TC_REC + 2 * 2 * TC_M * 16 + 16 * 8 + 16 + 16;
 }
 
 // Tensor-core form of launch_gateup / launch_down for Q4_K or Q6_K weights and Q8x
@@ -766,7 +838,20 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
     if (L.count) ++*L.count;
   }
   const size_t smem = tc_smem(q6);
-  const void *kern = q6 ? (const void *)k_tc<PM_TYPE_Q6_K> : (const void *)k_tc<PM_TYPE_Q4_K>;
+  const int row_tiles = down ? (W.rows + TC_M - 1) / TC_M : (W.rows + 63) / 64;
+  // Down tiles: one persistent CTA an SM. An item is short (ff / 256 blocks) and the next item's
+  // operands arrive during an item's last fold and its output writes: 20 % faster at ff 768
+  // (128 experts, 8192 tokens), 6 % at ff 2048.
+  // Gate/up tiles: a CTA an item. Their exchange of gate and up sums lives in the raw areas, so the
+  // next item's weights cannot be fetched early; run persistently they measured no faster (d 2048)
+  // or 9 % slower (d 7168) - also with the items drawn from a counter in global memory instead of a
+  // fixed share per CTA, and with the up sums exchanged through an area of their own.
+  const long items = (long)row_tiles * max_tiles;
+  const bool persist = down && items > L.n_sm;
+  const void *kern =
+      !down ? (q6 ? (const void *)k_tc<PM_TYPE_Q6_K, false, false> : (const void *)k_tc<PM_TYPE_Q4_K, false, false>)
+      : q6  ? (persist ? (const void *)k_tc<PM_TYPE_Q6_K, true, true> : (const void *)k_tc<PM_TYPE_Q6_K, false, true>)
+            : (persist ? (const void *)k_tc<PM_TYPE_Q4_K, true, true> : (const void *)k_tc<PM_TYPE_Q4_K, false, true>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   TcArgs A;
@@ -784,10 +869,10 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   A.tile_group = tile_group;
   A.tile_n0 = tile_n0;
   A.tile_r0 = tile_r0;
-  int row_tiles = down ? (W.rows + TC_M - 1) / TC_M : (W.rows + 63) / 64;
-  dim3 grid(row_tiles, max_tiles);
-  if (q6) k_tc<PM_TYPE_Q6_K><<<grid, TC_NT, smem, L.stream>>>(A);
-  else k_tc<PM_TYPE_Q4_K><<<grid, TC_NT, smem, L.stream>>>(A);
+  A.row_tiles = row_tiles;
+  void *args[] = {&A};
+  e = cudaLaunchKernel(kern, persist ? dim3(L.n_sm) : dim3(row_tiles, max_tiles), dim3(TC_NT), args, smem, L.stream);
+  if (e != cudaSuccess) return e;
   if (L.count) ++*L.count;
   return cudaGetLastError();
 }
