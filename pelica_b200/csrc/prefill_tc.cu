@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       if (next_item()) continue;
       break;
     }
-    const bool tc_trace_item = w == 0;
+    const bool tc_trace_item = w == (PERSIST ? (int)gridDim.x : 0);  // persistent form: CTA 0's second item
     (void)tc_trace_item;
     const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t idesc_h = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
@@ -569,7 +569,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       if (next_item()) continue;
       break;
     }
-    const bool tc_trace_item = w == 0;
+    const bool tc_trace_item = w == (PERSIST ? (int)gridDim.x : 0);  // persistent form: CTA 0's second item
     (void)tc_trace_item;
     bool msec;
     const int mrow = grow(m, msec);
@@ -609,16 +609,20 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
             const uint4 qlw = qlv[2 * qq + lh];
             const uint4 qhw = qhv[lh];
             const int sv = (int)(int8_t)((scw >> (8 * (2 * qq + lh))) & 0xff);
-            const uint32_t kk = (uint32_t)(4128 - 32 * sv) * 0x00010001u;
+            // z4 = 4 * (sv * (q - 32) + 4128) in [256, 32896]: its high byte is th, its low byte 4 * tl
+            // (v + 4128 = 64 th + tl). The low plane holds 4 * tl, the fold takes a quarter of d.
+            const uint32_t sv4 = (uint32_t)(4 * sv);
+            const uint32_t kk = (uint32_t)(4 * (4128 - 32 * sv)) * 0x00010001u;
             const uint32_t ws[4] = {qlw.x, qlw.y, qlw.z, qlw.w}, hs[4] = {qhw.x, qhw.y, qhw.z, qhw.w};
+            const int rot = (4 * p2 + 2 * qq - 4) & 31;  // brings the pair of high bits to bits 4, 5 of its byte
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-              const uint32_t qv = ((ws[i] >> (4 * p2)) & 0x0f0f0f0fu) | (((hs[i] >> (4 * p2 + 2 * qq)) & 0x03030303u) << 4);
-              // two values per 32-bit product: 16-bit lanes of sv * q + (4128 - 32 sv) >= 0
-              const uint32_t ze = (qv & 0x00ff00ffu) * (uint32_t)sv + kk;
-              const uint32_t zo = ((qv >> 8) & 0x00ff00ffu) * (uint32_t)sv + kk;
-              al[4 * (2 * qq + lh) + i] = __byte_perm(ze, zo, 0x6240) & 0x3f3f3f3fu;
-              ah[4 * (2 * qq + lh) + i] = __byte_perm(ze >> 6, zo >> 6, 0x6240);
+              const uint32_t qv = ((ws[i] >> (4 * p2)) & 0x0f0f0f0fu) | (__funnelshift_r(hs[i], hs[i], rot) & 0x30303030u);
+              // two values per 32-bit product (16-bit lanes, each lane's result positive): values 0, 2 and 1, 3
+              const uint32_t ze = __byte_perm(qv, 0u, 0x4240) * sv4 + kk;
+              const uint32_t zo = __byte_perm(qv, 0u, 0x4341) * sv4 + kk;
+              al[4 * (2 * qq + lh) + i] = __byte_perm(ze, zo, 0x6240);
+              ah[4 * (2 * qq + lh) + i] = __byte_perm(ze, zo, 0x7351);
             }
           }
         }
@@ -670,7 +674,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     take(0);
     for (int b = 0; b < nb; b++) {
       TC_STAMP(b, 0)
-      const float rd = nrd, rdmin = nrdmin;
+      const float rd = Q6 ? __fmul_rn(nrd, 0.25f) : nrd, rdmin = nrdmin;  // Q6_K: the products come out times 4
       // ---- 1. operand A of block b -> tensor memory (the previous block's products have
       // completed: every worker waited on their barrier) ----
       tc_st16(tlane + TC_A_HI + 16u * part, ah);
@@ -695,6 +699,39 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         const uint8_t *bst = sB + (size_t)sb * BSTAGE;  // column n: record n / 8, slot n % 8
         // (four columns a wait: eight a wait, and requesting a step ahead, both measured slower -
         // the extra live registers cost more than the read latency they hide)
+        if (ew <= 8) {  // tiles of at most 32 tokens: the thread's columns behind one wait
+          uint32_t v0[8], v1[8], v2[8];
+          tc_ld8(tlane + TC_ACC_HI + (uint32_t)ecol0, v0);
+          tc_ld8(tlane + TC_ACC_LO + (uint32_t)ecol0, v1);
+          if (!Q6) tc_ld8(tlane + TC_ACC_M + (uint32_t)ecol0, v2);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int h4 = 0; h4 < 8; h4 += 4) {
+            if (h4 < ew) {
+              const int n = ecol0 + h4;
+              const uint8_t *rcd = bst + (size_t)(n >> 3) * TC_REC + (n & 7) * 4;
+              const float4 x4 = *(const float4 *)(rcd + TC_REC_XD);
+              const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+              int ss[4] = {0, 0, 0, 0};
+              if (Q6) {
+                const int4 s4 = *(const int4 *)(rcd + TC_REC_XS);
+                ss[0] = s4.x; ss[1] = s4.y; ss[2] = s4.z; ss[3] = s4.w;
+              }
+#pragma unroll
+              for (int u = 0; u < 4; u++) {
+                float term;
+                if (Q6) {
+                  int isum = 256 * (int)v0[h4 + u] + (int)v1[h4 + u] - 16512 * ss[u];
+                  term = __fmul_rn(xs[u], __fmul_rn(rd, (float)isum));
+                } else {
+                  int isum = 8 * (int)v0[h4 + u] + (int)v1[h4 + u];
+                  term = __fmul_rn(xs[u], __fsub_rn(__fmul_rn(rd, (float)isum), __fmul_rn(rdmin, __uint_as_float(v2[h4 + u]))));
+                }
+                total[h4 + u] = __fadd_rn(total[h4 + u], term);
+              }
+            }
+          }
+        } else
 #pragma unroll
         for (int c4 = 0; c4 < 32; c4 += 4) {
           if (c4 < ew) {
@@ -719,7 +756,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
             for (int u = 0; u < 4; u++) {
               float term;
               if (Q6) {
-                int isum = 64 * (int)v0[u] + (int)v1[u] - 4128 * ss[u];
+                // 4 * isum (exact in int32; (d / 4) * float(4 isum) rounds as d * float(isum) does)
+                int isum = 256 * (int)v0[u] + (int)v1[u] - 16512 * ss[u];
                 term = __fmul_rn(xs[u], __fmul_rn(rd, (float)isum));
               } else {
                 int isum = 8 * (int)v0[u] + (int)v1[u];
@@ -841,7 +879,7 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   const int row_tiles = down ? (W.rows + TC_M - 1) / TC_M : (W.rows + 63) / 64;
   // Down tiles: one persistent CTA an SM. An item is short (ff / 256 blocks) and the next item's
   // operands arrive during an item's last fold and its output writes: 20 % faster at ff 768
-  // (128 experts, 8192 tokens), 6 % at ff 2048.
+  // (128 experts, 512 tokens), 6 % at ff 2048.
   // Gate/up tiles: a CTA an item. Their exchange of gate and up sums lives in the raw areas, so the
   // next item's weights cannot be fetched early; run persistently they measured no faster (d 2048)
   // or 9 % slower (d 7168) - also with the items drawn from a counter in global memory instead of a
