@@ -40,9 +40,9 @@
 #define TC_M 128
 #define TC_NMAX 128
 #define TC_TMEM_COLS 512
-#define TC_ACC_HI 0u              /* TMEM columns: accumulators ... */
-#define TC_ACC_LO 128u
-#define TC_ACC_M 256u
+/* TMEM columns 0..383: the accumulators hi, lo, mins - one set of three 128-column accumulators, or
+   (tiles of at most TC_DUAL_N tokens) two sets of three 64-column ones that the blocks use in turn */
+#define TC_DUAL_N 64
 #define TC_A_HI 384u              /* ... and operand A: 64 columns (256 K values) a plane */
 #define TC_A_LO 448u
 #define TC_RAW_Q4 (TC_M * 144)                       /* bytes of the raw staging area */
@@ -154,7 +154,8 @@ __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int *err
 int tc_max_tiles(int n_pairs, int max_groups);
 
 // Compile with -DPM_TC_TRACE=1 (gate/up launches) or =2 (down launches) to stamp the phases of
-// CTA (0, 0) with the SM clock: [thread 0 | thread 511][block][stamp]; read back with pm_debug_tc_trace.
+// CTA 0's first item (persistent form: its second) with the SM clock: [thread 0 | thread 511][block][stamp],
+// block slot 30 = the item's start, first block unpacked, blocks done, end; read back with pm_debug_tc_trace.
 #ifdef PM_TC_TRACE
 __device__ unsigned long long g_tc_trace[3 * 32 * 8];
 #define TC_STAMP(b, i)                                                                         \
@@ -298,7 +299,7 @@ __global__ void __launch_bounds__(256) k_tc_rows(Groups g, const uint32_t *__res
 // x.d for the fold. (The workers used to issue the copies themselves, the activations as
 // 16-byte cp.async pieces: those retire at about one warp instruction per 24 cycles on this
 // part, and waiting for them was the longest phase of a block.)
-template <int WT, bool PERSIST, bool DOWN>
+template <int WT, bool PERSIST, bool DOWN, bool SMALL>
 __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
   constexpr bool Q6 = WT == PM_TYPE_Q6_K;
   constexpr int NS = Q6 ? TC_RAW_STAGES_Q6 : TC_RAW_STAGES_Q4;
@@ -417,15 +418,19 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       tc_ready_wait();  // operand A in TMEM, the accumulators read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       TC_STAMP_M(b, 2)
+      // tiles of at most 64 tokens: two accumulator sets, blocks alternate (see the workers)
+      const bool dual = SMALL && npad <= TC_DUAL_N;
+      const uint32_t acc_w = dual ? (uint32_t)TC_DUAL_N : (uint32_t)TC_NMAX;
+      const uint32_t acc = tmem + (dual ? (uint32_t)(gb & 1) * (3u * TC_DUAL_N) : 0u);
       if ((tid & 31) == 0 && !(A.fault_block >= 0 && b >= A.fault_block)) {
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
           const uint64_t db = dB0 + (uint64_t)(ks * 16);  // two K chunks a step
-          tc_mma_i8_ta(tmem + TC_ACC_HI, tmem + TC_A_HI + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
-          tc_mma_i8_ta(tmem + TC_ACC_LO, tmem + TC_A_LO + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
+          tc_mma_i8_ta(acc, tmem + TC_A_HI + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
+          tc_mma_i8_ta(acc + acc_w, tmem + TC_A_LO + 8u * ks, db, idesc, ks > 0 ? 1u : 0u);
         }
         if (!Q6)
-          tc_mma_f16(tmem + TC_ACC_M, tc_desc(sAm_a + (uint32_t)(gb & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
+          tc_mma_f16(acc + 2u * acc_w, tc_desc(sAm_a + (uint32_t)(gb & 1) * (2 * TC_M * 16), TC_M * 16u, 128u),
                      tc_desc(bs + TC_REC_BM, 128u, (uint32_t)TC_REC), idesc_h, 0u);
         tc_commit(bar);
         tc_commit(empty_b + sb);
@@ -440,6 +445,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     const int lane = tid & 31;
     const uint32_t sRaw_a = tc_s32(sRaw);
     int gb = 0, k_local = 0;  // blocks and items this CTA has run so far
+    bool prev_small = false;  // the previous item's gate/up exchange took two raw areas only
     for (;;) {
     if (!local) {
       if (next_item()) continue;
@@ -474,11 +480,16 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     // [row][64 B], piece c at c ^ ((row >> 1) & 3) (both conflict-free for the row-per-lane reads
     // of the unpack); sc [row][16 B]; d: the aligned word holding the row's f16. A lane keeps its
     // piece column and walks rows: tile row i = i0 + step * j.
-    // gate/up: the previous item's exchange of gate and up sums lives in the raw areas; its readers
-    // must be done before this item's weights land there
-    if (!DOWN && k_local > 0) tc_wait(epi_done, (uint32_t)((k_local - 1) & 1), A.err, A.wait_ns);
+    // gate/up, persistent form: the previous item's exchange of gate and up sums lives in the raw
+    // areas and its readers must be done before this item's weights land there. A tile of at most 64
+    // tokens exchanges through the two areas that this item's blocks 2 and 3 will use, so blocks 0
+    // and 1 (and their tokens' records) are fetched during the previous item's epilogue.
+    const int wait_at = (!DOWN && PERSIST && k_local > 0) ? (prev_small ? (nb < 2 ? nb : 2) : 0) : -1;
+    const uint32_t epi_par = (uint32_t)((k_local - 1) & 1);
+    prev_small = NS == 4 && npad <= TC_DUAL_N;
     k_local++;
     for (int bb = 0; bb < nb; bb++, gb++) {
+      if (bb == wait_at) tc_wait(epi_done, epi_par, A.err, A.wait_ns);
       // ---- the weights of block bb -> the next raw area ----
       {
         const int st = gb % NS;
@@ -538,6 +549,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
                        : "memory");
       }
     }
+    if (wait_at == nb) tc_wait(epi_done, epi_par, A.err, A.wait_ns);  // (an item shorter than three blocks)
     if (!next_item()) break;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -571,6 +583,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
     }
     const bool tc_trace_item = w == (PERSIST ? (int)gridDim.x : 0);  // persistent form: CTA 0's second item
     (void)tc_trace_item;
+    TC_STAMP(30, 0)
     bool msec;
     const int mrow = grow(m, msec);
     // the f16 d of a Q6_K row sits in the low or high half of the staged word
@@ -671,39 +684,64 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
 #pragma unroll
     for (int i = 0; i < 32; i++) total[i] = 0.0f;
 
+    // Tiles of at most 64 tokens keep two accumulator sets in tensor memory: the float term of block
+    // b - 1 is then added while the products of block b run, and the period of a block is the
+    // products' time instead of products + float term. (Operand A has one buffer, so the products of
+    // consecutive blocks never overlap; wider tiles fill tensor memory with one set.)
+    const bool dual = SMALL && npad <= TC_DUAL_N;
+    const uint32_t acc_w = dual ? (uint32_t)TC_DUAL_N : (uint32_t)TC_NMAX;
+    float rd_p = 0.0f, rdmin_p = 0.0f;  // dual: the scales of the block whose float term is pending
     take(0);
-    for (int b = 0; b < nb; b++) {
-      TC_STAMP(b, 0)
-      const float rd = Q6 ? __fmul_rn(nrd, 0.25f) : nrd, rdmin = nrdmin;  // Q6_K: the products come out times 4
-      // ---- 1. operand A of block b -> tensor memory (the previous block's products have
-      // completed: every worker waited on their barrier) ----
-      tc_st16(tlane + TC_A_HI + 16u * part, ah);
-      tc_st16(tlane + TC_A_LO + 16u * part, al);
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the mins written by unpack(b)
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      tc_ready_arrive();
-      TC_STAMP(b, 1)
-      // ---- 2. while the products run: the next block -> registers ----
-      if (b + 1 < nb) take(b + 1);
-      TC_STAMP(b, 2)
-      // ---- 3. the block's float term, in block order ----
+    TC_STAMP(30, 1)
+    for (int b = 0; b <= nb; b++) {
       const int g = gb0 + b;
-      tc_wait(bar, (uint32_t)(g & 1), A.err, A.wait_ns);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int sb = g % 3;
-      tc_wait(full_b + sb, (uint32_t)((g / 3) & 1), A.err, A.wait_ns);  // (long complete) the block's x.d is visible
-      TC_STAMP(b, 3)
-      TC_STAMP(b, 4)
+      float rd_b = 0.0f, rdmin_b = 0.0f;
+      if (dual && b > 0) {  // the previous block's products: operand A is free, its accumulators are ready
+        tc_wait(bar, (uint32_t)((g - 1) & 1), A.err, A.wait_ns);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      if (b < nb) {
+        TC_STAMP(b, 0)
+        rd_b = Q6 ? __fmul_rn(nrd, 0.25f) : nrd;  // Q6_K: the products come out times 4
+        rdmin_b = nrdmin;
+        // ---- 1. operand A of block b -> tensor memory (the previous block's products have
+        // completed: every worker waited on their barrier) ----
+        tc_st16(tlane + TC_A_HI + 16u * part, ah);
+        tc_st16(tlane + TC_A_LO + 16u * part, al);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the mins written by unpack(b)
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        tc_ready_arrive();
+        TC_STAMP(b, 1)
+        // ---- 2. while the products run: the next block -> registers ----
+        if (b + 1 < nb) take(b + 1);
+        TC_STAMP(b, 2)
+        if (!dual) {
+          tc_wait(bar, (uint32_t)(g & 1), A.err, A.wait_ns);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        TC_STAMP(b, 3)
+      }
+      // ---- 3. the float term of block fb (this block, or in dual mode the previous one), in block order ----
+      const int fb = dual ? b - 1 : b;
+      const float rd = dual ? rd_p : rd_b, rdmin = dual ? rdmin_p : rdmin_b;
+      rd_p = rd_b;
+      rdmin_p = rdmin_b;
+      if (fb < 0 || fb >= nb) continue;
+      const int gf = gb0 + fb, sb = gf % 3;
+      tc_wait(full_b + sb, (uint32_t)((gf / 3) & 1), A.err, A.wait_ns);  // (long complete) the block's x.d is visible
+      const uint32_t acc_hi = tlane + (dual ? (uint32_t)(gf & 1) * (3u * TC_DUAL_N) : 0u) + (uint32_t)ecol0;
+      const uint32_t acc_lo = acc_hi + acc_w, acc_m = acc_lo + acc_w;
+      TC_STAMP(fb, 4)
       {
         const uint8_t *bst = sB + (size_t)sb * BSTAGE;  // column n: record n / 8, slot n % 8
         // (four columns a wait: eight a wait, and requesting a step ahead, both measured slower -
         // the extra live registers cost more than the read latency they hide)
         if (ew <= 8) {  // tiles of at most 32 tokens: the thread's columns behind one wait
           uint32_t v0[8], v1[8], v2[8];
-          tc_ld8(tlane + TC_ACC_HI + (uint32_t)ecol0, v0);
-          tc_ld8(tlane + TC_ACC_LO + (uint32_t)ecol0, v1);
-          if (!Q6) tc_ld8(tlane + TC_ACC_M + (uint32_t)ecol0, v2);
+          tc_ld8(acc_hi, v0);
+          tc_ld8(acc_lo, v1);
+          if (!Q6) tc_ld8(acc_m, v2);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
           for (int h4 = 0; h4 < 8; h4 += 4) {
@@ -736,9 +774,9 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         for (int c4 = 0; c4 < 32; c4 += 4) {
           if (c4 < ew) {
             uint32_t v0[4], v1[4], v2[4];
-            tc_ld4(tlane + TC_ACC_HI + (uint32_t)(ecol0 + c4), v0);
-            tc_ld4(tlane + TC_ACC_LO + (uint32_t)(ecol0 + c4), v1);
-            if (!Q6) tc_ld4(tlane + TC_ACC_M + (uint32_t)(ecol0 + c4), v2);
+            tc_ld4(acc_hi + (uint32_t)c4, v0);
+            tc_ld4(acc_lo + (uint32_t)c4, v1);
+            if (!Q6) tc_ld4(acc_m + (uint32_t)c4, v2);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const int n = ecol0 + c4;
             const uint8_t *rcd = bst + (size_t)(n >> 3) * TC_REC + (n & 7) * 4;
@@ -771,9 +809,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if ((tid & 31) == 0) tc_mbar_arrive(empty_b + sb);  // this warp has read the block's x.d
-      TC_STAMP(b, 5)
+      TC_STAMP(fb, 5)
     }
     gb0 += nb;
+    TC_STAMP(30, 2)
     if (!DOWN) tc_workers_sync();  // every worker has unpacked the item's last block: the raw areas carry the gate/up exchange
 
     const bool dead = *(volatile int *)A.err != 0;
@@ -791,10 +830,17 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         }
       }
     } else {
-      // gate rows in tile rows 0..63, up rows in 64..127: exchange through shared memory
+      // gate rows in tile rows 0..63, up rows in 64..127: exchange through shared memory. A tile of at
+      // most 64 tokens takes the two raw areas that held the item's last blocks - the next item's
+      // blocks 2 and 3 - and leaves the other two to the producer (Q4_K: four areas); a wider tile
+      // takes all of them.
+      const bool xsmall = NS == 4 && npad <= TC_DUAL_N;
+      const int xstride = xsmall ? TC_DUAL_N + 1 : TC_NMAX + 1;
+      float *sG = xsmall ? (float *)(sRaw + (size_t)((gb0 + 2) % NS) * RAWB) : sS;
+      float *sU = xsmall ? (float *)(sRaw + (size_t)((gb0 + 3) % NS) * RAWB) : sS + 64 * (TC_NMAX + 1);
 #pragma unroll
       for (int i = 0; i < 32; i++)
-        if (i < ew) sS[m * (TC_NMAX + 1) + ecol0 + i] = total[i];
+        if (i < ew) (m < 64 ? sG + m * xstride : sU + (m - 64) * xstride)[ecol0 + i] = total[i];
       tc_workers_sync();
       const pm_layer_desc &D = ly.desc;
       const bool fold = !A.shared && D.weight_fold == PM_FOLD_BEFORE_DOWN && A.wts;
@@ -803,7 +849,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
         for (int i = tid; i < nvalid * 64; i += TC_NW) {
           int j = i & 63, n = i >> 6;
           if (r0 + j >= rows) continue;
-          float gv = sS[j * (TC_NMAX + 1) + n], uv = sS[(64 + j) * (TC_NMAX + 1) + n];
+          float gv = sG[j * xstride + n], uv = sU[j * xstride + n];
           if (bias) {
             gv = __fadd_rn(gv, ly.bias_gate[(size_t)el * rows + r0 + j]);
             uv = __fadd_rn(uv, ly.bias_up[(size_t)el * rows + r0 + j]);
@@ -815,6 +861,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_tc(const TcArgs A) {
       __syncwarp();
       if (PERSIST && (tid & 31) == 0) tc_mbar_arrive(epi_done);  // this warp has read the exchange area
     }
+    TC_STAMP(30, 3)
     if (!next_item()) break;
     }
   }
@@ -880,16 +927,30 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   // Down tiles: one persistent CTA an SM. An item is short (ff / 256 blocks) and the next item's
   // operands arrive during an item's last fold and its output writes: 20 % faster at ff 768
   // (128 experts, 512 tokens), 6 % at ff 2048.
-  // Gate/up tiles: a CTA an item. Their exchange of gate and up sums lives in the raw areas, so the
-  // next item's weights cannot be fetched early; run persistently they measured no faster (d 2048)
-  // or 9 % slower (d 7168) - also with the items drawn from a counter in global memory instead of a
-  // fixed share per CTA, and with the up sums exchanged through an area of their own.
+  // Gate/up tiles of more than 64 tokens on average: a CTA an item. Their exchange of gate and up sums
+  // fills the raw areas, so the next item's weights cannot be fetched early; run persistently they
+  // measured no faster (d 2048) or 9 % slower (d 7168) - also with the items drawn from a counter in
+  // global memory instead of a fixed share per CTA, and with the up sums exchanged through an area
+  // of their own. Smaller gate/up tiles exchange through two of the four raw areas and run
+  // persistently too (the producer is two blocks into the next item during an item's epilogue): 9 %
+  // faster at 32 tokens an expert.
   const long items = (long)row_tiles * max_tiles;
-  const bool persist = down && items > L.n_sm;
-  const void *kern =
-      !down ? (q6 ? (const void *)k_tc<PM_TYPE_Q6_K, false, false> : (const void *)k_tc<PM_TYPE_Q4_K, false, false>)
-      : q6  ? (persist ? (const void *)k_tc<PM_TYPE_Q6_K, true, true> : (const void *)k_tc<PM_TYPE_Q6_K, false, true>)
-            : (persist ? (const void *)k_tc<PM_TYPE_Q4_K, true, true> : (const void *)k_tc<PM_TYPE_Q4_K, false, true>);
+  // tiles of at most 64 tokens on average: the instantiation with two accumulator sets (its larger
+  // register footprint costs wider tiles 4 %), and gate/up persistent as well
+  const bool small = (long)n_pairs <= 64L * (g.max_groups < n_pairs ? g.max_groups : n_pairs);
+  const bool persist = items > L.n_sm && (down || small);
+  const void *kern;
+  if (q6) {
+    kern = !down ? (small ? (persist ? (const void *)k_tc<PM_TYPE_Q6_K, true, false, true> : (const void *)k_tc<PM_TYPE_Q6_K, false, false, true>)
+                          : (const void *)k_tc<PM_TYPE_Q6_K, false, false, false>)
+           : small ? (persist ? (const void *)k_tc<PM_TYPE_Q6_K, true, true, true> : (const void *)k_tc<PM_TYPE_Q6_K, false, true, true>)
+                   : (persist ? (const void *)k_tc<PM_TYPE_Q6_K, true, true, false> : (const void *)k_tc<PM_TYPE_Q6_K, false, true, false>);
+  } else {
+    kern = !down ? (small ? (persist ? (const void *)k_tc<PM_TYPE_Q4_K, true, false, true> : (const void *)k_tc<PM_TYPE_Q4_K, false, false, true>)
+                          : (const void *)k_tc<PM_TYPE_Q4_K, false, false, false>)
+           : small ? (persist ? (const void *)k_tc<PM_TYPE_Q4_K, true, true, true> : (const void *)k_tc<PM_TYPE_Q4_K, false, true, true>)
+                   : (persist ? (const void *)k_tc<PM_TYPE_Q4_K, true, true, false> : (const void *)k_tc<PM_TYPE_Q4_K, false, true, false>);
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   TcArgs A;
