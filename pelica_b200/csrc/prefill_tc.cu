@@ -937,7 +937,9 @@ cudaError_t launch_tc_q4k(const Launch &L, const LayerDev &ly, bool shared, bool
   const long items = (long)row_tiles * max_tiles;
   // tiles of at most 64 tokens on average: the instantiation with two accumulator sets (its larger
   // register footprint costs wider tiles 4 %), and gate/up persistent as well
-  const bool small = (long)n_pairs <= 64L * (g.max_groups < n_pairs ? g.max_groups : n_pairs);
+  // (the experts that can have pairs: under expert parallelism the plan holds this rank's only)
+  const int n_groups = shared ? 1 : (g.max_groups < ly.n_local ? g.max_groups : ly.n_local);
+  const bool small = (long)n_pairs <= 64L * (n_groups < n_pairs ? n_groups : n_pairs);
   const bool persist = items > L.n_sm && (down || small);
   const void *kern;
   if (q6) {
