@@ -96,10 +96,16 @@ enum {
   PM_AQ_Q8X_256 = 1,  /* int8 per 256 values, f32 scale, 8 partial sums
                          (`Q8x`, src/ds4_cpu.rs:7-36); the hidden vector is
                          re-quantised before down (src/ds4_cpu.rs:306-317)        */
-  PM_AQ_Q8_32 = 2     /* int8 per 32 values, f32 scale (`Q8`, src/q4x_cpu.rs:13-51)
+  PM_AQ_Q8_32 = 2,    /* int8 per 32 values, f32 scale (`Q8`, src/q4x_cpu.rs:13-51)
                          against Q8_0 / IQ4_NL / IQ4_XS / IQ3_S weights: per block f16(d_w) * x.d * idot
                          (src/q4x_cpu.rs:85-101); hidden vector re-quantised the
                          same way before down (src/q4x_cpu.rs:399-440)            */
+  PM_AQ_Q8_32_F16 = 3 /* the same quantiser with the block scale rounded through f16 (a ggml Q8_0
+                         block's scale), for the 32-block types and, as a second mode that no
+                         reference code has, for Q4_K weights: per 32-value sub-block j of a
+                         super-block x.d[j] * ((d * sc_j) * isum_j - (dmin * m_j) * bsum_j),
+                         sub-blocks in ascending order. The reference pairs Q4_K with
+                         PM_AQ_Q8X_256 only (src/ds4_cpu.rs:59-83).                */
 };
 
 /* ---- where the routing weight is applied ------------------------------- */

@@ -456,6 +456,13 @@ void po_q8_32(const float *x, size_t n, int8_t *q, float *d) {
   }
 }
 
+/* PM_AQ_Q8_32_F16: `Q8::new` with the block scale a ggml Q8_0 block would store (f16). The int8
+ * values are those of po_q8_32 (rounded against the unrounded scale). No reference code. */
+void po_q8_32_f16(const float *x, size_t n, int8_t *q, float *d) {
+  po_q8_32(x, n, q, d);
+  for (size_t b = 0; b < n / 32; b++) d[b] = po_f16_to_f32(po_f32_to_f16(d[b]));
+}
+
 /* ------------------------------------------------------------------------ */
 /* rows                                                                      */
 /* ------------------------------------------------------------------------ */
@@ -583,7 +590,37 @@ float po_row_iq3s(const uint8_t *w, size_t ncols, const int8_t *q, const float *
 }
 
 /* a row of a type of the q4x path against 32-block Q8 activations (`row`, src/q4x_cpu.rs:367) */
+/* Q4_K row . 32-block Q8 activations. The reference has no such pair; this is `row_scalar`
+ * (src/ds4_cpu.rs:59-83) with the activation scale per 32-value sub-block instead of per
+ * super-block: total += x.d[j] * ((d * sc_j) * isum_j - (dmin * m_j) * bsum_j), ascending j. */
+float po_row_q4k_q8_32(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
+  float total = 0.0f;
+  size_t nb = ncols / 256;
+  for (size_t b = 0; b < nb; b++) {
+    const uint8_t *blk = w + b * 144;
+    float d = f16le(blk), dmin = f16le(blk + 2);
+    int32_t sc[8], m[8];
+    q4k_scales(blk + 4, sc, m);
+    const uint8_t *qs = blk + 16;
+    for (int j = 0; j < 8; j++) { /* chunk j / 2: low nibbles = sub-block 2c, high = 2c + 1 */
+      const uint8_t *qc = qs + 32 * (j / 2);
+      const int8_t *xq = q + b * 256 + 32 * (size_t)j;
+      int32_t isum = 0, bsum = 0;
+      for (int i = 0; i < 32; i++) {
+        int32_t nib = (j & 1) ? (qc[i] >> 4) : (qc[i] & 15);
+        isum += nib * (int32_t)xq[i];
+        bsum += (int32_t)xq[i];
+      }
+      float a = (d * (float)sc[j]) * (float)isum;
+      float c = (dmin * (float)m[j]) * (float)bsum;
+      total += d32[b * 8 + (size_t)j] * (a - c);
+    }
+  }
+  return total;
+}
+
 static float row_q8_32(int t, const uint8_t *w, size_t ncols, const int8_t *q, const float *d32) {
+  if (t == PM_TYPE_Q4_K) return po_row_q4k_q8_32(w, ncols, q, d32);
   if (t == PM_TYPE_IQ4_NL) return po_row_iq4nl(w, ncols, q, d32);
   if (t == PM_TYPE_IQ4_XS) return po_row_iq4xs(w, ncols, q, d32);
   if (t == PM_TYPE_IQ3_S) return po_row_iq3s(w, ncols, q, d32);
@@ -910,12 +947,15 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
       q8x_free(&xq);
       q8x_free(&hq);
     }
-  } else if (D->act_quant == PM_AQ_Q8_32) { /* src/q4x_cpu.rs:399-440 */
+  } else if (D->act_quant == PM_AQ_Q8_32 || D->act_quant == PM_AQ_Q8_32_F16) { /* src/q4x_cpu.rs:399-440 */
+    const int f16s = D->act_quant == PM_AQ_Q8_32_F16;
+    void (*quant)(const float *, size_t, int8_t *, float *) = f16s ? po_q8_32_f16 : po_q8_32;
     if (d % 32 || ff % 32) { free(h); return PM_ERR_INVALID; }
     {
       const int ts[3] = {D->type_gate, D->type_up, D->type_down};
       for (int i = 0; i < 3; i++)
-        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL && ts[i] != PM_TYPE_IQ4_XS && ts[i] != PM_TYPE_IQ3_S) {
+        if (ts[i] != PM_TYPE_Q8_0 && ts[i] != PM_TYPE_IQ4_NL && ts[i] != PM_TYPE_IQ4_XS && ts[i] != PM_TYPE_IQ3_S &&
+            !(f16s && ts[i] == PM_TYPE_Q4_K)) {
           free(h);
           return PM_ERR_UNSUPPORTED;
         }
@@ -923,7 +963,7 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
     int8_t *xq = (int8_t *)malloc((size_t)d), *hq = (int8_t *)malloc((size_t)ff);
     float *xd = (float *)malloc((size_t)d / 32 * 4), *hd = (float *)malloc((size_t)ff / 32 * 4);
     for (int t = 0; t < nt; t++) {
-      po_q8_32(xs[t], (size_t)d, xq, xd);
+      quant(xs[t], (size_t)d, xq, xd);
       for (int j = 0; j < ff; j++) {
         float g = row_q8_32(D->type_gate, W->gate + (size_t)j * bg, (size_t)d, xq, xd);
         float u = row_q8_32(D->type_up, W->up + (size_t)j * bu, (size_t)d, xq, xd);
@@ -931,7 +971,7 @@ int po_expert(const pm_layer_desc *D, const po_expert_w *W, int ff, const float 
         if (W->bias_up) u = u + W->bias_up[j];
         h[j] = act_fn(D, g, u, wts ? wts[t] : 1.0f, fold);
       }
-      po_q8_32(h, (size_t)ff, hq, hd);
+      quant(h, (size_t)ff, hq, hd);
       for (int r = 0; r < d; r++) {
         float o = row_q8_32(D->type_down, W->down + (size_t)r * bd, (size_t)ff, hq, hd);
         if (W->bias_down) o = o + W->bias_down[r];

@@ -57,6 +57,8 @@ int po_dequant(int ggml_type, const uint8_t *blocks, size_t n_values, float *out
 void po_q8x(const float *x, size_t n, int8_t *q, float *d, int32_t *bsum);
 /* `Q8::new` (src/q4x_cpu.rs:23-37): n % 32 == 0; q[n], d[n/32] */
 void po_q8_32(const float *x, size_t n, int8_t *q, float *d);
+/* the same with every block scale rounded through f16 (PM_AQ_Q8_32_F16; no reference code) */
+void po_q8_32_f16(const float *x, size_t n, int8_t *q, float *d);
 
 /* ---- rows -------------------------------------------------------------- */
 /* `row_scalar` (src/ds4_cpu.rs:59-83) */
@@ -84,6 +86,9 @@ float po_row_q6k(const uint8_t *w, size_t ncols, const int8_t *q, const float *d
 float po_row_q6k_fast(const uint8_t *w, size_t ncols, const int8_t *q, const float *d);
 /* Q8_0 row against 32-block activations (src/q4x_cpu.rs:85-90) */
 float po_row_q8_0(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
+/* Q4_K row against 32-block Q8 activations (no reference code pairs them: row_scalar,
+ * src/ds4_cpu.rs:59-83, restated with one activation scale per 32-value sub-block) */
+float po_row_q4k_q8_32(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
 /* IQ4_NL row against 32-block activations (src/q4x_cpu.rs:92-101) */
 float po_row_iq4nl(const uint8_t *w, size_t ncols, const int8_t *q, const float *d32);
 /* IQ4_XS row against 32-block activations (src/q4x_cpu.rs:102-117) */

@@ -80,11 +80,14 @@ def lib() -> C.CDLL:
         L.po_q8x.restype = None
         L.po_q8_32.argtypes = [f32p, C.c_size_t, i8p, f32p]
         L.po_q8_32.restype = None
+        L.po_q8_32_f16.argtypes = [f32p, C.c_size_t, i8p, f32p]
+        L.po_q8_32_f16.restype = None
         for name in ("po_row_q4k", "po_row_q4k_fast", "po_row_q4k_vnni"):
             fn = getattr(L, name)
             fn.restype = C.c_float
             fn.argtypes = [u8p, C.c_size_t, i8p, f32p, i32p]
-        for name in ("po_row_q6k", "po_row_q6k_fast", "po_row_q8_0", "po_row_iq4nl", "po_row_iq4xs", "po_row_iq3s"):
+        for name in ("po_row_q6k", "po_row_q6k_fast", "po_row_q8_0", "po_row_iq4nl", "po_row_iq4xs", "po_row_iq3s",
+                     "po_row_q4k_q8_32"):
             fn = getattr(L, name)
             fn.restype = C.c_float
             fn.argtypes = [u8p, C.c_size_t, i8p, f32p]
@@ -163,12 +166,16 @@ def q8x(x):
     return q, d, bsum
 
 
-def q8_32(x):
+def q8_32(x, f16_scale=False):
     x = _f32(x).ravel()
     q = np.empty(x.size, np.int8)
     d = np.empty(x.size // 32, np.float32)
-    lib().po_q8_32(_p(x), x.size, _p(q), _p(d))
+    (lib().po_q8_32_f16 if f16_scale else lib().po_q8_32)(_p(x), x.size, _p(q), _p(d))
     return q, d
+
+
+def row_q4k_q8_32(w, ncols, q, d32) -> float:
+    return lib().po_row_q4k_q8_32(_p(w), ncols, _p(q), _p(d32))
 
 
 def row_q4k(w, ncols, q, d, bsum, kind="scalar") -> float:

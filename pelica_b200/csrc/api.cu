@@ -434,13 +434,15 @@ static int32_t validate_desc(const pm_layer_desc *D) {
       if (t != PM_TYPE_Q4_K && t != PM_TYPE_Q6_K)
         return fail(PM_ERR_UNSUPPORTED, "Q8x activations pair with Q4_K / Q6_K weights only");
     if (D->shared && D->shared_ff % 256) return fail(PM_ERR_INVALID, "shared_ff %% 256");
-  } else if (D->act_quant == PM_AQ_Q8_32) {
+  } else if (D->act_quant == PM_AQ_Q8_32 || D->act_quant == PM_AQ_Q8_32_F16) {
     if (D->d % 32 || D->ff % 32 || (D->shared && D->shared_ff % 32))
       return fail(PM_ERR_INVALID, "32-block Q8 activations need d and ff multiples of 32 (src/q4x_cpu.rs:24)");
     const int t32[3] = {D->type_gate, D->type_up, D->type_down};
     for (int t : t32)
-      if (t != PM_TYPE_Q8_0 && t != PM_TYPE_IQ4_NL && t != PM_TYPE_IQ4_XS && t != PM_TYPE_IQ3_S)
-        return fail(PM_ERR_UNSUPPORTED, "32-block Q8 activations pair with Q8_0 / IQ4_NL / IQ4_XS / IQ3_S weights only");
+      if (t != PM_TYPE_Q8_0 && t != PM_TYPE_IQ4_NL && t != PM_TYPE_IQ4_XS && t != PM_TYPE_IQ3_S &&
+          !(t == PM_TYPE_Q4_K && D->act_quant == PM_AQ_Q8_32_F16))
+        return fail(PM_ERR_UNSUPPORTED, "32-block Q8 activations pair with Q8_0 / IQ4_NL / IQ4_XS / IQ3_S weights (and, with "
+                                        "the f16 scale, Q4_K) only");
   } else if (D->act_quant != PM_AQ_F32) {
     return fail(PM_ERR_UNSUPPORTED, "act_quant %d", D->act_quant);
   }
@@ -889,9 +891,10 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
   Launch L = c->launch();
   int P = T * D.top_k;
   Groups g = plan_groups(S.plan, D.n_exp);
-  bool q8 = D.act_quant == PM_AQ_Q8X_256, q32 = D.act_quant == PM_AQ_Q8_32;
+  const bool q8 = D.act_quant == PM_AQ_Q8X_256, f16s = D.act_quant == PM_AQ_Q8_32_F16;
+  const bool q32 = D.act_quant == PM_AQ_Q8_32 || f16s;
   if (q8 && !prequant) { PROF(c, PH_QUANT_X); launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs); }
-  if (q32 && !prequant) { PROF(c, PH_QUANT_X); launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd); }
+  if (q32 && !prequant) { PROF(c, PH_QUANT_X); launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd, f16s); }
   const bool tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   // MXFP4 weights with f32 activations: the bf16 tensor-core kernels (tolerance parity, not bits)
   const bool tcmx = D.act_quant == PM_AQ_F32 && D.type_gate == PM_TYPE_MXFP4 && D.type_up == PM_TYPE_MXFP4 &&
@@ -929,7 +932,7 @@ static int32_t dev_experts(pm_layer *ly, const float *x, int T, Scratch &S, cons
     }
   }
   if (q8) { PROF(c, PH_QUANT_H); launch_quant_q8x(L, S.h, (size_t)P, D.ff, S.hq, S.hd, S.hbsum, S.hbm, S.hs); }
-  if (q32) { PROF(c, PH_QUANT_H); launch_quant_q8_32(L, S.h, (size_t)P, D.ff, S.hq, S.hd); }
+  if (q32) { PROF(c, PH_QUANT_H); launch_quant_q8_32(L, S.h, (size_t)P, D.ff, S.hq, S.hd, f16s); }
   {
     PROF(c, PH_DOWN);
     if (tc) {
@@ -966,17 +969,18 @@ static int32_t dev_shared(pm_layer *ly, const float *x, int T, Scratch &S) {
   g.pair_token = S.iota;
   g.pair_src = nullptr;
   g.max_groups = 1;
-  bool q8 = D.act_quant == PM_AQ_Q8X_256, q32 = D.act_quant == PM_AQ_Q8_32;
+  const bool q8 = D.act_quant == PM_AQ_Q8X_256, f16s = D.act_quant == PM_AQ_Q8_32_F16;
+  const bool q32 = D.act_quant == PM_AQ_Q8_32 || f16s;
   // (S.xq holds the tokens' Q8x form already when the routed experts ran first)
   if (q8) launch_quant_q8x(L, x, (size_t)T, D.d, S.xq, S.xd, S.xbsum, S.xbm, S.xs);
-  if (q32) launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd);
+  if (q32) launch_quant_q8_32(L, x, (size_t)T, D.d, S.xq, S.xd, f16s);
   const bool use_tc = q8 && c->tc_min_tokens > 0 && T >= c->tc_min_tokens;
   if (use_tc && D.type_gate == D.type_up)
     CU(launch_tc_q4k(L, dv, true, false, g, T, S.tiles, S.rec, g.pair_token, S.xq, S.xd, S.xbm, S.xs, nullptr, S.sh, c->dev_err, c->wait_ns, c->tc_fault_block));
   else
     launch_gateup(L, dv, true, g, T, x, S.xq, S.xd, S.xbsum, nullptr, S.sh);
   if (q8) launch_quant_q8x(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, S.shbsum, S.shbm, S.shs);
-  if (q32) launch_quant_q8_32(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd);
+  if (q32) launch_quant_q8_32(L, S.sh, (size_t)T, D.shared_ff, S.shq, S.shd, f16s);
   if (use_tc)
     CU(launch_tc_q4k(L, dv, true, true, g, T, S.tiles, S.rec, nullptr, S.shq, S.shd, S.shbm, S.shs, nullptr, S.shared_out, c->dev_err, c->wait_ns, c->tc_fault_block));
   else
@@ -1382,8 +1386,9 @@ extern "C" int32_t pm_dequant(pm_ctx *c, int32_t type, const uint8_t *blocks, si
 extern "C" int32_t pm_quant_act(pm_ctx *c, int32_t mode, const float *x, size_t n, int8_t *q,
                                 float *scale, int32_t *bsum) {
   if (!c || !x || !q || !scale) return fail(PM_ERR_INVALID, "pm_quant_act: null argument");
-  if (mode != PM_AQ_Q8X_256 && mode != PM_AQ_Q8_32) return fail(PM_ERR_UNSUPPORTED, "pm_quant_act: mode %d", mode);
-  const bool q32 = mode == PM_AQ_Q8_32;
+  if (mode != PM_AQ_Q8X_256 && mode != PM_AQ_Q8_32 && mode != PM_AQ_Q8_32_F16)
+    return fail(PM_ERR_UNSUPPORTED, "pm_quant_act: mode %d", mode);
+  const bool q32 = mode != PM_AQ_Q8X_256;
   if (!q32 && !bsum) return fail(PM_ERR_INVALID, "pm_quant_act: null bsum");
   if (!q32 && n % 256) return fail(PM_ERR_INVALID, "pm_quant_act: n %% 256 != 0 (src/ds4_cpu.rs:15)");
   if (q32 && n % 32) return fail(PM_ERR_INVALID, "pm_quant_act: n %% 32 != 0 (src/q4x_cpu.rs:24)");
@@ -1396,7 +1401,7 @@ extern "C" int32_t pm_quant_act(pm_ctx *c, int32_t mode, const float *x, size_t 
   int8_t *qd = out_dev(c, q, n, ob[0]);
   if (q32) {
     float *sd = out_dev(c, scale, n / 32, ob[1]);
-    launch_quant_q8_32(c->launch(), xd, 1, (int)n, qd, sd);
+    launch_quant_q8_32(c->launch(), xd, 1, (int)n, qd, sd, mode == PM_AQ_Q8_32_F16);
     CU(cudaGetLastError());
     return out_flush(c, ob, 2);
   }

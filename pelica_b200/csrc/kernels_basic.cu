@@ -335,8 +335,9 @@ void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_
 
 // `Q8::new` (src/q4x_cpu.rs:23-37): per 32 values amax, d = amax / 127, values rounded
 // half away from zero and clamped; an all-zero block keeps d = 0. One warp per block.
+// f16_scale (PM_AQ_Q8_32_F16): the stored scale is rounded through f16, the values are not touched.
 __global__ void __launch_bounds__(256) k_quant_q8_32(const float *__restrict__ x, size_t n_blocks,
-                                                    int8_t *q, float *d) {
+                                                    int8_t *q, float *d, int f16_scale) {
   size_t b = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (b >= n_blocks) return;
   int lane = threadIdx.x & 31;
@@ -349,13 +350,17 @@ __global__ void __launch_bounds__(256) k_quant_q8_32(const float *__restrict__ x
     r = (int)fminf(fmaxf(f, -127.0f), 127.0f);
   }
   q[b * 32 + lane] = (int8_t)r;
-  if (lane == 0) d[b] = a != 0.0f ? __fdiv_rn(a, 127.0f) : 0.0f;
+  if (lane == 0) {
+    float s = a != 0.0f ? __fdiv_rn(a, 127.0f) : 0.0f;
+    if (f16_scale) s = __half2float(__float2half_rn(s));
+    d[b] = s;
+  }
 }
 
-void launch_quant_q8_32(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d) {
+void launch_quant_q8_32(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d, bool f16_scale) {
   size_t nb = rows * (size_t)(n / 32);
   if (nb == 0) return;
-  KLAUNCH(L, k_quant_q8_32, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d);
+  KLAUNCH(L, k_quant_q8_32, (unsigned)((nb + 7) / 8), 256, 0, x, nb, q, d, f16_scale ? 1 : 0);
 }
 
 // ===========================================================================
@@ -910,6 +915,48 @@ __device__ __forceinline__ float row_q8x(const WMat &W, int el, int r, const int
                      W.plane[3] + (size_t)el * W.stride[3] + rb * 2, nb, xq, xd, lane);
 }
 
+// Q4_K row . 32-block Q8 activations (PM_AQ_Q8_32_F16). No reference code pairs them: row_scalar
+// (src/ds4_cpu.rs:59-83) with the activation scale per 32-value sub-block j of a super-block,
+// total += x.d[j] * ((d * sc_j) * isum_j - (dmin * m_j) * bsum_j), sub-blocks in ascending order.
+// A lane takes a sub-block: 32 bytes of the block's quants hold sub-blocks 2c (low nibbles) and
+// 2c + 1 (high nibbles). Not inlined: the callers' register budget is set by their hot branches.
+__device__ __noinline__ float row_q4k_q8_32(const uint8_t *__restrict__ blks, int nb, const int8_t *__restrict__ xq,
+                                            const float *__restrict__ xd, int lane) {
+  float total = 0.0f;
+  for (int b0 = 0; b0 < nb; b0 += 32) {
+    const int b = b0 + lane;
+    float term = 0.0f;
+    if (b < nb) {
+      const uint8_t *blk = blks + (size_t)(b >> 3) * 144;
+      const int j = b & 7;
+      const uint4 hdr = __ldg((const uint4 *)blk);
+      const uint4 *qp = (const uint4 *)(blk + 16 + 32 * (j >> 1));
+      const uint4 q0 = __ldg(qp), q1 = __ldg(qp + 1);
+      const int sh = 4 * (j & 1);
+      const uint32_t M = 0x0f0f0f0fu;
+      const int4 *xp = (const int4 *)(xq + (size_t)b * 32);
+      const int4 x0 = xp[0], x1 = xp[1];
+      int is = 0, bs = 0;
+      is = __dp4a((int)((q0.x >> sh) & M), x0.x, is); is = __dp4a((int)((q0.y >> sh) & M), x0.y, is);
+      is = __dp4a((int)((q0.z >> sh) & M), x0.z, is); is = __dp4a((int)((q0.w >> sh) & M), x0.w, is);
+      is = __dp4a((int)((q1.x >> sh) & M), x1.x, is); is = __dp4a((int)((q1.y >> sh) & M), x1.y, is);
+      is = __dp4a((int)((q1.z >> sh) & M), x1.z, is); is = __dp4a((int)((q1.w >> sh) & M), x1.w, is);
+      const int one = 0x01010101;
+      bs = __dp4a(one, x0.x, bs); bs = __dp4a(one, x0.y, bs); bs = __dp4a(one, x0.z, bs); bs = __dp4a(one, x0.w, bs);
+      bs = __dp4a(one, x1.x, bs); bs = __dp4a(one, x1.y, bs); bs = __dp4a(one, x1.z, bs); bs = __dp4a(one, x1.w, bs);
+      int sc, mn;
+      pm_q4k_scmin(hdr.y, hdr.z, hdr.w, j, sc, mn);
+      const float dd = pm_f16(hdr.x), dmin = pm_f16(hdr.x >> 16);
+      const float a = __fmul_rn(__fmul_rn(dd, (float)sc), (float)is);
+      const float c = __fmul_rn(__fmul_rn(dmin, (float)mn), (float)bs);
+      term = __fmul_rn(xd[b], __fsub_rn(a, c));
+    }
+    const int n = min(32, nb - b0);
+    for (int jj = 0; jj < n; jj++) total = __fadd_rn(total, __shfl_sync(PM_FULL, term, jj));
+  }
+  return total;
+}
+
 // Q8_0 / IQ4_NL row . 32-block Q8 activations (src/q4x_cpu.rs:85-101): per block
 // total += f16(d_w) * x.d[b] * (float)idot, left to right, in block order. Lanes take
 // one block each; the 32 terms are then added in order.
@@ -919,6 +966,7 @@ __device__ __forceinline__ float row_q8_0_q8(const WMat &W, int el, int r, const
   const bool xs = W.type == PM_TYPE_IQ4_XS;
   const bool nl = W.type == PM_TYPE_IQ4_NL || xs;
   float total = 0.0f;
+  if (W.type == PM_TYPE_Q4_K) return row_q4k_q8_32(W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * (nb / 8) * 144, nb, xq, xd, lane);
   if (W.type == PM_TYPE_IQ3_S) {  // src/q4x_cpu.rs:118-127: per sub-block ((d * scale) * x.d) * idot
     const uint8_t *blks = W.plane[0] + (size_t)el * W.stride[0] + (size_t)r * (nb / 8) * 108;
     const uint8_t *ds = W.plane[1] + (size_t)el * W.stride[1] + (size_t)r * (nb / 8) * 2;
@@ -1246,7 +1294,7 @@ __global__ void __launch_bounds__(256, 3) k_gateup(LayerDev ly, int shared, Grou
         gv = row_q8x(G, el, r, q, qd, qb, lane);
         uv = row_q8x(U, el, r, q, qd, qb, lane);
       }
-    } else if (D.act_quant == PM_AQ_Q8_32) {
+    } else if (D.act_quant == PM_AQ_Q8_32 || D.act_quant == PM_AQ_Q8_32_F16) {
       const int8_t *q = xq + (size_t)t * d;
       const float *qd = xd + (size_t)t * (d / 32);
       gv = row_q8_0_q8(G, el, r, q, qd, lane);
@@ -1295,7 +1343,7 @@ __global__ void __launch_bounds__(256) k_down(LayerDev ly, int shared, Groups g,
     if (D.act_quant == PM_AQ_Q8X_256)
       o = row_q8x(Dn, el, r, hq + (size_t)p * ff, hd + (size_t)p * nbh,
                   hbsum + (size_t)p * nbh * 8, lane);
-    else if (D.act_quant == PM_AQ_Q8_32)
+    else if (D.act_quant == PM_AQ_Q8_32 || D.act_quant == PM_AQ_Q8_32_F16)
       o = row_q8_0_q8(Dn, el, r, hq + (size_t)p * ff, hd + (size_t)p * (ff / 32), lane);
     else
       o = row_f32(Dn, el, r, h + (size_t)p * ff, lane);

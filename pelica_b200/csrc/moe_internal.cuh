@@ -117,7 +117,7 @@ void launch_dequant(const Launch &L, int type, size_t n_values, const uint8_t *p
 // xs (optional): per block the sum of its 256 values (the Q6_K offset term)
 void launch_quant_q8x(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d,
                       int32_t *bsum, uint16_t *bm = nullptr, int32_t *xs = nullptr);
-void launch_quant_q8_32(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d);
+void launch_quant_q8_32(const Launch &L, const float *x, size_t rows, int n, int8_t *q, float *d, bool f16_scale);
 void launch_router(const Launch &L, const LayerDev &ly, const float *x, int T, float *logits);
 void launch_route(const Launch &L, const LayerDev &ly, const float *logits, int T, uint32_t *ids,
                   float *w);

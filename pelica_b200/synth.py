@@ -23,7 +23,7 @@ KV_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53
 
 GATE_SOFTMAX_ALL, GATE_SIGMOID, GATE_SQRT_SOFTPLUS, GATE_SOFTMAX_SELECTED = 0, 1, 2, 3
 ACT_SILU, ACT_SILU_CLAMP, ACT_OSS_GLU = 0, 1, 2
-AQ_F32, AQ_Q8X_256, AQ_Q8_32 = 0, 1, 2
+AQ_F32, AQ_Q8X_256, AQ_Q8_32, AQ_Q8_32_F16 = 0, 1, 2, 3
 FOLD_BEFORE_DOWN, FOLD_IN_COMBINE = 0, 1
 SHARED_NONE, SHARED_PLAIN, SHARED_SIGMOID_GATED = 0, 1, 2
 
@@ -416,8 +416,12 @@ C11_GLM = Config("glm-int4-gs64", d=2048, ff=1536, n_exp=64, top_k=8, gating=GAT
                  act=ACT_SILU_CLAMP, act_limit=10.0, type_gate=GLM_Q4, type_up=GLM_Q4, type_down=GLM_Q4,
                  act_quant=AQ_F32, weight_fold=FOLD_IN_COMBINE, shared=SHARED_PLAIN, shared_ff=1536,
                  select_bias_sigma=0.01)
+# the OLMoE shape with the activation format its benchmark description words literally: Q4_K weights
+# against 32-value int8 blocks with an f16 scale. No reference code pairs them (the reference's Q4_K
+# path is C1's Q8x); a labelled second mode.
+C12_Q4K_Q8_0 = C1_OLMOE.scaled(name="olmoe-q4_k-q8_0-acts", act_quant=AQ_Q8_32_F16)
 CONFIGS = {"c1": C1_OLMOE, "c2": C2_QWEN3, "c3": C3_GPTOSS, "c4": C4_DSV3, "c5": C5_ZIPF, "c6": C6_Q8_0,
-           "c7": C7_IQ4NL, "c8": C8_IQ4XS, "c9": C9_IQ3S, "c10": C10_Q5K, "c11": C11_GLM}
+           "c7": C7_IQ4NL, "c8": C8_IQ4XS, "c9": C9_IQ3S, "c10": C10_Q5K, "c11": C11_GLM, "c12": C12_Q4K_Q8_0}
 
 
 def make_weights(cfg: Config, seed: int, experts=None) -> dict:

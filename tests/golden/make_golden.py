@@ -28,12 +28,13 @@ SHAPES = {
     "c9": synth.C9_IQ3S.scaled(d=256, ff=96, n_exp=8, top_k=2),
     "c10": synth.C10_Q5K.scaled(d=256, ff=256, n_exp=8, top_k=2),
     "c11": synth.C11_GLM.scaled(d=256, ff=128, n_exp=8, top_k=2, shared_ff=128),
+    "c12": synth.C12_Q4K_Q8_0.scaled(d=256, ff=256, n_exp=8, top_k=2),
 }
 
 
 def case(name):
     cfg = SHAPES[name]
-    seed = {"c1": 101, "c2": 102, "c3": 103, "c4": 104, "c6": 106, "c9": 109, "c10": 110, "c11": 111}[name]
+    seed = {"c1": 101, "c2": 102, "c3": 103, "c4": 104, "c6": 106, "c9": 109, "c10": 110, "c11": 111, "c12": 112}[name]
     W = synth.make_weights(cfg, seed)
     x = synth.make_activations(5, cfg.d, seed + 1000)
     return cfg, W, x

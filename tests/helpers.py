@@ -64,6 +64,7 @@ SMALL = {
     "c9": synth.C9_IQ3S.scaled(d=512, ff=160, n_exp=16),
     "c10": synth.C10_Q5K.scaled(d=512, ff=256, n_exp=16),
     "c11": synth.C11_GLM.scaled(d=512, ff=192, n_exp=16, shared_ff=192),
+    "c12": synth.C12_Q4K_Q8_0.scaled(d=512, ff=256, n_exp=16),  # Q4_K against 32-block activations, f16 scale
 }
 
 

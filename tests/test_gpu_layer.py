@@ -141,7 +141,7 @@ def test_usage_counters(ctx, oracle):
     gl.close()
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c9", "c10", "c11"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c9", "c10", "c11", "c12"])
 def test_golden_fixtures(ctx, name):
     """The committed vectors (tests/golden), no oracle involved."""
     from tests.golden.make_golden import case
@@ -188,3 +188,14 @@ def test_synthetic_fill_round_trips_through_the_oracle(ctx, oracle):
         deq = oracle.dequant(cfg.type_gate, W["gate"][0], cfg.ff * cfg.d)
         assert 0.015 < deq.std() < 0.025 and abs(deq.mean()) < 2e-3
         gl.close()
+
+
+@pytest.mark.parametrize("T", [1, 9, 40])
+def test_q4k_with_32_block_activations_has_the_oracle_bits(ctx, oracle, T):
+    """The labelled second activation mode (Q4_K rows against 32-value int8 blocks with an f16
+    scale): integer sums and an ordered float tail, so the bits are the oracle's."""
+    cfg = SMALL["c12"]
+    ol, gl, _ = make_pair(oracle, pb, ctx, cfg, 31)
+    x = synth.make_activations(T, cfg.d, 400 + T)
+    assert bits_equal(gl.forward(x), ol.forward(x))
+    gl.close()

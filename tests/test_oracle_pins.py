@@ -219,7 +219,7 @@ def test_fast_layer_matches_canonical(oracle):
     assert np.abs(y - yf).max() <= 1e-3 * np.abs(y).max()
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c9", "c10", "c11"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c9", "c10", "c11", "c12"])
 def test_golden_layer_outputs(oracle, name):
     """The committed fixtures (tests/golden/make_golden.py) pin the oracle itself."""
     from tests.golden.make_golden import case
@@ -313,3 +313,47 @@ def test_q5k_and_iq3s_known_answers(oracle):
     assert grid.shape == (512, 4) and len({tuple(g) for g in grid}) == 512
     assert set(np.unique(grid)) <= set(range(1, 16, 2))
     assert tuple(grid[0]) == (1, 1, 1, 1) and tuple(grid[1]) == (3, 1, 1, 1)
+
+
+def test_q4k_against_32_block_activations(oracle):
+    """The second activation mode (Q4_K weights, 32-value int8 blocks with an f16 scale). No reference
+    code pairs them, so the pins are hand-computed: one super-block whose sub-block j has scale
+    j + 1, min 2 j, every nibble 3 in the even and 5 in the odd sub-blocks; d = 0.5, dmin = 0.25."""
+    blk = np.zeros(144, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(0.5).tobytes(), np.uint8)
+    blk[2:4] = np.frombuffer(np.float16(0.25).tobytes(), np.uint8)
+    sc = [j + 1 for j in range(8)]
+    mn = [2 * j for j in range(8)]
+    s = blk[4:16]
+    for j in range(4):  # the 12 packed bytes of scales and mins (src/ds4_cpu.rs:45-57)
+        s[j] = sc[j] | ((sc[j + 4] >> 4) << 6)
+        s[j + 4] = mn[j] | ((mn[j + 4] >> 4) << 6)
+        s[j + 8] = (sc[j + 4] & 15) | ((mn[j + 4] & 15) << 4)
+    blk[16:144] = 3 | (5 << 4)
+    q = np.zeros(256, np.int8)
+    d32 = np.zeros(8, np.float32)
+    want = 0.0
+    for j in range(8):
+        q[32 * j:32 * j + 32] = np.arange(32) - 10 - j  # sum = 176 - 32 j
+        d32[j] = np.float32(2.0 ** -(j % 3))
+        nib = 5 if j & 1 else 3
+        isum = nib * int(q[32 * j:32 * j + 32].sum())
+        bsum = int(q[32 * j:32 * j + 32].sum())
+        want += float(d32[j]) * ((0.5 * sc[j]) * isum - (0.25 * mn[j]) * bsum)  # every step exact in f32
+    got = oracle.row_q4k_q8_32(blk, 256, q, d32)
+    assert got == np.float32(want)
+    # the quantiser: the values of Q8::new, the scale rounded through f16
+    x = np.linspace(-3.7, 5.3, 64).astype(np.float32)
+    q0, d0 = oracle.q8_32(x)
+    q1, d1 = oracle.q8_32(x, f16_scale=True)
+    assert np.array_equal(q0, q1)
+    assert np.array_equal(d1, d0.astype(np.float16).astype(np.float32))
+    assert not np.array_equal(d0, d1)  # 5.3 / 127 is not an f16
+    # and a layer in this mode is the 32-block expert flow (src/q4x_cpu.rs:399-440) on Q4_K rows
+    cfg = synth.C12_Q4K_Q8_0.scaled(d=256, ff=256, n_exp=4, top_k=2)
+    W = synth.make_weights(cfg, 5)
+    L = oracle.Layer(oracle.LayerDesc(**cfg.desc_fields()), W)
+    xx = synth.make_activations(3, cfg.d, 6)
+    y = L.forward(xx)
+    ref = oracle.Layer(oracle.LayerDesc(**cfg.scaled(act_quant=synth.AQ_Q8X_256).desc_fields()), W).forward(xx)
+    assert np.all(np.isfinite(y)) and np.abs(y - ref).max() <= 0.02 * np.abs(ref).max()

@@ -91,7 +91,7 @@ def test_q8x_blocks(oracle, n):
     assert not zq.any()
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c10", "c11"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c6", "c10", "c11", "c12"])
 def test_layer_rows_do_not_depend_on_the_batch(oracle, name):
     """A token's output row has the same bits whether it is evaluated alone or in a batch:
     every step of the path is per token, and combine adds in fixed k order
