@@ -2,9 +2,10 @@
 // tensor cores (tcgen05.mma kind::i8, operand A and the accumulators in TMEM), exact in
 // the integer domain of the reference's CPU path (src/ds4_cpu.rs:59-83).
 //
-// One CTA = (128 weight rows of one active expert) x (up to 128 of its tokens): 16 worker
-// warps, one warp that issues the tensor-core instructions and one producer warp. Per
-// 256-value block b of the rows:
+// A work item = (128 weight rows of one active expert) x (up to 128 of its tokens); a CTA (16 worker
+// warps, one warp that issues the tensor-core instructions and one producer warp) runs one item, or -
+// persistent form - one item after another with its rings running on. Per 256-value block b of
+// the rows:
 //   1. the producer stages the block's bytes in row-contiguous pieces; each worker unpacks
 //      64 values of one row into two u8 operand planes IN REGISTERS and stores them to
 //      tensor memory (tcgen05.st), where the products read operand A from: shared memory
@@ -17,8 +18,10 @@
 //      TMEM accumulators and commits to an mbarrier; meanwhile the workers unpack the
 //      next block into registers;
 //   3. every worker reads its TMEM lane (tcgen05.ld) and adds the block's float term
-//      total += x.d[b] * (d * isum - dmin * msum) in block order, as `row_scalar`.
-// Gate and up rows share a CTA (64 + 64 rows) so SwiGLU is fused in the epilogue;
+//      total += x.d[b] * (d * isum - dmin * msum) in block order, as `row_scalar`. Tiles of at
+//      most 64 tokens have two accumulator sets, and step 3 of block b - 1 runs under step 2 of
+//      block b.
+// Gate and up rows share an item (64 + 64 rows) so SwiGLU is fused in the epilogue;
 // down rows write the pair outputs. Waits are time-bounded; TMEM is freed on
 // every exit path.
 #include <cuda_fp16.h>
@@ -288,7 +291,11 @@ __global__ void __launch_bounds__(256) k_tc_rows(Groups g, const uint32_t *__res
 //    f32, so the accumulator holds msum = sum_j m_j * bsum_j as an integer-valued float.
 //  PM_TYPE_Q6_K: the product v = sc * (q - 32) in [-4064, 4096] is split after the
 //    multiplication: v + 4128 = 64 * th + tl with th in [1, 128], tl in [0, 63] - two u8
-//    planes, and isum = 64 * (th . xq) + (tl . xq) - 4128 * sum(xq) exactly.
+//    planes, and isum = 64 * (th . xq) + (tl . xq) - 4128 * sum(xq) exactly. The planes are
+//    th and 4 * tl (the two bytes of 4 * (v + 4128)), so the products give 4 * isum and the
+//    fold multiplies by d / 4: both scalings are by a power of two, the rounding is that of
+//    d * float(isum).
+//  PERSIST, DOWN, SMALL: the launch's form (see launch_tc_q4k).
 // Memory: one producer warp feeds two rings, each with a full and an empty mbarrier per stage.
 // The weight bytes of a block go to one of TC_RAW_STAGES raw areas as stored, by 16-byte
 // cp.async pieces (consecutive lanes on consecutive pieces of a row; the completion of a
